@@ -1,0 +1,424 @@
+#!/usr/bin/env python
+"""Benchmark of the decode hot path: Q4_K GEMV over Q8_1 activations.
+
+Workload (N=1): the FFN products of one Gemma-3-4B-shaped decode step, all 34
+layers, Q4_K weights: per layer  x[b,2560] -> Q8_1 -> fused gate/up GeGLU
+product (two 10240x2560 matrices) -> Q8_1 -> down product (2560x10240).
+Each layer has its own weight copy (34 x 44.2 MB = 1.5 GB, far beyond the
+126 MB L2), so every launch streams its weights from HBM, the rotation the
+reference's own benchmark uses (benchmarks/vecq_bench.cc:119-121).
+
+One step = that whole pass for one batch.  `value` = algorithmic bytes of the
+step / device time (GB/s), inputs resident in HBM, the step replayed as one
+CUDA graph.  `e2e` = the same step driven through the C ABI from HOST buffers:
+pinned x copied in, y copied back, inside the timed region.
+
+N>1 (torchrun): N-column sharding.  Each rank owns 1/N of every matrix's
+output rows; the GLU output and the layer output are all-gathered with NCCL.
+Total work is fixed ("strong" scaling).
+
+--impl reference: the CPU arm.  GGML's CPU vec_dot is not part of the
+reference build, so the arm times the oracle's restatement of the same
+products on the host cores (kind "port").
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+LAYERS = 34
+HIDDEN, INTER = 2560, 10240
+SB = 144  # Q4_K super-block bytes
+METRIC = "q4k_decode_gemv_hbm_throughput"
+UNIT = "GB/s"
+
+
+def step_bytes(batch: int, layers: int = LAYERS) -> int:
+    """Algorithmic bytes of one step: every operand once."""
+    glu = 2 * INTER * (HIDDEN // 256) * SB + batch * (HIDDEN // 32 * 36) + batch * INTER * 4
+    down = HIDDEN * (INTER // 256) * SB + batch * (INTER // 32 * 36) + batch * HIDDEN * 4
+    return layers * (glu + down)
+
+
+def glu_launch_bytes(batch: int, shard: int = 1) -> int:
+    return 2 * (INTER // shard) * (HIDDEN // 256) * SB + batch * (HIDDEN // 32 * 36) + \
+        batch * (INTER // shard) * 4
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.lines: list[str] = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE,
+                stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------- CPU arm
+def run_reference(args, rank: int):
+    if rank != 0:
+        return
+    batch = args.batch
+    per_step = []
+    # A step of the arm = the 34-layer pass; each timed as a bounded sample of
+    # `sample_layers` layers scaled to 34 (every layer is the same work).
+    sample_layers = 4
+    total = args.warmup + args.steps
+    gbs_all, threads, text = [], 1, ""
+    for i in range(total):
+        gbs, per_layer, threads, text = _cpu_step(batch, sample_layers)
+        if i >= args.warmup:
+            gbs_all.append(gbs)
+            per_step.append(per_layer * LAYERS)
+    value = statistics.mean(gbs_all)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(value, 3), "unit": UNIT,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(1e3 * statistics.mean(per_step), 3), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "int8 dp4a -> int32 per block, f32 sums",
+        "data": "synthetic",
+        "config": {"workload": f"Gemma-3-4B FFN decode products, Q4_K, 34 layers, batch {batch}",
+                   "batch": batch, "timing": "host wall clock; weights beyond the CPU cache"},
+        "cpu_baseline": {"value": round(value, 3), "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": text},
+        "e2e": {"value": round(value, 3), "unit": UNIT, "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+_CPU_STATE = {}
+
+
+def _cpu_step(batch: int, layers: int):
+    """One bounded CPU sample: `layers` layer passes, weights built once."""
+    import numpy as np
+
+    from llmp_b200 import synth
+    from oracle import binding as orc
+
+    if "ws" not in _CPU_STATE:
+        orc.build()
+        rng = np.random.default_rng(0)
+        copies = 8  # 8 x 44 MB: beyond the host's last-level cache
+        _CPU_STATE["ws"] = [(synth.q4_k_weights(rng, INTER, HIDDEN),
+                             synth.q4_k_weights(rng, INTER, HIDDEN),
+                             synth.q4_k_weights(rng, HIDDEN, INTER)) for _ in range(copies)]
+        _CPU_STATE["x"] = rng.normal(0, 1, size=(batch, HIDDEN)).astype(np.float32)
+        _CPU_STATE["at"] = 0
+    threads = orc.host_threads()
+    x = _CPU_STATE["x"]
+    t0 = time.perf_counter()
+    for _ in range(layers):
+        gate, up, down = _CPU_STATE["ws"][_CPU_STATE["at"] % len(_CPU_STATE["ws"])]
+        _CPU_STATE["at"] += 1
+        q8 = orc.quantize_q8_1(x)
+        h = orc.vecq(orc.Q4_K, up, q8, HIDDEN, INTER, batch, g=gate, glu=orc.GLU_GEGLU,
+                     threads=threads)[:, 0, :]
+        orc.vecq(orc.Q4_K, down, orc.quantize_q8_1(h), INTER, HIDDEN, batch, threads=threads)
+    dt = time.perf_counter() - t0
+    per_layer = dt / layers
+    text = (f"{layers} of the step's 34 layer passes per step (gate/up GeGLU + down, Q4_K, batch "
+            f"{batch}) over 8 distinct layer copies; oracle port, {threads} threads")
+    return step_bytes(batch, 1) / per_layer / 1e9, per_layer, threads, text
+
+
+# --------------------------------------------------------------------------- GPU arm
+def make_q4k_device(torch, rows: int, k: int, gen):
+    """Random Q4_K blocks made on the device: random nibbles and 6-bit fields,
+    FP16 d = |N(0,0.02)|/480 and dmin = |N(0,0.02)|/32."""
+    nb = k // 256
+    w = torch.randint(0, 256, (rows, nb, SB), dtype=torch.uint8, device="cuda", generator=gen)
+    d = (torch.randn((rows, nb), device="cuda", generator=gen).abs() * (0.02 / 480.0)).half()
+    dmin = (torch.randn((rows, nb), device="cuda", generator=gen).abs() * (0.02 / 32.0)).half()
+    w[:, :, 0:2] = d.view(torch.uint8).view(rows, nb, 2)
+    w[:, :, 2:4] = dmin.view(torch.uint8).view(rows, nb, 2)
+    return w.view(rows, nb * SB)
+
+
+class FfnStep:
+    """The step's device state and launches, for one rank's shard."""
+
+    def __init__(self, torch, ops, batch: int, world: int, rank: int, dist):
+        self.torch, self.ops, self.batch, self.world, self.dist = torch, ops, batch, world, dist
+        gen = torch.Generator(device="cuda")
+        gen.manual_seed(1234 + rank)
+        self.n_glu = INTER // world
+        self.n_down = HIDDEN // world
+        self.layers = []
+        for _ in range(LAYERS):
+            self.layers.append((make_q4k_device(torch, self.n_glu, HIDDEN, gen),
+                                make_q4k_device(torch, self.n_glu, HIDDEN, gen),
+                                make_q4k_device(torch, self.n_down, INTER, gen)))
+        g2 = torch.Generator(device="cuda")
+        g2.manual_seed(99)
+        self.x = torch.randn((LAYERS, batch, HIDDEN), device="cuda", generator=g2)
+        self.q8x = torch.empty((batch, ops.q8_1_row_blocks(HIDDEN) * 36), dtype=torch.uint8,
+                               device="cuda")
+        self.q8h = torch.empty((batch, ops.q8_1_row_blocks(INTER) * 36), dtype=torch.uint8,
+                               device="cuda")
+        # shard-major gather buffers [world, batch, n/world]; the full vector is
+        # re-assembled by a strided view when world > 1
+        self.h_shard = torch.empty((batch, self.n_glu), device="cuda")
+        self.h_full = torch.empty((world, batch, self.n_glu), device="cuda")
+        self.h_rows = torch.empty((batch, INTER), device="cuda")
+        self.y_shard = torch.empty((batch, self.n_down), device="cuda")
+        self.y_full = torch.empty((LAYERS, world, batch, self.n_down), device="cuda")
+        self.launches_per_step = LAYERS * (4 + (1 if world > 1 else 0))
+
+    def layer(self, l: int, x):
+        ops, T = self.ops, self.ops.TYPE_Q4_K
+        gate, up, down = self.layers[l]
+        ops.quantize_q8(x, out=self.q8x)
+        ops.vecq(up, T, HIDDEN, self.n_glu, self.q8x, self.batch, gate=gate, glu=ops.GLU_GEGLU,
+                 out=self.h_shard)
+        if self.world > 1:
+            self.dist.all_gather_into_tensor(self.h_full, self.h_shard)
+            self.h_rows.view(self.batch, self.world, self.n_glu).copy_(self.h_full.transpose(0, 1))
+            h = self.h_rows
+        else:
+            h = self.h_shard
+        ops.quantize_q8(h, out=self.q8h)
+        ops.vecq(down, T, INTER, self.n_down, self.q8h, self.batch, out=self.y_shard)
+        if self.world > 1:
+            self.dist.all_gather_into_tensor(self.y_full[l], self.y_shard)
+
+    def step(self, x_all=None):
+        x_all = self.x if x_all is None else x_all
+        for l in range(LAYERS):
+            self.layer(l, x_all[l])
+
+    def glu_only(self):
+        """The dominant kernel alone, one launch per layer copy."""
+        ops, T = self.ops, self.ops.TYPE_Q4_K
+        for gate, up, _ in self.layers:
+            ops.vecq(up, T, HIDDEN, self.n_glu, self.q8x, self.batch, gate=gate,
+                     glu=ops.GLU_GEGLU, out=self.h_shard)
+
+
+def run_gpu(args, rank: int, world: int, local_rank: int):
+    import torch
+
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    else:
+        torch.cuda.set_device(0)
+    import llmp_b200 as ops
+    if not ops.available():
+        raise SystemExit("bench.py: no B200 / native library: " + ops._native.last_error())
+
+    batch = args.batch
+    st = FfnStep(torch, ops, batch, world, rank, dist)
+    stream = torch.cuda.Stream()
+    sync = torch.cuda.synchronize
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        sync()
+
+    with torch.cuda.stream(stream):
+        st.step()       # warm: module load, attributes
+        sync()
+        graph = None
+        if world == 1 and not args.no_graph:
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    st.step()
+            except Exception as e:  # capture refused: time plain launches
+                print(f"bench.py: graph capture unavailable ({e}); timing plain launches",
+                      file=sys.stderr)
+                graph = None
+                sync()
+        run = graph.replay if graph is not None else st.step
+        for _ in range(max(args.warmup, 3)):
+            run()
+        barrier()
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record(stream)
+        for _ in range(args.steps):
+            run()
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1) / args.steps
+        # ---- the dominant kernel alone (roofline): events around back-to-back launches
+        st.glu_only()
+        sync()
+        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 5
+        k0.record(stream)
+        for _ in range(reps):
+            st.glu_only()
+        k1.record(stream)
+        sync()
+        glu_us = 1e3 * k0.elapsed_time(k1) / (reps * LAYERS)
+        # ---- end to end through the C ABI from host buffers
+        hx = torch.randn((LAYERS, batch, HIDDEN)).pin_memory()
+        hy = torch.empty((LAYERS, world, batch, st.n_down)).pin_memory()
+        dx = torch.empty_like(st.x)
+
+        def e2e_step():
+            dx.copy_(hx, non_blocking=True)
+            st.step(dx)
+            hy.copy_(st.y_full, non_blocking=True)
+            stream.synchronize()
+
+        if world == 1:
+            # y_full is filled by the all-gather only when sharded; single GPU copies the shard out
+            def e2e_step():  # noqa: F811
+                dx.copy_(hx, non_blocking=True)
+                for l in range(LAYERS):
+                    st.layer(l, dx[l])
+                    st.y_full[l, 0].copy_(st.y_shard, non_blocking=True)
+                hy.copy_(st.y_full, non_blocking=True)
+                stream.synchronize()
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            e2e_step()
+        barrier()
+        e2e_ms = 1e3 * (time.perf_counter() - t0) / args.steps
+        clocks = sampler.stop() if rank == 0 else None
+
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms, glu_us], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms, glu_us = (float(v) for v in t.tolist())
+    if rank == 0:
+        sb = step_bytes(batch)
+        value = sb / (ms * 1e-3) / 1e9
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except OSError:
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        glu_b = glu_launch_bytes(batch, world)
+        achieved = glu_b / (glu_us * 1e-6) / 1e9
+        line = {
+            "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 5),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "int8 dp4a -> int32 per block, f32 sums", "data": "synthetic",
+            "config": {
+                "workload": f"Gemma-3-4B FFN decode products, Q4_K, 34 layers, batch {batch}",
+                "batch": batch, "layers": LAYERS, "gate_up": [INTER, HIDDEN],
+                "down": [HIDDEN, INTER],
+                "l2": "inputs larger than L2: 34 distinct layer copies, 1.5 GB, streamed in order",
+                "launch": "cuda graph replay" if graph is not None else "stream launches",
+                "parallelism": "single GPU" if world == 1 else f"N-column shards x{world}, "
+                               "NCCL all-gather of the GLU output and of the layer output",
+                "step_bytes": sb,
+            },
+            "e2e": {"value": round(sb / (e2e_ms * 1e-3) / 1e9, 2), "unit": UNIT,
+                    "ms_per_step": round(e2e_ms, 4),
+                    "h2d_bytes_per_step": LAYERS * batch * HIDDEN * 4,
+                    "d2h_bytes_per_step": LAYERS * batch * HIDDEN * 4},
+            "gpu_launches": st.launches_per_step * args.steps,
+            "roofline": {"bound": "hbm", "kernel": "VecQKernel<Q4_K, GLU> (fused gate/up)",
+                         "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(achieved / peak, 4),
+                         "peak_source": "measured (MEASURED_PEAKS.json hbm_gbs)" if peaks
+                         else "fallback 6650",
+                         "us_per_launch": round(glu_us, 3), "bytes_per_launch": glu_b,
+                         "frac_of_8tbs_spec": round(achieved / 8000.0, 4),
+                         "traffic": args.traffic},
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu:
+            _cpu_step(batch, 4)  # warm: builds the host weights
+            gbs, per_layer, threads, text = _cpu_step(batch, 24)
+            line["cpu_baseline"] = {"value": round(gbs, 3), "unit": UNIT, "cores": threads,
+                                    "kind": "port",
+                                    "ms_per_step": round(per_layer * LAYERS * 1e3, 1),
+                                    "sample": text}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--batch", type=int, default=1, choices=[1, 2, 4, 8])
+    ap.add_argument("--impl", default="llmp_b200", choices=["llmp_b200", "reference"])
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--traffic", type=float, default=None,
+                    help="dram bytes per launch of the dominant kernel from an ncu capture")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    run_gpu(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,113 @@
+/*
+ * llmp_b200: B200 (sm_100a) kernels for llmp's quantized matrix products,
+ * behind a C ABI shaped on the reference's own CUDA-type-free launch structs.
+ *
+ * Conventions (the reference's, src/kernels/ggml/mxfp8_cutlass.h:73-79 and
+ * src/kernels/common/selected_operation.h:26-35, 129-160):
+ *   - every pointer is a caller-owned DEVICE address unless a comment says
+ *     host; scratch is caller-allocated, 256-byte aligned, sized by the
+ *     matching *_scratch() call;
+ *   - a call only queues work on `stream` (a cudaStream_t passed as void*):
+ *     it never synchronizes, never allocates, and does nothing that depends
+ *     on a device value reaching the host;
+ *   - return 0: queued.  >0: refused before anything was queued (the shape or
+ *     an operand is not one this build takes; llmp_b200_last_error() says
+ *     why).  <0: a CUDA call failed after work may have been queued; the
+ *     caller must treat its stream's context as faulted;
+ *   - results are deterministic: no floating-point atomics, fixed summation
+ *     orders; a token's sums do not depend on which other tokens share a call;
+ *   - thread-compatible: one stream per calling thread.
+ *
+ * There is no CPU fallback: on a machine without an sm_100 GPU every launch
+ * entry point returns LLMP_B200_NO_DEVICE.
+ */
+#ifndef LLMP_B200_H_
+#define LLMP_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LLMP_B200_OK 0
+#define LLMP_B200_REJECTED 1  /* shape / operand not taken; nothing queued */
+#define LLMP_B200_NO_DEVICE 2 /* no sm_100 device is current; nothing queued */
+
+/* GGML type numbers of the block encodings (src/format/encoding.cc:111-115). */
+#define LLMP_B200_TYPE_Q8_0 8
+#define LLMP_B200_TYPE_Q8_1 9
+#define LLMP_B200_TYPE_Q4_K 12
+
+/* VecQGlu (src/kernels/ggml/llmp_ops.h:1072). */
+#define LLMP_B200_GLU_NONE 0
+#define LLMP_B200_GLU_SWIGLU 1
+#define LLMP_B200_GLU_SWIGLU_CLAMP 2
+#define LLMP_B200_GLU_GEGLU 3
+
+/* Replaces mxfp8::Available / moe::GroupedGemmAvailable
+ * (src/kernels/ggml/mxfp8_cutlass.h:71, moe_cutlass.h:66): 1 when the current
+ * device is compute capability 10.0 and the kernels were built for it. */
+int llmp_b200_available(void);
+/* SM count of the current device (the `sms` argument the reference's
+ * launchers take), or 0. */
+int llmp_b200_sm_count(void);
+/* Thread-local text for the last non-zero status on this thread. */
+const char* llmp_b200_last_error(void);
+
+/* ------------------------------------------------------------------ Q8_1 */
+/* Replaces RunQuantizeQ8 (src/kernels/ggml/vecq.cu:1095-1111), which calls
+ * GGML's quantize_row_q8_1_cuda.  x: F32 [k, rows, planes], strides in
+ * floats.  out: Q8_1 blocks (36 bytes: FP16 d, FP16 sum of the inputs, 32
+ * int8), each of the rows*planes rows padded with zero blocks to a multiple
+ * of 512 values (llmp_b200_q8_1_row_blocks(k) blocks a row). */
+int64_t llmp_b200_q8_1_row_blocks(int64_t k);
+int llmp_b200_q8_1_quantize(const float* x, int64_t k, int64_t rows, int64_t planes,
+                            int64_t stride_row, int64_t stride_plane, void* out, void* stream);
+
+/* ------------------------------------------------------------------ vecq */
+/* Field for field the reference's VecQDesc (src/kernels/ggml/vecq.h:23-42):
+ * weight offsets count the weight type's blocks, activation offsets count
+ * Q8_1 blocks, destination offsets count floats. */
+typedef struct llmp_b200_vecq_desc {
+  const void* w;      /* weights (the up projection with a GLU) */
+  const void* g;      /* gate weights, or NULL */
+  const void* y;      /* Q8_1 activations */
+  const int32_t* ids; /* NULL: dense / grouped; else I32 [used, tokens] */
+  float* dst;
+  int ncols_x;       /* k */
+  int nrows;         /* n */
+  int stride_row;    /* weight blocks between rows */
+  int stride_expert; /* weight blocks between experts / groups */
+  int y_token;       /* Q8_1 blocks between tokens' rows */
+  int y_slot;        /* between slots' rows (per-slot activations), else 0 */
+  int ids_stride;    /* ids between tokens */
+  int used;          /* slots a token (1 when dense) */
+  int tokens;        /* 1..16; used * tokens <= 128 */
+  int dst_token;     /* floats */
+  int dst_slot;
+  int glu;           /* LLMP_B200_GLU_* */
+  float limit;       /* clamp of LLMP_B200_GLU_SWIGLU_CLAMP */
+} llmp_b200_vecq_desc;
+
+/* Replaces VecQVariants / VecQVariantName / LaunchVecQ
+ * (src/kernels/ggml/vecq.h:44-49) together with the operand checks of
+ * CheckVecQ (src/kernels/ggml/llmp_ops.cc:2915-2982).  variant -1 picks the
+ * launch configuration for the shape.  Types: Q8_0, Q4_K. */
+int llmp_b200_vecq_variants(void);
+const char* llmp_b200_vecq_variant_name(int variant);
+int llmp_b200_vecq(int type, const llmp_b200_vecq_desc* desc, int variant, void* stream);
+
+/* Verification entry with no reference counterpart as a separate call: the
+ * int32 per-block sums the product kernels form (the quantity the reference
+ * checks bit for bit, tests/unit/dsv4_fast_test.cc:511-540), for nrows weight
+ * rows against ONE Q8_1 row.  Q8_0: dots[row][k/32].  Q4_K: dots[row][k/32]
+ * (sum code*q per 32-value sub-block) and qsums[row][k/32] (sum q). */
+int llmp_b200_vecq_block_sums(int type, const void* w, const void* y, int k, int nrows,
+                              int stride_row, int32_t* dots, int32_t* qsums, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LLMP_B200_H_ */

@@ -1,0 +1,80 @@
+"""ctypes binding of libllmp_b200.so.  There is no fallback: importing the
+operators without the built library raises."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "_lib", "libllmp_b200.so")
+
+OK, REJECTED, NO_DEVICE = 0, 1, 2
+TYPE_Q8_0, TYPE_Q8_1, TYPE_Q4_K = 8, 9, 12
+GLU_NONE, GLU_SWIGLU, GLU_SWIGLU_CLAMP, GLU_GEGLU = 0, 1, 2, 3
+
+
+class NativeLibraryMissing(ImportError):
+    pass
+
+
+class Rejected(ValueError):
+    """Status > 0: the call was refused before anything was queued."""
+
+
+class LaunchFailed(RuntimeError):
+    """Status < 0: a CUDA call failed after work may have been queued."""
+
+
+class VecQDesc(C.Structure):
+    """llmp_b200_vecq_desc (include/llmp_b200.h)."""
+    _fields_ = [("w", C.c_void_p), ("g", C.c_void_p), ("y", C.c_void_p), ("ids", C.c_void_p),
+                ("dst", C.c_void_p)] + [(n, C.c_int) for n in (
+                    "ncols_x", "nrows", "stride_row", "stride_expert", "y_token", "y_slot",
+                    "ids_stride", "used", "tokens", "dst_token", "dst_slot", "glu")] + [
+                        ("limit", C.c_float)]
+
+
+# name -> (restype, argtypes): every symbol include/llmp_b200.h declares.
+SIGNATURES = {
+    "llmp_b200_available": (C.c_int, []),
+    "llmp_b200_sm_count": (C.c_int, []),
+    "llmp_b200_last_error": (C.c_char_p, []),
+    "llmp_b200_q8_1_row_blocks": (C.c_int64, [C.c_int64]),
+    "llmp_b200_q8_1_quantize": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
+                                          C.c_int64, C.c_void_p, C.c_void_p]),
+    "llmp_b200_vecq_variants": (C.c_int, []),
+    "llmp_b200_vecq_variant_name": (C.c_char_p, [C.c_int]),
+    "llmp_b200_vecq": (C.c_int, [C.c_int, C.POINTER(VecQDesc), C.c_int, C.c_void_p]),
+    "llmp_b200_vecq_block_sums": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+                                            C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+}
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise NativeLibraryMissing(
+                f"{LIB_PATH} is not built: run `python -c 'import __graft_entry__ as g; g.build()'` "
+                "or `make -C llmp_b200/csrc`. llmp_b200 has no fallback path.")
+        L = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def last_error() -> str:
+    return (lib().llmp_b200_last_error() or b"").decode()
+
+
+def check(status: int, what: str) -> None:
+    if status == 0:
+        return
+    if status > 0:
+        raise Rejected(f"{what}: status {status}: {last_error()}")
+    raise LaunchFailed(f"{what}: status {status}: {last_error()}")

@@ -1,0 +1,111 @@
+// llmp.q8_1: F32 activations to Q8_1 blocks, the input every vecq product
+// reads.  Restates the quantizer the reference calls at
+// src/kernels/ggml/vecq.cu:1095-1111 (GGML quantize_row_q8_1_cuda): blocks of
+// 32, d = amax / 127 and the sum of the original inputs as FP16, q =
+// roundf(x / d), each row padded with zero blocks to a multiple of 512 values.
+//
+// Eight lanes share a block, four consecutive values a lane (one 16-byte
+// load).  The 32-value sum is formed as a butterfly over value indices 16, 8,
+// 4, 2, 1 apart, so the FP16 it rounds to does not depend on the lane layout.
+#include "common.cuh"
+
+namespace llmp_b200 {
+namespace {
+
+constexpr int kThreads = 256;
+
+template <bool kVec>
+__global__ void __launch_bounds__(kThreads)
+QuantizeQ8_1Kernel(const float* __restrict__ x, std::int64_t k, std::int64_t rows,
+                   std::int64_t stride_row, std::int64_t stride_plane, std::int64_t row_blocks,
+                   std::int64_t total_lanes, std::uint8_t* __restrict__ out) {
+  // The input is the kernel before's output; the products after this one may
+  // start fetching their weights now.
+  GridLaunchDependents();
+  GridDependencyWait();
+  const std::int64_t i = (static_cast<std::int64_t>(blockIdx.x) * kThreads) + threadIdx.x;
+  const bool live = i < total_lanes;  // whole groups of 8 lanes are live or not
+  const std::int64_t block = (live ? i : 0) / 8;
+  const int lane8 = static_cast<int>(i % 8);
+  const std::int64_t row = block / row_blocks;       // over rows * planes
+  const std::int64_t b = block % row_blocks;
+  const std::int64_t at = (b * 32) + (lane8 * 4);
+  const float* src = x + ((row / rows) * stride_plane) + ((row % rows) * stride_row) + at;
+  float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  if (live) {
+    if (kVec && at + 4 <= k) {
+      const float4 f = *reinterpret_cast<const float4*>(src);
+      v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+    } else {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        if (at + c < k) v[c] = src[c];
+      }
+    }
+  }
+  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+  float s[4] = {v[0], v[1], v[2], v[3]};
+#pragma unroll
+  for (int offset = 4; offset > 0; offset >>= 1) {
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      s[c] = s[c] + __shfl_xor_sync(0xffffffffu, s[c], offset);
+    }
+  }
+  const float sum = (s[0] + s[2]) + (s[1] + s[3]);
+  const float d = amax / 127.0f;
+  std::uint32_t packed = 0;
+  if (amax != 0.0f) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int q = static_cast<int>(roundf(v[c] / d));
+      packed |= (static_cast<std::uint32_t>(q) & 0xffu) << (8 * c);
+    }
+  }
+  if (!live) return;
+  std::uint8_t* o = out + (block * 36);
+  *reinterpret_cast<std::uint32_t*>(o + 4 + (lane8 * 4)) = packed;
+  if (lane8 == 0) {
+    const std::uint32_t ds = static_cast<std::uint32_t>(__half_as_ushort(__float2half_rn(d))) |
+                             (static_cast<std::uint32_t>(__half_as_ushort(__float2half_rn(sum)))
+                              << 16);
+    *reinterpret_cast<std::uint32_t*>(o) = ds;
+  }
+}
+
+}  // namespace
+}  // namespace llmp_b200
+
+extern "C" {
+
+int64_t llmp_b200_q8_1_row_blocks(int64_t k) { return (k + 511) / 512 * 512 / 32; }
+
+int llmp_b200_q8_1_quantize(const float* x, int64_t k, int64_t rows, int64_t planes,
+                            int64_t stride_row, int64_t stride_plane, void* out, void* stream) {
+  using namespace llmp_b200;
+  if (x == nullptr || out == nullptr || k < 1 || rows < 1 || planes < 1) {
+    return Reject("q8_1: F32 input [k, rows, planes] and an output, all non-empty");
+  }
+  if (!Aligned(x, 4) || !Aligned(out, 4) || stride_row < k || stride_plane < 0) {
+    return Reject("q8_1: 4-byte aligned operands, rows at least k floats apart");
+  }
+  if (const int status = DeviceStatus(); status != 0) return status;
+  const std::int64_t row_blocks = llmp_b200_q8_1_row_blocks(k);
+  const std::int64_t total = rows * planes * row_blocks * 8;
+  if (total / kThreads + 1 > 0x7fffffffLL) return Reject("q8_1: more blocks than a grid holds");
+  const bool vec = Aligned(x, 16) && stride_row % 4 == 0 && stride_plane % 4 == 0;
+  const dim3 grid(static_cast<unsigned>((total + kThreads - 1) / kThreads));
+  auto* o = static_cast<std::uint8_t*>(out);
+  const cudaError_t e =
+      vec ? LaunchPdl(QuantizeQ8_1Kernel<true>, grid, dim3(kThreads), 0,
+                      static_cast<cudaStream_t>(stream), x, k, rows, stride_row, stride_plane,
+                      row_blocks, total, o)
+          : LaunchPdl(QuantizeQ8_1Kernel<false>, grid, dim3(kThreads), 0,
+                      static_cast<cudaStream_t>(stream), x, k, rows, stride_row, stride_plane,
+                      row_blocks, total, o);
+  if (e != cudaSuccess) return Failed(e, "q8_1 launch");
+  return 0;
+}
+
+}  // extern "C"

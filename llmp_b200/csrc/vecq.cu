@@ -1,0 +1,223 @@
+// llmp.vecq entry points: operand checks, launch choice, and the per-block
+// int32 sums used to verify the product kernels.  The kernels themselves are
+// in vecq_impl.cuh, instantiated per weight type in vecq_q4k.cu / vecq_q8_0.cu.
+#include "vecq_impl.cuh"
+
+namespace llmp_b200 {
+namespace vecq {
+extern template cudaError_t LaunchType<Q4KUnit>(const Desc&, int, const Variant&, cudaStream_t);
+extern template cudaError_t LaunchType<Q8_0Unit<4>>(const Desc&, int, const Variant&, cudaStream_t);
+extern template cudaError_t LaunchType<Q8_0Unit<1>>(const Desc&, int, const Variant&, cudaStream_t);
+}  // namespace vecq
+namespace {
+using namespace vecq;
+
+// The int32 sums a product kernel forms, one thread a (row, unit): the same
+// decode and dp4a functions the product uses.
+__global__ void BlockSumsQ4K(const std::uint8_t* __restrict__ w, const std::uint8_t* __restrict__ y,
+                             int k, int nrows, int stride_row, std::int32_t* __restrict__ dots,
+                             std::int32_t* __restrict__ qsums) {
+  const int units = k / 64;
+  const long i = (static_cast<long>(blockIdx.x) * blockDim.x) + threadIdx.x;
+  if (i >= static_cast<long>(nrows) * units) return;
+  const int row = static_cast<int>(i / units);
+  const int u = static_cast<int>(i % units);
+  Q4KUnit raw;
+  raw.Load(w + (static_cast<std::size_t>(row) * stride_row * 144), u);
+  Q4KDecoded dec;
+  dec.From(raw, u);
+  uint4 a4[4];
+  int sums[2] = {0, 0};
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    const auto* src =
+        reinterpret_cast<const std::uint32_t*>(y + (static_cast<std::size_t>((u * 2) + g) * 36));
+    std::uint32_t v[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      v[q] = src[1 + q];
+      sums[g] = Dp4a(0x01010101, static_cast<int>(v[q]), sums[g]);
+    }
+    a4[2 * g] = make_uint4(v[0], v[1], v[2], v[3]);
+    a4[2 * g + 1] = make_uint4(v[4], v[5], v[6], v[7]);
+  }
+  int d0, d1;
+  Q4KDots(dec, a4, &d0, &d1);
+  const std::size_t at = (static_cast<std::size_t>(row) * (k / 32)) + (u * 2);
+  dots[at] = d0;
+  dots[at + 1] = d1;
+  qsums[at] = sums[0];
+  qsums[at + 1] = sums[1];
+}
+
+template <int kBlocks>
+__global__ void BlockSumsQ8_0(const std::uint8_t* __restrict__ w, const std::uint8_t* __restrict__ y,
+                              int k, int nrows, int stride_row, std::int32_t* __restrict__ dots) {
+  using Unit = Q8_0Unit<kBlocks>;
+  const int units = Unit::UnitsPerRow(k);
+  const long i = (static_cast<long>(blockIdx.x) * blockDim.x) + threadIdx.x;
+  if (i >= static_cast<long>(nrows) * units) return;
+  const int row = static_cast<int>(i / units);
+  const int u = static_cast<int>(i % units);
+  Unit raw;
+  raw.Load(w + (static_cast<std::size_t>(row) * stride_row * 34), u);
+#pragma unroll
+  for (int b = 0; b < kBlocks; ++b) {
+    const auto* src = reinterpret_cast<const std::uint32_t*>(
+        y + (static_cast<std::size_t>((u * kBlocks) + b) * 36));
+    int sumi = 0;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) sumi = Dp4a(raw.Int(b, q), static_cast<int>(src[1 + q]), sumi);
+    dots[(static_cast<std::size_t>(row) * (k / 32)) + (u * kBlocks) + b] = sumi;
+  }
+}
+
+// Operand checks: the part of CheckVecQ (src/kernels/ggml/llmp_ops.cc:2915-2982)
+// that a raw descriptor can express.
+int Check(int type, const Desc& d, bool* q8_fast) {
+  if (type != LLMP_B200_TYPE_Q8_0 && type != LLMP_B200_TYPE_Q4_K) {
+    return Reject("vecq: weight type %d is not one this build computes (Q8_0, Q4_K)", type);
+  }
+  if (d.w == nullptr || d.y == nullptr || d.dst == nullptr) {
+    return Reject("vecq: quantized weights, a llmp.q8_1 input and an F32 output");
+  }
+  if (d.tokens < 1 || d.tokens > 16 || d.glu < 0 || d.glu > 3 ||
+      ((d.glu != 0) != (d.g != nullptr))) {
+    return Reject("vecq: 1 to 16 tokens, and gate weights exactly with a GLU");
+  }
+  if (d.glu == LLMP_B200_GLU_GEGLU && d.limit != 0.0f) {
+    return Reject("vecq: GeGLU uses GELU-tanh without a clamp limit");
+  }
+  const int elems = type == LLMP_B200_TYPE_Q4_K ? 256 : 32;
+  if (d.ncols_x < elems || d.ncols_x % elems != 0 || d.nrows < 1) {
+    return Reject("vecq: k a positive multiple of the block's %d values, n >= 1", elems);
+  }
+  if (d.used < 1 || d.used > 256 || d.used * d.tokens > (d.ids != nullptr ? kMaxPairs : 256 * 16)) {
+    return Reject("vecq: used * tokens <= 128 routed; at most 256 groups");
+  }
+  if (d.ids == nullptr && d.tokens > kMaxPairs) return Reject("vecq: tokens");
+  if (d.stride_row < d.ncols_x / elems || d.stride_expert < 0 || d.y_token < 0 || d.y_slot < 0 ||
+      d.dst_token < 0 || d.dst_slot < 0 || (d.ids != nullptr && d.ids_stride < d.used)) {
+    return Reject("vecq: strides must cover a row and be non-negative");
+  }
+  if (!Aligned(d.dst, 4) || !Aligned(d.y, 4) || (d.ids != nullptr && !Aligned(d.ids, 4))) {
+    return Reject("vecq: output, Q8_1 input and ids 4-byte aligned");
+  }
+  if (type == LLMP_B200_TYPE_Q4_K) {
+    // 144-byte super-blocks: any block offset keeps a 16-byte aligned base aligned.
+    if (!Aligned(d.w, 16) || (d.g != nullptr && !Aligned(d.g, 16))) {
+      return Reject("vecq: Q4_K weights 16-byte aligned");
+    }
+  } else {
+    if (!Aligned(d.w, 2) || (d.g != nullptr && !Aligned(d.g, 2))) {
+      return Reject("vecq: Q8_0 weights 2-byte aligned");
+    }
+    *q8_fast = Aligned(d.w, 8) && (d.g == nullptr || Aligned(d.g, 8)) && d.stride_row % 4 == 0 &&
+               d.stride_expert % 4 == 0 && d.ncols_x % 128 == 0;
+  }
+  if (StageBytes(d.ncols_x, 1) > 200 * 1024) {
+    return Reject("vecq: k = %d does not fit the activation staging", d.ncols_x);
+  }
+  const std::uint64_t out = static_cast<std::uint64_t>(d.nrows) * d.used * d.tokens;
+  if (out > 0x7fffffffULL) return Reject("vecq: output beyond the kernel's int offsets");
+  const auto disjoint = [](const void* a, std::uint64_t an, const void* b, std::uint64_t bn) {
+    const auto x = reinterpret_cast<std::uintptr_t>(a), y = reinterpret_cast<std::uintptr_t>(b);
+    return x + an <= y || y + bn <= x;
+  };
+  const std::uint64_t dst_bytes =
+      (static_cast<std::uint64_t>(d.tokens - 1) * d.dst_token +
+       static_cast<std::uint64_t>(d.used - 1) * d.dst_slot + d.nrows) * 4;
+  const std::uint64_t w_bytes = (static_cast<std::uint64_t>(d.nrows - 1) * d.stride_row +
+                                 d.ncols_x / elems) * (type == LLMP_B200_TYPE_Q4_K ? 144 : 34);
+  if (!disjoint(d.dst, dst_bytes, d.w, w_bytes) ||
+      (d.g != nullptr && !disjoint(d.dst, dst_bytes, d.g, w_bytes)) ||
+      !disjoint(d.dst, dst_bytes, d.y, static_cast<std::uint64_t>(d.ncols_x / 32) * 36)) {
+    return Reject("vecq: a packed output disjoint from its operands");
+  }
+  return 0;
+}
+
+}  // namespace
+}  // namespace llmp_b200
+
+extern "C" {
+
+int llmp_b200_vecq_variants(void) { return llmp_b200::kVariantCount; }
+
+const char* llmp_b200_vecq_variant_name(int variant) {
+  if (variant < 0 || variant >= llmp_b200::kVariantCount) return "";
+  return llmp_b200::kVariants[variant].name;
+}
+
+int llmp_b200_vecq(int type, const llmp_b200_vecq_desc* desc, int variant, void* stream) {
+  using namespace llmp_b200;
+  if (desc == nullptr) return Reject("vecq: null descriptor");
+  bool q8_fast = false;
+  if (const int status = Check(type, *desc, &q8_fast); status != 0) return status;
+  if (variant < -1 || variant >= kVariantCount) return Reject("vecq: no variant %d", variant);
+  if (const int status = DeviceStatus(); status != 0) return status;
+  const Desc& d = *desc;
+  const bool glu = d.glu != LLMP_B200_GLU_NONE;
+  // Tokens a pass: the dense pairs are the tokens; a routed expert's pairs
+  // are at most used * tokens, usually few.
+  int p = 1;
+  const int most = d.ids != nullptr ? std::min(d.tokens, 8) : d.tokens;
+  while (p < most && p < 8) p *= 2;
+  while (p > 1 && StageBytes(d.ncols_x, p) > 200 * 1024) p /= 2;
+  const int slots = d.ids != nullptr ? d.used * d.tokens : d.used;
+  const int v = variant >= 0 ? variant
+                             : DefaultVariant(UnitsOf(type, d, q8_fast), d.nrows, slots, glu, p, SmCount());
+  const Variant& cfg = kVariants[v];
+  const long grid_x = (d.nrows + (cfg.warps * (32 / cfg.lpr) * cfg.r) - 1) /
+                      (cfg.warps * (32 / cfg.lpr) * cfg.r);
+  if (grid_x > 0x7fffffffL || slots > 65535) return Reject("vecq: grid too large");
+  cudaError_t e;
+  auto* s = static_cast<cudaStream_t>(stream);
+  if (type == LLMP_B200_TYPE_Q4_K) {
+    e = LaunchType<Q4KUnit>(d, p, cfg, s);
+  } else if (q8_fast) {
+    e = LaunchType<Q8_0Unit<4>>(d, p, cfg, s);
+  } else {
+    e = LaunchType<Q8_0Unit<1>>(d, p, cfg, s);
+  }
+  if (e != cudaSuccess) return Failed(e, "vecq launch");
+  return 0;
+}
+
+int llmp_b200_vecq_block_sums(int type, const void* w, const void* y, int k, int nrows,
+                              int stride_row, int32_t* dots, int32_t* qsums, void* stream) {
+  using namespace llmp_b200;
+  if (w == nullptr || y == nullptr || dots == nullptr || k < 1 || nrows < 1) {
+    return Reject("block_sums: weights, one Q8_1 row and an output");
+  }
+  if (const int status = DeviceStatus(); status != 0) return status;
+  auto* s = static_cast<cudaStream_t>(stream);
+  const auto* wp = static_cast<const std::uint8_t*>(w);
+  const auto* yp = static_cast<const std::uint8_t*>(y);
+  if (type == LLMP_B200_TYPE_Q4_K) {
+    if (k % 256 != 0 || qsums == nullptr || !Aligned(w, 16) || !Aligned(y, 4)) {
+      return Reject("block_sums: Q4_K needs k % 256 == 0, aligned operands and qsums");
+    }
+    const long total = static_cast<long>(nrows) * (k / 64);
+    BlockSumsQ4K<<<static_cast<unsigned>((total + 127) / 128), 128, 0, s>>>(wp, yp, k, nrows,
+                                                                              stride_row, dots, qsums);
+  } else if (type == LLMP_B200_TYPE_Q8_0) {
+    if (k % 32 != 0 || !Aligned(w, 2) || !Aligned(y, 4)) {
+      return Reject("block_sums: Q8_0 needs k % 32 == 0 and aligned operands");
+    }
+    if (Aligned(w, 8) && stride_row % 4 == 0 && k % 128 == 0) {
+      const long total = static_cast<long>(nrows) * (k / 128);
+      BlockSumsQ8_0<4><<<static_cast<unsigned>((total + 127) / 128), 128, 0, s>>>(
+          wp, yp, k, nrows, stride_row, dots);
+    } else {
+      const long total = static_cast<long>(nrows) * (k / 32);
+      BlockSumsQ8_0<1><<<static_cast<unsigned>((total + 127) / 128), 128, 0, s>>>(
+          wp, yp, k, nrows, stride_row, dots);
+    }
+  } else {
+    return Reject("block_sums: type %d", type);
+  }
+  return Launched("block_sums launch");
+}
+
+}  // extern "C"

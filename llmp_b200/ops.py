@@ -1,0 +1,141 @@
+"""Host-side mirror of the reference's operators for the quantized-product
+path (src/kernels/ggml/llmp_ops.h:1072-1085 QuantizeQ8 / VecQ, ...), over
+torch CUDA tensors.  Each function checks what the C ABI cannot see (dtype,
+device, contiguity), fills the launch descriptor and queues the kernels on the
+current torch stream.  Nothing here computes: without the native library or a
+B200 the calls raise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _native as N
+from ._native import (GLU_GEGLU, GLU_NONE, GLU_SWIGLU, GLU_SWIGLU_CLAMP, TYPE_Q4_K, TYPE_Q8_0,
+                      LaunchFailed, Rejected)
+
+__all__ = ["available", "sm_count", "block_bytes", "block_elems", "q8_1_row_blocks",
+           "quantize_q8", "vecq", "vecq_variants", "vecq_block_sums", "TYPE_Q8_0", "TYPE_Q4_K",
+           "GLU_NONE", "GLU_SWIGLU", "GLU_SWIGLU_CLAMP", "GLU_GEGLU", "Rejected", "LaunchFailed"]
+
+_BLOCK = {TYPE_Q8_0: (32, 34), TYPE_Q4_K: (256, 144), N.TYPE_Q8_1: (32, 36)}
+
+
+def available() -> bool:
+    return bool(N.lib().llmp_b200_available())
+
+
+def sm_count() -> int:
+    return int(N.lib().llmp_b200_sm_count())
+
+
+def block_elems(t: int) -> int:
+    return _BLOCK[t][0]
+
+
+def block_bytes(t: int) -> int:
+    return _BLOCK[t][1]
+
+
+def q8_1_row_blocks(k: int) -> int:
+    return int(N.lib().llmp_b200_q8_1_row_blocks(k))
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need(t: torch.Tensor, dtype, what: str) -> None:
+    if not (isinstance(t, torch.Tensor) and t.is_cuda and t.dtype == dtype):
+        raise Rejected(f"{what}: a CUDA tensor of {dtype}")
+
+
+def quantize_q8(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """QuantizeQ8: x F32 [rows, k] or [planes, rows, k] (last dim contiguous) ->
+    uint8 [planes*rows, q8_1_row_blocks(k) * 36]."""
+    _need(x, torch.float32, "quantize_q8 input")
+    if x.dim() == 2:
+        x = x.unsqueeze(0)
+    if x.dim() != 3 or x.stride(2) != 1:
+        raise Rejected("quantize_q8: F32 [k, rows, planes] with k contiguous")
+    planes, rows, k = x.shape
+    nb = q8_1_row_blocks(k)
+    if out is None:
+        out = torch.empty((planes * rows, nb * 36), dtype=torch.uint8, device=x.device)
+    _need(out, torch.uint8, "quantize_q8 output")
+    if out.numel() != planes * rows * nb * 36 or not out.is_contiguous():
+        raise Rejected("quantize_q8: output of rows * row_blocks * 36 bytes")
+    N.check(N.lib().llmp_b200_q8_1_quantize(x.data_ptr(), k, rows, planes, x.stride(1), x.stride(0),
+                                            out.data_ptr(), _stream()), "llmp_b200_q8_1_quantize")
+    return out
+
+
+def vecq_variants() -> list[str]:
+    L = N.lib()
+    return [L.llmp_b200_vecq_variant_name(i).decode() for i in range(L.llmp_b200_vecq_variants())]
+
+
+def vecq(weights: torch.Tensor, wtype: int, k: int, n: int, q8: torch.Tensor, tokens: int, *,
+         ids: torch.Tensor | None = None, per_slot: bool = False, gate: torch.Tensor | None = None,
+         glu: int = GLU_NONE, limit: float = 0.0, groups: int = 1, stride_row: int | None = None,
+         stride_expert: int | None = None, variant: int = -1,
+         out: torch.Tensor | None = None) -> torch.Tensor:
+    """VecQ.  Dense: weights [n, k] blocks, q8 of [tokens, k] -> F32 [tokens, n].
+    Grouped (groups > 1, per_slot): matrix g over row g of q8 of [tokens, groups, k]
+    -> F32 [tokens, groups, n].  Routed: weights [experts, n, k], ids I32 [tokens, used];
+    q8 of [tokens, k] or, per_slot, [tokens, used, k] -> F32 [tokens, used, n].
+    gate: weights like `weights`; the result is glu(gate.x, weights.x)."""
+    _need(weights, torch.uint8, "vecq weights")
+    _need(q8, torch.uint8, "vecq q8")
+    elems, nbytes = _BLOCK[wtype] if wtype in (TYPE_Q8_0, TYPE_Q4_K) else (0, 0)
+    if elems == 0:
+        raise Rejected(f"vecq: weight type {wtype}")
+    routed = ids is not None
+    used = ids.shape[1] if routed else groups
+    d = N.VecQDesc()
+    d.w = weights.data_ptr()
+    d.g = gate.data_ptr() if gate is not None else None
+    if gate is not None:
+        _need(gate, torch.uint8, "vecq gate")
+    d.y = q8.data_ptr()
+    if routed:
+        _need(ids, torch.int32, "vecq ids")
+        if ids.dim() != 2 or ids.shape[0] != tokens or ids.stride(1) != 1:
+            raise Rejected("vecq: ids I32 [used, tokens]")
+        d.ids = ids.data_ptr()
+        d.ids_stride = ids.stride(0)
+    d.ncols_x, d.nrows = k, n
+    d.stride_row = k // elems if stride_row is None else stride_row
+    d.stride_expert = (n * d.stride_row if (routed or groups > 1) else 0) \
+        if stride_expert is None else stride_expert
+    y_row = q8_1_row_blocks(k)
+    d.y_token = y_row * used if per_slot else y_row
+    d.y_slot = y_row if per_slot else 0
+    d.used, d.tokens = used, tokens
+    slotted = routed or groups > 1
+    shape = (tokens, used, n) if slotted else (tokens, n)
+    if out is None:
+        out = torch.empty(shape, dtype=torch.float32, device=weights.device)
+    _need(out, torch.float32, "vecq output")
+    if tuple(out.shape) != shape or not out.is_contiguous():
+        raise Rejected(f"vecq: a packed F32 output {shape}")
+    d.dst = out.data_ptr()
+    d.dst_token = used * n if slotted else n
+    d.dst_slot = n if slotted else 0
+    d.glu, d.limit = glu, limit
+    N.check(N.lib().llmp_b200_vecq(wtype, C.byref(d), variant, _stream()), "llmp_b200_vecq")
+    return out
+
+
+def vecq_block_sums(weights: torch.Tensor, wtype: int, k: int, n: int, q8_row: torch.Tensor):
+    """The int32 per-block sums of n weight rows against one Q8_1 row:
+    (dots [n, k/32], qsums [n, k/32] or None for Q8_0)."""
+    _need(weights, torch.uint8, "block_sums weights")
+    _need(q8_row, torch.uint8, "block_sums q8")
+    dots = torch.empty((n, k // 32), dtype=torch.int32, device=weights.device)
+    qsums = torch.empty_like(dots) if wtype == TYPE_Q4_K else None
+    N.check(N.lib().llmp_b200_vecq_block_sums(
+        wtype, weights.data_ptr(), q8_row.data_ptr(), k, n, k // _BLOCK[wtype][0], dots.data_ptr(),
+        qsums.data_ptr() if qsums is not None else None, _stream()), "llmp_b200_vecq_block_sums")
+    return dots, qsums
