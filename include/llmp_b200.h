@@ -56,6 +56,12 @@ int llmp_b200_sm_count(void);
 /* Thread-local text for the last non-zero status on this thread. */
 const char* llmp_b200_last_error(void);
 
+/* Diagnostics, no reference counterpart: how many bounded device-side waits
+ * (an mbarrier that a bulk copy should have completed) ran out since the
+ * library was loaded.  0 on a healthy device; synchronizes the device, so it
+ * is for tests and post-mortems, never for the launch path.  -1: unreadable. */
+int llmp_b200_device_faults(void);
+
 /* ------------------------------------------------------------------ Q8_1 */
 /* Replaces RunQuantizeQ8 (src/kernels/ggml/vecq.cu:1095-1111), which calls
  * GGML's quantize_row_q8_1_cuda.  x: F32 [k, rows, planes], strides in

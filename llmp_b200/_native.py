@@ -39,6 +39,7 @@ SIGNATURES = {
     "llmp_b200_available": (C.c_int, []),
     "llmp_b200_sm_count": (C.c_int, []),
     "llmp_b200_last_error": (C.c_char_p, []),
+    "llmp_b200_device_faults": (C.c_int, []),
     "llmp_b200_q8_1_row_blocks": (C.c_int64, [C.c_int64]),
     "llmp_b200_q8_1_quantize": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
                                           C.c_int64, C.c_void_p, C.c_void_p]),

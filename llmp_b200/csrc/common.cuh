@@ -20,6 +20,9 @@ int Reject(const char* format, ...);                 // returns LLMP_B200_REJECT
 int Failed(cudaError_t error, const char* what);     // returns a negative status
 int DeviceStatus();                                  // 0 or LLMP_B200_NO_DEVICE
 int SmCount();
+// Device address of the counter of bounded waits that ran out (per device), or null.
+unsigned int* FaultCounter();
+int ReadFaultCounter();
 
 // After a launch: 0, or a negative status carrying the CUDA error.
 inline int Launched(const char* what) {

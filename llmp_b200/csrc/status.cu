@@ -70,10 +70,42 @@ int DeviceStatus() {
 
 int SmCount() { return DeviceStatus() == 0 ? Facts().sms : 0; }
 
+// Raised by a kernel whose bounded wait ran out; never by a healthy run.
+__device__ unsigned int g_wait_timeouts = 0;
+
+unsigned int* FaultCounter() {
+  static thread_local int cached_device = -1;
+  static thread_local unsigned int* cached = nullptr;
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess) return nullptr;
+  if (device != cached_device) {
+    void* address = nullptr;
+    if (cudaGetSymbolAddress(&address, g_wait_timeouts) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    cached = static_cast<unsigned int*>(address);
+    cached_device = device;
+  }
+  return cached;
+}
+
+int ReadFaultCounter() {
+  unsigned int count = 0;
+  if (cudaMemcpyFromSymbol(&count, g_wait_timeouts, sizeof(count)) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  return static_cast<int>(count);
+}
+
 }  // namespace llmp_b200
 
 extern "C" {
 int llmp_b200_available(void) { return llmp_b200::DeviceStatus() == 0 ? 1 : 0; }
 int llmp_b200_sm_count(void) { return llmp_b200::SmCount(); }
 const char* llmp_b200_last_error(void) { return llmp_b200::ErrorBuffer(); }
+int llmp_b200_device_faults(void) {
+  return llmp_b200::DeviceStatus() != 0 ? 0 : llmp_b200::ReadFaultCounter();
+}
 }

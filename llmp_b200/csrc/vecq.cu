@@ -1,14 +1,18 @@
 // llmp.vecq entry points: operand checks, launch choice, and the per-block
 // int32 sums used to verify the product kernels.  The kernels themselves are
 // in vecq_impl.cuh, instantiated per weight type in vecq_q4k.cu / vecq_q8_0.cu.
-#include "vecq_impl.cuh"
+#include "vecq_stream.cuh"
 
 namespace llmp_b200 {
 namespace vecq {
 extern template cudaError_t LaunchType<Q4KUnit>(const Desc&, int, const Variant&, cudaStream_t);
 extern template cudaError_t LaunchType<Q8_0Unit<4>>(const Desc&, int, const Variant&, cudaStream_t);
 extern template cudaError_t LaunchType<Q8_0Unit<1>>(const Desc&, int, const Variant&, cudaStream_t);
+extern template cudaError_t LaunchStream<Q4KUnit>(const Desc&, int, const StreamPlan&, cudaStream_t);
+extern template cudaError_t LaunchStream<Q8_0Unit<4>>(const Desc&, int, const StreamPlan&,
+                                                      cudaStream_t);
 }  // namespace vecq
+
 namespace {
 using namespace vecq;
 
@@ -165,14 +169,32 @@ int llmp_b200_vecq(int type, const llmp_b200_vecq_desc* desc, int variant, void*
   while (p < most && p < 8) p *= 2;
   while (p > 1 && StageBytes(d.ncols_x, p) > 200 * 1024) p /= 2;
   const int slots = d.ids != nullptr ? d.used * d.tokens : d.used;
+  auto* s = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  // Dense products whose rows start on 16-byte boundaries stream through the
+  // TMA ring; the rest (routed, grouped, more than 8 tokens, odd alignment)
+  // take the register-staged kernel.
+  StreamPlan plan;
+  const bool dense = d.ids == nullptr && d.used == 1 && d.tokens <= (type == LLMP_B200_TYPE_Q4_K ? 8 : 4);
+  const bool q4 = type == LLMP_B200_TYPE_Q4_K;
+  const bool stream_ok =
+      dense && (q4 || q8_fast) && Aligned(d.w, 16) && (d.g == nullptr || Aligned(d.g, 16)) &&
+      PlanStream(d, q4 ? 64 : 128, q4 ? 144 : 34, q4 ? 256 : 32, p, SmCount(), &plan);
+  if (variant == kStreamVariant && !stream_ok) {
+    return Reject("vecq: the stream variant takes dense products of 16-byte aligned rows only");
+  }
+  if (stream_ok && (variant == kStreamVariant || variant < 0)) {
+    e = q4 ? LaunchStream<Q4KUnit>(d, p, plan, s) : LaunchStream<Q8_0Unit<4>>(d, p, plan, s);
+    if (e != cudaSuccess) return Failed(e, "vecq stream launch");
+    return 0;
+  }
   const int v = variant >= 0 ? variant
-                             : DefaultVariant(UnitsOf(type, d, q8_fast), d.nrows, slots, glu, p, SmCount());
+                             : DefaultVariant(UnitsOf(type, d, q8_fast), d.nrows, slots, glu, p,
+                                              SmCount());
   const Variant& cfg = kVariants[v];
   const long grid_x = (d.nrows + (cfg.warps * (32 / cfg.lpr) * cfg.r) - 1) /
                       (cfg.warps * (32 / cfg.lpr) * cfg.r);
   if (grid_x > 0x7fffffffL || slots > 65535) return Reject("vecq: grid too large");
-  cudaError_t e;
-  auto* s = static_cast<cudaStream_t>(stream);
   if (type == LLMP_B200_TYPE_Q4_K) {
     e = LaunchType<Q4KUnit>(d, p, cfg, s);
   } else if (q8_fast) {

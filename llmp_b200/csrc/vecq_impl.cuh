@@ -61,6 +61,14 @@ struct Q4KUnit {
     q[0] = LoadStream16(chunk);
     q[1] = LoadStream16(chunk + 16);
   }
+  // The same unit out of a row staged in shared memory (16-byte aligned).
+  __device__ __forceinline__ void LoadShared(const std::uint8_t* row, int u) {
+    const std::uint8_t* sb = row + (static_cast<std::size_t>(u >> 2) * kBlockBytes);
+    head = *reinterpret_cast<const uint4*>(sb);
+    const std::uint8_t* chunk = sb + 16 + ((u & 3) * 32);
+    q[0] = *reinterpret_cast<const uint4*>(chunk);
+    q[1] = *reinterpret_cast<const uint4*>(chunk + 16);
+  }
 };
 
 // The 6-bit scale and minimum of sub-blocks 2c and 2c+1 of a super-block whose
@@ -160,6 +168,21 @@ struct Q8_0Unit {
         w[1 + i] = static_cast<std::uint32_t>(__ldg(h + 1 + (2 * i))) |
                    (static_cast<std::uint32_t>(__ldg(h + 2 + (2 * i))) << 16);
       }
+    }
+  }
+  // Four-block units out of a row staged in shared memory (8-byte aligned).
+  __device__ __forceinline__ void LoadShared(const std::uint8_t* row, int u) {
+    static_assert(kBlocks == 4 || kBlocks == 1, "unit sizes");
+    const std::uint8_t* p = row + (static_cast<std::size_t>(u) * kBlockBytes * kBlocks);
+    if constexpr (kBlocks == 4) {
+#pragma unroll
+      for (int i = 0; i < 17; ++i) {
+        const uint2 v = *reinterpret_cast<const uint2*>(p + (8 * i));
+        w[2 * i] = v.x;
+        w[2 * i + 1] = v.y;
+      }
+    } else {
+      Load(row, u);
     }
   }
   // Block j's scale and its int `i` (4 values) out of the unit's words.
@@ -460,8 +483,11 @@ constexpr Variant kVariants[] = {
     {"l32r2u2w8", 32, 2, 2, 8}, {"l8r1u4w4", 8, 1, 4, 4},   {"l16r1u4w4", 16, 1, 4, 4},
     {"l32r1u4w4", 32, 1, 4, 4}, {"l8r1u4w8", 8, 1, 4, 8},   {"l16r1u4w8", 16, 1, 4, 8},
     {"l32r1u4w8", 32, 1, 4, 8},
+    // The persistent TMA-fed stream kernel (vecq_stream.cuh); dense products only.
+    {"stream", 0, 0, 0, 0},
 };
 constexpr int kVariantCount = static_cast<int>(sizeof(kVariants) / sizeof(kVariants[0]));
+constexpr int kStreamVariant = kVariantCount - 1;
 
 template <typename Unit, int P, int LPR, int R, int U, bool kGlu>
 cudaError_t LaunchOne(const Desc& d, int warps, cudaStream_t stream) {

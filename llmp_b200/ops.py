@@ -15,7 +15,7 @@ from . import _native as N
 from ._native import (GLU_GEGLU, GLU_NONE, GLU_SWIGLU, GLU_SWIGLU_CLAMP, TYPE_Q4_K, TYPE_Q8_0,
                       LaunchFailed, Rejected)
 
-__all__ = ["available", "sm_count", "block_bytes", "block_elems", "q8_1_row_blocks",
+__all__ = ["available", "sm_count", "device_faults", "block_bytes", "block_elems", "q8_1_row_blocks",
            "quantize_q8", "vecq", "vecq_variants", "vecq_block_sums", "TYPE_Q8_0", "TYPE_Q4_K",
            "GLU_NONE", "GLU_SWIGLU", "GLU_SWIGLU_CLAMP", "GLU_GEGLU", "Rejected", "LaunchFailed"]
 
@@ -24,6 +24,11 @@ _BLOCK = {TYPE_Q8_0: (32, 34), TYPE_Q4_K: (256, 144), N.TYPE_Q8_1: (32, 36)}
 
 def available() -> bool:
     return bool(N.lib().llmp_b200_available())
+
+
+def device_faults() -> int:
+    """Bounded device-side waits that ran out since load (0 when healthy)."""
+    return int(N.lib().llmp_b200_device_faults())
 
 
 def sm_count() -> int:

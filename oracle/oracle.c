@@ -353,9 +353,13 @@ static float row_dot_f32(int type, const uint8_t* w, const uint8_t* y, int64_t k
       const float d = orc_f16_to_f32(load_u16(wb)), dmin = orc_f16_to_f32(load_u16(wb + 2));
       acc += d * sumf_d - dmin * sumf_m;
       if (sum64) {
-        const double p = orc_q4_k_block_product(wb, yb);
-        s64 += p;
-        a64 += fabs(p);
+        s64 += orc_q4_k_block_product(wb, yb);
+        /* magnitude of the terms the sum is made of: per 32-value sub-block the
+         * scale product and the minimum product */
+        for (int g = 0; g < 8; ++g) {
+          const double d8 = orc_f16_to_f32(load_u16(yb + g * ORC_Q8_1_BYTES));
+          a64 += fabs(d8 * (double)d * sc[g] * dots[g]) + fabs(d8 * (double)dmin * mn[g] * qsums[g]);
+        }
       }
     }
   }

@@ -82,7 +82,8 @@ typedef struct {
 } orc_vecq_desc;
 /* F32 result, accumulated in float in block order.  If dst64/abs64 are not
  * NULL (dense, no GLU only) they receive, laid out as dst, the sum in double
- * of the scalar block products and the sum of their magnitudes. */
+ * of the scalar block products and the sum of the magnitudes of their terms
+ * (per block for Q8_0; per 32-value sub-block scale and minimum term for Q4_K). */
 int orc_vecq(int type, const orc_vecq_desc* d, double* dst64, double* abs64, int threads);
 
 /* ---- Q8_1-MMQ activation blocks, DS4 layout (PARITY UNPINNED) ---- */

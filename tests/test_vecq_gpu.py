@@ -230,3 +230,9 @@ def test_operands_the_kernels_do_not_take_are_refused_before_launch(cuda, orc):
     with pytest.raises(ops.Rejected):
         ops.vecq(w, orc.Q4_K, 500, 8, q8, 1)                          # k not whole blocks
     torch.cuda.synchronize()                                          # nothing was queued
+
+
+def test_no_bounded_wait_ran_out(cuda):
+    """Collected after the product tests of this file: the TMA-fed kernels'
+    bounded mbarrier waits never expired."""
+    assert _ops().device_faults() == 0
