@@ -9,6 +9,8 @@ extern template cudaError_t LaunchType<Q4KUnit>(const Desc&, int, const Variant&
 extern template cudaError_t LaunchType<Q8_0Unit<4>>(const Desc&, int, const Variant&, cudaStream_t);
 extern template cudaError_t LaunchType<Q8_0Unit<1>>(const Desc&, int, const Variant&, cudaStream_t);
 extern template cudaError_t LaunchStream<Q4KUnit>(const Desc&, int, const StreamPlan&, cudaStream_t);
+extern template cudaError_t LaunchStream<Q4KBlockUnit>(const Desc&, int, const StreamPlan&,
+                                                       cudaStream_t);
 extern template cudaError_t LaunchStream<Q8_0Unit<4>>(const Desc&, int, const StreamPlan&,
                                                       cudaStream_t);
 }  // namespace vecq
@@ -21,37 +23,44 @@ using namespace vecq;
 __global__ void BlockSumsQ4K(const std::uint8_t* __restrict__ w, const std::uint8_t* __restrict__ y,
                              int k, int nrows, int stride_row, std::int32_t* __restrict__ dots,
                              std::int32_t* __restrict__ qsums) {
-  const int units = k / 64;
+  const int blocks = k / 256;
   const long i = (static_cast<long>(blockIdx.x) * blockDim.x) + threadIdx.x;
-  if (i >= static_cast<long>(nrows) * units) return;
-  const int row = static_cast<int>(i / units);
-  const int u = static_cast<int>(i % units);
-  Q4KUnit raw;
-  raw.Load(w + (static_cast<std::size_t>(row) * stride_row * 144), u);
-  Q4KDecoded dec;
-  dec.From(raw, u);
-  uint4 a4[4];
-  int sums[2] = {0, 0};
+  if (i >= static_cast<long>(nrows) * blocks) return;
+  const int row = static_cast<int>(i / blocks);
+  const int u = static_cast<int>(i % blocks);
+  // Both decodes the product kernels use must give the same integers.
+  Q4KBlockUnit raw;
+  raw.LoadShared(w + (static_cast<std::size_t>(row) * stride_row * 144), u);  // plain loads
+  UnitActs<Q4KBlockUnit> acts;
+  acts.Load(y, u);
+  int whole[8];
+  Q4KBlockDots(raw, acts.q, whole);
+  const std::size_t at = (static_cast<std::size_t>(row) * (k / 32)) + (u * 8);
 #pragma unroll
-  for (int g = 0; g < 2; ++g) {
-    const auto* src =
-        reinterpret_cast<const std::uint32_t*>(y + (static_cast<std::size_t>((u * 2) + g) * 36));
-    std::uint32_t v[8];
-#pragma unroll
-    for (int q = 0; q < 8; ++q) {
-      v[q] = src[1 + q];
-      sums[g] = Dp4a(0x01010101, static_cast<int>(v[q]), sums[g]);
-    }
-    a4[2 * g] = make_uint4(v[0], v[1], v[2], v[3]);
-    a4[2 * g + 1] = make_uint4(v[4], v[5], v[6], v[7]);
+  for (int c = 0; c < 4; ++c) {
+    Q4KUnit part;
+    part.Load(w + (static_cast<std::size_t>(row) * stride_row * 144), (u * 4) + c);
+    Q4KDecoded dec;
+    dec.From(part, c);
+    const uint4 a4[4] = {
+        make_uint4(acts.q[16 * c + 0], acts.q[16 * c + 1], acts.q[16 * c + 2], acts.q[16 * c + 3]),
+        make_uint4(acts.q[16 * c + 4], acts.q[16 * c + 5], acts.q[16 * c + 6], acts.q[16 * c + 7]),
+        make_uint4(acts.q[16 * c + 8], acts.q[16 * c + 9], acts.q[16 * c + 10], acts.q[16 * c + 11]),
+        make_uint4(acts.q[16 * c + 12], acts.q[16 * c + 13], acts.q[16 * c + 14],
+                   acts.q[16 * c + 15])};
+    int d0, d1;
+    Q4KDots(dec, a4, &d0, &d1);
+    // A disagreement between the two decodes is reported as an impossible sum.
+    dots[at + (2 * c)] = d0 == whole[2 * c] ? d0 : 0x7fffffff;
+    dots[at + (2 * c) + 1] = d1 == whole[(2 * c) + 1] ? d1 : 0x7fffffff;
   }
-  int d0, d1;
-  Q4KDots(dec, a4, &d0, &d1);
-  const std::size_t at = (static_cast<std::size_t>(row) * (k / 32)) + (u * 2);
-  dots[at] = d0;
-  dots[at + 1] = d1;
-  qsums[at] = sums[0];
-  qsums[at + 1] = sums[1];
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    int s = 0;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) s = Dp4a(0x01010101, acts.q[(8 * g) + q], s);
+    qsums[at + g] = s;
+  }
 }
 
 template <int kBlocks>
@@ -179,12 +188,15 @@ int llmp_b200_vecq(int type, const llmp_b200_vecq_desc* desc, int variant, void*
   const bool q4 = type == LLMP_B200_TYPE_Q4_K;
   const bool stream_ok =
       dense && (q4 || q8_fast) && Aligned(d.w, 16) && (d.g == nullptr || Aligned(d.g, 16)) &&
-      PlanStream(d, q4 ? 64 : 128, q4 ? 144 : 34, q4 ? 256 : 32, p, SmCount(), &plan);
+      PlanStream(d, q4 ? (p == 1 ? 256 : 64) : 128, q4 ? 144 : 34, q4 ? 256 : 32, p, SmCount(),
+                 &plan);
   if (variant == kStreamVariant && !stream_ok) {
     return Reject("vecq: the stream variant takes dense products of 16-byte aligned rows only");
   }
   if (stream_ok && (variant == kStreamVariant || variant < 0)) {
-    e = q4 ? LaunchStream<Q4KUnit>(d, p, plan, s) : LaunchStream<Q8_0Unit<4>>(d, p, plan, s);
+    e = !q4      ? LaunchStream<Q8_0Unit<4>>(d, p, plan, s)
+        : p == 1 ? LaunchStream<Q4KBlockUnit>(d, p, plan, s)
+                 : LaunchStream<Q4KUnit>(d, p, plan, s);
     if (e != cudaSuccess) return Failed(e, "vecq stream launch");
     return 0;
   }
@@ -220,7 +232,7 @@ int llmp_b200_vecq_block_sums(int type, const void* w, const void* y, int k, int
     if (k % 256 != 0 || qsums == nullptr || !Aligned(w, 16) || !Aligned(y, 4)) {
       return Reject("block_sums: Q4_K needs k % 256 == 0, aligned operands and qsums");
     }
-    const long total = static_cast<long>(nrows) * (k / 64);
+    const long total = static_cast<long>(nrows) * (k / 256);
     BlockSumsQ4K<<<static_cast<unsigned>((total + 127) / 128), 128, 0, s>>>(wp, yp, k, nrows,
                                                                               stride_row, dots, qsums);
   } else if (type == LLMP_B200_TYPE_Q8_0) {

@@ -86,9 +86,103 @@ __device__ __forceinline__ void FenceProxyAsync() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// One whole Q4_K super-block a thread (144 bytes, nine 128-bit shared loads):
+// the 6-bit scales are unpacked once for the eight sub-blocks.  The one-token
+// stream uses this unit; its activations (256 values) fit a thread's registers.
+struct Q4KBlockUnit {
+  static constexpr int kType = LLMP_B200_TYPE_Q4_K;
+  static constexpr int kBlockBytes = 144;
+  static constexpr int kBlockElems = 256;
+  static constexpr int kUnitElems = 256;
+  uint4 head;
+  uint4 q[8];
+  __device__ __forceinline__ void LoadShared(const std::uint8_t* row, int u) {
+    const auto* sb = reinterpret_cast<const uint4*>(row + (static_cast<std::size_t>(u) * 144));
+    head = sb[0];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) q[i] = sb[1 + i];
+  }
+};
+
+// u8 x s8 dot product of four bytes into an s32 sum.
+__device__ __forceinline__ int Dp4aU8S8(std::uint32_t a, int b, int c) {
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
 // A thread's activations for its unit, one token.
 template <typename Unit>
 struct UnitActs;
+
+template <>
+struct UnitActs<Q4KBlockUnit> {
+  int q[64];     // 256 int8
+  float d8[8];   // per 32-value block: d
+  float fs[8];   // d * sum q
+  __device__ __forceinline__ void Load(const std::uint8_t* y, int u) {
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      const auto* src = reinterpret_cast<const std::uint32_t*>(
+          y + (static_cast<std::size_t>((u * 8) + g) * 36));
+      int isum = 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        q[(8 * g) + i] = static_cast<int>(src[1 + i]);
+        isum = Dp4a(0x01010101, q[(8 * g) + i], isum);
+      }
+      d8[g] = HalfBitsToFloat(src[0] & 0xffffu);
+      fs[g] = d8[g] * static_cast<float>(isum);
+    }
+  }
+};
+
+// The eight per-sub-block int32 sums (sum code * q) of a super-block.  The
+// high nibbles are multiplied in place (16 * code as an unsigned byte) and
+// the exact factor 16 is shifted out of the sum.
+__device__ __forceinline__ void Q4KBlockDots(const Q4KBlockUnit& w, const int* aq, int dots[8]) {
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const std::uint32_t words[8] = {w.q[2 * c].x,     w.q[2 * c].y,     w.q[2 * c].z,
+                                    w.q[2 * c].w,     w.q[2 * c + 1].x, w.q[2 * c + 1].y,
+                                    w.q[2 * c + 1].z, w.q[2 * c + 1].w};
+    int lo = 0, hi = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      lo = Dp4aU8S8(words[i] & 0x0f0f0f0fu, aq[(16 * c) + i], lo);
+      hi = Dp4aU8S8(words[i] & 0xf0f0f0f0u, aq[(16 * c) + 8 + i], hi);
+    }
+    dots[2 * c] = lo;
+    dots[(2 * c) + 1] = hi >> 4;
+  }
+}
+
+__device__ __forceinline__ void Q4KBlockScales(const Q4KBlockUnit& w, int sc[8], int mn[8]) {
+  const std::uint32_t s0 = w.head.y, s1 = w.head.z, s2 = w.head.w;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    sc[i] = static_cast<int>((s0 >> (8 * i)) & 63u);
+    mn[i] = static_cast<int>((s1 >> (8 * i)) & 63u);
+    sc[4 + i] = static_cast<int>(((s2 >> (8 * i)) & 15u) | (((s0 >> ((8 * i) + 6)) & 3u) << 4));
+    mn[4 + i] = static_cast<int>(((s2 >> ((8 * i) + 4)) & 15u) | (((s1 >> ((8 * i) + 6)) & 3u) << 4));
+  }
+}
+
+// d * sum_g d8_g * (sc_g * dot_g)  -  dmin * sum_g (d8_g * sum q_g) * m_g
+__device__ __forceinline__ float UnitDot(const Q4KBlockUnit& w, const UnitActs<Q4KBlockUnit>& a) {
+  int dots[8], sc[8], mn[8];
+  Q4KBlockDots(w, a.q, dots);
+  Q4KBlockScales(w, sc, mn);
+  float sumd = 0.0f, summ = 0.0f;
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    sumd = fmaf(a.d8[g], static_cast<float>(dots[g] * sc[g]), sumd);
+    summ = fmaf(a.fs[g], static_cast<float>(mn[g]), summ);
+  }
+  const float d = HalfBitsToFloat(w.head.x & 0xffffu);
+  const float dmin = HalfBitsToFloat(w.head.x >> 16);
+  return (d * sumd) - (dmin * summ);
+}
 
 template <>
 struct UnitActs<Q4KUnit> {
@@ -240,10 +334,12 @@ VecQStreamKernel(const Desc a, const StreamPlan plan) {
     const int s = it % S;
     const int r0 = row_begin + (it * RG);
     const int rows = min(RG, row_end - r0);
-    if (healthy && !MbarWait(&full[s], static_cast<std::uint32_t>((it / S) & 1))) {
+    // One lane polls; its warp follows through the warp barrier.
+    if (healthy && lane == 0 && !MbarWait(&full[s], static_cast<std::uint32_t>((it / S) & 1))) {
       healthy = false;
       atomicAdd(plan.faults, 1u);
     }
+    __syncwarp();
     const unsigned char* base = smem + (static_cast<std::size_t>(s) * plan.stage_bytes);
     float* part = partial + ((it & 1) * partial_stride);
     if (active) {
@@ -253,7 +349,7 @@ VecQStreamKernel(const Desc a, const StreamPlan plan) {
           const std::uint8_t* rowp = base + ((static_cast<std::size_t>(m) * RG + r) * plan.row_bytes);
           Unit raw;
           raw.LoadShared(rowp, u);
-          if constexpr (Unit::kType == LLMP_B200_TYPE_Q4_K) {
+          if constexpr (Unit::kUnitElems == 64) {
             Q4KDecoded dec;
             dec.From(raw, u);
 #pragma unroll
@@ -355,7 +451,10 @@ cudaError_t LaunchStream(const Desc& d, int p, const StreamPlan& plan, cudaStrea
   if (p == PP)                                                                \
     return glu ? LaunchStreamOne<Unit, PP, true>(d, plan, stream)             \
                : LaunchStreamOne<Unit, PP, false>(d, plan, stream);
-  LLMP_P(1) LLMP_P(2) LLMP_P(4) LLMP_P(8)
+  LLMP_P(1)
+  if constexpr (Unit::kUnitElems != 256) {  // the whole-super-block unit is one-token only
+    LLMP_P(2) LLMP_P(4) LLMP_P(8)
+  }
 #undef LLMP_P
   return cudaErrorInvalidValue;
 }

@@ -149,8 +149,11 @@ def test_fused_glu_equals_glu_of_the_unfused_products(cuda, orc, wtype, n, k, to
     g = ops.vecq(dgate, t, k, n, q8, tokens).cpu().numpy()
     want = np.array([[orc.glu(glu, g[i, j], u[i, j], limit) for j in range(n)]
                      for i in range(tokens)], np.float32)
-    # same sums in, GLU evaluated by two math libraries: a few ulp
-    assert np.allclose(fused, want, rtol=2e-6, atol=1e-30)
+    # same sums in, GLU evaluated by two math libraries: a few ulp of the factors
+    # (1 + tanh and 1 + exp cancel for negative gates, so the bound is on the
+    # factors' scale, not on the result's)
+    bound = 2e-6 * np.abs(want) + 4e-7 * np.abs(u) * np.maximum(1.0, np.abs(g))
+    assert (np.abs(fused - want) <= bound).all()
     # and against the oracle end to end at the F32 bar
     ref = orc.vecq(t, up, q8.cpu().numpy(), k, n, tokens, g=gate, glu=glu, limit=limit)[:, 0, :]
     assert float(np.abs(fused - ref).max()) <= 1e-5 * max(float(np.abs(ref).max()), 1e-30) * 4
