@@ -1,7 +1,7 @@
 // llmp.vecq entry points: operand checks, launch choice, and the per-block
 // int32 sums used to verify the product kernels.  The kernels themselves are
 // in vecq_impl.cuh, instantiated per weight type in vecq_q4k.cu / vecq_q8_0.cu.
-#include "vecq_stream.cuh"
+#include "vecq_rowlane.cuh"
 
 namespace llmp_b200 {
 namespace vecq {
@@ -190,6 +190,17 @@ int llmp_b200_vecq(int type, const llmp_b200_vecq_desc* desc, int variant, void*
       dense && (q4 || q8_fast) && Aligned(d.w, 16) && (d.g == nullptr || Aligned(d.g, 16)) &&
       PlanStream(d, q4 ? (p == 1 ? 256 : 64) : 128, q4 ? 144 : 34, q4 ? 256 : 32, p, SmCount(),
                  &plan);
+  RowLanePlan lanes;
+  const bool rowlane_ok = dense && q4 && Aligned(d.w, 16) && (d.g == nullptr || Aligned(d.g, 16)) &&
+                          PlanRowLane(d, p, SmCount(), &lanes);
+  if (variant == kRowLaneVariant && !rowlane_ok) {
+    return Reject("vecq: the rowlane variant takes dense Q4_K products of up to 8 tokens only");
+  }
+  if (rowlane_ok && (variant == kRowLaneVariant || variant < 0)) {
+    e = LaunchRowLane(d, p, lanes, s);
+    if (e != cudaSuccess) return Failed(e, "vecq rowlane launch");
+    return 0;
+  }
   if (variant == kStreamVariant && !stream_ok) {
     return Reject("vecq: the stream variant takes dense products of 16-byte aligned rows only");
   }

@@ -485,9 +485,13 @@ constexpr Variant kVariants[] = {
     {"l32r1u4w8", 32, 1, 4, 8},
     // The persistent TMA-fed stream kernel (vecq_stream.cuh); dense products only.
     {"stream", 0, 0, 0, 0},
+    // One lane per weight row over warp-private TMA rings (vecq_rowlane.cuh);
+    // dense Q4_K products of up to 8 tokens.
+    {"rowlane", 0, 0, 0, 0},
 };
 constexpr int kVariantCount = static_cast<int>(sizeof(kVariants) / sizeof(kVariants[0]));
-constexpr int kStreamVariant = kVariantCount - 1;
+constexpr int kStreamVariant = kVariantCount - 2;
+constexpr int kRowLaneVariant = kVariantCount - 1;
 
 template <typename Unit, int P, int LPR, int R, int U, bool kGlu>
 cudaError_t LaunchOne(const Desc& d, int warps, cudaStream_t stream) {

@@ -1,0 +1,336 @@
+// Dense Q4_K llmp.vecq for 1..8 tokens as a persistent HBM stream with one
+// lane per weight row.  Interface and sums' contract are the reference's
+// (src/kernels/ggml/vecq.h:23-49, vecq.cu:457-665); the structure is B200's.
+//
+//   * One CTA per SM owns a contiguous, evenly divided range of output rows;
+//     its W warps split that range, R rows a warp (R a power of two <= 32).
+//   * A lane is (row r, phase ph), PH = 32 / R phases.  The warp sweeps the
+//     row's super-blocks ("columns") PH at a time; lane (r, ph) decodes column
+//     j * PH + ph of row r.  A lane therefore accumulates its row's whole dot
+//     product in registers; the PH phases meet in a fixed xor-shuffle tree at
+//     the end.  No atomics, no cross-warp traffic, and a (token, row) sum does
+//     not depend on the other tokens of the launch.
+//   * Weights reach shared memory through the TMA bulk-copy engine: for every
+//     column step each row's PH consecutive super-blocks (PH * 144 bytes) are
+//     one cp.async.bulk into the warp's PRIVATE ring of stages, completing on
+//     that stage's mbarrier.  Warps never synchronize with each other in the
+//     main loop.  The ring holds most of the CTA's bytes, so nearly the whole
+//     matrix is requested in the first microsecond: that, not arithmetic, is
+//     what bounds a 15-30 MB product.
+//   * The first stages are requested BEFORE the programmatic-dependency wait
+//     (weights depend on no earlier kernel); activations are staged after it.
+//   * Row pieces sit at a pitch chosen so that the eight lanes of a quarter
+//     warp read distinct bank groups (128-bit shared loads, no conflicts).
+//   * Activations are staged once a CTA, interleaved by column so that the
+//     lanes of different phases read adjacent 16-byte chunks and lanes of the
+//     same phase broadcast.
+//   * Every mbarrier wait is bounded and reports through the fault counter.
+#ifndef LLMP_B200_CSRC_VECQ_ROWLANE_CUH_
+#define LLMP_B200_CSRC_VECQ_ROWLANE_CUH_
+
+#include "vecq_stream.cuh"
+
+namespace llmp_b200 {
+namespace vecq {
+
+constexpr int kRowLaneMaxWarps = 12;
+constexpr int kRowLaneMaxStages = 8;
+
+struct RowLanePlan {
+  int warps;         // W
+  int rows;          // R rows a warp (power of two)
+  int phases;        // PH = 32 / R
+  int columns;       // UR = k / 256
+  int steps;         // J = ceil(UR / PH)
+  int stages;        // S_w, ring depth a warp
+  int pitch;         // bytes between a stage's rows
+  int stage_bytes;   // R * pitch * mats
+  int acts_bytes;    // one token's staged activations
+  int smem_bytes;
+  int grid;
+  unsigned int* faults;
+};
+
+template <int P, bool kGlu>
+__global__ void __launch_bounds__(kRowLaneMaxWarps * 32, 1)
+VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
+  constexpr int kMats = kGlu ? 2 : 1;
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(8) std::uint64_t full[kRowLaneMaxWarps][kRowLaneMaxStages];
+
+  const int tid = static_cast<int>(threadIdx.x);
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int R = plan.rows;
+  const int PH = plan.phases;
+  const int UR = plan.columns;
+  const int J = plan.steps;
+  const int S = plan.stages;
+  const int r = lane % R;
+  const int ph = lane / R;
+
+  // This CTA's rows, then this warp's share of them (at most R).
+  const int cta_begin = static_cast<int>((static_cast<long>(blockIdx.x) * a.nrows) / gridDim.x);
+  const int cta_end = static_cast<int>((static_cast<long>(blockIdx.x + 1) * a.nrows) / gridDim.x);
+  const int cta_rows = cta_end - cta_begin;
+  const int row_begin = cta_begin + ((warp * cta_rows) / plan.warps);
+  const int row_end = cta_begin + (((warp + 1) * cta_rows) / plan.warps);
+  const int my_rows = row_end - row_begin;  // <= R by the plan
+
+  unsigned char* acts = smem;
+  unsigned char* ring = smem + (static_cast<std::size_t>(P) * plan.acts_bytes) +
+                        (static_cast<std::size_t>(warp) * S * plan.stage_bytes);
+
+  const std::uint8_t* mats[kMats];
+  mats[0] = static_cast<const std::uint8_t*>(a.w);
+  if constexpr (kGlu) mats[1] = static_cast<const std::uint8_t*>(a.g);
+
+  if (lane == 0) {
+    for (int s = 0; s < S; ++s) MbarInit(&full[warp][s], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+
+  // Requests column step j of this warp's rows into its stage.
+  auto request = [&](int j) {
+    const int s = j % S;
+    const int cols = min(PH, UR - (j * PH));
+    const std::uint32_t piece = static_cast<std::uint32_t>(cols) * 144u;
+    unsigned char* base = ring + (static_cast<std::size_t>(s) * plan.stage_bytes);
+    if (lane == 0) {
+      MbarExpectTx(&full[warp][s], piece * static_cast<std::uint32_t>(my_rows * kMats));
+    }
+    __syncwarp();
+    for (int c = lane; c < my_rows * kMats; c += 32) {
+      const int m = c / my_rows;
+      const int row = c % my_rows;
+      const std::uint8_t* src =
+          mats[m] + ((static_cast<std::size_t>(row_begin + row) * a.stride_row +
+                      static_cast<std::size_t>(j) * PH) * 144);
+      BulkLoad(base + ((static_cast<std::size_t>(m) * R + row) * plan.pitch), src, piece,
+               &full[warp][s]);
+    }
+  };
+
+  GridLaunchDependents();
+  if (my_rows > 0) {
+    for (int j = 0; j < min(S, J); ++j) request(j);
+  }
+  GridDependencyWait();
+
+  // Stage the tokens' activations: one Q8_1 block a thread.  Column c's i-th
+  // 16-byte chunk is chunk (i * UR + c); its scales follow in four float4
+  // planes: d[0..3], d[4..7], d * sum q [0..3], [4..7].
+  {
+    const int blocks = UR * 8;
+    for (int t = 0; t < P; ++t) {
+      const int token = min(t, a.tokens - 1);
+      const std::uint8_t* y = static_cast<const std::uint8_t*>(a.y) +
+                              (static_cast<std::size_t>(token) * a.y_token * 36);
+      uint4* q = reinterpret_cast<uint4*>(acts + (static_cast<std::size_t>(t) * plan.acts_bytes));
+      float* sc = reinterpret_cast<float*>(q + (16 * UR));
+      for (int b = tid; b < blocks; b += static_cast<int>(blockDim.x)) {
+        const auto* src = reinterpret_cast<const std::uint32_t*>(y + (static_cast<std::size_t>(b) * 36));
+        std::uint32_t v[8];
+        int isum = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          v[i] = src[1 + i];
+          isum = Dp4a(0x01010101, static_cast<int>(v[i]), isum);
+        }
+        const int c = b >> 3, g = b & 7;
+        q[((2 * g) * UR) + c] = make_uint4(v[0], v[1], v[2], v[3]);
+        q[((2 * g + 1) * UR) + c] = make_uint4(v[4], v[5], v[6], v[7]);
+        const float d = HalfBitsToFloat(src[0] & 0xffffu);
+        sc[((((g >> 2)) * UR + c) * 4) + (g & 3)] = d;
+        sc[((((2 + (g >> 2))) * UR + c) * 4) + (g & 3)] = d * static_cast<float>(isum);
+      }
+    }
+  }
+  __syncthreads();
+  if (my_rows == 0) return;
+
+  float acc[P][kMats];
+#pragma unroll
+  for (int t = 0; t < P; ++t)
+#pragma unroll
+    for (int m = 0; m < kMats; ++m) acc[t][m] = 0.0f;
+
+  bool healthy = true;
+  for (int j = 0; j < J; ++j) {
+    const int s = j % S;
+    if (healthy && lane == 0 &&
+        !MbarWait(&full[warp][s], static_cast<std::uint32_t>((j / S) & 1))) {
+      healthy = false;
+      atomicAdd(plan.faults, 1u);
+    }
+    __syncwarp();
+    const int c = (j * PH) + ph;
+    if (c < UR && r < my_rows) {
+      const unsigned char* base = ring + (static_cast<std::size_t>(s) * plan.stage_bytes);
+#pragma unroll
+      for (int m = 0; m < kMats; ++m) {
+        Q4KBlockUnit raw;
+        raw.LoadShared(base + ((static_cast<std::size_t>(m) * R + r) * plan.pitch), ph);
+        int sc[8], mn[8];
+        Q4KBlockScales(raw, sc, mn);
+        float fmn[8];
+#pragma unroll
+        for (int g = 0; g < 8; ++g) fmn[g] = static_cast<float>(mn[g]);
+        float sumd[P], summ[P];
+#pragma unroll
+        for (int t = 0; t < P; ++t) sumd[t] = summ[t] = 0.0f;
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          const std::uint32_t words[8] = {raw.q[2 * cc].x,     raw.q[2 * cc].y,
+                                          raw.q[2 * cc].z,     raw.q[2 * cc].w,
+                                          raw.q[2 * cc + 1].x, raw.q[2 * cc + 1].y,
+                                          raw.q[2 * cc + 1].z, raw.q[2 * cc + 1].w};
+          std::uint32_t lo[8], hi[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            lo[i] = words[i] & 0x0f0f0f0fu;
+            hi[i] = words[i] & 0xf0f0f0f0u;  // 16 * code: the factor is shifted out below
+          }
+#pragma unroll
+          for (int t = 0; t < P; ++t) {
+            const uint4* q =
+                reinterpret_cast<const uint4*>(acts + (static_cast<std::size_t>(t) * plan.acts_bytes));
+            const float* scl = reinterpret_cast<const float*>(q + (16 * UR));
+            const uint4 a0 = q[((4 * cc) * UR) + c], a1 = q[((4 * cc + 1) * UR) + c];
+            const uint4 a2 = q[((4 * cc + 2) * UR) + c], a3 = q[((4 * cc + 3) * UR) + c];
+            int d0 = 0, d1 = 0;
+            d0 = Dp4aU8S8(lo[0], static_cast<int>(a0.x), d0);
+            d0 = Dp4aU8S8(lo[1], static_cast<int>(a0.y), d0);
+            d0 = Dp4aU8S8(lo[2], static_cast<int>(a0.z), d0);
+            d0 = Dp4aU8S8(lo[3], static_cast<int>(a0.w), d0);
+            d0 = Dp4aU8S8(lo[4], static_cast<int>(a1.x), d0);
+            d0 = Dp4aU8S8(lo[5], static_cast<int>(a1.y), d0);
+            d0 = Dp4aU8S8(lo[6], static_cast<int>(a1.z), d0);
+            d0 = Dp4aU8S8(lo[7], static_cast<int>(a1.w), d0);
+            d1 = Dp4aU8S8(hi[0], static_cast<int>(a2.x), d1);
+            d1 = Dp4aU8S8(hi[1], static_cast<int>(a2.y), d1);
+            d1 = Dp4aU8S8(hi[2], static_cast<int>(a2.z), d1);
+            d1 = Dp4aU8S8(hi[3], static_cast<int>(a2.w), d1);
+            d1 = Dp4aU8S8(hi[4], static_cast<int>(a3.x), d1);
+            d1 = Dp4aU8S8(hi[5], static_cast<int>(a3.y), d1);
+            d1 = Dp4aU8S8(hi[6], static_cast<int>(a3.z), d1);
+            d1 = Dp4aU8S8(hi[7], static_cast<int>(a3.w), d1);
+            d1 >>= 4;
+            // sub-blocks 2cc and 2cc+1: scale planes hold four blocks a float4
+            const int plane = cc >> 1, at = (cc & 1) * 2;
+            const float* dd = scl + (((plane * UR) + c) * 4) + at;
+            const float* ff = scl + ((((2 + plane) * UR) + c) * 4) + at;
+            sumd[t] = fmaf(dd[0], static_cast<float>(d0 * sc[2 * cc]), sumd[t]);
+            sumd[t] = fmaf(dd[1], static_cast<float>(d1 * sc[2 * cc + 1]), sumd[t]);
+            summ[t] = fmaf(ff[0], fmn[2 * cc], summ[t]);
+            summ[t] = fmaf(ff[1], fmn[2 * cc + 1], summ[t]);
+          }
+        }
+        const float d = HalfBitsToFloat(raw.head.x & 0xffffu);
+        const float dmin = HalfBitsToFloat(raw.head.x >> 16);
+#pragma unroll
+        for (int t = 0; t < P; ++t) acc[t][m] += (d * sumd[t]) - (dmin * summ[t]);
+      }
+    }
+    __syncwarp();
+    if (j + S < J) {
+      FenceProxyAsync();
+      request(j + S);
+    }
+  }
+
+  // The phases of a row meet: lanes r, r + R, r + 2R, ...
+#pragma unroll
+  for (int t = 0; t < P; ++t) {
+    float v[kMats];
+#pragma unroll
+    for (int m = 0; m < kMats; ++m) {
+      v[m] = acc[t][m];
+      for (int offset = 16; offset >= R; offset >>= 1) {
+        v[m] += __shfl_xor_sync(0xffffffffu, v[m], offset);
+      }
+    }
+    if (ph == 0 && r < my_rows && t < a.tokens) {
+      float* dst = a.dst + (static_cast<std::size_t>(t) * a.dst_token) + row_begin + r;
+      if constexpr (kGlu) {
+        *dst = Glu(a.glu, v[1], v[0], a.limit);
+      } else {
+        *dst = v[0];
+      }
+    }
+  }
+}
+
+// Host: the geometry for a dense Q4_K product, or false if it does not fit.
+inline bool PlanRowLane(const Desc& d, int p, int sms, RowLanePlan* plan) {
+  const int mats = d.glu != LLMP_B200_GLU_NONE ? 2 : 1;
+  const int ur = d.ncols_x / 256;
+  if (ur < 1) return false;
+  const int grid = std::max(1, std::min(sms, d.nrows));
+  const int cta_rows = (d.nrows + grid - 1) / grid;
+  const int acts_bytes = (ur * 256) + (ur * 64);
+  const int budget = 220 * 1024 - (p * acts_bytes) - 1024;
+  if (budget <= 0) return false;
+  double best_score = -1.0;
+  RowLanePlan best{};
+  for (int rows = 1; rows <= 32; rows *= 2) {
+    const int warps = (cta_rows + rows - 1) / rows;
+    if (warps < 1 || warps > kRowLaneMaxWarps) continue;
+    const int phases = 32 / rows;
+    const int steps = (ur + phases - 1) / phases;
+    // pitch / 16 must be congruent to 8 / min(rows, 8) (mod 8) times an odd number
+    const int rq = std::min(rows, 8);
+    int pitch16 = phases * 9;
+    const int want = 8 / rq;  // 1, 2, 4 or 8
+    while ((pitch16 % (2 * want)) != (want % (2 * want))) ++pitch16;
+    const int pitch = pitch16 * 16;
+    const int stage_bytes = rows * pitch * mats;
+    int stages = std::min({steps, kRowLaneMaxStages, budget / (warps * stage_bytes)});
+    if (stages < 1) continue;
+    if (stages < steps && stages < 2) continue;
+    // Lane utilization, with a preference for more warps and for a ring that
+    // holds the whole range.
+    const double lanes = static_cast<double>(cta_rows) * ur /
+                         (static_cast<double>(warps) * rows * steps * phases);
+    const double score = lanes * (0.6 + 0.4 * std::min(1.0, warps / 8.0)) *
+                         (0.7 + 0.3 * static_cast<double>(stages) / steps);
+    if (score > best_score) {
+      best_score = score;
+      best.warps = warps;
+      best.rows = rows;
+      best.phases = phases;
+      best.columns = ur;
+      best.steps = steps;
+      best.stages = stages;
+      best.pitch = pitch;
+      best.stage_bytes = stage_bytes;
+      best.acts_bytes = acts_bytes;
+      best.smem_bytes = (p * acts_bytes) + (warps * stages * stage_bytes);
+      best.grid = grid;
+    }
+  }
+  if (best_score < 0.0) return false;
+  best.faults = FaultCounter();
+  if (best.faults == nullptr) return false;
+  *plan = best;
+  return true;
+}
+
+template <int P, bool kGlu>
+cudaError_t LaunchRowLaneOne(const Desc& d, const RowLanePlan& plan, cudaStream_t stream) {
+  auto* kernel = VecQRowLaneKernel<P, kGlu>;
+  const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             plan.smem_bytes);
+  if (e != cudaSuccess) return e;
+  return LaunchPdl(kernel, dim3(static_cast<unsigned>(plan.grid)),
+                   dim3(static_cast<unsigned>(plan.warps * 32)),
+                   static_cast<std::size_t>(plan.smem_bytes), stream, d, plan);
+}
+
+cudaError_t LaunchRowLane(const Desc& d, int p, const RowLanePlan& plan, cudaStream_t stream);
+
+}  // namespace vecq
+}  // namespace llmp_b200
+
+#endif  // LLMP_B200_CSRC_VECQ_ROWLANE_CUH_
