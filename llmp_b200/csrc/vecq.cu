@@ -191,12 +191,14 @@ int llmp_b200_vecq(int type, const llmp_b200_vecq_desc* desc, int variant, void*
       PlanStream(d, q4 ? (p == 1 ? 256 : 64) : 128, q4 ? 144 : 34, q4 ? 256 : 32, p, SmCount(),
                  &plan);
   RowLanePlan lanes;
+  const bool wants_rowlane = variant >= kRowLaneVariant;
   const bool rowlane_ok = dense && q4 && Aligned(d.w, 16) && (d.g == nullptr || Aligned(d.g, 16)) &&
-                          PlanRowLane(d, p, SmCount(), &lanes);
-  if (variant == kRowLaneVariant && !rowlane_ok) {
-    return Reject("vecq: the rowlane variant takes dense Q4_K products of up to 8 tokens only");
+                          PlanRowLane(d, p, SmCount(), wants_rowlane ? kVariants[variant].r : 0,
+                                      &lanes);
+  if (wants_rowlane && !rowlane_ok) {
+    return Reject("vecq: this rowlane variant does not take the product (dense Q4_K, <= 8 tokens)");
   }
-  if (rowlane_ok && (variant == kRowLaneVariant || variant < 0)) {
+  if (rowlane_ok && (wants_rowlane || variant < 0)) {
     e = LaunchRowLane(d, p, lanes, s);
     if (e != cudaSuccess) return Failed(e, "vecq rowlane launch");
     return 0;

@@ -488,10 +488,17 @@ constexpr Variant kVariants[] = {
     // One lane per weight row over warp-private TMA rings (vecq_rowlane.cuh);
     // dense Q4_K products of up to 8 tokens.
     {"rowlane", 0, 0, 0, 0},
+    // The same with the rows a warp forced (r field), for measurement.
+    {"rowlane.r1", 0, 1, 0, 0},
+    {"rowlane.r2", 0, 2, 0, 0},
+    {"rowlane.r4", 0, 4, 0, 0},
+    {"rowlane.r8", 0, 8, 0, 0},
+    {"rowlane.r16", 0, 16, 0, 0},
+    {"rowlane.r32", 0, 32, 0, 0},
 };
 constexpr int kVariantCount = static_cast<int>(sizeof(kVariants) / sizeof(kVariants[0]));
-constexpr int kStreamVariant = kVariantCount - 2;
-constexpr int kRowLaneVariant = kVariantCount - 1;
+constexpr int kStreamVariant = kVariantCount - 8;
+constexpr int kRowLaneVariant = kVariantCount - 7;  // and the six forced forms after it
 
 template <typename Unit, int P, int LPR, int R, int U, bool kGlu>
 cudaError_t LaunchOne(const Desc& d, int warps, cudaStream_t stream) {

@@ -168,6 +168,11 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
     const int c = (j * PH) + ph;
     if (c < UR && r < my_rows) {
       const unsigned char* base = ring + (static_cast<std::size_t>(s) * plan.stage_bytes);
+      const uint4* act_q[P];  // this column's first chunk, per token
+#pragma unroll
+      for (int t = 0; t < P; ++t) {
+        act_q[t] = reinterpret_cast<const uint4*>(acts + (static_cast<std::size_t>(t) * plan.acts_bytes)) + c;
+      }
 #pragma unroll
       for (int m = 0; m < kMats; ++m) {
         Q4KBlockUnit raw;
@@ -178,6 +183,7 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
 #pragma unroll
         for (int g = 0; g < 8; ++g) fmn[g] = static_cast<float>(mn[g]);
         float sumd[P], summ[P];
+        int dots[P][8];
 #pragma unroll
         for (int t = 0; t < P; ++t) sumd[t] = summ[t] = 0.0f;
 #pragma unroll
@@ -194,11 +200,9 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
           }
 #pragma unroll
           for (int t = 0; t < P; ++t) {
-            const uint4* q =
-                reinterpret_cast<const uint4*>(acts + (static_cast<std::size_t>(t) * plan.acts_bytes));
-            const float* scl = reinterpret_cast<const float*>(q + (16 * UR));
-            const uint4 a0 = q[((4 * cc) * UR) + c], a1 = q[((4 * cc + 1) * UR) + c];
-            const uint4 a2 = q[((4 * cc + 2) * UR) + c], a3 = q[((4 * cc + 3) * UR) + c];
+            const uint4* q = act_q[t] + ((4 * cc) * UR);
+            const uint4 a0 = q[0], a1 = q[UR];
+            const uint4 a2 = q[2 * UR], a3 = q[3 * UR];
             int d0 = 0, d1 = 0;
             d0 = Dp4aU8S8(lo[0], static_cast<int>(a0.x), d0);
             d0 = Dp4aU8S8(lo[1], static_cast<int>(a0.y), d0);
@@ -216,15 +220,21 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
             d1 = Dp4aU8S8(hi[5], static_cast<int>(a3.y), d1);
             d1 = Dp4aU8S8(hi[6], static_cast<int>(a3.z), d1);
             d1 = Dp4aU8S8(hi[7], static_cast<int>(a3.w), d1);
-            d1 >>= 4;
-            // sub-blocks 2cc and 2cc+1: scale planes hold four blocks a float4
-            const int plane = cc >> 1, at = (cc & 1) * 2;
-            const float* dd = scl + (((plane * UR) + c) * 4) + at;
-            const float* ff = scl + ((((2 + plane) * UR) + c) * 4) + at;
-            sumd[t] = fmaf(dd[0], static_cast<float>(d0 * sc[2 * cc]), sumd[t]);
-            sumd[t] = fmaf(dd[1], static_cast<float>(d1 * sc[2 * cc + 1]), sumd[t]);
-            summ[t] = fmaf(ff[0], fmn[2 * cc], summ[t]);
-            summ[t] = fmaf(ff[1], fmn[2 * cc + 1], summ[t]);
+            dots[t][2 * cc] = d0;
+            dots[t][(2 * cc) + 1] = d1 >> 4;
+          }
+        }
+        // d * sum_g d8_g * (sc_g * dot_g)  -  dmin * sum_g (d8_g * sum q_g) * m_g
+#pragma unroll
+        for (int t = 0; t < P; ++t) {
+          const float4* scl = reinterpret_cast<const float4*>(act_q[t] + (16 * UR));
+          const float4 dA = scl[0], dB = scl[UR], fA = scl[2 * UR], fB = scl[3 * UR];
+          const float dd[8] = {dA.x, dA.y, dA.z, dA.w, dB.x, dB.y, dB.z, dB.w};
+          const float ff[8] = {fA.x, fA.y, fA.z, fA.w, fB.x, fB.y, fB.z, fB.w};
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            sumd[t] = fmaf(dd[g], static_cast<float>(dots[t][g] * sc[g]), sumd[t]);
+            summ[t] = fmaf(ff[g], fmn[g], summ[t]);
           }
         }
         const float d = HalfBitsToFloat(raw.head.x & 0xffffu);
@@ -263,7 +273,7 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
 }
 
 // Host: the geometry for a dense Q4_K product, or false if it does not fit.
-inline bool PlanRowLane(const Desc& d, int p, int sms, RowLanePlan* plan) {
+inline bool PlanRowLane(const Desc& d, int p, int sms, int force_rows, RowLanePlan* plan) {
   const int mats = d.glu != LLMP_B200_GLU_NONE ? 2 : 1;
   const int ur = d.ncols_x / 256;
   if (ur < 1) return false;
@@ -275,6 +285,7 @@ inline bool PlanRowLane(const Desc& d, int p, int sms, RowLanePlan* plan) {
   double best_score = -1.0;
   RowLanePlan best{};
   for (int rows = 1; rows <= 32; rows *= 2) {
+    if (force_rows > 0 && rows != force_rows) continue;
     const int warps = (cta_rows + rows - 1) / rows;
     if (warps < 1 || warps > kRowLaneMaxWarps) continue;
     const int phases = 32 / rows;
