@@ -194,7 +194,7 @@ int llmp_b200_vecq(int type, const llmp_b200_vecq_desc* desc, int variant, void*
   const bool wants_rowlane = variant >= kRowLaneVariant;
   const bool rowlane_ok = dense && q4 && Aligned(d.w, 16) && (d.g == nullptr || Aligned(d.g, 16)) &&
                           PlanRowLane(d, p, SmCount(), wants_rowlane ? kVariants[variant].r : 0,
-                                      &lanes);
+                                      wants_rowlane && kVariants[variant].u == 1, &lanes);
   if (wants_rowlane && !rowlane_ok) {
     return Reject("vecq: this rowlane variant does not take the product (dense Q4_K, <= 8 tokens)");
   }

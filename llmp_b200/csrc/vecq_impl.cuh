@@ -495,10 +495,12 @@ constexpr Variant kVariants[] = {
     {"rowlane.r8", 0, 8, 0, 0},
     {"rowlane.r16", 0, 16, 0, 0},
     {"rowlane.r32", 0, 32, 0, 0},
+    // Half an SM a CTA (u field = 1), so consecutive kernels overlap.
+    {"rowlane.half", 0, 0, 1, 0},
 };
 constexpr int kVariantCount = static_cast<int>(sizeof(kVariants) / sizeof(kVariants[0]));
-constexpr int kStreamVariant = kVariantCount - 8;
-constexpr int kRowLaneVariant = kVariantCount - 7;  // and the six forced forms after it
+constexpr int kStreamVariant = kVariantCount - 9;
+constexpr int kRowLaneVariant = kVariantCount - 8;  // and its seven forced forms after it
 
 template <typename Unit, int P, int LPR, int R, int U, bool kGlu>
 cudaError_t LaunchOne(const Desc& d, int warps, cudaStream_t stream) {

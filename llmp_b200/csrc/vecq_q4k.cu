@@ -10,8 +10,10 @@ cudaError_t LaunchRowLane(const Desc& d, int p, const RowLanePlan& plan, cudaStr
   const bool glu = d.glu != LLMP_B200_GLU_NONE;
 #define LLMP_P(PP)                                                   \
   if (p == PP)                                                       \
-    return glu ? LaunchRowLaneOne<PP, true>(d, plan, stream)         \
-               : LaunchRowLaneOne<PP, false>(d, plan, stream);
+    return plan.half ? (glu ? LaunchRowLaneOne<PP, true, true>(d, plan, stream)    \
+                            : LaunchRowLaneOne<PP, false, true>(d, plan, stream))  \
+                     : (glu ? LaunchRowLaneOne<PP, true, false>(d, plan, stream)   \
+                            : LaunchRowLaneOne<PP, false, false>(d, plan, stream));
   LLMP_P(1) LLMP_P(2) LLMP_P(4) LLMP_P(8)
 #undef LLMP_P
   return cudaErrorInvalidValue;

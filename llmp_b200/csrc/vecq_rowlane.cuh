@@ -33,7 +33,8 @@
 namespace llmp_b200 {
 namespace vecq {
 
-constexpr int kRowLaneMaxWarps = 12;
+constexpr int kRowLaneMaxWarps = 12;      // a CTA that owns its SM
+constexpr int kRowLaneHalfWarps = 9;      // a CTA that shares its SM with the next kernel's
 constexpr int kRowLaneMaxStages = 8;
 
 struct RowLanePlan {
@@ -48,11 +49,16 @@ struct RowLanePlan {
   int acts_bytes;    // one token's staged activations
   int smem_bytes;
   int grid;
+  int half;          // the kHalf instantiation
   unsigned int* faults;
 };
 
-template <int P, bool kGlu>
-__global__ void __launch_bounds__(kRowLaneMaxWarps * 32, 1)
+// kHalf: at most half an SM's registers and shared memory, so that the kernel
+// after this one (launched as a programmatic dependent) becomes resident and
+// requests its weights while this one still computes.
+template <int P, bool kGlu, bool kHalf>
+__global__ void __launch_bounds__(kHalf ? kRowLaneHalfWarps * 32 : kRowLaneMaxWarps * 32,
+                                  kHalf ? 2 : 1)
 VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
   constexpr int kMats = kGlu ? 2 : 1;
   extern __shared__ __align__(128) unsigned char smem[];
@@ -273,21 +279,23 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
 }
 
 // Host: the geometry for a dense Q4_K product, or false if it does not fit.
-inline bool PlanRowLane(const Desc& d, int p, int sms, int force_rows, RowLanePlan* plan) {
+inline bool PlanRowLane(const Desc& d, int p, int sms, int force_rows, bool half,
+                        RowLanePlan* plan) {
   const int mats = d.glu != LLMP_B200_GLU_NONE ? 2 : 1;
   const int ur = d.ncols_x / 256;
   if (ur < 1) return false;
   const int grid = std::max(1, std::min(sms, d.nrows));
   const int cta_rows = (d.nrows + grid - 1) / grid;
   const int acts_bytes = (ur * 256) + (ur * 64);
-  const int budget = 220 * 1024 - (p * acts_bytes) - 1024;
+  const int budget = (half ? 110 : 220) * 1024 - (p * acts_bytes) - 1024;
+  const int max_warps = half ? kRowLaneHalfWarps : kRowLaneMaxWarps;
   if (budget <= 0) return false;
   double best_score = -1.0;
   RowLanePlan best{};
   for (int rows = 1; rows <= 32; rows *= 2) {
     if (force_rows > 0 && rows != force_rows) continue;
     const int warps = (cta_rows + rows - 1) / rows;
-    if (warps < 1 || warps > kRowLaneMaxWarps) continue;
+    if (warps < 1 || warps > max_warps) continue;
     const int phases = 32 / rows;
     const int steps = (ur + phases - 1) / phases;
     // pitch / 16 must be congruent to 8 / min(rows, 8) (mod 8) times an odd number
@@ -319,6 +327,7 @@ inline bool PlanRowLane(const Desc& d, int p, int sms, int force_rows, RowLanePl
       best.acts_bytes = acts_bytes;
       best.smem_bytes = (p * acts_bytes) + (warps * stages * stage_bytes);
       best.grid = grid;
+      best.half = half ? 1 : 0;
     }
   }
   if (best_score < 0.0) return false;
@@ -328,9 +337,9 @@ inline bool PlanRowLane(const Desc& d, int p, int sms, int force_rows, RowLanePl
   return true;
 }
 
-template <int P, bool kGlu>
+template <int P, bool kGlu, bool kHalf>
 cudaError_t LaunchRowLaneOne(const Desc& d, const RowLanePlan& plan, cudaStream_t stream) {
-  auto* kernel = VecQRowLaneKernel<P, kGlu>;
+  auto* kernel = VecQRowLaneKernel<P, kGlu, kHalf>;
   const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              plan.smem_bytes);
   if (e != cudaSuccess) return e;
