@@ -113,6 +113,45 @@ int llmp_b200_vecq(int type, const llmp_b200_vecq_desc* desc, int variant, void*
 int llmp_b200_vecq_block_sums(int type, const void* w, const void* y, int k, int nrows,
                               int stride_row, int32_t* dots, int32_t* qsums, void* stream);
 
+/* ------------------------------------------------------------------ MXFP8 */
+/* MXFP8: E4M3 codes with one E8M0 scale per 32 values along K.  Scales live in
+ * "scale atoms" (src/format/layout.h:97-112, == moe_cutlass.h:42-46 SfOffset):
+ * 128 rows x 4 scales per 512-byte atom, atoms along K first, rows padded to a
+ * multiple of 128 with zero scales.  The atom is also the layout tcgen05.cp
+ * reads, so the GEMM copies atoms unchanged. */
+uint64_t llmp_b200_mxfp8_padded_rows(uint64_t rows);
+uint64_t llmp_b200_mxfp8_scale_offset(uint64_t row, uint64_t block, uint64_t blocks);
+
+/* Replaces RunMxfp8Quantize (src/kernels/ggml/llmp_ops.cu:868; kernel :610-650,
+ * arithmetic mxfp8_quant.cuh:22-46).  x: F32 or BF16 [k, rows], row stride in
+ * elements.  codes: rows * k bytes.  scales: padded_rows(rows) * k / 32 bytes
+ * in scale atoms (the caller places them; RowsLayout of mxfp8_cutlass.h:42-49
+ * puts them 256-byte aligned after the codes). */
+int llmp_b200_mxfp8_quantize(const void* x, int is_bf16, int64_t row_stride, int k, int rows,
+                             void* codes, void* scales, void* stream);
+/* Replaces RunMxfp8Swizzle (llmp_ops.cu:895; kernel :652-663): weight scales
+ * [n, k/32] row-major -> scale atoms of padded_rows(n) rows. */
+int llmp_b200_mxfp8_swizzle(const void* in, void* out, int n, int blocks, void* stream);
+
+/* Field for field mxfp8::Gemm (src/kernels/ggml/mxfp8_cutlass.h:56-68). */
+typedef struct llmp_b200_mxfp8_gemm_desc {
+  int m, n, k;
+  const void* a;        /* codes, m rows of k */
+  const void* a_scales; /* scale atoms */
+  const void* b;        /* codes, n rows of k */
+  const void* b_scales; /* scale atoms */
+  void* d;              /* m rows of n */
+  int bf16;             /* D in BF16, else F32 */
+  void* scratch;        /* llmp_b200_mxfp8_gemm_scratch() bytes (0: may be NULL) */
+} llmp_b200_mxfp8_gemm_desc;
+
+/* Replace mxfp8::Available / Scratch / Run (mxfp8_cutlass.h:70-79): D[m,n] =
+ * A[m,k] . B[n,k]^T with F32 accumulation on tcgen05 (kind::mxf8f6f4
+ * block_scale).  k % 128 == 0.  sms <= 0: every SM of the device. */
+int llmp_b200_mxfp8_gemm_available(void);
+size_t llmp_b200_mxfp8_gemm_scratch(const llmp_b200_mxfp8_gemm_desc* gemm, int sms);
+int llmp_b200_mxfp8_gemm(const llmp_b200_mxfp8_gemm_desc* gemm, int sms, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -34,6 +34,13 @@ class VecQDesc(C.Structure):
                         ("limit", C.c_float)]
 
 
+class Mxfp8GemmDesc(C.Structure):
+    """llmp_b200_mxfp8_gemm_desc (include/llmp_b200.h)."""
+    _fields_ = [("m", C.c_int), ("n", C.c_int), ("k", C.c_int), ("a", C.c_void_p),
+                ("a_scales", C.c_void_p), ("b", C.c_void_p), ("b_scales", C.c_void_p),
+                ("d", C.c_void_p), ("bf16", C.c_int), ("scratch", C.c_void_p)]
+
+
 # name -> (restype, argtypes): every symbol include/llmp_b200.h declares.
 SIGNATURES = {
     "llmp_b200_available": (C.c_int, []),
@@ -46,6 +53,14 @@ SIGNATURES = {
     "llmp_b200_vecq_variants": (C.c_int, []),
     "llmp_b200_vecq_variant_name": (C.c_char_p, [C.c_int]),
     "llmp_b200_vecq": (C.c_int, [C.c_int, C.POINTER(VecQDesc), C.c_int, C.c_void_p]),
+    "llmp_b200_mxfp8_padded_rows": (C.c_uint64, [C.c_uint64]),
+    "llmp_b200_mxfp8_scale_offset": (C.c_uint64, [C.c_uint64, C.c_uint64, C.c_uint64]),
+    "llmp_b200_mxfp8_quantize": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int,
+                                           C.c_void_p, C.c_void_p, C.c_void_p]),
+    "llmp_b200_mxfp8_swizzle": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
+    "llmp_b200_mxfp8_gemm_available": (C.c_int, []),
+    "llmp_b200_mxfp8_gemm_scratch": (C.c_size_t, [C.POINTER(Mxfp8GemmDesc), C.c_int]),
+    "llmp_b200_mxfp8_gemm": (C.c_int, [C.POINTER(Mxfp8GemmDesc), C.c_int, C.c_void_p]),
     "llmp_b200_vecq_block_sums": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
                                             C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
 }

@@ -16,7 +16,8 @@ from ._native import (GLU_GEGLU, GLU_NONE, GLU_SWIGLU, GLU_SWIGLU_CLAMP, TYPE_Q4
                       LaunchFailed, Rejected)
 
 __all__ = ["available", "sm_count", "device_faults", "block_bytes", "block_elems", "q8_1_row_blocks",
-           "quantize_q8", "vecq", "vecq_variants", "vecq_block_sums", "TYPE_Q8_0", "TYPE_Q4_K",
+           "quantize_q8", "vecq", "vecq_variants", "vecq_block_sums", "mxfp8_padded_rows",
+           "mxfp8_quantize", "mxfp8_swizzle", "mxfp8_gemm", "TYPE_Q8_0", "TYPE_Q4_K",
            "GLU_NONE", "GLU_SWIGLU", "GLU_SWIGLU_CLAMP", "GLU_GEGLU", "Rejected", "LaunchFailed"]
 
 _BLOCK = {TYPE_Q8_0: (32, 34), TYPE_Q4_K: (256, 144), N.TYPE_Q8_1: (32, 36)}
@@ -144,3 +145,62 @@ def vecq_block_sums(weights: torch.Tensor, wtype: int, k: int, n: int, q8_row: t
         wtype, weights.data_ptr(), q8_row.data_ptr(), k, n, k // _BLOCK[wtype][0], dots.data_ptr(),
         qsums.data_ptr() if qsums is not None else None, _stream()), "llmp_b200_vecq_block_sums")
     return dots, qsums
+
+
+# ----------------------------------------------------------------------- MXFP8
+def mxfp8_padded_rows(rows: int) -> int:
+    return int(N.lib().llmp_b200_mxfp8_padded_rows(rows))
+
+
+def mxfp8_quantize(x: torch.Tensor):
+    """Mxfp8Quantize: x F32 or BF16 [rows, k] -> (codes uint8 [rows, k], scale atoms uint8
+    [padded_rows(rows) * k / 32])."""
+    if not (x.is_cuda and x.dtype in (torch.float32, torch.bfloat16) and x.dim() == 2
+            and x.stride(1) == 1):
+        raise Rejected("mxfp8_quantize: a CUDA F32 or BF16 [rows, k] tensor, k contiguous")
+    rows, k = x.shape
+    codes = torch.empty((rows, k), dtype=torch.uint8, device=x.device)
+    scales = torch.empty((mxfp8_padded_rows(rows) * (k // 32),), dtype=torch.uint8, device=x.device)
+    N.check(N.lib().llmp_b200_mxfp8_quantize(x.data_ptr(), int(x.dtype == torch.bfloat16),
+                                             x.stride(0), k, rows, codes.data_ptr(),
+                                             scales.data_ptr(), _stream()),
+            "llmp_b200_mxfp8_quantize")
+    return codes, scales
+
+
+def mxfp8_swizzle(scales: torch.Tensor) -> torch.Tensor:
+    """Mxfp8Swizzle: weight scales uint8 [n, k / 32] row-major -> scale atoms."""
+    _need(scales, torch.uint8, "mxfp8_swizzle scales")
+    if scales.dim() != 2 or not scales.is_contiguous():
+        raise Rejected("mxfp8_swizzle: packed [n, k / 32] scales")
+    n, blocks = scales.shape
+    out = torch.empty((mxfp8_padded_rows(n) * blocks,), dtype=torch.uint8, device=scales.device)
+    N.check(N.lib().llmp_b200_mxfp8_swizzle(scales.data_ptr(), out.data_ptr(), n, blocks,
+                                            _stream()), "llmp_b200_mxfp8_swizzle")
+    return out
+
+
+def mxfp8_gemm(a: torch.Tensor, a_scales: torch.Tensor, b: torch.Tensor, b_scales: torch.Tensor,
+               *, bf16: bool = True, out: torch.Tensor | None = None, sms: int = 0) -> torch.Tensor:
+    """Mxfp8Gemm: D[m, n] = A[m, k] . B[n, k]^T; codes uint8, scales in atoms."""
+    for t, what in ((a, "a"), (b, "b"), (a_scales, "a_scales"), (b_scales, "b_scales")):
+        _need(t, torch.uint8, f"mxfp8_gemm {what}")
+    m, k = a.shape
+    n = b.shape[0]
+    if b.shape[1] != k or not a.is_contiguous() or not b.is_contiguous():
+        raise Rejected("mxfp8_gemm: packed codes [m, k] and [n, k]")
+    if a_scales.numel() < mxfp8_padded_rows(m) * (k // 32) or \
+            b_scales.numel() < mxfp8_padded_rows(n) * (k // 32):
+        raise Rejected("mxfp8_gemm: scale atoms for the padded rows")
+    dtype = torch.bfloat16 if bf16 else torch.float32
+    if out is None:
+        out = torch.empty((m, n), dtype=dtype, device=a.device)
+    if out.dtype != dtype or tuple(out.shape) != (m, n) or not out.is_contiguous():
+        raise Rejected("mxfp8_gemm: a packed [m, n] output of the requested type")
+    g = N.Mxfp8GemmDesc()
+    g.m, g.n, g.k = m, n, k
+    g.a, g.a_scales, g.b, g.b_scales = a.data_ptr(), a_scales.data_ptr(), b.data_ptr(), \
+        b_scales.data_ptr()
+    g.d, g.bf16, g.scratch = out.data_ptr(), int(bf16), None
+    N.check(N.lib().llmp_b200_mxfp8_gemm(C.byref(g), sms, _stream()), "llmp_b200_mxfp8_gemm")
+    return out
