@@ -113,6 +113,42 @@ int llmp_b200_vecq(int type, const llmp_b200_vecq_desc* desc, int variant, void*
 int llmp_b200_vecq_block_sums(int type, const void* w, const void* y, int k, int nrows,
                               int stride_row, int32_t* dots, int32_t* qsums, void* stream);
 
+/* ------------------------------------------------------------------ MMQ */
+/* Replaces GGML's quantize_mmq_q8_1_cuda as the reference calls it
+ * (src/kernels/ggml/mul_mat_q.cu:606-610, 806; the D2S6 sibling is restated
+ * in-tree at mul_mat_q_glu.cu:170-218).  x: F32 or BF16 [k, rows], row stride
+ * in elements.  out: block_q8_1_mmq in the DS4 layout (144 bytes: four (FP16
+ * d, FP16 sum of the inputs) pairs, then 128 int8), ordered [k / 128][cols].
+ * ids_src (device, or NULL): column c quantizes input row ids_src[c] (the
+ * scatter to an expert-sorted order). */
+int64_t llmp_b200_mmq_q8_1_bytes(int64_t k, int64_t cols);
+int llmp_b200_mmq_quantize(const void* x, int is_bf16, int64_t row_stride, int64_t k, int64_t cols,
+                           const int32_t* ids_src, void* out, void* stream);
+
+/* The operands GGML's mmq_args carry as the reference fills them
+ * (src/kernels/ggml/mul_mat_q.cu:632-658). */
+typedef struct llmp_b200_mmq_desc {
+  int type;                     /* LLMP_B200_TYPE_Q4_K */
+  const void* w;                /* weight blocks [experts][nrows][k / 256] */
+  const void* y;                /* Q8_1-MMQ blocks [k / 128][ncols] */
+  const int32_t* ids_dst;       /* device: sorted column -> output column, or NULL */
+  const int32_t* expert_bounds; /* device: experts + 1 column bounds, or NULL (dense) */
+  float* dst;                   /* F32 [out column][nrows], dst_col_stride floats apart */
+  int k, nrows, ncols;          /* ncols: columns of y */
+  int stride_row;               /* weight blocks between rows */
+  int stride_expert;            /* weight blocks between experts */
+  int dst_col_stride;
+  int experts;                  /* with expert_bounds */
+  int max_cols_per_expert;      /* host-known bound on an expert's columns (<= ncols) */
+} llmp_b200_mmq_desc;
+
+/* Replace PlanMulMatQ's scratch sizing and MulMatQ / RunExpertProducts
+ * (src/kernels/ggml/mul_mat_q.cu:317-397, 453-462, 551-737): D[col][row] =
+ * W[row] . Y[col] with exact int32 group sums on tcgen05 (kind::i8) and the
+ * F32 scale fold of GGML's MMQ.  No stream-k fixup: scratch is 0 bytes. */
+size_t llmp_b200_mmq_scratch(const llmp_b200_mmq_desc* desc, int sms);
+int llmp_b200_mmq(const llmp_b200_mmq_desc* desc, int sms, void* stream);
+
 /* ------------------------------------------------------------------ MXFP8 */
 /* MXFP8: E4M3 codes with one E8M0 scale per 32 values along K.  Scales live in
  * "scale atoms" (src/format/layout.h:97-112, == moe_cutlass.h:42-46 SfOffset):

@@ -41,6 +41,15 @@ class Mxfp8GemmDesc(C.Structure):
                 ("d", C.c_void_p), ("bf16", C.c_int), ("scratch", C.c_void_p)]
 
 
+class MmqDesc(C.Structure):
+    """llmp_b200_mmq_desc (include/llmp_b200.h)."""
+    _fields_ = [("type", C.c_int), ("w", C.c_void_p), ("y", C.c_void_p), ("ids_dst", C.c_void_p),
+                ("expert_bounds", C.c_void_p), ("dst", C.c_void_p), ("k", C.c_int),
+                ("nrows", C.c_int), ("ncols", C.c_int), ("stride_row", C.c_int),
+                ("stride_expert", C.c_int), ("dst_col_stride", C.c_int), ("experts", C.c_int),
+                ("max_cols_per_expert", C.c_int)]
+
+
 # name -> (restype, argtypes): every symbol include/llmp_b200.h declares.
 SIGNATURES = {
     "llmp_b200_available": (C.c_int, []),
@@ -53,6 +62,11 @@ SIGNATURES = {
     "llmp_b200_vecq_variants": (C.c_int, []),
     "llmp_b200_vecq_variant_name": (C.c_char_p, [C.c_int]),
     "llmp_b200_vecq": (C.c_int, [C.c_int, C.POINTER(VecQDesc), C.c_int, C.c_void_p]),
+    "llmp_b200_mmq_q8_1_bytes": (C.c_int64, [C.c_int64, C.c_int64]),
+    "llmp_b200_mmq_quantize": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int64,
+                                         C.c_void_p, C.c_void_p, C.c_void_p]),
+    "llmp_b200_mmq_scratch": (C.c_size_t, [C.POINTER(MmqDesc), C.c_int]),
+    "llmp_b200_mmq": (C.c_int, [C.POINTER(MmqDesc), C.c_int, C.c_void_p]),
     "llmp_b200_mxfp8_padded_rows": (C.c_uint64, [C.c_uint64]),
     "llmp_b200_mxfp8_scale_offset": (C.c_uint64, [C.c_uint64, C.c_uint64, C.c_uint64]),
     "llmp_b200_mxfp8_quantize": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int,

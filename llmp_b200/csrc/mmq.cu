@@ -1,0 +1,485 @@
+// MMQ on B200: the prefill product of Q4_K weights with Q8_1-MMQ activations,
+// dense or per routed expert.  Semantics follow the reference's use of GGML's
+// mul_mat_q (src/kernels/ggml/mul_mat_q.cu:67-130, 453-462, 551-737; the tile
+// loop's shape in-tree at mul_mat_q_glu.cu:93-135; the activation block's
+// writer at mul_mat_q_glu.cu:170-218): per 32-value group an exact int32
+// product C = sum code * q, then in F32
+//     sum += (d * sc)_half * d8 * C;   sum += (-dmin * m)_half * s8
+// with d8, s8 the group's FP16 scale and stored input sum.
+//
+// The int8 contraction runs on tcgen05 (kind::i8, int32 accumulators in TMEM).
+// Q4_K's per-group scales forbid accumulating across groups in the tensor
+// core, so every 128x128x32 MMA lands in its own TMEM buffer (four of them, so
+// the tensor core runs up to four groups ahead) and a wide epilogue (8 warps)
+// folds each group's int32 tile into F32 register accumulators.  That fold is
+// CUDA-core work per output element per group and bounds the kernel.
+//
+//   warp 0      TMA: activation int8 tiles (128 tokens x 128 K bytes) straight
+//               out of the [k/128][col] block array through a 3-D tensor map
+//               (row pitch 144 B, origin past the 16-byte block header);
+//   warps 1-4   decode: one weight row a thread; unpack the k-block's 128
+//               nibbles to int8 into the 128-byte-swizzled K-major tile the MMA
+//               reads, and the four groups' (d*sc, -dmin*m) half products;
+//               also stage the tokens' (d8, s8) as F32;
+//   warp 5      allocates TMEM and issues the MMAs;
+//   warps 6-13  epilogue: thread = (weight row, half of the token columns).
+// Every wait is bounded; a wait that runs out raises the device fault counter.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "tc.cuh"
+
+namespace llmp_b200 {
+namespace {
+
+using Desc = llmp_b200_mmq_desc;
+
+// ------------------------------------------------------------------ quantizer
+// block_q8_1_mmq, DS4 layout: 4 x (FP16 d, FP16 sum of the inputs), 128 int8.
+// Blocks ordered [k / 128][col].  Eight lanes a 32-value group, four values a
+// lane; the sum is taken four-per-lane then over the lanes 4, 2, 1 apart.
+template <bool kBf16>
+__global__ void __launch_bounds__(256)
+QuantizeMmqKernel(const void* __restrict__ x, std::int64_t row_stride, int k, std::int64_t cols,
+                  const std::int32_t* __restrict__ ids_src, std::uint8_t* __restrict__ out,
+                  std::int64_t lanes_total) {
+  GridLaunchDependents();
+  GridDependencyWait();
+  const std::int64_t i = (static_cast<std::int64_t>(blockIdx.x) * 256) + threadIdx.x;
+  const bool live = i < lanes_total;
+  const std::int64_t group = (live ? i : 0) / 8;  // (col, k / 32)
+  const int part = static_cast<int>(i % 8);
+  const int groups = k / 32;
+  const std::int64_t col = group / groups;
+  const int g = static_cast<int>(group % groups);
+  float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  if (live) {
+    const std::int64_t src_row = ids_src != nullptr ? ids_src[col] : col;
+    const std::int64_t at = (src_row * row_stride) + (g * 32) + (part * 4);
+    if constexpr (kBf16) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(x) + at);
+      v[0] = __uint_as_float(raw.x << 16);
+      v[1] = __uint_as_float(raw.x & 0xffff0000u);
+      v[2] = __uint_as_float(raw.y << 16);
+      v[3] = __uint_as_float(raw.y & 0xffff0000u);
+    } else {
+      const float4 f = *reinterpret_cast<const float4*>(static_cast<const float*>(x) + at);
+      v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+    }
+  }
+  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+  float sum = ((v[0] + v[1]) + v[2]) + v[3];
+#pragma unroll
+  for (int offset = 4; offset > 0; offset >>= 1) {
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
+    sum = sum + __shfl_xor_sync(0xffffffffu, sum, offset);
+  }
+  if (!live) return;
+  std::uint32_t packed = 0;
+  float d = 0.0f;
+  if (amax > 0.0f) {
+    const float d_inv = 127.0f / amax;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int q = static_cast<int>(roundf(v[c] * d_inv));
+      packed |= (static_cast<std::uint32_t>(q) & 0xffu) << (8 * c);
+    }
+    d = 1.0f / d_inv;
+  }
+  std::uint8_t* block = out + ((static_cast<std::int64_t>(g / 4) * cols + col) * 144);
+  *reinterpret_cast<std::uint32_t*>(block + 16 + ((g % 4) * 32) + (part * 4)) = packed;
+  if (part == 0) {
+    const std::uint32_t ds = static_cast<std::uint32_t>(__half_as_ushort(__float2half_rn(d))) |
+                             (static_cast<std::uint32_t>(__half_as_ushort(__float2half_rn(sum)))
+                              << 16);
+    *reinterpret_cast<std::uint32_t*>(block + ((g % 4) * 4)) = ds;
+  }
+}
+
+// ------------------------------------------------------------------ GEMM
+constexpr int kTileRows = 128;  // weight rows: the MMA's M, one TMEM lane each
+constexpr int kTileCols = 128;  // tokens: the MMA's N
+constexpr int kBK = 128;        // K bytes a stage: four 32-value groups
+constexpr int kStages = 4;
+constexpr int kBuffers = 4;     // TMEM group-result buffers of kTileCols columns
+constexpr int kWBytes = kTileRows * kBK, kYBytes = kTileCols * kBK;
+constexpr int kScaleBytes = 4 * 128 * 4;  // [group][row or col] F32
+constexpr int kStageBytes = kWBytes + kYBytes + (4 * kScaleBytes);
+constexpr int kThreads = 14 * 32;
+constexpr int kEpilogueWarps = 8;
+constexpr int kSmem = (kStages * kStageBytes) + 1024 + 512;
+
+struct Shared {
+  std::uint64_t y_full[kStages];
+  std::uint64_t w_full[kStages];
+  std::uint64_t empty[kStages];
+  std::uint64_t tmem_full[kBuffers];
+  std::uint64_t tmem_empty[kBuffers];
+  std::uint32_t tmem_base;
+  std::uint32_t abort;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const Desc a, unsigned int* faults) {
+  extern __shared__ unsigned char raw_smem[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<std::uintptr_t>(raw_smem) + 1023) & ~static_cast<std::uintptr_t>(1023));
+  unsigned char* w_tiles = smem;
+  unsigned char* y_tiles = w_tiles + (kStages * kWBytes);
+  float* scales = reinterpret_cast<float*>(y_tiles + (kStages * kYBytes));
+  Shared* sh = reinterpret_cast<Shared*>(reinterpret_cast<unsigned char*>(scales) +
+                                         (kStages * 4 * kScaleBytes));
+  // scales of stage s: ax[4][128], ay[4][128] (weight rows), bx[4][128], by[4][128] (tokens)
+  auto stage_scales = [&](int s) { return scales + (static_cast<std::size_t>(s) * 4 * 512); };
+
+  const int warp = static_cast<int>(threadIdx.x) >> 5;
+  const int lane = static_cast<int>(threadIdx.x) & 31;
+  const int ksteps = a.k / kBK;
+
+  // The tile: weight rows [row0, row0 + 128) of expert e against sorted
+  // columns [col0, col0 + 128) of that expert's range [c_begin, c_end).
+  const int expert = static_cast<int>(blockIdx.z);
+  const int c_begin = a.expert_bounds != nullptr ? a.expert_bounds[expert] : 0;
+  const int c_end = a.expert_bounds != nullptr ? a.expert_bounds[expert + 1] : a.ncols;
+  const int col0 = c_begin + (static_cast<int>(blockIdx.y) * kTileCols);
+  const int row0 = static_cast<int>(blockIdx.x) * kTileRows;
+  if (col0 >= c_end) return;  // uniform for the CTA, before any barrier
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      tc::MbarInit(&sh->y_full[s], 1);
+      tc::MbarInit(&sh->w_full[s], 4);
+      tc::MbarInit(&sh->empty[s], kEpilogueWarps);
+    }
+    for (int b = 0; b < kBuffers; ++b) {
+      tc::MbarInit(&sh->tmem_full[b], 1);
+      tc::MbarInit(&sh->tmem_empty[b], kEpilogueWarps);
+    }
+    sh->abort = 0;
+    tc::MbarInitFence();
+  }
+  if (warp == 5) {
+    tc::TmemAlloc(&sh->tmem_base, 512);
+    tc::TmemRelinquish();
+  }
+  tc::TcFenceBefore();
+  __syncthreads();
+  tc::TcFenceAfter();
+  const std::uint32_t tmem = sh->tmem_base;
+  volatile std::uint32_t* abort_flag = &sh->abort;
+  auto give_up = [&]() {
+    *abort_flag = 1;
+    atomicAdd(faults, 1u);
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tc::PrefetchMap(&map_y);
+      for (int ks = 0; ks < ksteps && !*abort_flag; ++ks) {
+        const int s = ks % kStages;
+        if (!tc::MbarWait(&sh->empty[s], ((ks / kStages) & 1) ^ 1)) {
+          give_up();
+          break;
+        }
+        tc::MbarExpectTx(&sh->y_full[s], kYBytes);
+        asm volatile(
+            "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+            " [%0], [%1, {%3, %4, %5}], [%2];"
+            ::"r"(tc::Smem(y_tiles + (s * kYBytes))), "l"(&map_y), "r"(tc::Smem(&sh->y_full[s])),
+              "r"(0), "r"(col0), "r"(ks)
+            : "memory");
+      }
+    }
+  } else if (warp >= 1 && warp <= 4) {
+    // ------------------------------------------------------------ decode
+    const int t = (static_cast<int>(threadIdx.x) - 32);  // 0..127: weight row / token of the tile
+    const int row = min(row0 + t, a.nrows - 1);
+    const bool row_live = row0 + t < a.nrows;
+    const std::uint8_t* wrow = static_cast<const std::uint8_t*>(a.w) +
+                               ((static_cast<std::size_t>(expert) * a.stride_expert +
+                                 static_cast<std::size_t>(row) * a.stride_row) * 144);
+    const int col = min(col0 + t, a.ncols - 1);
+    const std::uint8_t* ycol = static_cast<const std::uint8_t*>(a.y) + (static_cast<std::size_t>(col) * 144);
+    for (int ks = 0; ks < ksteps && !*abort_flag; ++ks) {
+      const int s = ks % kStages;
+      // Fetch before waiting for the stage: global latency overlaps the wait.
+      const std::uint8_t* sb = wrow + (static_cast<std::size_t>(ks >> 1) * 144);
+      const int half = ks & 1;
+      const uint4 head = LoadStream16(sb);
+      uint4 q[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) q[i] = LoadStream16(sb + 16 + (half * 64) + (i * 16));
+      const uint4 ds = *reinterpret_cast<const uint4*>(
+          ycol + (static_cast<std::size_t>(ks) * a.ncols * 144));
+      bool ok = true;
+      if (lane == 0) ok = tc::MbarWait(&sh->empty[s], ((ks / kStages) & 1) ^ 1);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) {
+        if (lane == 0) give_up();
+        break;
+      }
+      // int8 codes into the swizzled K-major tile: row t, 16-byte chunk j at j ^ (t % 8)
+      unsigned char* wt = w_tiles + (s * kWBytes) + ((t >> 3) * 1024) + ((t & 7) * 128);
+      const std::uint32_t z = row_live ? 0xffffffffu : 0u;
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const uint4 lo0 = make_uint4(q[2 * cc].x & 0x0f0f0f0fu & z, q[2 * cc].y & 0x0f0f0f0fu & z,
+                                     q[2 * cc].z & 0x0f0f0f0fu & z, q[2 * cc].w & 0x0f0f0f0fu & z);
+        const uint4 lo1 = make_uint4(q[2 * cc + 1].x & 0x0f0f0f0fu & z, q[2 * cc + 1].y & 0x0f0f0f0fu & z,
+                                     q[2 * cc + 1].z & 0x0f0f0f0fu & z, q[2 * cc + 1].w & 0x0f0f0f0fu & z);
+        const uint4 hi0 = make_uint4((q[2 * cc].x >> 4) & 0x0f0f0f0fu & z, (q[2 * cc].y >> 4) & 0x0f0f0f0fu & z,
+                                     (q[2 * cc].z >> 4) & 0x0f0f0f0fu & z, (q[2 * cc].w >> 4) & 0x0f0f0f0fu & z);
+        const uint4 hi1 = make_uint4((q[2 * cc + 1].x >> 4) & 0x0f0f0f0fu & z, (q[2 * cc + 1].y >> 4) & 0x0f0f0f0fu & z,
+                                     (q[2 * cc + 1].z >> 4) & 0x0f0f0f0fu & z, (q[2 * cc + 1].w >> 4) & 0x0f0f0f0fu & z);
+        const int j = cc * 4;  // groups 2cc (chunks j, j+1) and 2cc+1 (chunks j+2, j+3)
+        *reinterpret_cast<uint4*>(wt + (((j + 0) ^ (t & 7)) * 16)) = lo0;
+        *reinterpret_cast<uint4*>(wt + (((j + 1) ^ (t & 7)) * 16)) = lo1;
+        *reinterpret_cast<uint4*>(wt + (((j + 2) ^ (t & 7)) * 16)) = hi0;
+        *reinterpret_cast<uint4*>(wt + (((j + 3) ^ (t & 7)) * 16)) = hi1;
+      }
+      // The four groups' half products (d * sc, -dmin * m): GGML's tile loader
+      // multiplies in half precision.
+      float* sc = stage_scales(s);
+      {
+        const std::uint32_t s0 = head.y, s1 = head.z, s2 = head.w;
+        const __half d = __ushort_as_half(static_cast<unsigned short>(head.x & 0xffffu));
+        const __half dmin = __hneg(__ushort_as_half(static_cast<unsigned short>(head.x >> 16)));
+#pragma unroll
+        for (int gl = 0; gl < 4; ++gl) {
+          int scv, mnv;
+          if (half == 0) {
+            scv = static_cast<int>((s0 >> (8 * gl)) & 63u);
+            mnv = static_cast<int>((s1 >> (8 * gl)) & 63u);
+          } else {
+            scv = static_cast<int>(((s2 >> (8 * gl)) & 15u) | (((s0 >> ((8 * gl) + 6)) & 3u) << 4));
+            mnv = static_cast<int>(((s2 >> ((8 * gl) + 4)) & 15u) | (((s1 >> ((8 * gl) + 6)) & 3u) << 4));
+          }
+          sc[(gl * 128) + t] = row_live ? __half2float(__hmul(d, __int2half_rn(scv))) : 0.0f;
+          sc[512 + (gl * 128) + t] = row_live ? __half2float(__hmul(dmin, __int2half_rn(mnv))) : 0.0f;
+        }
+        const std::uint32_t dsw[4] = {ds.x, ds.y, ds.z, ds.w};
+#pragma unroll
+        for (int gl = 0; gl < 4; ++gl) {
+          sc[1024 + (gl * 128) + t] = HalfBitsToFloat(dsw[gl] & 0xffffu);
+          sc[1536 + (gl * 128) + t] = HalfBitsToFloat(dsw[gl] >> 16);
+        }
+      }
+      tc::FenceProxyAsync();  // generic-proxy writes, read by the tensor core's proxy
+      __syncwarp();
+      if (lane == 0) tc::MbarArrive(&sh->w_full[s]);
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const std::uint32_t idesc = tc::IdescI8(kTileRows, kTileCols, false, true);
+      std::uint32_t group = 0;
+      for (int ks = 0; ks < ksteps && !*abort_flag; ++ks) {
+        const int s = ks % kStages;
+        if (!tc::MbarWait(&sh->w_full[s], (ks / kStages) & 1) ||
+            !tc::MbarWait(&sh->y_full[s], (ks / kStages) & 1)) {
+          give_up();
+          break;
+        }
+        tc::TcFenceAfter();
+        const std::uint64_t wdesc = tc::SmemDesc(w_tiles + (s * kWBytes), true, 1024);
+        const std::uint64_t ydesc = tc::SmemDesc(y_tiles + (s * kYBytes), true, 1024);
+        for (int gl = 0; gl < 4; ++gl, ++group) {
+          const int b = static_cast<int>(group % kBuffers);
+          if (!tc::MbarWait(&sh->tmem_empty[b], ((group / kBuffers) & 1u) ^ 1u)) {
+            give_up();
+            break;
+          }
+          tc::TcFenceAfter();
+          tc::MmaI8(tmem + (b * kTileCols), wdesc + (gl * 2), ydesc + (gl * 2), idesc, false);
+          tc::TcCommit(&sh->tmem_full[b]);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int ew = warp - 6;           // 0..7
+    const int quadrant = warp & 3;     // TMEM lanes this warp may read
+    const int colhalf = ew >> 2;       // warps 6..9 take columns 0..63, 10..13 take 64..127
+    const int rt = (quadrant * 32) + lane;  // weight row of the tile
+    float acc[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) acc[i] = 0.0f;
+    std::uint32_t group = 0;
+    bool ok = true;
+    for (int ks = 0; ks < ksteps && ok; ++ks) {
+      const int s = ks % kStages;
+      const float* sc = stage_scales(s);
+      for (int gl = 0; gl < 4 && ok; ++gl, ++group) {
+        const int b = static_cast<int>(group % kBuffers);
+        if (lane == 0) ok = tc::MbarWait(&sh->tmem_full[b], (group / kBuffers) & 1u);
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok || *abort_flag) {
+          if (lane == 0 && !ok) give_up();
+          ok = false;
+          break;
+        }
+        tc::TcFenceAfter();
+        const float ax = sc[(gl * 128) + rt];
+        const float ay = sc[512 + (gl * 128) + rt];
+        const float* bx = sc + 1024 + (gl * 128) + (colhalf * 64);
+        const float* by = sc + 1536 + (gl * 128) + (colhalf * 64);
+#pragma unroll
+        for (int part = 0; part < 2; ++part) {
+          std::uint32_t r[32];
+          tc::TmemLoad32(tmem + (static_cast<std::uint32_t>(quadrant * 32) << 16) +
+                             (b * kTileCols) + (colhalf * 64) + (part * 32), r);
+          tc::TmemLoadWait();
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            const float4 x4 = *reinterpret_cast<const float4*>(bx + (part * 32) + (v * 4));
+            const float4 y4 = *reinterpret_cast<const float4*>(by + (part * 32) + (v * 4));
+            const float xs[4] = {x4.x, x4.y, x4.z, x4.w};
+            const float ys[4] = {y4.x, y4.y, y4.z, y4.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int i = (part * 32) + (v * 4) + j;
+              acc[i] = fmaf(ax * xs[j], static_cast<float>(static_cast<int>(r[(v * 4) + j])), acc[i]);
+              acc[i] = fmaf(ay, ys[j], acc[i]);
+            }
+          }
+        }
+        tc::TcFenceBefore();
+        __syncwarp();
+        if (lane == 0) tc::MbarArrive(&sh->tmem_empty[b]);
+      }
+      __syncwarp();
+      if (lane == 0 && ok) tc::MbarArrive(&sh->empty[s]);  // the stage's scales are consumed
+    }
+    if (ok && row0 + rt < a.nrows) {
+#pragma unroll 4
+      for (int i = 0; i < 64; ++i) {
+        const int c = col0 + (colhalf * 64) + i;
+        if (c < c_end) {
+          const int dst_col = a.ids_dst != nullptr ? a.ids_dst[c] : c;
+          a.dst[(static_cast<std::size_t>(dst_col) * a.dst_col_stride) + row0 + rt] = acc[i];
+        }
+      }
+    }
+  }
+
+  tc::TcFenceBefore();
+  __syncthreads();
+  if (warp == 5) {
+    tc::TcFenceAfter();
+    tc::TmemDealloc(tmem, 512);
+  }
+}
+
+int CheckDesc(const Desc& d) {
+  if (d.type != LLMP_B200_TYPE_Q4_K) {
+    return Reject("mmq: weight type %d is not one this build computes (Q4_K)", d.type);
+  }
+  if (d.w == nullptr || d.y == nullptr || d.dst == nullptr || d.k < 256 || d.k % 256 != 0 ||
+      d.nrows < 1 || d.ncols < 1) {
+    return Reject("mmq: Q4_K weights [k, n], Q8_1-MMQ activations of ncols columns, an F32 output; "
+                  "k a positive multiple of 256");
+  }
+  if (d.stride_row < d.k / 256 || d.stride_expert < 0 || d.dst_col_stride < d.nrows) {
+    return Reject("mmq: strides must cover a row");
+  }
+  if (!Aligned(d.w, 16) || !Aligned(d.y, 16) || !Aligned(d.dst, 4)) {
+    return Reject("mmq: weights and activation blocks 16-byte aligned");
+  }
+  if (d.expert_bounds == nullptr && d.experts > 1) {
+    return Reject("mmq: expert bounds exactly with experts");
+  }
+  if (d.expert_bounds != nullptr && (d.experts < 1 || d.experts > 65535)) {
+    return Reject("mmq: 1 to 65535 experts");
+  }
+  return 0;
+}
+
+}  // namespace
+}  // namespace llmp_b200
+
+extern "C" {
+
+int64_t llmp_b200_mmq_q8_1_bytes(int64_t k, int64_t cols) { return (k / 128) * cols * 144; }
+
+int llmp_b200_mmq_quantize(const void* x, int is_bf16, int64_t row_stride, int64_t k, int64_t cols,
+                           const int32_t* ids_src, void* out, void* stream) {
+  using namespace llmp_b200;
+  if (x == nullptr || out == nullptr || k < 128 || k % 128 != 0 || cols < 1 || row_stride < k) {
+    return Reject("mmq.quantize: [k, rows] input with k a positive multiple of 128, cols >= 1");
+  }
+  const int elem = is_bf16 ? 2 : 4;
+  if (!Aligned(x, 16) || (row_stride * elem) % 16 != 0 || !Aligned(out, 16)) {
+    return Reject("mmq.quantize: input rows and output 16-byte aligned");
+  }
+  if (const int status = DeviceStatus(); status != 0) return status;
+  const std::int64_t lanes = cols * (k / 32) * 8;
+  const std::int64_t grid = (lanes + 255) / 256;
+  if (grid > 0x7fffffffLL) return Reject("mmq.quantize: more blocks than a grid holds");
+  auto* s = static_cast<cudaStream_t>(stream);
+  const cudaError_t e =
+      is_bf16 ? LaunchPdl(QuantizeMmqKernel<true>, dim3(static_cast<unsigned>(grid)), dim3(256), 0,
+                          s, x, row_stride, static_cast<int>(k), cols, ids_src,
+                          static_cast<std::uint8_t*>(out), lanes)
+              : LaunchPdl(QuantizeMmqKernel<false>, dim3(static_cast<unsigned>(grid)), dim3(256), 0,
+                          s, x, row_stride, static_cast<int>(k), cols, ids_src,
+                          static_cast<std::uint8_t*>(out), lanes);
+  if (e != cudaSuccess) return Failed(e, "mmq.quantize launch");
+  return 0;
+}
+
+size_t llmp_b200_mmq_scratch(const llmp_b200_mmq_desc* desc, int sms) {
+  (void)desc;
+  (void)sms;
+  return 0;  // group results live in tensor memory; no stream-k fixup pass
+}
+
+int llmp_b200_mmq(const llmp_b200_mmq_desc* desc, int sms, void* stream) {
+  using namespace llmp_b200;
+  (void)sms;
+  if (desc == nullptr) return Reject("mmq: null descriptor");
+  const Desc& d = *desc;
+  if (const int status = CheckDesc(d); status != 0) return status;
+  if (const int status = DeviceStatus(); status != 0) return status;
+  const tc::EncodeTiledFn encode = tc::EncodeTiled();
+  if (encode == nullptr) return Reject("mmq: the driver has no tensor-map encoder");
+  CUtensorMap map_y;
+  {
+    const cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(d.ncols),
+                                static_cast<cuuint64_t>(d.k / 128)};
+    const cuuint64_t strides[2] = {144, static_cast<cuuint64_t>(d.ncols) * 144};
+    const cuuint32_t box[3] = {128, kTileCols, 1};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    void* base = const_cast<std::uint8_t*>(static_cast<const std::uint8_t*>(d.y) + 16);
+    if (encode(&map_y, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, base, dims, strides, box, elem,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+      return Reject("mmq: the driver refused a tensor map for the activation blocks");
+    }
+  }
+  unsigned int* faults = FaultCounter();
+  if (faults == nullptr) return Reject("mmq: no fault counter on this device");
+  static thread_local int configured_device = -1;
+  int device = -1;
+  cudaGetDevice(&device);
+  if (configured_device != device) {
+    const cudaError_t e =
+        cudaFuncSetAttribute(MmqQ4KKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    if (e != cudaSuccess) return Failed(e, "mmq attribute");
+    configured_device = device;
+  }
+  const int experts = d.expert_bounds != nullptr ? d.experts : 1;
+  const int max_cols = d.expert_bounds != nullptr ? d.max_cols_per_expert : d.ncols;
+  if (max_cols < 1) return Reject("mmq: max_cols_per_expert >= 1 with experts");
+  const dim3 grid(static_cast<unsigned>((d.nrows + kTileRows - 1) / kTileRows),
+                  static_cast<unsigned>((max_cols + kTileCols - 1) / kTileCols),
+                  static_cast<unsigned>(experts));
+  if (grid.y > 65535u) return Reject("mmq: more column tiles than a grid holds");
+  MmqQ4KKernel<<<grid, kThreads, kSmem, static_cast<cudaStream_t>(stream)>>>(map_y, d, faults);
+  const cudaError_t e = cudaPeekAtLastError();
+  if (e != cudaSuccess) return Failed(cudaGetLastError(), "mmq launch");
+  return 0;
+}
+
+}  // extern "C"

@@ -17,7 +17,7 @@ from ._native import (GLU_GEGLU, GLU_NONE, GLU_SWIGLU, GLU_SWIGLU_CLAMP, TYPE_Q4
 
 __all__ = ["available", "sm_count", "device_faults", "block_bytes", "block_elems", "q8_1_row_blocks",
            "quantize_q8", "vecq", "vecq_variants", "vecq_block_sums", "mxfp8_padded_rows",
-           "mxfp8_quantize", "mxfp8_swizzle", "mxfp8_gemm", "TYPE_Q8_0", "TYPE_Q4_K",
+           "mxfp8_quantize", "mxfp8_swizzle", "mxfp8_gemm", "mmq_quantize", "mmq", "TYPE_Q8_0", "TYPE_Q4_K",
            "GLU_NONE", "GLU_SWIGLU", "GLU_SWIGLU_CLAMP", "GLU_GEGLU", "Rejected", "LaunchFailed"]
 
 _BLOCK = {TYPE_Q8_0: (32, 34), TYPE_Q4_K: (256, 144), N.TYPE_Q8_1: (32, 36)}
@@ -203,4 +203,53 @@ def mxfp8_gemm(a: torch.Tensor, a_scales: torch.Tensor, b: torch.Tensor, b_scale
         b_scales.data_ptr()
     g.d, g.bf16, g.scratch = out.data_ptr(), int(bf16), None
     N.check(N.lib().llmp_b200_mxfp8_gemm(C.byref(g), sms, _stream()), "llmp_b200_mxfp8_gemm")
+    return out
+
+
+# ----------------------------------------------------------------------- MMQ
+def mmq_quantize(x: torch.Tensor, ids_src: torch.Tensor | None = None,
+                 cols: int | None = None) -> torch.Tensor:
+    """x F32 or BF16 [rows, k] -> Q8_1-MMQ blocks uint8 [k / 128, cols, 144]; with ids_src
+    (I32 [cols]) column c quantizes row ids_src[c]."""
+    if not (x.is_cuda and x.dtype in (torch.float32, torch.bfloat16) and x.dim() == 2
+            and x.stride(1) == 1):
+        raise Rejected("mmq_quantize: a CUDA F32 or BF16 [rows, k] tensor, k contiguous")
+    rows, k = x.shape
+    if ids_src is not None:
+        _need(ids_src, torch.int32, "mmq_quantize ids_src")
+    cols = (rows if ids_src is None else ids_src.numel()) if cols is None else cols
+    out = torch.empty((max(k // 128, 1), cols, 144), dtype=torch.uint8, device=x.device)
+    N.check(N.lib().llmp_b200_mmq_quantize(
+        x.data_ptr(), int(x.dtype == torch.bfloat16), x.stride(0), k, cols,
+        ids_src.data_ptr() if ids_src is not None else None, out.data_ptr(), _stream()),
+        "llmp_b200_mmq_quantize")
+    return out
+
+
+def mmq(weights: torch.Tensor, yq: torch.Tensor, k: int, n: int, *, wtype: int = TYPE_Q4_K,
+        ids_dst: torch.Tensor | None = None, expert_bounds: torch.Tensor | None = None,
+        out_cols: int | None = None, max_cols_per_expert: int | None = None,
+        stride_row: int | None = None, stride_expert: int | None = None,
+        out: torch.Tensor | None = None) -> torch.Tensor:
+    """MulMatQ: weights Q4_K [n, k] (or [experts, n, k] with expert_bounds over the sorted
+    columns of yq) x Q8_1-MMQ activations -> F32 [out_cols, n]."""
+    _need(weights, torch.uint8, "mmq weights")
+    _need(yq, torch.uint8, "mmq activations")
+    ncols = yq.shape[1]
+    out_cols = ncols if out_cols is None else out_cols
+    if out is None:
+        out = torch.empty((out_cols, n), dtype=torch.float32, device=weights.device)
+    _need(out, torch.float32, "mmq output")
+    d = N.MmqDesc()
+    d.type, d.w, d.y, d.dst = wtype, weights.data_ptr(), yq.data_ptr(), out.data_ptr()
+    d.ids_dst = ids_dst.data_ptr() if ids_dst is not None else None
+    d.expert_bounds = expert_bounds.data_ptr() if expert_bounds is not None else None
+    d.k, d.nrows, d.ncols = k, n, ncols
+    d.stride_row = k // 256 if stride_row is None else stride_row
+    d.stride_expert = (n * d.stride_row if expert_bounds is not None else 0) \
+        if stride_expert is None else stride_expert
+    d.dst_col_stride = out.stride(0)
+    d.experts = expert_bounds.numel() - 1 if expert_bounds is not None else 1
+    d.max_cols_per_expert = ncols if max_cols_per_expert is None else max_cols_per_expert
+    N.check(N.lib().llmp_b200_mmq(C.byref(d), 0, _stream()), "llmp_b200_mmq")
     return out
