@@ -149,6 +149,61 @@ typedef struct llmp_b200_mmq_desc {
 size_t llmp_b200_mmq_scratch(const llmp_b200_mmq_desc* desc, int sms);
 int llmp_b200_mmq(const llmp_b200_mmq_desc* desc, int sms, void* stream);
 
+/* ------------------------------------------------------------------ MoE */
+/* Replaces RunMoeRoute (src/kernels/ggml/llmp_moe.cu:760; kernels :81-160).
+ * ids: I32 [used, tokens], ids_stride ints between tokens.  out: the I32 blob
+ * of moe::RouteLayout (moe_layout.h:47-83), llmp_b200_moe_route_ints() ints:
+ *   offsets[experts+1]     expert e's rows are offsets[e]..offsets[e+1] of the
+ *                          sorted order (slots in token order within an expert)
+ *   scale_rows[experts+1]  prefix of each expert's rows rounded up to 128
+ *   position[slots]        each slot's sorted row (slot = t * used + j; -1 for
+ *                          an id outside the experts)
+ *   token[slots], expert[slots]   each sorted row's token and expert (rows no
+ *                          slot reaches hold 0)
+ *   counts[chunks*experts] the counting blocks' work space (64 tokens a chunk) */
+int64_t llmp_b200_moe_route_ints(int experts, int used, int tokens);
+int llmp_b200_moe_route(const int32_t* ids, int ids_stride, int experts, int used, int tokens,
+                        int32_t* out, void* stream);
+
+/* Shaped on moe::GroupedGemm (src/kernels/ggml/moe_cutlass.h:48-63).  The
+ * reference multiplies NVFP4 operands; this build's experts are Q4_K blocks
+ * and its activations Q8_1-MMQ blocks, so `a` holds the blocks' scales and no
+ * separate scale arrays are passed. */
+typedef struct llmp_b200_grouped_gemm_desc {
+  int groups;               /* experts */
+  int n;                    /* output features (weight rows an expert) */
+  int k;                    /* a multiple of 256 */
+  int rows;                 /* sorted activation rows (columns of `a`) */
+  const int32_t* offsets;   /* device, groups + 1: a route's offsets */
+  const void* a;            /* Q8_1-MMQ blocks [k / 128][rows], expert-sorted rows */
+  const void* weights;      /* Q4_K blocks: expert e at weights + e * expert_stride */
+  uint64_t expert_stride;   /* bytes, a multiple of 144 */
+  void* d;                  /* F32 [rows][n] */
+  void* scratch;            /* llmp_b200_grouped_gemm_scratch() bytes, 256-byte aligned */
+} llmp_b200_grouped_gemm_desc;
+
+/* Replace moe::GroupedGemmAvailable / GroupedGemmScratch / RunGroupedGemm
+ * (moe_cutlass.h:64-76): per expert e, D_e[M_e, n] = A_e[M_e, k] . W_e^T with the
+ * arithmetic of llmp_b200_mmq.  The tile list is built on the device from
+ * `offsets` into `scratch` (the reference's SetupGroups), then the tensor-core
+ * kernel runs one CTA a listed tile. */
+int llmp_b200_grouped_gemm_available(void);
+size_t llmp_b200_grouped_gemm_scratch(int groups, int rows, int sms);
+int llmp_b200_grouped_gemm(const llmp_b200_grouped_gemm_desc* gemm, int sms, void* stream);
+
+/* Replaces llmp.moe.glu_quantize (llmp_moe.cu:348-392) for this build's
+ * activation format: gate_up F32 [2 f, rows] (gate then up in a row); out:
+ * Q8_1-MMQ blocks [f / 128][rows] of glu(gate, up). */
+int llmp_b200_moe_glu_quantize(const float* gate_up, int64_t row_stride, int f, int64_t rows,
+                               int glu, float limit, void* out, void* stream);
+
+/* Replaces llmp.moe.combine_sorted (llmp_moe.cu:393-435) without NVFP4's global
+ * scales and the shared expert: dst[t] = sum over the token's slots, in slot
+ * order, of rows[position[t * used + j]] * weights[t * used + j]. */
+int llmp_b200_moe_combine(const float* rows, int64_t row_stride, const int32_t* position,
+                          const float* weights, int used, int tokens, int width, float* dst,
+                          void* stream);
+
 /* ------------------------------------------------------------------ MXFP8 */
 /* MXFP8: E4M3 codes with one E8M0 scale per 32 values along K.  Scales live in
  * "scale atoms" (src/format/layout.h:97-112, == moe_cutlass.h:42-46 SfOffset):

@@ -50,6 +50,13 @@ class MmqDesc(C.Structure):
                 ("max_cols_per_expert", C.c_int)]
 
 
+class GroupedGemmDesc(C.Structure):
+    """llmp_b200_grouped_gemm_desc (include/llmp_b200.h)."""
+    _fields_ = [("groups", C.c_int), ("n", C.c_int), ("k", C.c_int), ("rows", C.c_int),
+                ("offsets", C.c_void_p), ("a", C.c_void_p), ("weights", C.c_void_p),
+                ("expert_stride", C.c_uint64), ("d", C.c_void_p), ("scratch", C.c_void_p)]
+
+
 # name -> (restype, argtypes): every symbol include/llmp_b200.h declares.
 SIGNATURES = {
     "llmp_b200_available": (C.c_int, []),
@@ -67,6 +74,16 @@ SIGNATURES = {
                                          C.c_void_p, C.c_void_p, C.c_void_p]),
     "llmp_b200_mmq_scratch": (C.c_size_t, [C.POINTER(MmqDesc), C.c_int]),
     "llmp_b200_mmq": (C.c_int, [C.POINTER(MmqDesc), C.c_int, C.c_void_p]),
+    "llmp_b200_moe_route_ints": (C.c_int64, [C.c_int, C.c_int, C.c_int]),
+    "llmp_b200_moe_route": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
+                                      C.c_void_p]),
+    "llmp_b200_grouped_gemm_available": (C.c_int, []),
+    "llmp_b200_grouped_gemm_scratch": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
+    "llmp_b200_grouped_gemm": (C.c_int, [C.POINTER(GroupedGemmDesc), C.c_int, C.c_void_p]),
+    "llmp_b200_moe_glu_quantize": (C.c_int, [C.c_void_p, C.c_int64, C.c_int, C.c_int64, C.c_int,
+                                             C.c_float, C.c_void_p, C.c_void_p]),
+    "llmp_b200_moe_combine": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int,
+                                        C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "llmp_b200_mxfp8_padded_rows": (C.c_uint64, [C.c_uint64]),
     "llmp_b200_mxfp8_scale_offset": (C.c_uint64, [C.c_uint64, C.c_uint64, C.c_uint64]),
     "llmp_b200_mxfp8_quantize": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int,

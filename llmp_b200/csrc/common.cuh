@@ -88,6 +88,21 @@ __device__ __forceinline__ std::uint32_t LoadStream4(const void* p) {
 __device__ __forceinline__ float HalfBitsToFloat(std::uint32_t bits16) {
   return __half2float(__ushort_as_half(static_cast<unsigned short>(bits16)));
 }
+
+__device__ __forceinline__ float Silu(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float GeluTanh(float x) {
+  return 0.5f * x * (1.0f + tanhf(0.79788456080286535587989211986876f * x *
+                                  (1.0f + 0.044715f * x * x)));
+}
+// src/kernels/ggml/vecq.cu:184-195.
+__device__ __forceinline__ float Glu(int glu, float gate, float up, float limit) {
+  if (glu == LLMP_B200_GLU_GEGLU) return GeluTanh(gate) * up;
+  if (glu == LLMP_B200_GLU_SWIGLU_CLAMP) {
+    gate = fminf(gate, limit);
+    up = fmaxf(fminf(up, limit), -limit);
+  }
+  return Silu(gate) * up;
+}
 #endif  // __CUDACC__
 
 }  // namespace llmp_b200

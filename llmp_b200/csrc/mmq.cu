@@ -27,6 +27,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include "mmq.cuh"
 #include "tc.cuh"
 
 namespace llmp_b200 {
@@ -120,7 +121,8 @@ struct Shared {
 };
 
 __global__ void __launch_bounds__(kThreads, 1)
-MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const Desc a, unsigned int* faults) {
+MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const Desc a,
+             const std::int32_t* __restrict__ worklist, unsigned int* faults) {
   extern __shared__ unsigned char raw_smem[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<std::uintptr_t>(raw_smem) + 1023) & ~static_cast<std::uintptr_t>(1023));
@@ -138,10 +140,19 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const Desc a, unsigned i
 
   // The tile: weight rows [row0, row0 + 128) of expert e against sorted
   // columns [col0, col0 + 128) of that expert's range [c_begin, c_end).
-  const int expert = static_cast<int>(blockIdx.z);
-  const int c_begin = a.expert_bounds != nullptr ? a.expert_bounds[expert] : 0;
+  // With a worklist (built on the device from the expert bounds) grid row y
+  // names entry y: {expert, first column}; entry 0 holds the entry count.
+  int expert = static_cast<int>(blockIdx.z);
+  int col0;
+  if (worklist != nullptr) {
+    if (static_cast<int>(blockIdx.y) >= worklist[0]) return;
+    expert = worklist[1 + (2 * blockIdx.y)];
+    col0 = worklist[2 + (2 * blockIdx.y)];
+  } else {
+    const int c_begin = a.expert_bounds != nullptr ? a.expert_bounds[expert] : 0;
+    col0 = c_begin + (static_cast<int>(blockIdx.y) * kTileCols);
+  }
   const int c_end = a.expert_bounds != nullptr ? a.expert_bounds[expert + 1] : a.ncols;
-  const int col0 = c_begin + (static_cast<int>(blockIdx.y) * kTileCols);
   const int row0 = static_cast<int>(blockIdx.x) * kTileRows;
   if (col0 >= c_end) return;  // uniform for the CTA, before any barrier
 
@@ -396,6 +407,58 @@ int CheckDesc(const Desc& d) {
 }
 
 }  // namespace
+
+int LaunchMmq(const llmp_b200_mmq_desc& d, const std::int32_t* worklist, int max_tiles,
+              void* stream) {
+  if (const int status = CheckDesc(d); status != 0) return status;
+  if (const int status = DeviceStatus(); status != 0) return status;
+  const tc::EncodeTiledFn encode = tc::EncodeTiled();
+  if (encode == nullptr) return Reject("mmq: the driver has no tensor-map encoder");
+  CUtensorMap map_y;
+  {
+    const cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(d.ncols),
+                                static_cast<cuuint64_t>(d.k / 128)};
+    const cuuint64_t strides[2] = {144, static_cast<cuuint64_t>(d.ncols) * 144};
+    const cuuint32_t box[3] = {128, kTileCols, 1};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    void* base = const_cast<std::uint8_t*>(static_cast<const std::uint8_t*>(d.y) + 16);
+    if (encode(&map_y, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, base, dims, strides, box, elem,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+      return Reject("mmq: the driver refused a tensor map for the activation blocks");
+    }
+  }
+  unsigned int* faults = FaultCounter();
+  if (faults == nullptr) return Reject("mmq: no fault counter on this device");
+  static thread_local int configured_device = -1;
+  int device = -1;
+  cudaGetDevice(&device);
+  if (configured_device != device) {
+    const cudaError_t e =
+        cudaFuncSetAttribute(MmqQ4KKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    if (e != cudaSuccess) return Failed(e, "mmq attribute");
+    configured_device = device;
+  }
+  dim3 grid(static_cast<unsigned>((d.nrows + kTileRows - 1) / kTileRows), 1, 1);
+  if (worklist != nullptr) {
+    if (max_tiles < 1) return Reject("mmq: a worklist needs its capacity");
+    grid.y = static_cast<unsigned>(max_tiles);
+  } else {
+    const int experts = d.expert_bounds != nullptr ? d.experts : 1;
+    const int max_cols = d.expert_bounds != nullptr ? d.max_cols_per_expert : d.ncols;
+    if (max_cols < 1) return Reject("mmq: max_cols_per_expert >= 1 with experts");
+    grid.y = static_cast<unsigned>((max_cols + kTileCols - 1) / kTileCols);
+    grid.z = static_cast<unsigned>(experts);
+  }
+  if (grid.y > 65535u) return Reject("mmq: more column tiles than a grid holds");
+  MmqQ4KKernel<<<grid, kThreads, kSmem, static_cast<cudaStream_t>(stream)>>>(map_y, d, worklist,
+                                                                             faults);
+  const cudaError_t e = cudaPeekAtLastError();
+  if (e != cudaSuccess) return Failed(cudaGetLastError(), "mmq launch");
+  return 0;
+}
+
 }  // namespace llmp_b200
 
 extern "C" {
@@ -435,51 +498,9 @@ size_t llmp_b200_mmq_scratch(const llmp_b200_mmq_desc* desc, int sms) {
 }
 
 int llmp_b200_mmq(const llmp_b200_mmq_desc* desc, int sms, void* stream) {
-  using namespace llmp_b200;
   (void)sms;
-  if (desc == nullptr) return Reject("mmq: null descriptor");
-  const Desc& d = *desc;
-  if (const int status = CheckDesc(d); status != 0) return status;
-  if (const int status = DeviceStatus(); status != 0) return status;
-  const tc::EncodeTiledFn encode = tc::EncodeTiled();
-  if (encode == nullptr) return Reject("mmq: the driver has no tensor-map encoder");
-  CUtensorMap map_y;
-  {
-    const cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(d.ncols),
-                                static_cast<cuuint64_t>(d.k / 128)};
-    const cuuint64_t strides[2] = {144, static_cast<cuuint64_t>(d.ncols) * 144};
-    const cuuint32_t box[3] = {128, kTileCols, 1};
-    const cuuint32_t elem[3] = {1, 1, 1};
-    void* base = const_cast<std::uint8_t*>(static_cast<const std::uint8_t*>(d.y) + 16);
-    if (encode(&map_y, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, base, dims, strides, box, elem,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-               CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
-      return Reject("mmq: the driver refused a tensor map for the activation blocks");
-    }
-  }
-  unsigned int* faults = FaultCounter();
-  if (faults == nullptr) return Reject("mmq: no fault counter on this device");
-  static thread_local int configured_device = -1;
-  int device = -1;
-  cudaGetDevice(&device);
-  if (configured_device != device) {
-    const cudaError_t e =
-        cudaFuncSetAttribute(MmqQ4KKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
-    if (e != cudaSuccess) return Failed(e, "mmq attribute");
-    configured_device = device;
-  }
-  const int experts = d.expert_bounds != nullptr ? d.experts : 1;
-  const int max_cols = d.expert_bounds != nullptr ? d.max_cols_per_expert : d.ncols;
-  if (max_cols < 1) return Reject("mmq: max_cols_per_expert >= 1 with experts");
-  const dim3 grid(static_cast<unsigned>((d.nrows + kTileRows - 1) / kTileRows),
-                  static_cast<unsigned>((max_cols + kTileCols - 1) / kTileCols),
-                  static_cast<unsigned>(experts));
-  if (grid.y > 65535u) return Reject("mmq: more column tiles than a grid holds");
-  MmqQ4KKernel<<<grid, kThreads, kSmem, static_cast<cudaStream_t>(stream)>>>(map_y, d, faults);
-  const cudaError_t e = cudaPeekAtLastError();
-  if (e != cudaSuccess) return Failed(cudaGetLastError(), "mmq launch");
-  return 0;
+  if (desc == nullptr) return llmp_b200::Reject("mmq: null descriptor");
+  return llmp_b200::LaunchMmq(*desc, nullptr, 0, stream);
 }
 
 }  // extern "C"

@@ -1,0 +1,21 @@
+// Internal launcher of the Q4_K x Q8_1-MMQ tensor-core GEMM, shared by the
+// dense / per-expert entry point and the grouped (worklist) one.
+#ifndef LLMP_B200_CSRC_MMQ_CUH_
+#define LLMP_B200_CSRC_MMQ_CUH_
+
+#include <cstdint>
+
+#include "llmp_b200.h"
+
+namespace llmp_b200 {
+
+constexpr int kMmqTileCols = 128;  // token columns a tile
+
+// worklist (device, or null): int32 {count, (expert, first column) x count};
+// grid row y takes entry y and exits when y >= count.  max_tiles: its capacity.
+int LaunchMmq(const llmp_b200_mmq_desc& d, const std::int32_t* worklist, int max_tiles,
+              void* stream);
+
+}  // namespace llmp_b200
+
+#endif  // LLMP_B200_CSRC_MMQ_CUH_

@@ -1,0 +1,367 @@
+// Routed-expert (MoE) products on B200: the expert counting sort, the grouped
+// expert GEMM over expert-sorted rows, the GLU + requantization between the
+// two expert GEMMs, and the ordered weighted combine.
+//
+// Interfaces follow the reference's routed path (src/kernels/ggml/moe_layout.h
+// :47-83 RouteLayout, llmp_moe.cu:81-160 route, :308-435 quantize / GLU /
+// combine, moe_cutlass.h:48-76 grouped GEMM).  The reference's grouped GEMM
+// multiplies NVFP4 operands with CUTLASS; this build's experts are Q4_K, so
+// the grouped GEMM is the Q4_K x Q8_1-MMQ tensor-core kernel of mmq.cu driven
+// by a tile worklist built ON THE DEVICE from the route's offsets (the role
+// of the reference's SetupGroups): nothing waits on the host.
+#include "mmq.cuh"
+#include "tc.cuh"
+
+namespace llmp_b200 {
+namespace {
+
+constexpr int kRouteChunk = 64;   // tokens a counting block (moe_layout.h:42)
+constexpr int kScaleRows = 128;   // rows a group's scales are padded to (:44)
+constexpr int kMaxExperts = 1024;
+
+struct Route {
+  std::int32_t* offsets;
+  std::int32_t* scale_rows;
+  std::int32_t* position;
+  std::int32_t* token;
+  std::int32_t* expert;
+  std::int32_t* counts;
+  int experts, used, tokens, chunks;
+};
+
+__host__ Route RouteOf(std::int32_t* base, int experts, int used, int tokens) {
+  const std::int64_t slots = static_cast<std::int64_t>(used) * tokens;
+  Route r;
+  r.experts = experts;
+  r.used = used;
+  r.tokens = tokens;
+  r.chunks = (tokens + kRouteChunk - 1) / kRouteChunk;
+  r.offsets = base;
+  r.scale_rows = base + (experts + 1);
+  r.position = base + (2 * (experts + 1));
+  r.token = r.position + slots;
+  r.expert = r.token + slots;
+  r.counts = r.expert + slots;
+  return r;
+}
+
+// Each block counts its chunk's ids per expert (llmp_moe.cu:81-106).
+__global__ void RouteCount(const std::int32_t* __restrict__ ids, int ids_stride, Route r) {
+  extern __shared__ int hist[];
+  for (int e = threadIdx.x; e < r.experts; e += blockDim.x) hist[e] = 0;
+  __syncthreads();
+  const int c = blockIdx.x;
+  const int t0 = c * kRouteChunk;
+  const int t1 = min(t0 + kRouteChunk, r.tokens);
+  const int n = (t1 - t0) * r.used;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int t = t0 + (i / r.used);
+    const int e = ids[(static_cast<std::int64_t>(t) * ids_stride) + (i % r.used)];
+    if (e >= 0 && e < r.experts) atomicAdd(&hist[e], 1);  // integer counts: order-free
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < r.experts; e += blockDim.x) {
+    r.counts[(static_cast<std::int64_t>(c) * r.experts) + e] = hist[e];
+  }
+}
+
+// One block: chunk counts -> chunk bases, expert offsets and scale rows
+// (llmp_moe.cu:108-133); also clears the sorted rows' token / expert so that
+// rows no slot reaches read as row 0 of expert 0.
+__global__ void RouteScan(Route r) {
+  extern __shared__ int total[];
+  for (int e = threadIdx.x; e < r.experts; e += blockDim.x) {
+    int running = 0;
+    for (int c = 0; c < r.chunks; ++c) {
+      std::int32_t* at = r.counts + (static_cast<std::int64_t>(c) * r.experts) + e;
+      const int v = *at;
+      *at = running;
+      running += v;
+    }
+    total[e] = running;
+  }
+  const std::int64_t slots = static_cast<std::int64_t>(r.used) * r.tokens;
+  for (std::int64_t i = threadIdx.x; i < slots; i += blockDim.x) {
+    r.token[i] = 0;
+    r.expert[i] = 0;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    r.offsets[0] = 0;
+    r.scale_rows[0] = 0;
+    for (int e = 0; e < r.experts; ++e) {
+      r.offsets[e + 1] = r.offsets[e] + total[e];
+      r.scale_rows[e + 1] = r.scale_rows[e] + ((total[e] + kScaleRows - 1) / kScaleRows * kScaleRows);
+    }
+  }
+}
+
+// Places a chunk's slots in token order within each expert.  One thread an
+// expert walks the chunk's ids (staged in shared memory) in slot order: the
+// same placement as the reference's one-thread loop (llmp_moe.cu:135-160),
+// every expert at once, no atomics.
+__global__ void RouteAssign(const std::int32_t* __restrict__ ids, int ids_stride, Route r) {
+  extern __shared__ int chunk_ids[];
+  const int c = blockIdx.x;
+  const int t0 = c * kRouteChunk;
+  const int t1 = min(t0 + kRouteChunk, r.tokens);
+  const int n = (t1 - t0) * r.used;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int t = t0 + (i / r.used);
+    const int e = ids[(static_cast<std::int64_t>(t) * ids_stride) + (i % r.used)];
+    chunk_ids[i] = e;
+    if (e < 0 || e >= r.experts) r.position[(static_cast<std::int64_t>(t0) * r.used) + i] = -1;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < r.experts; e += blockDim.x) {
+    int row = r.offsets[e] + r.counts[(static_cast<std::int64_t>(c) * r.experts) + e];
+    for (int i = 0; i < n; ++i) {
+      if (chunk_ids[i] == e) {
+        const std::int64_t slot = (static_cast<std::int64_t>(t0) * r.used) + i;
+        r.position[slot] = row;
+        r.token[row] = t0 + (i / r.used);
+        r.expert[row] = e;
+        ++row;
+      }
+    }
+  }
+}
+
+// The grouped GEMM's tile list from the experts' offsets: entry 0 the count,
+// then (expert, first column) per 128-column tile, experts in order.
+__global__ void BuildTiles(const std::int32_t* __restrict__ offsets, int groups, int capacity,
+                           std::int32_t* __restrict__ worklist) {
+  extern __shared__ int first[];  // groups + 1 tile prefix
+  if (threadIdx.x == 0) {
+    int running = 0;
+    for (int e = 0; e < groups; ++e) {
+      first[e] = running;
+      running += (offsets[e + 1] - offsets[e] + kMmqTileCols - 1) / kMmqTileCols;
+    }
+    first[groups] = running;
+    worklist[0] = min(running, capacity);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < groups; e += blockDim.x) {
+    const int tiles = first[e + 1] - first[e];
+    for (int i = 0; i < tiles; ++i) {
+      const int at = first[e] + i;
+      if (at < capacity) {
+        worklist[1 + (2 * at)] = e;
+        worklist[2 + (2 * at)] = offsets[e] + (i * kMmqTileCols);
+      }
+    }
+  }
+}
+
+// GLU of the gate and up halves of a row, then the Q8_1-MMQ quantizer of
+// mmq.cu on the result (llmp.moe.glu_quantize, llmp_moe.cu:348-392, with this
+// build's activation format).  x: F32 [rows][2 f], gate first.
+__global__ void __launch_bounds__(256)
+GluQuantizeKernel(const float* __restrict__ x, std::int64_t row_stride, int f, std::int64_t rows,
+                  int glu, float limit, std::uint8_t* __restrict__ out, std::int64_t lanes_total) {
+  GridLaunchDependents();
+  GridDependencyWait();
+  const std::int64_t i = (static_cast<std::int64_t>(blockIdx.x) * 256) + threadIdx.x;
+  const bool live = i < lanes_total;
+  const std::int64_t group = (live ? i : 0) / 8;
+  const int part = static_cast<int>(i % 8);
+  const int groups = f / 32;
+  const std::int64_t row = group / groups;
+  const int g = static_cast<int>(group % groups);
+  float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  if (live) {
+    const float* p = x + (row * row_stride) + (g * 32) + (part * 4);
+    const float4 gate = *reinterpret_cast<const float4*>(p);
+    const float4 up = *reinterpret_cast<const float4*>(p + f);
+    v[0] = Glu(glu, gate.x, up.x, limit);
+    v[1] = Glu(glu, gate.y, up.y, limit);
+    v[2] = Glu(glu, gate.z, up.z, limit);
+    v[3] = Glu(glu, gate.w, up.w, limit);
+  }
+  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+  float sum = ((v[0] + v[1]) + v[2]) + v[3];
+#pragma unroll
+  for (int offset = 4; offset > 0; offset >>= 1) {
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
+    sum = sum + __shfl_xor_sync(0xffffffffu, sum, offset);
+  }
+  if (!live) return;
+  std::uint32_t packed = 0;
+  float d = 0.0f;
+  if (amax > 0.0f) {
+    const float d_inv = 127.0f / amax;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int q = static_cast<int>(roundf(v[c] * d_inv));
+      packed |= (static_cast<std::uint32_t>(q) & 0xffu) << (8 * c);
+    }
+    d = 1.0f / d_inv;
+  }
+  std::uint8_t* block = out + ((static_cast<std::int64_t>(g / 4) * rows + row) * 144);
+  *reinterpret_cast<std::uint32_t*>(block + 16 + ((g % 4) * 32) + (part * 4)) = packed;
+  if (part == 0) {
+    const std::uint32_t ds = static_cast<std::uint32_t>(__half_as_ushort(__float2half_rn(d))) |
+                             (static_cast<std::uint32_t>(__half_as_ushort(__float2half_rn(sum)))
+                              << 16);
+    *reinterpret_cast<std::uint32_t*>(block + ((g % 4) * 4)) = ds;
+  }
+}
+
+// dst[t][c] = sum over the token's slots, in slot order, of rows[position][c] *
+// weight; a slot outside the experts contributes NaN (llmp_moe.cu:393-435
+// without the NVFP4 global scales and the shared expert).
+__global__ void CombineKernel(const float* __restrict__ rows, std::int64_t row_stride,
+                              const std::int32_t* __restrict__ position,
+                              const float* __restrict__ weights, int used, int width4,
+                              std::int64_t total4, float4* __restrict__ dst) {
+  const std::int64_t i = (static_cast<std::int64_t>(blockIdx.x) * blockDim.x) + threadIdx.x;
+  if (i >= total4) return;
+  const std::int64_t t = i / width4;
+  const std::int64_t c4 = i % width4;
+  const float nan = __uint_as_float(0x7fc00000u);
+  float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  for (int j = 0; j < used; ++j) {
+    const int p = position[(t * used) + j];
+    const float w = weights[(t * used) + j];
+    float4 v = make_float4(nan, nan, nan, nan);
+    if (p >= 0) v = *reinterpret_cast<const float4*>(rows + (static_cast<std::int64_t>(p) * row_stride) + (c4 * 4));
+    const float4 e = make_float4(__fmul_rn(v.x, w), __fmul_rn(v.y, w), __fmul_rn(v.z, w),
+                                 __fmul_rn(v.w, w));
+    acc = j == 0 ? e : make_float4(acc.x + e.x, acc.y + e.y, acc.z + e.z, acc.w + e.w);
+  }
+  dst[i] = acc;
+}
+
+int CheckGrouped(const llmp_b200_grouped_gemm_desc& g) {
+  if (g.groups < 1 || g.groups > kMaxExperts || g.n < 1 || g.k < 256 || g.k % 256 != 0 ||
+      g.rows < 1) {
+    return Reject("grouped_gemm: 1..1024 groups, n >= 1, k a positive multiple of 256, rows >= 1");
+  }
+  if (g.offsets == nullptr || g.a == nullptr || g.weights == nullptr || g.d == nullptr) {
+    return Reject("grouped_gemm: offsets, activation blocks, weights and an output");
+  }
+  if (g.expert_stride % 144 != 0 || g.expert_stride < static_cast<std::uint64_t>(g.n) * (g.k / 256) * 144) {
+    return Reject("grouped_gemm: expert stride a whole number of Q4_K blocks covering n rows");
+  }
+  return 0;
+}
+
+llmp_b200_mmq_desc MmqOf(const llmp_b200_grouped_gemm_desc& g) {
+  llmp_b200_mmq_desc d{};
+  d.type = LLMP_B200_TYPE_Q4_K;
+  d.w = g.weights;
+  d.y = g.a;
+  d.ids_dst = nullptr;
+  d.expert_bounds = g.offsets;
+  d.dst = static_cast<float*>(g.d);
+  d.k = g.k;
+  d.nrows = g.n;
+  d.ncols = g.rows;
+  d.stride_row = g.k / 256;
+  d.stride_expert = static_cast<int>(g.expert_stride / 144);
+  d.dst_col_stride = g.n;
+  d.experts = g.groups;
+  d.max_cols_per_expert = g.rows;
+  return d;
+}
+
+int TileCapacity(int groups, int rows) { return ((rows + kMmqTileCols - 1) / kMmqTileCols) + groups; }
+
+}  // namespace
+}  // namespace llmp_b200
+
+extern "C" {
+
+int64_t llmp_b200_moe_route_ints(int experts, int used, int tokens) {
+  const int64_t slots = static_cast<int64_t>(used) * tokens;
+  const int64_t chunks = (tokens + llmp_b200::kRouteChunk - 1) / llmp_b200::kRouteChunk;
+  return (2 * (static_cast<int64_t>(experts) + 1)) + (3 * slots) + (chunks * experts);
+}
+
+int llmp_b200_moe_route(const int32_t* ids, int ids_stride, int experts, int used, int tokens,
+                        int32_t* out, void* stream) {
+  using namespace llmp_b200;
+  if (ids == nullptr || out == nullptr || experts < 1 || experts > kMaxExperts || used < 1 ||
+      tokens < 1 || ids_stride < used || used * kRouteChunk > 8192) {
+    return Reject("moe.route: ids I32 [used, tokens], 1..1024 experts, used <= 128");
+  }
+  if (const int status = DeviceStatus(); status != 0) return status;
+  auto* s = static_cast<cudaStream_t>(stream);
+  const Route r = RouteOf(out, experts, used, tokens);
+  RouteCount<<<r.chunks, 256, experts * sizeof(int), s>>>(ids, ids_stride, r);
+  RouteScan<<<1, 256, experts * sizeof(int), s>>>(r);
+  RouteAssign<<<r.chunks, 256, used * kRouteChunk * sizeof(int), s>>>(ids, ids_stride, r);
+  return Launched("moe.route launch");
+}
+
+int llmp_b200_grouped_gemm_available(void) { return llmp_b200_available(); }
+
+size_t llmp_b200_grouped_gemm_scratch(int groups, int rows, int sms) {
+  (void)sms;
+  if (groups < 1 || rows < 1) return 0;
+  const size_t ints = 1 + (2 * static_cast<size_t>(llmp_b200::TileCapacity(groups, rows)));
+  return (ints * sizeof(int32_t) + 255) / 256 * 256;
+}
+
+int llmp_b200_grouped_gemm(const llmp_b200_grouped_gemm_desc* gemm, int sms, void* stream) {
+  using namespace llmp_b200;
+  (void)sms;
+  if (gemm == nullptr) return Reject("grouped_gemm: null descriptor");
+  const llmp_b200_grouped_gemm_desc& g = *gemm;
+  if (const int status = CheckGrouped(g); status != 0) return status;
+  if (g.scratch == nullptr || !Aligned(g.scratch, 256)) {
+    return Reject("grouped_gemm: 256-byte aligned scratch of llmp_b200_grouped_gemm_scratch bytes");
+  }
+  if (const int status = DeviceStatus(); status != 0) return status;
+  const int capacity = TileCapacity(g.groups, g.rows);
+  auto* worklist = static_cast<std::int32_t*>(g.scratch);
+  BuildTiles<<<1, 256, (g.groups + 1) * sizeof(int), static_cast<cudaStream_t>(stream)>>>(
+      g.offsets, g.groups, capacity, worklist);
+  if (const int status = Launched("grouped_gemm tile list"); status != 0) return status;
+  const int status = LaunchMmq(MmqOf(g), worklist, capacity, stream);
+  // The tile list is queued: a refusal now would leave work behind, so report
+  // it as a failure after queueing.
+  return status > 0 ? -status : status;
+}
+
+int llmp_b200_moe_glu_quantize(const float* gate_up, int64_t row_stride, int f, int64_t rows,
+                               int glu, float limit, void* out, void* stream) {
+  using namespace llmp_b200;
+  if (gate_up == nullptr || out == nullptr || f < 128 || f % 128 != 0 || rows < 1 ||
+      row_stride < 2 * static_cast<int64_t>(f) || glu < 1 || glu > 3) {
+    return Reject("moe.glu_quantize: F32 [2 f, rows] with f a positive multiple of 128, a GLU");
+  }
+  if (!Aligned(gate_up, 16) || row_stride % 4 != 0 || !Aligned(out, 16)) {
+    return Reject("moe.glu_quantize: rows and output 16-byte aligned");
+  }
+  if (const int status = DeviceStatus(); status != 0) return status;
+  const std::int64_t lanes = rows * (f / 32) * 8;
+  const std::int64_t grid = (lanes + 255) / 256;
+  if (grid > 0x7fffffffLL) return Reject("moe.glu_quantize: more blocks than a grid holds");
+  const cudaError_t e = LaunchPdl(GluQuantizeKernel, dim3(static_cast<unsigned>(grid)), dim3(256), 0,
+                                  static_cast<cudaStream_t>(stream), gate_up, row_stride, f, rows,
+                                  glu, limit, static_cast<std::uint8_t*>(out), lanes);
+  if (e != cudaSuccess) return Failed(e, "moe.glu_quantize launch");
+  return 0;
+}
+
+int llmp_b200_moe_combine(const float* rows, int64_t row_stride, const int32_t* position,
+                          const float* weights, int used, int tokens, int width, float* dst,
+                          void* stream) {
+  using namespace llmp_b200;
+  if (rows == nullptr || position == nullptr || weights == nullptr || dst == nullptr || used < 1 ||
+      tokens < 1 || width < 4 || width % 4 != 0 || row_stride < width || row_stride % 4 != 0) {
+    return Reject("moe.combine: sorted rows F32 [width, slots], width a positive multiple of 4");
+  }
+  if (!Aligned(rows, 16) || !Aligned(dst, 16)) return Reject("moe.combine: 16-byte aligned rows");
+  if (const int status = DeviceStatus(); status != 0) return status;
+  const std::int64_t total4 = static_cast<std::int64_t>(tokens) * (width / 4);
+  CombineKernel<<<static_cast<unsigned>((total4 + 255) / 256), 256, 0,
+                  static_cast<cudaStream_t>(stream)>>>(rows, row_stride, position, weights, used,
+                                                       width / 4, total4,
+                                                       reinterpret_cast<float4*>(dst));
+  return Launched("moe.combine launch");
+}
+
+}  // extern "C"

@@ -236,21 +236,6 @@ __device__ __forceinline__ void StageRow(const std::uint8_t* __restrict__ y, int
   }
 }
 
-__device__ __forceinline__ float Silu(float x) { return x / (1.0f + expf(-x)); }
-__device__ __forceinline__ float GeluTanh(float x) {
-  return 0.5f * x * (1.0f + tanhf(0.79788456080286535587989211986876f * x *
-                                  (1.0f + 0.044715f * x * x)));
-}
-// src/kernels/ggml/vecq.cu:184-195.
-__device__ __forceinline__ float Glu(int glu, float gate, float up, float limit) {
-  if (glu == LLMP_B200_GLU_GEGLU) return GeluTanh(gate) * up;
-  if (glu == LLMP_B200_GLU_SWIGLU_CLAMP) {
-    gate = fminf(gate, limit);
-    up = fmaxf(fminf(up, limit), -limit);
-  }
-  return Silu(gate) * up;
-}
-
 // ------------------------------------------------------------------ kernel
 // Unit: Q4KUnit or Q8_0Unit<>.  P tokens a pass, LPR lanes a row, R rows a
 // team at once, U units a lane in flight per row, kGlu: gate and up together.

@@ -17,7 +17,8 @@ from ._native import (GLU_GEGLU, GLU_NONE, GLU_SWIGLU, GLU_SWIGLU_CLAMP, TYPE_Q4
 
 __all__ = ["available", "sm_count", "device_faults", "block_bytes", "block_elems", "q8_1_row_blocks",
            "quantize_q8", "vecq", "vecq_variants", "vecq_block_sums", "mxfp8_padded_rows",
-           "mxfp8_quantize", "mxfp8_swizzle", "mxfp8_gemm", "mmq_quantize", "mmq", "TYPE_Q8_0", "TYPE_Q4_K",
+           "mxfp8_quantize", "mxfp8_swizzle", "mxfp8_gemm", "mmq_quantize", "mmq", "moe_route", "grouped_gemm",
+           "moe_glu_quantize", "moe_combine", "moe_ffn", "TYPE_Q8_0", "TYPE_Q4_K",
            "GLU_NONE", "GLU_SWIGLU", "GLU_SWIGLU_CLAMP", "GLU_GEGLU", "Rejected", "LaunchFailed"]
 
 _BLOCK = {TYPE_Q8_0: (32, 34), TYPE_Q4_K: (256, 144), N.TYPE_Q8_1: (32, 36)}
@@ -253,3 +254,103 @@ def mmq(weights: torch.Tensor, yq: torch.Tensor, k: int, n: int, *, wtype: int =
     d.max_cols_per_expert = ncols if max_cols_per_expert is None else max_cols_per_expert
     N.check(N.lib().llmp_b200_mmq(C.byref(d), 0, _stream()), "llmp_b200_mmq")
     return out
+
+
+# ----------------------------------------------------------------------- MoE
+def moe_route(ids: torch.Tensor, experts: int) -> dict:
+    """MoeRoute: ids I32 [tokens, used] -> the route blob and views of its parts."""
+    _need(ids, torch.int32, "moe_route ids")
+    if ids.dim() != 2 or ids.stride(1) != 1:
+        raise Rejected("moe_route: ids I32 [used, tokens]")
+    tokens, used = ids.shape
+    n = int(N.lib().llmp_b200_moe_route_ints(experts, used, tokens))
+    blob = torch.empty((n,), dtype=torch.int32, device=ids.device)
+    N.check(N.lib().llmp_b200_moe_route(ids.data_ptr(), ids.stride(0), experts, used, tokens,
+                                        blob.data_ptr(), _stream()), "llmp_b200_moe_route")
+    slots, e1 = tokens * used, experts + 1
+    return {"blob": blob, "offsets": blob[:e1], "scale_rows": blob[e1:2 * e1],
+            "position": blob[2 * e1:2 * e1 + slots],
+            "token": blob[2 * e1 + slots:2 * e1 + 2 * slots],
+            "expert": blob[2 * e1 + 2 * slots:2 * e1 + 3 * slots],
+            "counts": blob[2 * e1 + 3 * slots:], "experts": experts, "used": used,
+            "tokens": tokens}
+
+
+def grouped_gemm(weights: torch.Tensor, a: torch.Tensor, offsets: torch.Tensor, k: int, n: int,
+                 *, out: torch.Tensor | None = None,
+                 scratch: torch.Tensor | None = None) -> torch.Tensor:
+    """MoeGemm: weights Q4_K [groups, n, k]; a Q8_1-MMQ blocks [k / 128, rows, 144] of
+    expert-sorted rows; offsets I32 [groups + 1] -> F32 [rows, n]."""
+    _need(weights, torch.uint8, "grouped_gemm weights")
+    _need(a, torch.uint8, "grouped_gemm activations")
+    _need(offsets, torch.int32, "grouped_gemm offsets")
+    groups, rows = offsets.numel() - 1, a.shape[1]
+    if out is None:
+        out = torch.empty((rows, n), dtype=torch.float32, device=weights.device)
+    need = int(N.lib().llmp_b200_grouped_gemm_scratch(groups, rows, 0))
+    if scratch is None:
+        scratch = torch.empty((need,), dtype=torch.uint8, device=weights.device)
+    g = N.GroupedGemmDesc()
+    g.groups, g.n, g.k, g.rows = groups, n, k, rows
+    g.offsets, g.a, g.weights = offsets.data_ptr(), a.data_ptr(), weights.data_ptr()
+    g.expert_stride = weights.stride(0) if weights.dim() == 3 else n * (k // 256) * 144
+    g.d, g.scratch = out.data_ptr(), scratch.data_ptr()
+    N.check(N.lib().llmp_b200_grouped_gemm(C.byref(g), 0, _stream()), "llmp_b200_grouped_gemm")
+    return out
+
+
+def moe_glu_quantize(gate_up: torch.Tensor, f: int, glu: int = GLU_SWIGLU,
+                     limit: float = 0.0) -> torch.Tensor:
+    """MoeGluQuantize: gate_up F32 [rows, 2 f] -> Q8_1-MMQ blocks [f / 128, rows, 144]."""
+    _need(gate_up, torch.float32, "moe_glu_quantize input")
+    rows = gate_up.shape[0]
+    out = torch.empty((f // 128, rows, 144), dtype=torch.uint8, device=gate_up.device)
+    N.check(N.lib().llmp_b200_moe_glu_quantize(gate_up.data_ptr(), gate_up.stride(0), f, rows, glu,
+                                               limit, out.data_ptr(), _stream()),
+            "llmp_b200_moe_glu_quantize")
+    return out
+
+
+def moe_combine(rows: torch.Tensor, position: torch.Tensor, weights: torch.Tensor, tokens: int,
+                used: int) -> torch.Tensor:
+    """MoeCombineSorted: rows F32 [slots, width] -> F32 [tokens, width]."""
+    _need(rows, torch.float32, "moe_combine rows")
+    _need(position, torch.int32, "moe_combine position")
+    _need(weights, torch.float32, "moe_combine weights")
+    width = rows.shape[1]
+    out = torch.empty((tokens, width), dtype=torch.float32, device=rows.device)
+    N.check(N.lib().llmp_b200_moe_combine(rows.data_ptr(), rows.stride(0), position.data_ptr(),
+                                          weights.data_ptr(), used, tokens, width, out.data_ptr(),
+                                          _stream()), "llmp_b200_moe_combine")
+    return out
+
+
+def moe_ffn(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, gate_up: torch.Tensor,
+            down: torch.Tensor, hidden: int, inter: int, glu: int = GLU_SWIGLU) -> torch.Tensor:
+    """The routed-expert block as the reference wires it (tests/unit/qwen38_moe_test.cc:487-497):
+    route -> quantize (scattered to expert-sorted rows) -> grouped GEMM gate|up -> GLU +
+    requantize -> grouped GEMM down -> ordered weighted combine.  x F32/BF16 [tokens, hidden];
+    ids I32 [tokens, used]; weights F32 [tokens, used]; gate_up Q4_K [experts, 2 inter, hidden]
+    (gate rows then up rows); down Q4_K [experts, hidden, inter].  Tokens of up to 16 take the
+    decode products (llmp.vecq routed) instead of the tensor-core GEMM."""
+    tokens, used = ids.shape
+    experts = gate_up.shape[0]
+    if tokens <= 16 and tokens * used <= 128:
+        q8 = quantize_q8(x.float())
+        gate_w = gate_up[:, :inter]
+        up_w = gate_up[:, inter:]
+        bpr = hidden // 256
+        h = vecq(up_w, TYPE_Q4_K, hidden, inter, q8, tokens, ids=ids, gate=gate_w, glu=glu,
+                 stride_row=bpr, stride_expert=2 * inter * bpr)
+        q8h = quantize_q8(h.view(tokens * used, inter))
+        y = vecq(down, TYPE_Q4_K, inter, hidden, q8h, tokens, ids=ids, per_slot=True)
+        position = torch.arange(tokens * used, dtype=torch.int32, device=x.device)
+        return moe_combine(y.view(tokens * used, hidden), position, weights.contiguous(), tokens,
+                           used)
+    route = moe_route(ids, experts)
+    slots = tokens * used
+    aq = mmq_quantize(x, ids_src=route["token"], cols=slots)
+    gu = grouped_gemm(gate_up, aq, route["offsets"], hidden, 2 * inter)
+    hq = moe_glu_quantize(gu, inter, glu)
+    y = grouped_gemm(down, hq, route["offsets"], inter, hidden)
+    return moe_combine(y, route["position"], weights.contiguous(), tokens, used)

@@ -1,0 +1,158 @@
+"""GPU parity of the routed-expert path against the CPU oracle through the C
+ABI: the counting sort (bit-exact), the grouped Q4_K GEMM over expert-sorted
+rows, GLU + requantization, the ordered combine (bit-exact), and the whole
+block at the MoE config's shape (128 experts, top-8, hidden 2048, expert
+intermediate 768; tests/unit/qwen38_moe_test.cc:427-611 is the model)."""
+import numpy as np
+import pytest
+
+from helpers import to_dev
+from llmp_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def _ops():
+    import llmp_b200
+    return llmp_b200
+
+
+@pytest.mark.parametrize("tokens,experts,used", [(1, 128, 8), (64, 128, 8), (200, 16, 4),
+                                                 (4096, 128, 8), (65, 7, 3)])
+def test_route_is_bit_exact(cuda, orc, tokens, experts, used):
+    torch = cuda
+    ops = _ops()
+    rng = np.random.default_rng(tokens + experts)
+    ids, _ = synth.topk_route(rng, tokens, experts, used)
+    if tokens > 2:
+        ids[1, 0] = -1
+        ids[2, used - 1] = experts        # ids outside the experts
+    got = ops.moe_route(to_dev(torch, ids), experts)
+    want = orc.moe_route(ids, experts)
+    valid = int(want["offsets"][-1])
+    for key in ("offsets", "scale_rows", "position", "counts"):
+        assert np.array_equal(got[key].cpu().numpy(), want[key]), key
+    assert np.array_equal(got["token"].cpu().numpy()[:valid], want["token"][:valid])
+    assert np.array_equal(got["expert"].cpu().numpy()[:valid], want["expert"][:valid])
+    assert (got["token"].cpu().numpy()[valid:] == 0).all()
+
+
+def test_combine_is_bit_exact(cuda, orc):
+    torch = cuda
+    ops = _ops()
+    rng = np.random.default_rng(8)
+    tokens, used, width = 37, 8, 256
+    rows = rng.normal(0, 1, size=(tokens * used, width)).astype(np.float32)
+    position = rng.permutation(tokens * used).astype(np.int32)
+    position[5] = -1
+    w = rng.uniform(0, 1, size=(tokens, used)).astype(np.float32)
+    got = ops.moe_combine(to_dev(torch, rows), to_dev(torch, position), to_dev(torch, w), tokens,
+                          used).cpu().numpy()
+    want = orc.moe_combine(rows, position, w, tokens, used)
+    assert np.array_equal(np.isnan(got), np.isnan(want))
+    assert np.array_equal(got[~np.isnan(want)], want[~np.isnan(want)])
+
+
+def test_grouped_gemm_matches_the_oracle(cuda, orc):
+    torch = cuda
+    ops = _ops()
+    rng = np.random.default_rng(9)
+    experts, used, tokens, n, k = 12, 3, 300, 256, 768
+    w = synth.q4_k_weights(rng, experts * n, k).reshape(experts, n, -1)
+    ids, _ = synth.topk_route(rng, tokens, experts, used)
+    ids[:, 0] = 5                                  # one crowded expert: several tiles
+    route = ops.moe_route(to_dev(torch, ids), experts)
+    x = rng.normal(0, 1, size=(tokens, k)).astype(np.float32)
+    aq = ops.mmq_quantize(to_dev(torch, x), ids_src=route["token"], cols=tokens * used)
+    buf = torch.full((tokens * used * n + 64,), float("nan"), device="cuda")
+    out = buf[: tokens * used * n].view(tokens * used, n)
+    ops.grouped_gemm(to_dev(torch, w), aq, route["offsets"], k, n, out=out)
+    torch.cuda.synchronize()
+    assert ops.device_faults() == 0
+    assert torch.isnan(buf[tokens * used * n:]).all()
+    bounds = route["offsets"].cpu().numpy()
+    want32, want64 = orc.mmq_q4_k(w, aq.cpu().numpy(), k, n, expert_bounds=bounds,
+                                  stride_expert=n * (k // 256), want64=True)
+    got = out.cpu().numpy().astype(np.float64)
+    assert np.isfinite(got).all()
+    assert np.abs(got - want64).max() <= 1e-5 * np.abs(want64).max()
+    assert ((got - want64) ** 2).sum() / (want64 ** 2).sum() <= 1e-10
+
+
+def test_glu_quantize_matches_quantizing_the_glu(cuda, orc):
+    torch = cuda
+    ops = _ops()
+    rng = np.random.default_rng(10)
+    rows, f = 70, 768
+    gu = rng.normal(0, 2, size=(rows, 2 * f)).astype(np.float32)
+    got = ops.moe_glu_quantize(to_dev(torch, gu), f, ops.GLU_SWIGLU).cpu().numpy()
+    h = np.array([[orc.glu(orc.GLU_SWIGLU, gu[r, j], gu[r, f + j]) for j in range(f)]
+                  for r in range(rows)], np.float32)
+    want = orc.quantize_mmq_q8_1(h)
+    assert got.shape == want.shape
+    # the device's expf and the host's differ in the last bits: codes may move by one,
+    # scales by one FP16 step
+    dq = got[:, :, 16:].view(np.int8).astype(int) - want[:, :, 16:].view(np.int8).astype(int)
+    assert np.abs(dq).max() <= 1 and (dq != 0).mean() < 1e-3
+    gh = got[:, :, :16].copy().view(np.float16).astype(np.float32)
+    wh = want[:, :, :16].copy().view(np.float16).astype(np.float32)
+    assert np.allclose(gh, wh, rtol=2e-3, atol=1e-6)
+
+
+def _oracle_moe(orc, x, ids, w, gate_up, down, hidden, inter, experts):
+    tokens, used = ids.shape
+    route = orc.moe_route(ids, experts)
+    slots = tokens * used
+    aq = orc.quantize_mmq_q8_1(x, ids_src=route["token"][:slots].clip(0), cols=slots)
+    gu = orc.mmq_q4_k(gate_up, aq, hidden, 2 * inter, expert_bounds=route["offsets"],
+                      stride_expert=2 * inter * (hidden // 256))
+    h = np.array([[orc.glu(orc.GLU_SWIGLU, gu[r, j], gu[r, inter + j]) for j in range(inter)]
+                  for r in range(slots)], np.float32)
+    hq = orc.quantize_mmq_q8_1(h)
+    y = orc.mmq_q4_k(down, hq, inter, hidden, expert_bounds=route["offsets"],
+                     stride_expert=hidden * (inter // 256))
+    return orc.moe_combine(y, route["position"], w, tokens, used)
+
+
+@pytest.mark.parametrize("tokens", [17, 64])
+def test_routed_expert_block_matches_the_oracle(cuda, orc, tokens):
+    torch = cuda
+    ops = _ops()
+    rng = np.random.default_rng(tokens)
+    experts, used, hidden, inter = 128, 8, 2048, 768
+    gate_up = synth.q4_k_weights(rng, experts * 2 * inter, hidden).reshape(experts, 2 * inter, -1)
+    down = synth.q4_k_weights(rng, experts * hidden, inter).reshape(experts, hidden, -1)
+    x = rng.normal(0, 1, size=(tokens, hidden)).astype(np.float32)
+    ids, w = synth.topk_route(rng, tokens, experts, used)
+    got = ops.moe_ffn(to_dev(torch, x), to_dev(torch, ids), to_dev(torch, w),
+                      to_dev(torch, gate_up), to_dev(torch, down), hidden, inter).cpu().numpy()
+    assert ops.device_faults() == 0
+    want = _oracle_moe(orc, x, ids, w, gate_up, down, hidden, inter, experts)
+    assert np.isfinite(got).all()
+    nmse = float(((got - want) ** 2).sum() / (want ** 2).sum())
+    assert nmse <= 1e-5, nmse
+
+
+def test_decode_tokens_take_the_vecq_products(cuda, orc):
+    """Up to 16 tokens: routed llmp.vecq with a fused GLU, per-slot down products, combine.
+    Q8_1 activations instead of Q8_1-MMQ ones: compared with the double product of the
+    dequantized weights at the bound the reference uses across formats (NMSE 3e-2)."""
+    torch = cuda
+    ops = _ops()
+    rng = np.random.default_rng(3)
+    experts, used, hidden, inter, tokens = 128, 8, 2048, 768, 1
+    gate_up = synth.q4_k_weights(rng, experts * 2 * inter, hidden).reshape(experts, 2 * inter, -1)
+    down = synth.q4_k_weights(rng, experts * hidden, inter).reshape(experts, hidden, -1)
+    x = rng.normal(0, 1, size=(tokens, hidden)).astype(np.float32)
+    ids, w = synth.topk_route(rng, tokens, experts, used)
+    got = ops.moe_ffn(to_dev(torch, x), to_dev(torch, ids), to_dev(torch, w),
+                      to_dev(torch, gate_up), to_dev(torch, down), hidden, inter).cpu().numpy()
+    ref = np.zeros((tokens, hidden))
+    for t in range(tokens):
+        for j in range(used):
+            e = ids[t, j]
+            gu = orc.dequant(orc.Q4_K, gate_up[e]).reshape(2 * inter, hidden).astype(np.float64)
+            dn = orc.dequant(orc.Q4_K, down[e]).reshape(hidden, inter).astype(np.float64)
+            g, u = gu[:inter] @ x[t], gu[inter:] @ x[t]
+            ref[t] += w[t, j] * (dn @ (g / (1 + np.exp(-g)) * u))
+    assert ((got - ref) ** 2).sum() / (ref ** 2).sum() <= 3e-2
