@@ -39,6 +39,9 @@ if ROOT not in sys.path:
 LAYERS = 34
 HIDDEN, INTER = 2560, 10240
 SB = 144  # Q4_K super-block bytes
+# dram__bytes_read.sum + dram__bytes_write.sum of one fused gate/up launch at batch 1
+# (profiles/vecq_rowlane_glu_b1.md): the matrices' 29,491,200 bytes plus activations.
+NCU_GLU_DRAM_BYTES_B1 = 29532928
 METRIC = "q4k_decode_gemv_hbm_throughput"
 UNIT = "GB/s"
 
@@ -231,9 +234,11 @@ class FfnStep:
         else:
             h = self.h_shard
         ops.quantize_q8(h, out=self.q8h)
-        ops.vecq(down, T, INTER, self.n_down, self.q8h, self.batch, out=self.y_shard)
         if self.world > 1:
+            ops.vecq(down, T, INTER, self.n_down, self.q8h, self.batch, out=self.y_shard)
             self.dist.all_gather_into_tensor(self.y_full[l], self.y_shard)
+        else:
+            ops.vecq(down, T, INTER, self.n_down, self.q8h, self.batch, out=self.y_full[l, 0])
 
     def step(self, x_all=None):
         x_all = self.x if x_all is None else x_all
@@ -301,14 +306,28 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
         e1.record(stream)
         barrier()
         ms = e0.elapsed_time(e1) / args.steps
-        # ---- the dominant kernel alone (roofline): events around back-to-back launches
+        # ---- the dominant kernel alone (roofline): one launch per layer copy, replayed
+        # as a CUDA graph so the host's launch rate is not what is timed; CUDA events
+        # on the launching stream around the replays
         st.glu_only()
         sync()
+        glu_graph = None
+        if world == 1 and not args.no_graph:
+            try:
+                glu_graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(glu_graph, stream=stream):
+                    st.glu_only()
+            except Exception:
+                glu_graph = None
+                sync()
+        run_glu = glu_graph.replay if glu_graph is not None else st.glu_only
+        run_glu()
+        sync()
         k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        reps = 5
+        reps = 10
         k0.record(stream)
         for _ in range(reps):
-            st.glu_only()
+            run_glu()
         k1.record(stream)
         sync()
         glu_us = 1e3 * k0.elapsed_time(k1) / (reps * LAYERS)
@@ -317,21 +336,35 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
         hy = torch.empty((LAYERS, world, batch, st.n_down)).pin_memory()
         dx = torch.empty_like(st.x)
 
-        def e2e_step():
+        def e2e_body():
             dx.copy_(hx, non_blocking=True)
-            st.step(dx)
+            for l in range(LAYERS):
+                st.layer(l, dx[l])
             hy.copy_(st.y_full, non_blocking=True)
+
+        # The step as a caller would queue it: pinned-host input copy, the C-ABI
+        # launches, pinned-host output copy, all captured once and replayed (the
+        # reference replays captured steps too, src/engine/step_runs.cc:323).
+        e2e_graph = None
+        if world == 1 and not args.no_graph:
+            try:
+                e2e_body()
+                sync()
+                e2e_graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(e2e_graph, stream=stream):
+                    e2e_body()
+            except Exception as e:
+                print(f"bench.py: e2e graph capture unavailable ({e})", file=sys.stderr)
+                e2e_graph = None
+                sync()
+
+        def e2e_step():
+            if e2e_graph is not None:
+                e2e_graph.replay()
+            else:
+                e2e_body()
             stream.synchronize()
 
-        if world == 1:
-            # y_full is filled by the all-gather only when sharded; single GPU copies the shard out
-            def e2e_step():  # noqa: F811
-                dx.copy_(hx, non_blocking=True)
-                for l in range(LAYERS):
-                    st.layer(l, dx[l])
-                    st.y_full[l, 0].copy_(st.y_shard, non_blocking=True)
-                hy.copy_(st.y_full, non_blocking=True)
-                stream.synchronize()
         for _ in range(3):
             e2e_step()
         barrier()
@@ -374,6 +407,9 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
             },
             "e2e": {"value": round(sb / (e2e_ms * 1e-3) / 1e9, 2), "unit": UNIT,
                     "ms_per_step": round(e2e_ms, 4),
+                    "how": "host wall clock around pinned H2D of x, the step's C-ABI launches and "
+                           "pinned D2H of y, with a stream synchronize per step"
+                           + (" (captured once, replayed)" if e2e_graph is not None else ""),
                     "h2d_bytes_per_step": LAYERS * batch * HIDDEN * 4,
                     "d2h_bytes_per_step": LAYERS * batch * HIDDEN * 4},
             "gpu_launches": st.launches_per_step * args.steps,
@@ -384,7 +420,8 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
                          else "fallback 6650",
                          "us_per_launch": round(glu_us, 3), "bytes_per_launch": glu_b,
                          "frac_of_8tbs_spec": round(achieved / 8000.0, 4),
-                         "traffic": args.traffic},
+                         "traffic": args.traffic if args.traffic is not None else
+                         (NCU_GLU_DRAM_BYTES_B1 if batch == 1 and world == 1 else None)},
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu:
@@ -409,7 +446,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--traffic", type=float, default=None,
-                    help="dram bytes per launch of the dominant kernel from an ncu capture")
+                    help="dram bytes per launch of the dominant kernel from an ncu capture "
+                         "(default: the figure in profiles/vecq_rowlane_glu_b1.md at batch 1)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
