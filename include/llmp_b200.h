@@ -191,6 +191,25 @@ int llmp_b200_grouped_gemm_available(void);
 size_t llmp_b200_grouped_gemm_scratch(int groups, int rows, int sms);
 int llmp_b200_grouped_gemm(const llmp_b200_grouped_gemm_desc* gemm, int sms, void* stream);
 
+/* No counterpart in the reference.  The grouped GEMM for callers that have no
+ * way to hand over scratch: code running where device allocation is off the
+ * table (a latency-critical serving loop that must never take the allocator's
+ * device-wide synchronization, a host that pre-sized all of its memory and has
+ * none left to carve a work area from, a plug-in boundary whose contract
+ * forbids the callee's caller from allocating on its behalf).  It is
+ * llmp_b200_grouped_gemm with the tile list kept in a 6,400-byte array built
+ * into the library's device image instead of `scratch` (which is ignored and
+ * may be NULL).  It calls no allocator of any kind.
+ *   - Limits: at most 256 groups and 65,536 sorted rows; larger problems are
+ *     refused (status > 0) with a message naming the limits.
+ *   - The first call on each device looks the array's device address up
+ *     (cudaGetSymbolAddress); make that first call before starting any stream
+ *     capture.
+ *   - All calls on a device share the one array: two calls whose kernels may
+ *     overlap on the GPU (different streams, no ordering) race on it.  Calls
+ *     ordered on one stream are safe; each rebuilds the list it uses. */
+int llmp_b200_grouped_gemm_static(const llmp_b200_grouped_gemm_desc* gemm, int sms, void* stream);
+
 /* Replaces llmp.moe.glu_quantize (llmp_moe.cu:348-392) for this build's
  * activation format: gate_up F32 [2 f, rows] (gate then up in a row); out:
  * Q8_1-MMQ blocks [f / 128][rows] of glu(gate, up). */

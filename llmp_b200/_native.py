@@ -80,6 +80,7 @@ SIGNATURES = {
     "llmp_b200_grouped_gemm_available": (C.c_int, []),
     "llmp_b200_grouped_gemm_scratch": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
     "llmp_b200_grouped_gemm": (C.c_int, [C.POINTER(GroupedGemmDesc), C.c_int, C.c_void_p]),
+    "llmp_b200_grouped_gemm_static": (C.c_int, [C.POINTER(GroupedGemmDesc), C.c_int, C.c_void_p]),
     "llmp_b200_moe_glu_quantize": (C.c_int, [C.c_void_p, C.c_int64, C.c_int, C.c_int64, C.c_int,
                                              C.c_float, C.c_void_p, C.c_void_p]),
     "llmp_b200_moe_combine": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int,

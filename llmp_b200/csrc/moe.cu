@@ -268,6 +268,38 @@ llmp_b200_mmq_desc MmqOf(const llmp_b200_grouped_gemm_desc& g) {
 
 int TileCapacity(int groups, int rows) { return ((rows + kMmqTileCols - 1) / kMmqTileCols) + groups; }
 
+// ---- the tile list of llmp_b200_grouped_gemm_static --------------------------
+// Sized for the largest problem that entry point takes: 256 groups over 65,536
+// sorted rows is at most 512 + 256 tiles.  Every GPU that loads the library
+// holds these 6,400 bytes until the process exits.
+constexpr int kStaticMaxGroups = 256;
+constexpr int kStaticMaxRows = 65536;
+constexpr int kStaticMaxTiles = (kStaticMaxRows / kMmqTileCols) + kStaticMaxGroups;
+static __device__ __align__(256) std::int32_t g_static_tiles[1 + (2 * kStaticMaxTiles) + 63];
+
+// The array's DEVICE address on the current device.  `g_static_tiles` named in
+// host code is only the host-side handle of the symbol, never an address a
+// kernel may dereference; the runtime translates it, once per device, with
+// that device current.
+std::int32_t* StaticTiles() {
+  constexpr int kMaxDevices = 64;
+  static std::int32_t* table[kMaxDevices] = {};
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  if (table[device] == nullptr) {
+    void* address = nullptr;
+    if (cudaGetSymbolAddress(&address, g_static_tiles) != cudaSuccess || address == nullptr) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    table[device] = static_cast<std::int32_t*>(address);  // the same value whoever stores it
+  }
+  return table[device];
+}
+
 }  // namespace
 }  // namespace llmp_b200
 
@@ -322,6 +354,32 @@ int llmp_b200_grouped_gemm(const llmp_b200_grouped_gemm_desc* gemm, int sms, voi
   const int status = LaunchMmq(MmqOf(g), worklist, capacity, stream);
   // The tile list is queued: a refusal now would leave work behind, so report
   // it as a failure after queueing.
+  return status > 0 ? -status : status;
+}
+
+int llmp_b200_grouped_gemm_static(const llmp_b200_grouped_gemm_desc* gemm, int sms, void* stream) {
+  using namespace llmp_b200;
+  (void)sms;
+  if (gemm == nullptr) return Reject("grouped_gemm_static: null descriptor");
+  const llmp_b200_grouped_gemm_desc& g = *gemm;
+  if (const int status = CheckGrouped(g); status != 0) return status;
+  if (g.groups > kStaticMaxGroups || g.rows > kStaticMaxRows) {
+    return Reject("grouped_gemm_static: %d groups over %d rows is beyond the built-in tile list "
+                  "(at most %d groups, %d rows); use llmp_b200_grouped_gemm with caller scratch",
+                  g.groups, g.rows, kStaticMaxGroups, kStaticMaxRows);
+  }
+  if (const int status = DeviceStatus(); status != 0) return status;
+  std::int32_t* worklist = StaticTiles();  // first call on a device resolves the address
+  if (worklist == nullptr) {
+    return Reject("grouped_gemm_static: the runtime gave no device address for the tile list");
+  }
+  const int capacity = TileCapacity(g.groups, g.rows);
+  // BuildTiles rewrites the count and every entry it will hand out, so nothing
+  // of an earlier call's list needs clearing.
+  BuildTiles<<<1, 256, (g.groups + 1) * sizeof(int), static_cast<cudaStream_t>(stream)>>>(
+      g.offsets, g.groups, capacity, worklist);
+  if (const int status = Launched("grouped_gemm_static tile list"); status != 0) return status;
+  const int status = LaunchMmq(MmqOf(g), worklist, capacity, stream);
   return status > 0 ? -status : status;
 }
 
