@@ -46,11 +46,11 @@ METRIC = "q4k_decode_gemv_hbm_throughput"
 UNIT = "GB/s"
 
 
-def step_bytes(batch: int, layers: int = LAYERS) -> int:
+def step_bytes(batch: int, layers: int | None = None) -> int:
     """Algorithmic bytes of one step: every operand once."""
     glu = 2 * INTER * (HIDDEN // 256) * SB + batch * (HIDDEN // 32 * 36) + batch * INTER * 4
     down = HIDDEN * (INTER // 256) * SB + batch * (INTER // 32 * 36) + batch * HIDDEN * 4
-    return layers * (glu + down)
+    return (LAYERS if layers is None else layers) * (glu + down)
 
 
 def glu_launch_bytes(batch: int, shard: int = 1) -> int:
@@ -131,7 +131,7 @@ def run_reference(args, rank: int):
         "ms_per_step": round(1e3 * statistics.mean(per_step), 3), "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "int8 dp4a -> int32 per block, f32 sums",
         "data": "synthetic",
-        "config": {"workload": f"Gemma-3-4B FFN decode products, Q4_K, 34 layers, batch {batch}",
+        "config": {"workload": f"Gemma-3-4B FFN decode products, Q4_K, {LAYERS} layers, batch {batch}",
                    "batch": batch, "timing": "host wall clock; weights beyond the CPU cache"},
         "cpu_baseline": {"value": round(value, 3), "unit": UNIT, "cores": threads, "kind": "port",
                          "sample": text},
@@ -396,10 +396,11 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "int8 dp4a -> int32 per block, f32 sums", "data": "synthetic",
             "config": {
-                "workload": f"Gemma-3-4B FFN decode products, Q4_K, 34 layers, batch {batch}",
+                "workload": f"Gemma-3-4B FFN decode products, Q4_K, {LAYERS} layers, batch {batch}",
                 "batch": batch, "layers": LAYERS, "gate_up": [INTER, HIDDEN],
                 "down": [HIDDEN, INTER],
-                "l2": "inputs larger than L2: 34 distinct layer copies, 1.5 GB, streamed in order",
+                "l2": f"inputs larger than L2: {LAYERS} distinct layer copies, "
+                      f"{LAYERS * 44.2e-3:.2f} GB, streamed in order",
                 "launch": "cuda graph replay" if graph is not None else "stream launches",
                 "parallelism": "single GPU" if world == 1 else f"N-column shards x{world}, "
                                "NCCL all-gather of the GLU output and of the layer output",
@@ -436,24 +437,132 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------- other configs
+def run_other(args):
+    """The other BASELINE configs' kernels, one JSON line each (not the headline
+    bench line; parity cases that also serve as small, committed ncu drivers).
+    Operands rotate over two copies so that a launch's inputs are not L2-resident."""
+    import torch
+
+    torch.cuda.set_device(0)
+    import llmp_b200 as ops
+    if not ops.available():
+        raise SystemExit("bench.py: no B200 / native library: " + ops._native.last_error())
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(0)
+    peaks = {"mxf8f6f4": 4466.5, "i8": 4567.3}  # profiles/tcgen05_issue_peaks.md
+
+    def timed(fns, steps, warmup):
+        for i in range(max(warmup, 3)):
+            fns[i % len(fns)]()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fns[i % len(fns)]()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    if args.workload == "mxfp8_gemm":
+        m, n, k = args.m or 2048, 12288, 4096
+        x = torch.randn((m, k), device="cuda", generator=gen).bfloat16()
+        a, a_s = ops.mxfp8_quantize(x)
+        sets = []
+        for _ in range(2):
+            w = torch.randn((n, k), device="cuda", generator=gen) * 0.02
+            b, bs = ops.mxfp8_quantize(w)
+            sets.append((b, bs, torch.empty((m, n), dtype=torch.bfloat16, device="cuda")))
+        fns = [lambda t=t: ops.mxfp8_gemm(a, a_s, t[0], t[1], bf16=True, out=t[2]) for t in sets]
+        ms = timed(fns, args.steps, args.warmup)
+        rate = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+        line = {"metric": "mxfp8_gemm_throughput", "value": round(rate, 1), "unit": "TFLOP/s",
+                "ms_per_step": round(ms, 5),
+                "config": {"workload": f"MXFP8 block-scaled GEMM M {m} K {k} N {n}, BF16 out"},
+                "roofline": {"bound": "tensor", "achieved": round(rate, 1),
+                             "peak": peaks["mxf8f6f4"], "unit": "TFLOP/s",
+                             "frac": round(rate / peaks["mxf8f6f4"], 4),
+                             "peak_source": "bare tcgen05.mma loop on this pool "
+                                            "(profiles/tcgen05_issue_peaks.md)"}}
+    elif args.workload == "mmq_q4k":
+        m, n, k = args.m or 4096, 14336, 4096
+        x = torch.randn((m, k), device="cuda", generator=gen).bfloat16()
+        yq = ops.mmq_quantize(x)
+        sets = [(make_q4k_device(torch, n, k, gen), torch.empty((m, n), device="cuda"))
+                for _ in range(2)]
+        fns = [lambda t=t: ops.mmq(t[0], yq, k, n, out=t[1]) for t in sets]
+        ms = timed(fns, args.steps, args.warmup)
+        rate = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+        line = {"metric": "mmq_q4k_int8_gemm_throughput", "value": round(rate, 1), "unit": "TOP/s",
+                "ms_per_step": round(ms, 5),
+                "config": {"workload": f"Q4_K x Q8_1-MMQ int8 GEMM M {m} K {k} N {n}"},
+                "roofline": {"bound": "tensor", "achieved": round(rate, 1), "peak": peaks["i8"],
+                             "unit": "TOP/s", "frac": round(rate / peaks["i8"], 4),
+                             "peak_source": "bare tcgen05.mma loop on this pool "
+                                            "(profiles/tcgen05_issue_peaks.md)"}}
+    else:  # moe
+        import numpy as np
+
+        from llmp_b200 import synth
+        tokens = args.m or 4096
+        experts, used, hidden, inter = 128, 8, 2048, 768
+        gate_up = make_q4k_device(torch, experts * 2 * inter, hidden, gen).view(experts, 2 * inter, -1)
+        down = make_q4k_device(torch, experts * hidden, inter, gen).view(experts, hidden, -1)
+        ids, w = synth.topk_route(np.random.default_rng(0), tokens, experts, used)
+        ids_d, w_d = torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda()
+        x = torch.randn((tokens, hidden), device="cuda", generator=gen)
+        fns = [lambda: ops.moe_ffn(x, ids_d, w_d, gate_up, down, hidden, inter)]
+        ms = timed(fns, args.steps, args.warmup)
+        distinct = int(np.unique(ids).size)
+        if tokens <= 16:
+            nbytes = distinct * 2654208
+            line = {"metric": "moe_decode_hbm_throughput", "unit": "GB/s",
+                    "value": round(nbytes / (ms * 1e-3) / 1e9, 1)}
+        else:
+            ops_count = 3 * 2.0 * hidden * inter * tokens * used
+            line = {"metric": "moe_grouped_gemm_throughput", "unit": "TOP/s",
+                    "value": round(ops_count / (ms * 1e-3) / 1e12, 1)}
+        line.update({"ms_per_step": round(ms, 5),
+                     "config": {"workload": f"MoE block, 128 experts top-8, hidden 2048, "
+                                            f"intermediate 768, Q4_K, {tokens} tokens "
+                                            f"({distinct} distinct experts)"}})
+    line.update({"n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+                 "higher_is_better": True, "data": "synthetic", "vs_baseline": None,
+                 "faults": ops.device_faults()})
+    print(json.dumps(line), flush=True)
+
+
 def main():
+    global LAYERS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--batch", type=int, default=1, choices=[1, 2, 4, 8])
     ap.add_argument("--impl", default="llmp_b200", choices=["llmp_b200", "reference"])
+    ap.add_argument("--layers", type=int, default=34,
+                    help="distinct layer copies a step walks (34: the model's; fewer for a small "
+                         "ncu capture, keep >= 4 so the weights exceed L2)")
+    ap.add_argument("--workload", default="ffn_q4k",
+                    choices=["ffn_q4k", "mxfp8_gemm", "mmq_q4k", "moe"],
+                    help="ffn_q4k is the bench line; the others time the other configs' kernels")
+    ap.add_argument("--m", type=int, default=0, help="tokens / rows of the other workloads")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--traffic", type=float, default=None,
                     help="dram bytes per launch of the dominant kernel from an ncu capture "
                          "(default: the figure in profiles/vecq_rowlane_glu_b1.md at batch 1)")
     args = ap.parse_args()
+    LAYERS = args.layers
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.workload != "ffn_q4k":
+        if rank == 0:
+            run_other(args)
         return
     run_gpu(args, rank, world, local_rank)
 
