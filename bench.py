@@ -532,6 +532,68 @@ def run_other(args):
     print(json.dumps(line), flush=True)
 
 
+def run_moe_ep(args, rank: int, world: int, local_rank: int):
+    """Expert-parallel MoE block: each rank owns 128 / world whole experts and `--m` tokens
+    (weak scaling); rows travel to their experts' owners and back with NCCL all-to-all
+    (llmp_b200/shard.py) and are combined on the home rank in slot order."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    torch.cuda.set_device(local_rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    import llmp_b200 as ops
+    from llmp_b200 import shard, synth
+    tokens = args.m or 4096
+    experts, used, hidden, inter = 128, 8, 2048, 768
+    b, e = shard.expert_range(experts, world, rank)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(100 + rank)
+    gate_up = make_q4k_device(torch, (e - b) * 2 * inter, hidden, gen).view(e - b, 2 * inter, -1)
+    down = make_q4k_device(torch, (e - b) * hidden, inter, gen).view(e - b, hidden, -1)
+    ids, w = synth.topk_route(np.random.default_rng(rank), tokens, experts, used)
+    ids_d, w_d = torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda()
+    x = torch.randn((tokens, hidden), device="cuda", generator=gen)
+
+    def local(rows, local_ids):
+        ones = torch.ones((rows.shape[0], 1), device=rows.device)
+        return ops.moe_ffn(rows, local_ids.view(-1, 1).contiguous(), ones, gate_up, down, hidden,
+                           inter)
+
+    def step():
+        return shard.ep_moe_ffn(x, ids_d, w_d, experts, local)
+
+    for _ in range(max(args.warmup, 3)):
+        out = step()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        out = step()
+    e1.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ok = torch.tensor([float(torch.isfinite(out).all())], device="cuda")
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        ms = float(t.item())
+        ops_count = 3 * 2.0 * hidden * inter * tokens * used * world
+        print(json.dumps({
+            "metric": "moe_grouped_gemm_throughput", "unit": "TOP/s",
+            "value": round(ops_count / (ms * 1e-3) / 1e12, 1), "ms_per_step": round(ms, 4),
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "higher_is_better": True, "scaling": "weak", "data": "synthetic", "vs_baseline": None,
+            "finite": bool(ok.item()), "faults": ops.device_faults(),
+            "config": {"workload": f"MoE block, 128 experts top-8, hidden 2048, intermediate 768, "
+                                   f"Q4_K, {tokens} tokens a rank",
+                       "parallelism": f"expert parallel x{world}, NCCL all-to-all dispatch and "
+                                      "combine, tokens data-parallel"}}), flush=True)
+    dist.destroy_process_group()
+
+
 def main():
     global LAYERS
     ap = argparse.ArgumentParser()
@@ -559,6 +621,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.workload == "moe" and world > 1:
+        run_moe_ep(args, rank, world, local_rank)
         return
     if args.workload != "ffn_q4k":
         if rank == 0:
