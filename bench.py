@@ -281,6 +281,8 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
         st.step()       # warm: module load, attributes
         sync()
         graph = None
+        # Graph replay on one GPU only: a step with NCCL collectives is queued as
+        # plain stream launches.
         if world == 1 and not args.no_graph:
             try:
                 graph = torch.cuda.CUDAGraph()
@@ -465,7 +467,7 @@ def run_other(args):
         return e0.elapsed_time(e1) / steps
 
     if args.workload == "mxfp8_gemm":
-        m, n, k = args.m or 2048, 12288, 4096
+        m, n, k = args.tokens or 2048, 12288, 4096
         x = torch.randn((m, k), device="cuda", generator=gen).bfloat16()
         a, a_s = ops.mxfp8_quantize(x)
         sets = []
@@ -485,7 +487,7 @@ def run_other(args):
                              "peak_source": "bare tcgen05.mma loop on this pool "
                                             "(profiles/tcgen05_issue_peaks.md)"}}
     elif args.workload == "mmq_q4k":
-        m, n, k = args.m or 4096, 14336, 4096
+        m, n, k = args.tokens or 4096, 14336, 4096
         x = torch.randn((m, k), device="cuda", generator=gen).bfloat16()
         yq = ops.mmq_quantize(x)
         sets = [(make_q4k_device(torch, n, k, gen), torch.empty((m, n), device="cuda"))
@@ -504,7 +506,7 @@ def run_other(args):
         import numpy as np
 
         from llmp_b200 import synth
-        tokens = args.m or 4096
+        tokens = args.tokens or 4096
         experts, used, hidden, inter = 128, 8, 2048, 768
         gate_up = make_q4k_device(torch, experts * 2 * inter, hidden, gen).view(experts, 2 * inter, -1)
         down = make_q4k_device(torch, experts * hidden, inter, gen).view(experts, hidden, -1)
@@ -533,7 +535,7 @@ def run_other(args):
 
 
 def run_moe_ep(args, rank: int, world: int, local_rank: int):
-    """Expert-parallel MoE block: each rank owns 128 / world whole experts and `--m` tokens
+    """Expert-parallel MoE block: each rank owns 128 / world whole experts and `--tokens` tokens
     (weak scaling); rows travel to their experts' owners and back with NCCL all-to-all
     (llmp_b200/shard.py) and are combined on the home rank in slot order."""
     import numpy as np
@@ -544,7 +546,7 @@ def run_moe_ep(args, rank: int, world: int, local_rank: int):
     dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     import llmp_b200 as ops
     from llmp_b200 import shard, synth
-    tokens = args.m or 4096
+    tokens = args.tokens or 4096
     experts, used, hidden, inter = 128, 8, 2048, 768
     b, e = shard.expert_range(experts, world, rank)
     gen = torch.Generator(device="cuda")
@@ -608,7 +610,8 @@ def main():
     ap.add_argument("--workload", default="ffn_q4k",
                     choices=["ffn_q4k", "mxfp8_gemm", "mmq_q4k", "moe"],
                     help="ffn_q4k is the bench line; the others time the other configs' kernels")
-    ap.add_argument("--m", type=int, default=0, help="tokens / rows of the other workloads")
+    ap.add_argument("--tokens", type=int, default=0,
+                    help="tokens / rows of the other workloads")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--traffic", type=float, default=None,
