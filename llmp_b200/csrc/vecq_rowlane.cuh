@@ -3,12 +3,12 @@
 // (src/kernels/ggml/vecq.h:23-49, vecq.cu:457-665); the structure is B200's.
 //
 //   * One CTA per SM owns a contiguous, evenly divided range of output rows;
-//     its W warps split that range, R rows a warp (R a power of two <= 32).
-//   * A lane is (row r, phase ph), PH = 32 / R phases.  The warp sweeps the
+//     its W warps split that range, R rows a warp.
+//   * A lane is (row r, phase ph), R * PH <= 32 (6 x 5 for k = 2560: ten
+//     super-blocks a row in two steps of five).  The warp sweeps the
 //     row's super-blocks ("columns") PH at a time; lane (r, ph) decodes column
 //     j * PH + ph of row r.  A lane therefore accumulates its row's whole dot
-//     product in registers; the PH phases meet in a fixed xor-shuffle tree at
-//     the end.  No atomics, no cross-warp traffic, and a (token, row) sum does
+//     product in registers; the PH phases meet in phase order at the end.  No atomics, no cross-warp traffic, and a (token, row) sum does
 //     not depend on the other tokens of the launch.
 //   * Weights reach shared memory through the TMA bulk-copy engine: for every
 //     column step each row's PH consecutive super-blocks (PH * 144 bytes) are
@@ -39,8 +39,8 @@ constexpr int kRowLaneMaxStages = 8;
 
 struct RowLanePlan {
   int warps;         // W
-  int rows;          // R rows a warp (power of two)
-  int phases;        // PH = 32 / R
+  int rows;          // R rows a warp
+  int phases;        // PH phases, R * PH <= 32
   int columns;       // UR = k / 256
   int steps;         // J = ceil(UR / PH)
   int stages;        // S_w, ring depth a warp
@@ -50,6 +50,7 @@ struct RowLanePlan {
   int smem_bytes;
   int grid;
   int half;          // the kHalf instantiation
+  double score;      // the planner's figure of merit (lane use x warps x ring depth)
   unsigned int* faults;
 };
 
@@ -72,6 +73,7 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
   const int UR = plan.columns;
   const int J = plan.steps;
   const int S = plan.stages;
+  // Lanes R * PH and up (when R * PH < 32) idle through the column steps.
   const int r = lane % R;
   const int ph = lane / R;
 
@@ -172,7 +174,7 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
     }
     __syncwarp();
     const int c = (j * PH) + ph;
-    if (c < UR && r < my_rows) {
+    if (ph < PH && c < UR && r < my_rows) {
       const unsigned char* base = ring + (static_cast<std::size_t>(s) * plan.stage_bytes);
       const uint4* act_q[P];  // this column's first chunk, per token
 #pragma unroll
@@ -209,25 +211,27 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
             const uint4* q = act_q[t] + ((4 * cc) * UR);
             const uint4 a0 = q[0], a1 = q[UR];
             const uint4 a2 = q[2 * UR], a3 = q[3 * UR];
-            int d0 = 0, d1 = 0;
+            // Two short chains per sub-block instead of one of eight: integer
+            // sums, so the grouping changes no bit.
+            int d0 = 0, e0 = 0, d1 = 0, e1 = 0;
             d0 = Dp4aU8S8(lo[0], static_cast<int>(a0.x), d0);
-            d0 = Dp4aU8S8(lo[1], static_cast<int>(a0.y), d0);
-            d0 = Dp4aU8S8(lo[2], static_cast<int>(a0.z), d0);
-            d0 = Dp4aU8S8(lo[3], static_cast<int>(a0.w), d0);
-            d0 = Dp4aU8S8(lo[4], static_cast<int>(a1.x), d0);
-            d0 = Dp4aU8S8(lo[5], static_cast<int>(a1.y), d0);
-            d0 = Dp4aU8S8(lo[6], static_cast<int>(a1.z), d0);
-            d0 = Dp4aU8S8(lo[7], static_cast<int>(a1.w), d0);
+            e0 = Dp4aU8S8(lo[4], static_cast<int>(a1.x), e0);
             d1 = Dp4aU8S8(hi[0], static_cast<int>(a2.x), d1);
+            e1 = Dp4aU8S8(hi[4], static_cast<int>(a3.x), e1);
+            d0 = Dp4aU8S8(lo[1], static_cast<int>(a0.y), d0);
+            e0 = Dp4aU8S8(lo[5], static_cast<int>(a1.y), e0);
             d1 = Dp4aU8S8(hi[1], static_cast<int>(a2.y), d1);
+            e1 = Dp4aU8S8(hi[5], static_cast<int>(a3.y), e1);
+            d0 = Dp4aU8S8(lo[2], static_cast<int>(a0.z), d0);
+            e0 = Dp4aU8S8(lo[6], static_cast<int>(a1.z), e0);
             d1 = Dp4aU8S8(hi[2], static_cast<int>(a2.z), d1);
+            e1 = Dp4aU8S8(hi[6], static_cast<int>(a3.z), e1);
+            d0 = Dp4aU8S8(lo[3], static_cast<int>(a0.w), d0);
+            e0 = Dp4aU8S8(lo[7], static_cast<int>(a1.w), e0);
             d1 = Dp4aU8S8(hi[3], static_cast<int>(a2.w), d1);
-            d1 = Dp4aU8S8(hi[4], static_cast<int>(a3.x), d1);
-            d1 = Dp4aU8S8(hi[5], static_cast<int>(a3.y), d1);
-            d1 = Dp4aU8S8(hi[6], static_cast<int>(a3.z), d1);
-            d1 = Dp4aU8S8(hi[7], static_cast<int>(a3.w), d1);
-            dots[t][2 * cc] = d0;
-            dots[t][(2 * cc) + 1] = d1 >> 4;
+            e1 = Dp4aU8S8(hi[7], static_cast<int>(a3.w), e1);
+            dots[t][2 * cc] = d0 + e0;
+            dots[t][(2 * cc) + 1] = (d1 + e1) >> 4;
           }
         }
         // d * sum_g d8_g * (sc_g * dot_g)  -  dmin * sum_g (d8_g * sum q_g) * m_g
@@ -256,15 +260,15 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
     }
   }
 
-  // The phases of a row meet: lanes r, r + R, r + 2R, ...
+  // The phases of a row meet in phase order: lane r adds lanes r + R, r + 2R, ...
 #pragma unroll
   for (int t = 0; t < P; ++t) {
     float v[kMats];
 #pragma unroll
     for (int m = 0; m < kMats; ++m) {
       v[m] = acc[t][m];
-      for (int offset = 16; offset >= R; offset >>= 1) {
-        v[m] += __shfl_xor_sync(0xffffffffu, v[m], offset);
+      for (int k = 1; k < PH; ++k) {
+        v[m] += __shfl_sync(0xffffffffu, acc[t][m], (r + (k * R)) & 31);
       }
     }
     if (ph == 0 && r < my_rows && t < a.tokens) {
@@ -292,17 +296,35 @@ inline bool PlanRowLane(const Desc& d, int p, int sms, int force_rows, bool half
   if (budget <= 0) return false;
   double best_score = -1.0;
   RowLanePlan best{};
-  for (int rows = 1; rows <= 32; rows *= 2) {
+  for (int rows = 1; rows <= 32; ++rows) {
     if (force_rows > 0 && rows != force_rows) continue;
     const int warps = (cta_rows + rows - 1) / rows;
     if (warps < 1 || warps > max_warps) continue;
-    const int phases = 32 / rows;
+    for (int phases = 1; phases <= 32 / rows; ++phases) {
     const int steps = (ur + phases - 1) / phases;
-    // pitch / 16 must be congruent to 8 / min(rows, 8) (mod 8) times an odd number
-    const int rq = std::min(rows, 8);
+    // The pitch between a stage's rows: the pad (in 16-byte units) that leaves the
+    // fewest quarter-warp bank-group collisions for 128-bit loads, lane (r, ph)
+    // reading at r * pitch + ph * 144.
     int pitch16 = phases * 9;
-    const int want = 8 / rq;  // 1, 2, 4 or 8
-    while ((pitch16 % (2 * want)) != (want % (2 * want))) ++pitch16;
+    {
+      int best_pad = 0, best_hits = 1 << 30;
+      for (int pad = 0; pad < 8; ++pad) {
+        int hits = 0;
+        for (int q = 0; q < 4; ++q) {
+          int seen[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+          for (int l = 8 * q; l < (8 * q) + 8; ++l) {
+            if (l >= rows * phases) continue;
+            const int bank = ((l % rows) * (pitch16 + pad) + (l / rows) * 9) % 8;
+            hits += seen[bank]++;
+          }
+        }
+        if (hits < best_hits) {
+          best_hits = hits;
+          best_pad = pad;
+        }
+      }
+      pitch16 += best_pad;
+    }
     const int pitch = pitch16 * 16;
     const int stage_bytes = rows * pitch * mats;
     int stages = std::min({steps, kRowLaneMaxStages, budget / (warps * stage_bytes)});
@@ -310,8 +332,9 @@ inline bool PlanRowLane(const Desc& d, int p, int sms, int force_rows, bool half
     if (stages < steps && stages < 2) continue;
     // Lane utilization, with a preference for more warps and for a ring that
     // holds the whole range.
+    // (all 32 lanes of every warp count: lanes past R * PH idle)
     const double lanes = static_cast<double>(cta_rows) * ur /
-                         (static_cast<double>(warps) * rows * steps * phases);
+                         (static_cast<double>(warps) * 32 * steps);
     const double score = lanes * (0.6 + 0.4 * std::min(1.0, warps / 8.0)) *
                          (0.7 + 0.3 * static_cast<double>(stages) / steps);
     if (score > best_score) {
@@ -328,6 +351,8 @@ inline bool PlanRowLane(const Desc& d, int p, int sms, int force_rows, bool half
       best.smem_bytes = (p * acts_bytes) + (warps * stages * stage_bytes);
       best.grid = grid;
       best.half = half ? 1 : 0;
+      best.score = score;
+    }
     }
   }
   if (best_score < 0.0) return false;

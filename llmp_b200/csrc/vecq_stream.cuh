@@ -71,6 +71,7 @@ __device__ __forceinline__ bool MbarWait(std::uint64_t* bar, std::uint32_t parit
         : "r"(addr), "r"(parity)
         : "memory");
     if (done) return true;
+    if (i > 4) __nanosleep(40);  // leave the issue slots to the warps that have data
   }
   return false;
 }

@@ -158,11 +158,15 @@ def test_fused_glu_equals_glu_of_the_unfused_products(cuda, orc, wtype, n, k, to
     g = ops.vecq(dgate, t, k, n, q8, tokens).cpu().numpy()
     want = np.array([[orc.glu(glu, g[i, j], u[i, j], limit) for j in range(n)]
                      for i in range(tokens)], np.float32)
-    # same sums in, GLU evaluated by two math libraries: a few ulp of the factors
-    # (1 + tanh and 1 + exp cancel for negative gates, so the bound is on the
-    # factors' scale, not on the result's)
-    bound = 2e-6 * np.abs(want) + 4e-7 * np.abs(u) * np.maximum(1.0, np.abs(g))
-    assert (np.abs(fused - want) <= bound).all()
+    # The fused and the unfused launches may take different geometries (their shared-memory
+    # budgets differ), so the gate / up sums agree to F32 summation order, not bit for bit;
+    # the GLU is evaluated by two math libraries.  Bar: 1e-5 of the output's scale, and a few
+    # ulp of the factors where the geometry is the same (one token).
+    scale = max(float(np.abs(want).max()), 1e-30)
+    assert float(np.abs(fused - want).max()) <= 1e-5 * scale
+    if tokens == 1:
+        bound = 2e-6 * np.abs(want) + 4e-7 * np.abs(u) * np.maximum(1.0, np.abs(g))
+        assert (np.abs(fused - want) <= bound).all()
     # and against the oracle end to end at the F32 bar
     ref = orc.vecq(t, up, q8.cpu().numpy(), k, n, tokens, g=gate, glu=glu, limit=limit)[:, 0, :]
     assert float(np.abs(fused - ref).max()) <= 1e-5 * max(float(np.abs(ref).max()), 1e-30) * 4
