@@ -7,18 +7,23 @@
 // a hand-written sm_100a one).
 //
 // The GEMM is a persistent, warp-specialised tcgen05 kernel:
-//   warp 0   TMA producer: A (128 x 128 B) and B (256 x 128 B) tiles through
+//   warp 0   TMA producer: A (128 x 128 B) and B (192 x 128 B) tiles through
 //            128-byte-swizzled tensor maps, and the tiles' scale atoms (512 B
 //            each, already in the layout tcgen05.cp wants) as bulk copies,
-//            into a 4-stage shared-memory ring;
+//            into a 5-stage shared-memory ring;
 //   warp 1   allocates tensor memory and issues the MMAs: per stage it copies
 //            the scale atoms to TMEM (tcgen05.cp 32x128b.warpx4) and issues
-//            four tcgen05.mma.kind::mxf8f6f4.block_scale of 128x256x32 whose
-//            scale-factor ids pick the stage's four K blocks; the accumulator
-//            (128 lanes x 256 F32 columns) lives in TMEM;
+//            four tcgen05.mma.kind::mxf8f6f4.block_scale of 128x192x32 whose
+//            scale-factor ids pick the stage's four K blocks; TWO accumulators
+//            (128 lanes x 192 F32 columns each) live in TMEM, so the next
+//            tile's main loop runs while the epilogue drains the last one;
 //   warps 2-5 epilogue: tcgen05.ld the accumulator 32 columns at a time, convert
 //            and store the rows.
-// Tiles are walked M-fastest so the CTAs running together share B tiles in L2.
+// 128 x 192 tiles: two accumulators plus the scale columns fit the 512 TMEM
+// columns, and the benchmark shape (2048 x 12288) makes 1,024 tiles = 6.9 waves
+// of 148 CTAs.  A 192-row B tile starts on a scale-atom boundary or in the
+// middle of an atom; the atom copies are offset by two TMEM columns for the
+// latter.  Tiles are walked M-fastest so co-running CTAs share B tiles in L2.
 // Every mbarrier wait is bounded; a wait that runs out raises the fault counter
 // and the CTA drains and frees its tensor memory.
 #include <cuda_bf16.h>
@@ -113,20 +118,25 @@ __global__ void SwizzleKernel(const std::uint8_t* __restrict__ in, std::uint8_t*
 }
 
 // ------------------------------------------------------------------ GEMM
-constexpr int kBM = 128, kBN = 256, kBK = 128, kStages = 4, kUmmaK = 32;
+constexpr int kBM = 128, kBN = 192, kBK = 128, kStages = 5, kUmmaK = 32;
 constexpr int kABytes = kBM * kBK, kBBytes = kBN * kBK;
 constexpr int kSfaBytes = 512, kSfbBytes = 1024;
 constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
 constexpr int kGemmThreads = 192;
 constexpr int kTmemColumns = 512;
-constexpr int kSfaColumn = 256, kSfbColumn = 288;  // + stage * 4, + stage * 8
+// Two accumulators of kBN columns, then per stage 16 scale columns: A's atom at
+// +0..3, B's two atoms at +4..7 and +8..11; the tile's 192 rows' scales start at
+// +4 (tile on an atom boundary) or +6 (tile starting in the middle of an atom).
+constexpr int kAccColumns = kBN;
+constexpr int kSfColumn = 2 * kBN;
+constexpr int kSfStride = 16;
 constexpr int kGemmSmem = (kStages * kStageBytes) + 1024 /* alignment */ + 256 /* barriers */;
 
 struct GemmShared {
   std::uint64_t full[kStages];
   std::uint64_t empty[kStages];
-  std::uint64_t tmem_full;
-  std::uint64_t tmem_empty;
+  std::uint64_t tmem_full[2];
+  std::uint64_t tmem_empty[2];
   std::uint32_t tmem_base;
   std::uint32_t abort;
 };
@@ -158,8 +168,10 @@ Mxfp8GemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       tc::MbarInit(&sh->full[s], 1);
       tc::MbarInit(&sh->empty[s], 1);
     }
-    tc::MbarInit(&sh->tmem_full, 1);
-    tc::MbarInit(&sh->tmem_empty, 4);
+    for (int b = 0; b < 2; ++b) {
+      tc::MbarInit(&sh->tmem_full[b], 1);
+      tc::MbarInit(&sh->tmem_empty[b], 4);
+    }
     sh->abort = 0;
     tc::MbarInitFence();
   }
@@ -188,7 +200,9 @@ Mxfp8GemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             atomicAdd(faults, 1u);
             break;
           }
-          const bool second = (nb * kBN) + 128 < sfb_rows_padded;
+          // The tile's B rows [nb * 192, +192) touch two scale atoms (128 rows each).
+          const int atom0 = (nb * kBN) / 128;
+          const bool second = (atom0 + 1) * 128 < sfb_rows_padded;
           tc::MbarExpectTx(&sh->full[s], kABytes + kBBytes + kSfaBytes + (second ? 1024u : 512u));
           tc::TmaLoad2D(a_tiles + (s * kABytes), &map_a, ks * kBK, mb * kBM, &sh->full[s]);
           tc::TmaLoad2D(b_tiles + (s * kBBytes), &map_b, ks * kBK, nb * kBN, &sh->full[s]);
@@ -196,11 +210,11 @@ Mxfp8GemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                        sfa + ((static_cast<std::size_t>(mb) * (kb / 4) + ks) * 512), 512,
                        &sh->full[s]);
           tc::BulkLoad(sfb_tiles + (s * kSfbBytes),
-                       sfb + ((static_cast<std::size_t>(nb * 2) * (kb / 4) + ks) * 512), 512,
+                       sfb + ((static_cast<std::size_t>(atom0) * (kb / 4) + ks) * 512), 512,
                        &sh->full[s]);
           if (second) {
             tc::BulkLoad(sfb_tiles + (s * kSfbBytes) + 512,
-                         sfb + ((static_cast<std::size_t>((nb * 2) + 1) * (kb / 4) + ks) * 512), 512,
+                         sfb + ((static_cast<std::size_t>(atom0 + 1) * (kb / 4) + ks) * 512), 512,
                          &sh->full[s]);
           }
         }
@@ -211,12 +225,19 @@ Mxfp8GemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     if (lane == 0) {
       std::uint32_t it = 0, tile_it = 0;
       for (int t = static_cast<int>(blockIdx.x); t < tiles && !*abort_flag; t += gridDim.x, ++tile_it) {
-        if (!tc::MbarWait(&sh->tmem_empty, (tile_it & 1u) ^ 1u)) {
+        const int nb = t / tiles_m;
+        const int acc = static_cast<int>(tile_it & 1u);
+        if (!tc::MbarWait(&sh->tmem_empty[acc], ((tile_it >> 1) & 1u) ^ 1u)) {
           *abort_flag = 1;
           atomicAdd(faults, 1u);
           break;
         }
         tc::TcFenceAfter();
+        const std::uint32_t tacc = tmem + (acc * kAccColumns);
+        // The two atoms always land on 4-column boundaries (tcgen05.cp's unit); an
+        // odd tile starts in the middle of its first atom, whose last two columns
+        // (rows 64..127) are the tile's first two: the MMA reads from +2.
+        const int shift = (nb & 1) ? 2 : 0;
         for (int ks = 0; ks < ksteps; ++ks, ++it) {
           const int s = static_cast<int>(it % kStages);
           if (!tc::MbarWait(&sh->full[s], (it / kStages) & 1u)) {
@@ -225,22 +246,23 @@ Mxfp8GemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             break;
           }
           tc::TcFenceAfter();
-          const std::uint32_t tsfa = tmem + kSfaColumn + (s * 4);
-          const std::uint32_t tsfb = tmem + kSfbColumn + (s * 8);
+          const std::uint32_t tsfa = tmem + kSfColumn + (s * kSfStride);
+          const std::uint32_t tsfb = tsfa + 4 + shift;
           tc::TmemCopyScales(tsfa, tc::SmemDesc(sfa_tiles + (s * kSfaBytes), false, 128));
-          tc::TmemCopyScales(tsfb, tc::SmemDesc(sfb_tiles + (s * kSfbBytes), false, 128));
-          tc::TmemCopyScales(tsfb + 4, tc::SmemDesc(sfb_tiles + (s * kSfbBytes) + 512, false, 128));
+          tc::TmemCopyScales(tsfa + 4, tc::SmemDesc(sfb_tiles + (s * kSfbBytes), false, 128));
+          tc::TmemCopyScales(tsfa + 8,
+                             tc::SmemDesc(sfb_tiles + (s * kSfbBytes) + 512, false, 128));
           const std::uint64_t adesc = tc::SmemDesc(a_tiles + (s * kABytes), true, 1024);
           const std::uint64_t bdesc = tc::SmemDesc(b_tiles + (s * kBBytes), true, 1024);
 #pragma unroll
           for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
             // 32 bytes along K inside the 128-byte swizzle row: +2 in 16-byte units
-            tc::MmaMxf8(tmem, adesc + (kk * 2), bdesc + (kk * 2), tc::IdescMxf8(kBM, kBN, kk, kk),
+            tc::MmaMxf8(tacc, adesc + (kk * 2), bdesc + (kk * 2), tc::IdescMxf8(kBM, kBN, kk, kk),
                         ks > 0 || kk > 0, tsfa, tsfb);
           }
           tc::TcCommit(&sh->empty[s]);  // the stage's bytes are free once these MMAs retire
         }
-        tc::TcCommit(&sh->tmem_full);
+        tc::TcCommit(&sh->tmem_full[acc]);
       }
     }
   } else {
@@ -249,8 +271,9 @@ Mxfp8GemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     std::uint32_t tile_it = 0;
     for (int t = static_cast<int>(blockIdx.x); t < tiles; t += gridDim.x, ++tile_it) {
       const int mb = t % tiles_m, nb = t / tiles_m;
+      const int acc = static_cast<int>(tile_it & 1u);
       bool ok = true;
-      if (lane == 0) ok = tc::MbarWait(&sh->tmem_full, tile_it & 1u);
+      if (lane == 0) ok = tc::MbarWait(&sh->tmem_full[acc], (tile_it >> 1) & 1u);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok || *abort_flag) {
         if (lane == 0 && !ok) {
@@ -264,7 +287,8 @@ Mxfp8GemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll 1
       for (int c = 0; c < kBN / 32; ++c) {
         std::uint32_t r[32];
-        tc::TmemLoad32(tmem + (static_cast<std::uint32_t>(quadrant * 32) << 16) + (c * 32), r);
+        tc::TmemLoad32(tmem + (static_cast<std::uint32_t>(quadrant * 32) << 16) +
+                           (acc * kAccColumns) + (c * 32), r);
         tc::TmemLoadWait();
         const int col = (nb * kBN) + (c * 32);
         if (row < m && col < n) {
@@ -305,7 +329,7 @@ Mxfp8GemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       }
       tc::TcFenceBefore();
       __syncwarp();
-      if (lane == 0) tc::MbarArrive(&sh->tmem_empty);
+      if (lane == 0) tc::MbarArrive(&sh->tmem_empty[acc]);
     }
   }
 
