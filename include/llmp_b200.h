@@ -243,6 +243,14 @@ int llmp_b200_mxfp8_quantize(const void* x, int is_bf16, int64_t row_stride, int
  * [n, k/32] row-major -> scale atoms of padded_rows(n) rows. */
 int llmp_b200_mxfp8_swizzle(const void* in, void* out, int n, int blocks, void* stream);
 
+/* Replaces RunMxfp8MulMatVec (src/kernels/ggml/llmp_ops.cu:744; kernels :145-423):
+ * the decode product for up to 16 activation columns.  codes: E4M3 [k, n];
+ * scales: E8M0 [k / 32, n] ROW-MAJOR (not atoms); x: F32 columns x_stride floats
+ * apart; y: F32 [n] per column, y_stride floats apart. */
+int llmp_b200_mxfp8_mul_mat_vec(const void* codes, const void* scales, const float* x,
+                                int64_t x_stride, float* y, int64_t y_stride, int n, int k,
+                                int columns, void* stream);
+
 /* Field for field mxfp8::Gemm (src/kernels/ggml/mxfp8_cutlass.h:56-68). */
 typedef struct llmp_b200_mxfp8_gemm_desc {
   int m, n, k;

@@ -90,6 +90,9 @@ SIGNATURES = {
     "llmp_b200_mxfp8_quantize": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int,
                                            C.c_void_p, C.c_void_p, C.c_void_p]),
     "llmp_b200_mxfp8_swizzle": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
+    "llmp_b200_mxfp8_mul_mat_vec": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
+                                              C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_int,
+                                              C.c_void_p]),
     "llmp_b200_mxfp8_gemm_available": (C.c_int, []),
     "llmp_b200_mxfp8_gemm_scratch": (C.c_size_t, [C.POINTER(Mxfp8GemmDesc), C.c_int]),
     "llmp_b200_mxfp8_gemm": (C.c_int, [C.POINTER(Mxfp8GemmDesc), C.c_int, C.c_void_p]),

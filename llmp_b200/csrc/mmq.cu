@@ -23,6 +23,10 @@
 //               also stage the tokens' (d8, s8) as F32;
 //   warp 5      allocates TMEM and issues the MMAs;
 //   warps 6-13  epilogue: thread = (weight row, half of the token columns).
+// Two measured alternatives are kept behind build macros because both lost on
+// this part: 16 epilogue warps (LLMP_MMQ_EPILOGUE_WARPS=16: 100 against 122
+// TOP/s) and accumulating onto a preloaded bias 0x4B400000 so that the int32 sum
+// reads as the float 12582912 + C without a conversion (LLMP_MMQ_MAGIC=1: 82).
 // Every wait is bounded; a wait that runs out raises the device fault counter.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -106,8 +110,21 @@ constexpr int kBuffers = 4;     // TMEM group-result buffers of kTileCols column
 constexpr int kWBytes = kTileRows * kBK, kYBytes = kTileCols * kBK;
 constexpr int kScaleBytes = 4 * 128 * 4;  // [group][row or col] F32
 constexpr int kStageBytes = kWBytes + kYBytes + (4 * kScaleBytes);
-constexpr int kThreads = 14 * 32;
-constexpr int kEpilogueWarps = 8;
+#ifndef LLMP_MMQ_EPILOGUE_WARPS
+#define LLMP_MMQ_EPILOGUE_WARPS 8
+#endif
+#ifndef LLMP_MMQ_MAGIC
+#define LLMP_MMQ_MAGIC 0
+#endif
+constexpr int kEpilogueWarps = LLMP_MMQ_EPILOGUE_WARPS;
+constexpr bool kUseMagic = LLMP_MMQ_MAGIC != 0;
+constexpr int kThreads = (6 + kEpilogueWarps) * 32;
+constexpr int kEpilogueCols = kTileCols / (kEpilogueWarps / 4);  // columns a thread
+// An int32 sum C added to this bit pattern reads, as a float, 12582912 + C
+// exactly (|C| < 2^22): the accumulators start from it so that the epilogue
+// needs no integer-to-float conversion.
+constexpr std::uint32_t kMagicBits = 0x4B400000u;
+constexpr float kMagic = 12582912.0f;
 constexpr int kSmem = (kStages * kStageBytes) + 1024 + 512;
 
 struct Shared {
@@ -297,33 +314,51 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const Desc a,
         const std::uint64_t ydesc = tc::SmemDesc(y_tiles + (s * kYBytes), true, 1024);
         for (int gl = 0; gl < 4; ++gl, ++group) {
           const int b = static_cast<int>(group % kBuffers);
-          if (!tc::MbarWait(&sh->tmem_empty[b], ((group / kBuffers) & 1u) ^ 1u)) {
+          // Phase n of tmem_empty[b] completes when the epilogue has (re)loaded the
+          // buffer with the magic bias for its n-th use.
+          if (!tc::MbarWait(&sh->tmem_empty[b],
+                            kUseMagic ? ((group / kBuffers) & 1u) : (((group / kBuffers) & 1u) ^ 1u))) {
             give_up();
             break;
           }
           tc::TcFenceAfter();
-          tc::MmaI8(tmem + (b * kTileCols), wdesc + (gl * 2), ydesc + (gl * 2), idesc, false);
+          tc::MmaI8(tmem + (b * kTileCols), wdesc + (gl * 2), ydesc + (gl * 2), idesc, kUseMagic);
           tc::TcCommit(&sh->tmem_full[b]);
         }
       }
     }
   } else {
     // ------------------------------------------------------------ epilogue
-    const int ew = warp - 6;           // 0..7
-    const int quadrant = warp & 3;     // TMEM lanes this warp may read
-    const int colhalf = ew >> 2;       // warps 6..9 take columns 0..63, 10..13 take 64..127
+    const int ew = warp - 6;                // 0..15
+    const int quadrant = warp & 3;          // TMEM lanes this warp may touch
+    const int colgroup = ew >> 2;           // which kEpilogueCols columns
     const int rt = (quadrant * 32) + lane;  // weight row of the tile
-    float acc[64];
+    const std::uint32_t lane_base = static_cast<std::uint32_t>(quadrant * 32) << 16;
+    float acc[kEpilogueCols];
 #pragma unroll
-    for (int i = 0; i < 64; ++i) acc[i] = 0.0f;
+    for (int i = 0; i < kEpilogueCols; ++i) acc[i] = 0.0f;
+    // Every buffer starts from the bias.
+    for (int bb = 0; kUseMagic && bb < kBuffers; ++bb) {
+#pragma unroll
+      for (int part = 0; part < kEpilogueCols / 32; ++part) {
+        tc::TmemFill32(tmem + lane_base + (bb * kTileCols) + (colgroup * kEpilogueCols) +
+                           (part * 32), kMagicBits);
+      }
+    }
+    tc::TmemStoreWait();
+    tc::TcFenceBefore();
+    __syncwarp();
+    if (kUseMagic && lane == 0) {
+      for (int bb = 0; bb < kBuffers; ++bb) tc::MbarArrive(&sh->tmem_empty[bb]);
+    }
     std::uint32_t group = 0;
     bool ok = true;
     for (int ks = 0; ks < ksteps && ok; ++ks) {
       const int s = ks % kStages;
       const float* sc = stage_scales(s);
       for (int gl = 0; gl < 4 && ok; ++gl, ++group) {
-        const int b = static_cast<int>(group % kBuffers);
-        if (lane == 0) ok = tc::MbarWait(&sh->tmem_full[b], (group / kBuffers) & 1u);
+        const int bb = static_cast<int>(group % kBuffers);
+        if (lane == 0) ok = tc::MbarWait(&sh->tmem_full[bb], (group / kBuffers) & 1u);
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         if (!ok || *abort_flag) {
           if (lane == 0 && !ok) give_up();
@@ -333,14 +368,17 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const Desc a,
         tc::TcFenceAfter();
         const float ax = sc[(gl * 128) + rt];
         const float ay = sc[512 + (gl * 128) + rt];
-        const float* bx = sc + 1024 + (gl * 128) + (colhalf * 64);
-        const float* by = sc + 1536 + (gl * 128) + (colhalf * 64);
+        const float cx = -kMagic * ax;  // exact: a half-precision ax times 3 * 2^22
+        const float* bx = sc + 1024 + (gl * 128) + (colgroup * kEpilogueCols);
+        const float* by = sc + 1536 + (gl * 128) + (colgroup * kEpilogueCols);
 #pragma unroll
-        for (int part = 0; part < 2; ++part) {
+        for (int part = 0; part < kEpilogueCols / 32; ++part) {
           std::uint32_t r[32];
-          tc::TmemLoad32(tmem + (static_cast<std::uint32_t>(quadrant * 32) << 16) +
-                             (b * kTileCols) + (colhalf * 64) + (part * 32), r);
+          const std::uint32_t at = tmem + lane_base + (bb * kTileCols) +
+                                   (colgroup * kEpilogueCols) + (part * 32);
+          tc::TmemLoad32(at, r);
           tc::TmemLoadWait();
+          if (kUseMagic) tc::TmemFill32(at, kMagicBits);  // ready for the buffer's next use
 #pragma unroll
           for (int v = 0; v < 8; ++v) {
             const float4 x4 = *reinterpret_cast<const float4*>(bx + (part * 32) + (v * 4));
@@ -350,22 +388,27 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const Desc a,
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const int i = (part * 32) + (v * 4) + j;
-              acc[i] = fmaf(ax * xs[j], static_cast<float>(static_cast<int>(r[(v * 4) + j])), acc[i]);
+              // ax * C, rounded once: ax * (magic + C) - magic * ax
+              const float u = kUseMagic
+                                  ? fmaf(__uint_as_float(r[(v * 4) + j]), ax, cx)
+                                  : ax * static_cast<float>(static_cast<int>(r[(v * 4) + j]));
+              acc[i] = fmaf(u, xs[j], acc[i]);
               acc[i] = fmaf(ay, ys[j], acc[i]);
             }
           }
         }
+        if (kUseMagic) tc::TmemStoreWait();
         tc::TcFenceBefore();
         __syncwarp();
-        if (lane == 0) tc::MbarArrive(&sh->tmem_empty[b]);
+        if (lane == 0) tc::MbarArrive(&sh->tmem_empty[bb]);
       }
       __syncwarp();
       if (lane == 0 && ok) tc::MbarArrive(&sh->empty[s]);  // the stage's scales are consumed
     }
     if (ok && row0 + rt < a.nrows) {
 #pragma unroll 4
-      for (int i = 0; i < 64; ++i) {
-        const int c = col0 + (colhalf * 64) + i;
+      for (int i = 0; i < kEpilogueCols; ++i) {
+        const int c = col0 + (colgroup * kEpilogueCols) + i;
         if (c < c_end) {
           const int dst_col = a.ids_dst != nullptr ? a.ids_dst[c] : c;
           a.dst[(static_cast<std::size_t>(dst_col) * a.dst_col_stride) + row0 + rt] = acc[i];

@@ -17,7 +17,7 @@ from ._native import (GLU_GEGLU, GLU_NONE, GLU_SWIGLU, GLU_SWIGLU_CLAMP, TYPE_Q4
 
 __all__ = ["available", "sm_count", "device_faults", "block_bytes", "block_elems", "q8_1_row_blocks",
            "quantize_q8", "vecq", "vecq_variants", "vecq_block_sums", "mxfp8_padded_rows",
-           "mxfp8_quantize", "mxfp8_swizzle", "mxfp8_gemm", "mmq_quantize", "mmq", "moe_route", "grouped_gemm",
+           "mxfp8_quantize", "mxfp8_swizzle", "mxfp8_gemm", "mxfp8_mul_mat_vec", "mmq_quantize", "mmq", "moe_route", "grouped_gemm",
            "moe_glu_quantize", "moe_combine", "moe_ffn", "TYPE_Q8_0", "TYPE_Q4_K",
            "GLU_NONE", "GLU_SWIGLU", "GLU_SWIGLU_CLAMP", "GLU_GEGLU", "Rejected", "LaunchFailed"]
 
@@ -354,3 +354,20 @@ def moe_ffn(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, gate_up: 
     hq = moe_glu_quantize(gu, inter, glu)
     y = grouped_gemm(down, hq, route["offsets"], inter, hidden)
     return moe_combine(y, route["position"], weights.contiguous(), tokens, used)
+
+
+def mxfp8_mul_mat_vec(codes: torch.Tensor, scales: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    """Mxfp8MulMatVec: codes uint8 [n, k], scales uint8 [n, k / 32] row-major, x F32
+    [columns <= 16, k] -> F32 [columns, n]."""
+    _need(codes, torch.uint8, "mxfp8_mul_mat_vec codes")
+    _need(scales, torch.uint8, "mxfp8_mul_mat_vec scales")
+    _need(x, torch.float32, "mxfp8_mul_mat_vec x")
+    n, k = codes.shape
+    cols = x.shape[0]
+    if not codes.is_contiguous() or not scales.is_contiguous() or x.stride(1) != 1:
+        raise Rejected("mxfp8_mul_mat_vec: packed codes and scales, k-contiguous activations")
+    y = torch.empty((cols, n), dtype=torch.float32, device=codes.device)
+    N.check(N.lib().llmp_b200_mxfp8_mul_mat_vec(codes.data_ptr(), scales.data_ptr(), x.data_ptr(),
+                                                x.stride(0), y.data_ptr(), y.stride(0), n, k, cols,
+                                                _stream()), "llmp_b200_mxfp8_mul_mat_vec")
+    return y

@@ -129,3 +129,26 @@ def test_gemm_refuses_shapes_it_does_not_take(cuda):
     with pytest.raises(ops.Rejected):
         ops.mxfp8_gemm(a, s, a, s)                        # k not a multiple of 128
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("n,k,cols", [(10240, 2560, 1), (333, 512, 16), (7, 64, 3), (1, 32, 1)])
+def test_decode_gemv_matches_the_double_product(cuda, orc, n, k, cols):
+    """llmp.mxfp8.mul_mat_vec: MXFP8 weights with ROW-MAJOR scales times F32 columns
+    (tests/unit/qwen38_ops_test.cc:207-352): F32 sums within 1e-5 of the output's scale of
+    the double product of the decoded weights; a lone column gives the bits it gives in a batch."""
+    torch = cuda
+    ops = _ops()
+    rng = np.random.default_rng(n + k + cols)
+    codes = rng.integers(0, 256, size=(n, k), dtype=np.uint8)
+    codes[(codes & 0x7F) == 0x7F] = 0x3A                  # no NaN codes
+    scales = rng.integers(118, 130, size=(n, k // 32), dtype=np.uint8)
+    x = rng.normal(0, 1, size=(cols, k)).astype(np.float32)
+    e4m3 = np.array([orc.lib().orc_e4m3_to_f32(i) for i in range(256)], np.float64)
+    w = e4m3[codes] * np.repeat(np.exp2(scales.astype(np.float64) - 127), 32, axis=1)
+    want = x.astype(np.float64) @ w.T
+    dc, ds, dx = to_dev(torch, codes), to_dev(torch, scales), to_dev(torch, x)
+    got = ops.mxfp8_mul_mat_vec(dc, ds, dx).cpu().numpy()
+    assert np.isfinite(got).all()
+    assert float(np.abs(got - want).max()) <= 1e-5 * float(np.abs(want).max())
+    alone = ops.mxfp8_mul_mat_vec(dc, ds, dx[:1].contiguous()).cpu().numpy()
+    assert np.array_equal(alone[0], got[0])
