@@ -194,8 +194,9 @@ def make_q4k_device(torch, rows: int, k: int, gen):
 class FfnStep:
     """The step's device state and launches, for one rank's shard."""
 
-    def __init__(self, torch, ops, batch: int, world: int, rank: int, dist):
+    def __init__(self, torch, ops, batch: int, world: int, rank: int, dist, fused: bool = False):
         self.torch, self.ops, self.batch, self.world, self.dist = torch, ops, batch, world, dist
+        self.fused = fused
         gen = torch.Generator(device="cuda")
         gen.manual_seed(1234 + rank)
         self.n_glu = INTER // world
@@ -219,11 +220,18 @@ class FfnStep:
         self.h_rows = torch.empty((batch, INTER), device="cuda")
         self.y_shard = torch.empty((batch, self.n_down), device="cuda")
         self.y_full = torch.empty((LAYERS, world, batch, self.n_down), device="cuda")
-        self.launches_per_step = LAYERS * (4 + (1 if world > 1 else 0))
+        self.launches_per_step = LAYERS * (2 if (world == 1 and fused) else 4 + (1 if world > 1 else 0))
 
     def layer(self, l: int, x):
         ops, T = self.ops, self.ops.TYPE_Q4_K
         gate, up, down = self.layers[l]
+        if self.world == 1 and self.fused:
+            # Two launches a layer: each product quantizes its F32 input itself
+            # (llmp_b200_vecq_f32), with the quantizer's arithmetic.
+            ops.vecq_f32(up, T, HIDDEN, self.n_glu, x, gate=gate, glu=ops.GLU_GEGLU,
+                         out=self.h_shard)
+            ops.vecq_f32(down, T, INTER, self.n_down, self.h_shard, out=self.y_full[l, 0])
+            return
         ops.quantize_q8(x, out=self.q8x)
         ops.vecq(up, T, HIDDEN, self.n_glu, self.q8x, self.batch, gate=gate, glu=ops.GLU_GEGLU,
                  out=self.h_shard)
@@ -248,6 +256,11 @@ class FfnStep:
     def glu_only(self):
         """The dominant kernel alone, one launch per layer copy."""
         ops, T = self.ops, self.ops.TYPE_Q4_K
+        if self.world == 1 and self.fused:
+            for l, (gate, up, _) in enumerate(self.layers):
+                ops.vecq_f32(up, T, HIDDEN, self.n_glu, self.x[l], gate=gate, glu=ops.GLU_GEGLU,
+                             out=self.h_shard)
+            return
         for gate, up, _ in self.layers:
             ops.vecq(up, T, HIDDEN, self.n_glu, self.q8x, self.batch, gate=gate,
                      glu=ops.GLU_GEGLU, out=self.h_shard)
@@ -268,7 +281,7 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
         raise SystemExit("bench.py: no B200 / native library: " + ops._native.last_error())
 
     batch = args.batch
-    st = FfnStep(torch, ops, batch, world, rank, dist)
+    st = FfnStep(torch, ops, batch, world, rank, dist, fused=args.fused)
     stream = torch.cuda.Stream()
     sync = torch.cuda.synchronize
 
@@ -404,6 +417,7 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
                 "l2": f"inputs larger than L2: {LAYERS} distinct layer copies, "
                       f"{LAYERS * 44.2e-3:.2f} GB, streamed in order",
                 "launch": "cuda graph replay" if graph is not None else "stream launches",
+                "launches_per_layer": 2 if (world == 1 and args.fused) else 4,
                 "parallelism": "single GPU" if world == 1 else f"N-column shards x{world}, "
                                "NCCL all-gather of the GLU output and of the layer output",
                 "step_bytes": sb,
@@ -612,6 +626,10 @@ def main():
                     help="ffn_q4k is the bench line; the others time the other configs' kernels")
     ap.add_argument("--tokens", type=int, default=0,
                     help="tokens / rows of the other workloads")
+    ap.add_argument("--fused", action="store_true",
+                    help="llmp_b200_vecq_f32: each product quantizes its F32 input itself (two "
+                         "launches a layer instead of four; measured slower: 2,200 against 2,717 "
+                         "GB/s, the per-CTA quantization sits on the critical path)")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--traffic", type=float, default=None,

@@ -105,6 +105,17 @@ int llmp_b200_vecq_variants(void);
 const char* llmp_b200_vecq_variant_name(int variant);
 int llmp_b200_vecq(int type, const llmp_b200_vecq_desc* desc, int variant, void* stream);
 
+/* The product with its activation quantization fused: the reference lowers a
+ * shared QuantizeQ8 node in front of its products (src/kernels/ggml/shared_q8.h
+ * :20-47, vecq.cu:1095-1175); here desc->y points at the F32 activations
+ * themselves ([k, tokens], y_token FLOATS between tokens) and every CTA
+ * quantizes them to Q8_1 in shared memory with the quantizer's arithmetic, so
+ * the sums are the two-call path's bit for bit and one launch is saved.  Taken
+ * for dense Q4_K products of up to 8 tokens (others: status > 0, use the two
+ * calls).  q8_out (or NULL): receives the Q8_1 blocks of the first k / 32
+ * blocks of each token's row, rows llmp_b200_q8_1_row_blocks(k) blocks apart. */
+int llmp_b200_vecq_f32(int type, const llmp_b200_vecq_desc* desc, void* q8_out, void* stream);
+
 /* Verification entry with no reference counterpart as a separate call: the
  * int32 per-block sums the product kernels form (the quantity the reference
  * checks bit for bit, tests/unit/dsv4_fast_test.cc:511-540), for nrows weight

@@ -162,8 +162,27 @@ const char* llmp_b200_vecq_variant_name(int variant) {
   return llmp_b200::kVariants[variant].name;
 }
 
+namespace llmp_b200 {
+namespace {
+int LaunchVecQ(int type, const llmp_b200_vecq_desc* desc, int variant, bool f32_input, void* q8_out,
+               void* stream);
+}  // namespace
+}  // namespace llmp_b200
+
 int llmp_b200_vecq(int type, const llmp_b200_vecq_desc* desc, int variant, void* stream) {
-  using namespace llmp_b200;
+  return llmp_b200::LaunchVecQ(type, desc, variant, false, nullptr, stream);
+}
+
+int llmp_b200_vecq_f32(int type, const llmp_b200_vecq_desc* desc, void* q8_out, void* stream) {
+  return llmp_b200::LaunchVecQ(type, desc, -1, true, q8_out, stream);
+}
+
+}  // extern "C"
+
+namespace llmp_b200 {
+namespace {
+int LaunchVecQ(int type, const llmp_b200_vecq_desc* desc, int variant, bool f32_input, void* q8_out,
+               void* stream) {
   if (desc == nullptr) return Reject("vecq: null descriptor");
   bool q8_fast = false;
   if (const int status = Check(type, *desc, &q8_fast); status != 0) return status;
@@ -215,6 +234,16 @@ int llmp_b200_vecq(int type, const llmp_b200_vecq_desc* desc, int variant, void*
   if (wants_rowlane && !rowlane_ok) {
     return Reject("vecq: this rowlane variant does not take the product (dense Q4_K, <= 8 tokens)");
   }
+  if (f32_input) {
+    // The fused quantize-and-multiply form exists in the rowlane kernel only.
+    if (!rowlane_ok || d.ncols_x % 32 != 0 || !Aligned(d.y, 16) || d.y_token % 4 != 0 ||
+        d.y_token < d.ncols_x) {
+      return Reject("vecq_f32: dense Q4_K products of up to 8 tokens over 16-byte aligned F32 rows");
+    }
+    lanes.f32_input = 1;
+    lanes.q8_out = static_cast<std::uint8_t*>(q8_out);
+    lanes.q8_row_blocks = (d.ncols_x + 511) / 512 * 512 / 32;
+  }
   if (rowlane_ok && (wants_rowlane || variant < 0)) {
     e = LaunchRowLane(d, p, lanes, s);
     if (e != cudaSuccess) return Failed(e, "vecq rowlane launch");
@@ -247,6 +276,10 @@ int llmp_b200_vecq(int type, const llmp_b200_vecq_desc* desc, int variant, void*
   if (e != cudaSuccess) return Failed(e, "vecq launch");
   return 0;
 }
+}  // namespace
+}  // namespace llmp_b200
+
+extern "C" {
 
 int llmp_b200_vecq_block_sums(int type, const void* w, const void* y, int k, int nrows,
                               int stride_row, int32_t* dots, int32_t* qsums, void* stream) {

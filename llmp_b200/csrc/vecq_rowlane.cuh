@@ -51,6 +51,9 @@ struct RowLanePlan {
   int grid;
   int half;          // the kHalf instantiation
   double score;      // the planner's figure of merit (lane use x warps x ring depth)
+  int f32_input;     // activations are F32: quantize to Q8_1 while staging
+  int q8_row_blocks; // Q8_1 blocks between tokens' rows in q8_out
+  std::uint8_t* q8_out;  // optional: the Q8_1 blocks, written by CTA 0
   unsigned int* faults;
 };
 
@@ -128,28 +131,81 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
 
   // Stage the tokens' activations: one Q8_1 block a thread.  Column c's i-th
   // 16-byte chunk is chunk (i * UR + c); its scales follow in four float4
-  // planes: d[0..3], d[4..7], d * sum q [0..3], [4..7].
+  // planes: d[0..3], d[4..7], d * sum q [0..3], [4..7].  With plan.f32_input the
+  // activations are F32 and every CTA quantizes them itself, with the
+  // arithmetic of the Q8_1 quantizer (q8_1.cu: d = amax / 127 rounded to FP16,
+  // q = roundf(x / d), the sum a butterfly over indices 16, 8, 4, 2, 1 apart),
+  // so the staged values are the blocks' values bit for bit; CTA 0 also writes
+  // the blocks out when the caller wants them.
   {
     const int blocks = UR * 8;
     for (int t = 0; t < P; ++t) {
       const int token = min(t, a.tokens - 1);
-      const std::uint8_t* y = static_cast<const std::uint8_t*>(a.y) +
-                              (static_cast<std::size_t>(token) * a.y_token * 36);
       uint4* q = reinterpret_cast<uint4*>(acts + (static_cast<std::size_t>(t) * plan.acts_bytes));
       float* sc = reinterpret_cast<float*>(q + (16 * UR));
       for (int b = tid; b < blocks; b += static_cast<int>(blockDim.x)) {
-        const auto* src = reinterpret_cast<const std::uint32_t*>(y + (static_cast<std::size_t>(b) * 36));
         std::uint32_t v[8];
         int isum = 0;
+        float d;
+        if (plan.f32_input) {
+          const float4* src = reinterpret_cast<const float4*>(
+              static_cast<const float*>(a.y) + (static_cast<std::size_t>(token) * a.y_token) +
+              (static_cast<std::size_t>(b) * 32));
+          float x[32], sum[32];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          v[i] = src[1 + i];
-          isum = Dp4a(0x01010101, static_cast<int>(v[i]), isum);
+          for (int i = 0; i < 8; ++i) {
+            const float4 f = src[i];
+            x[4 * i] = f.x; x[4 * i + 1] = f.y; x[4 * i + 2] = f.z; x[4 * i + 3] = f.w;
+          }
+          float amax = 0.0f;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            amax = fmaxf(amax, fabsf(x[i]));
+            sum[i] = x[i];
+          }
+#pragma unroll
+          for (int offset = 16; offset > 0; offset >>= 1) {
+#pragma unroll
+            for (int i = 0; i < offset; ++i) sum[i] = sum[i] + sum[i + offset];
+          }
+          const float df = amax / 127.0f;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            std::uint32_t packed = 0;
+            if (amax != 0.0f) {
+#pragma unroll
+              for (int c4 = 0; c4 < 4; ++c4) {
+                const int qi = static_cast<int>(roundf(x[(4 * i) + c4] / df));
+                packed |= (static_cast<std::uint32_t>(qi) & 0xffu) << (8 * c4);
+              }
+            }
+            v[i] = packed;
+            isum = Dp4a(0x01010101, static_cast<int>(packed), isum);
+          }
+          const __half dh = __float2half_rn(df);
+          d = __half2float(dh);
+          if (plan.q8_out != nullptr && blockIdx.x == 0 && t < a.tokens) {
+            auto* out = reinterpret_cast<std::uint32_t*>(
+                plan.q8_out + ((static_cast<std::size_t>(t) * plan.q8_row_blocks + b) * 36));
+            out[0] = static_cast<std::uint32_t>(__half_as_ushort(dh)) |
+                     (static_cast<std::uint32_t>(__half_as_ushort(__float2half_rn(sum[0]))) << 16);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) out[1 + i] = v[i];
+          }
+        } else {
+          const auto* src = reinterpret_cast<const std::uint32_t*>(
+              static_cast<const std::uint8_t*>(a.y) +
+              ((static_cast<std::size_t>(token) * a.y_token + b) * 36));
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            v[i] = src[1 + i];
+            isum = Dp4a(0x01010101, static_cast<int>(v[i]), isum);
+          }
+          d = HalfBitsToFloat(src[0] & 0xffffu);
         }
         const int c = b >> 3, g = b & 7;
         q[((2 * g) * UR) + c] = make_uint4(v[0], v[1], v[2], v[3]);
         q[((2 * g + 1) * UR) + c] = make_uint4(v[4], v[5], v[6], v[7]);
-        const float d = HalfBitsToFloat(src[0] & 0xffffu);
         sc[((((g >> 2)) * UR + c) * 4) + (g & 3)] = d;
         sc[((((2 + (g >> 2))) * UR + c) * 4) + (g & 3)] = d * static_cast<float>(isum);
       }
@@ -352,6 +408,9 @@ inline bool PlanRowLane(const Desc& d, int p, int sms, int force_rows, bool half
       best.grid = grid;
       best.half = half ? 1 : 0;
       best.score = score;
+      best.f32_input = 0;
+      best.q8_row_blocks = 0;
+      best.q8_out = nullptr;
     }
     }
   }

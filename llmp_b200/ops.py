@@ -16,7 +16,7 @@ from ._native import (GLU_GEGLU, GLU_NONE, GLU_SWIGLU, GLU_SWIGLU_CLAMP, TYPE_Q4
                       LaunchFailed, Rejected)
 
 __all__ = ["available", "sm_count", "device_faults", "block_bytes", "block_elems", "q8_1_row_blocks",
-           "quantize_q8", "vecq", "vecq_variants", "vecq_block_sums", "mxfp8_padded_rows",
+           "quantize_q8", "vecq", "vecq_f32", "vecq_variants", "vecq_block_sums", "mxfp8_padded_rows",
            "mxfp8_quantize", "mxfp8_swizzle", "mxfp8_gemm", "mxfp8_mul_mat_vec", "mmq_quantize", "mmq", "moe_route", "grouped_gemm",
            "moe_glu_quantize", "moe_combine", "moe_ffn", "TYPE_Q8_0", "TYPE_Q4_K",
            "GLU_NONE", "GLU_SWIGLU", "GLU_SWIGLU_CLAMP", "GLU_GEGLU", "Rejected", "LaunchFailed"]
@@ -132,6 +132,35 @@ def vecq(weights: torch.Tensor, wtype: int, k: int, n: int, q8: torch.Tensor, to
     d.dst_slot = n if slotted else 0
     d.glu, d.limit = glu, limit
     N.check(N.lib().llmp_b200_vecq(wtype, C.byref(d), variant, _stream()), "llmp_b200_vecq")
+    return out
+
+
+def vecq_f32(weights: torch.Tensor, wtype: int, k: int, n: int, x: torch.Tensor, *,
+             gate: torch.Tensor | None = None, glu: int = GLU_NONE, limit: float = 0.0,
+             out: torch.Tensor | None = None, q8_out: torch.Tensor | None = None) -> torch.Tensor:
+    """QuantizeQ8 + VecQ in one launch: x F32 [tokens <= 8, k] (rows 16-byte aligned), dense
+    Q4_K weights [n, k] -> F32 [tokens, n].  q8_out (uint8 [tokens, q8_1_row_blocks(k) * 36])
+    optionally receives the Q8_1 blocks the kernel formed."""
+    _need(weights, torch.uint8, "vecq_f32 weights")
+    _need(x, torch.float32, "vecq_f32 activations")
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise Rejected("vecq_f32: F32 [k, tokens] with k contiguous")
+    tokens = x.shape[0]
+    d = N.VecQDesc()
+    d.w = weights.data_ptr()
+    d.g = gate.data_ptr() if gate is not None else None
+    d.y = x.data_ptr()
+    d.ncols_x, d.nrows = k, n
+    d.stride_row = k // _BLOCK[wtype][0]
+    d.y_token = x.stride(0)
+    d.used, d.tokens = 1, tokens
+    if out is None:
+        out = torch.empty((tokens, n), dtype=torch.float32, device=weights.device)
+    d.dst, d.dst_token = out.data_ptr(), n
+    d.glu, d.limit = glu, limit
+    N.check(N.lib().llmp_b200_vecq_f32(wtype, C.byref(d),
+                                       q8_out.data_ptr() if q8_out is not None else None,
+                                       _stream()), "llmp_b200_vecq_f32")
     return out
 
 

@@ -248,6 +248,32 @@ def test_operands_the_kernels_do_not_take_are_refused_before_launch(cuda, orc):
     torch.cuda.synchronize()                                          # nothing was queued
 
 
+@pytest.mark.parametrize("n,k,tokens,glu", [(10240, 2560, 1, 3), (2560, 10240, 1, 0),
+                                            (333, 2560, 8, 1), (64, 512, 3, 0)])
+def test_fused_quantization_gives_the_two_call_bits(cuda, orc, n, k, tokens, glu):
+    """llmp_b200_vecq_f32 quantizes the F32 activations inside the product kernel: its Q8_1
+    blocks are the quantizer's bit for bit, and so are the sums of the two-call path."""
+    torch = cuda
+    ops = _ops()
+    rng = np.random.default_rng(n + k + tokens)
+    w = to_dev(torch, synth.q4_k_weights(rng, n, k))
+    g = to_dev(torch, synth.q4_k_weights(rng, n, k)) if glu else None
+    x = rng.normal(0, 1, size=(tokens, k)).astype(np.float32)
+    x[0, 32:64] = 0.0
+    xd = to_dev(torch, x)
+    q8 = ops.quantize_q8(xd)
+    want = ops.vecq(w, orc.Q4_K, k, n, q8, tokens, gate=g, glu=glu)
+    q8_out = torch.zeros_like(q8)
+    got = ops.vecq_f32(w, orc.Q4_K, k, n, xd, gate=g, glu=glu, q8_out=q8_out)
+    assert torch.equal(got, want)
+    blocks = k // 32
+    a = q8_out.view(tokens, -1, 36)[:, :blocks]
+    b = q8.view(tokens, -1, 36)[:, :blocks]
+    assert torch.equal(a, b)
+    assert np.array_equal(b.cpu().numpy().reshape(tokens, -1),
+                          orc.quantize_q8_1(x)[:, :blocks * 36])
+
+
 def test_no_bounded_wait_ran_out(cuda):
     """Collected after the product tests of this file: the TMA-fed kernels'
     bounded mbarrier waits never expired."""
