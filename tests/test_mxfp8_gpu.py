@@ -63,12 +63,16 @@ def _operands(torch, orc, rng, m, n, k):
     return a, a_s, b, bs
 
 
-@pytest.mark.parametrize("m,n,k,bf16", [
-    (128, 256, 128, False), (128, 256, 512, False), (256, 512, 1024, True),
-    (100, 200, 256, False),          # ragged rows and columns
-    (1, 8, 128, False), (129, 257, 384, True), (384, 1280, 2048, True),
+@pytest.mark.parametrize("m,n,k,bf16,sms", [
+    (128, 256, 128, False, 0), (128, 256, 512, False, 0), (256, 512, 1024, True, 0),
+    (100, 200, 256, False, 0),          # ragged rows and columns
+    (1, 8, 128, False, 0), (129, 257, 384, True, 0), (384, 1280, 2048, True, 0),
+    # a caller that grants few SMs: every CTA walks many tiles, so both TMEM
+    # accumulators and every smem stage are reused many times over
+    (256, 512, 1024, False, 1), (384, 1280, 2048, True, 2), (129, 600, 384, False, 1),
+    (700, 400, 256, True, 3),
 ])
-def test_gemm_equals_the_product_of_its_quantized_operands(cuda, orc, m, n, k, bf16):
+def test_gemm_equals_the_product_of_its_quantized_operands(cuda, orc, m, n, k, bf16, sms):
     torch = cuda
     ops = _ops()
     rng = np.random.default_rng(m + n + k)
@@ -77,7 +81,7 @@ def test_gemm_equals_the_product_of_its_quantized_operands(cuda, orc, m, n, k, b
     esz = torch.bfloat16 if bf16 else torch.float32
     buf = torch.full((m * n + 64,), float("nan"), dtype=esz, device="cuda")
     out = buf[: m * n].view(m, n)
-    ops.mxfp8_gemm(a, a_s, b, bs, bf16=bf16, out=out)
+    ops.mxfp8_gemm(a, a_s, b, bs, bf16=bf16, out=out, sms=sms)
     torch.cuda.synchronize()
     assert ops.device_faults() == 0
     assert torch.isnan(buf[m * n:]).all()
