@@ -117,12 +117,13 @@ constexpr int kStageBytes = kWBytes + kYBytes + (4 * kScaleBytes);
 #define LLMP_MMQ_MAGIC 0
 #endif
 constexpr int kEpilogueWarps = LLMP_MMQ_EPILOGUE_WARPS;
-constexpr bool kUseMagic = LLMP_MMQ_MAGIC != 0;
+constexpr bool kRegMagic = LLMP_MMQ_MAGIC != 0;
 constexpr int kThreads = (6 + kEpilogueWarps) * 32;
 constexpr int kEpilogueCols = kTileCols / (kEpilogueWarps / 4);  // columns a thread
+constexpr int kChunk = 16;                                       // columns a TMEM load
+constexpr int kChunks = kEpilogueCols / kChunk;
 // An int32 sum C added to this bit pattern reads, as a float, 12582912 + C
-// exactly (|C| < 2^22): the accumulators start from it so that the epilogue
-// needs no integer-to-float conversion.
+// exactly (|C| < 2^22): an integer add in place of an integer-to-float conversion.
 constexpr std::uint32_t kMagicBits = 0x4B400000u;
 constexpr float kMagic = 12582912.0f;
 constexpr int kSmem = (kStages * kStageBytes) + 1024 + 512;
@@ -314,22 +315,19 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const Desc a,
         const std::uint64_t ydesc = tc::SmemDesc(y_tiles + (s * kYBytes), true, 1024);
         for (int gl = 0; gl < 4; ++gl, ++group) {
           const int b = static_cast<int>(group % kBuffers);
-          // Phase n of tmem_empty[b] completes when the epilogue has (re)loaded the
-          // buffer with the magic bias for its n-th use.
-          if (!tc::MbarWait(&sh->tmem_empty[b],
-                            kUseMagic ? ((group / kBuffers) & 1u) : (((group / kBuffers) & 1u) ^ 1u))) {
+          if (!tc::MbarWait(&sh->tmem_empty[b], ((group / kBuffers) & 1u) ^ 1u)) {
             give_up();
             break;
           }
           tc::TcFenceAfter();
-          tc::MmaI8(tmem + (b * kTileCols), wdesc + (gl * 2), ydesc + (gl * 2), idesc, kUseMagic);
+          tc::MmaI8(tmem + (b * kTileCols), wdesc + (gl * 2), ydesc + (gl * 2), idesc, false);
           tc::TcCommit(&sh->tmem_full[b]);
         }
       }
     }
   } else {
     // ------------------------------------------------------------ epilogue
-    const int ew = warp - 6;                // 0..15
+    const int ew = warp - 6;
     const int quadrant = warp & 3;          // TMEM lanes this warp may touch
     const int colgroup = ew >> 2;           // which kEpilogueCols columns
     const int rt = (quadrant * 32) + lane;  // weight row of the tile
@@ -337,28 +335,15 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const Desc a,
     float acc[kEpilogueCols];
 #pragma unroll
     for (int i = 0; i < kEpilogueCols; ++i) acc[i] = 0.0f;
-    // Every buffer starts from the bias.
-    for (int bb = 0; kUseMagic && bb < kBuffers; ++bb) {
-#pragma unroll
-      for (int part = 0; part < kEpilogueCols / 32; ++part) {
-        tc::TmemFill32(tmem + lane_base + (bb * kTileCols) + (colgroup * kEpilogueCols) +
-                           (part * 32), kMagicBits);
-      }
-    }
-    tc::TmemStoreWait();
-    tc::TcFenceBefore();
-    __syncwarp();
-    if (kUseMagic && lane == 0) {
-      for (int bb = 0; bb < kBuffers; ++bb) tc::MbarArrive(&sh->tmem_empty[bb]);
-    }
-    std::uint32_t group = 0;
     bool ok = true;
     for (int ks = 0; ks < ksteps && ok; ++ks) {
       const int s = ks % kStages;
       const float* sc = stage_scales(s);
-      for (int gl = 0; gl < 4 && ok; ++gl, ++group) {
-        const int bb = static_cast<int>(group % kBuffers);
-        if (lane == 0) ok = tc::MbarWait(&sh->tmem_full[bb], (group / kBuffers) & 1u);
+      static_assert(kBuffers == 4, "group gl of every k-step lands in buffer gl");
+#pragma unroll
+      for (int gl = 0; gl < 4; ++gl) {
+        if (!ok) break;
+        if (lane == 0) ok = tc::MbarWait(&sh->tmem_full[gl], static_cast<std::uint32_t>(ks) & 1u);
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         if (!ok || *abort_flag) {
           if (lane == 0 && !ok) give_up();
@@ -366,47 +351,52 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const Desc a,
           break;
         }
         tc::TcFenceAfter();
+        const std::uint32_t at = tmem + lane_base + (gl * kTileCols) + (colgroup * kEpilogueCols);
+        // Two register buffers: chunk c + 1 is in flight while chunk c is folded.
+        std::uint32_t r[2][kChunk];
+        tc::TmemLoad16(at, r[0]);
         const float ax = sc[(gl * 128) + rt];
         const float ay = sc[512 + (gl * 128) + rt];
         const float cx = -kMagic * ax;  // exact: a half-precision ax times 3 * 2^22
         const float* bx = sc + 1024 + (gl * 128) + (colgroup * kEpilogueCols);
         const float* by = sc + 1536 + (gl * 128) + (colgroup * kEpilogueCols);
 #pragma unroll
-        for (int part = 0; part < kEpilogueCols / 32; ++part) {
-          std::uint32_t r[32];
-          const std::uint32_t at = tmem + lane_base + (bb * kTileCols) +
-                                   (colgroup * kEpilogueCols) + (part * 32);
-          tc::TmemLoad32(at, r);
-          tc::TmemLoadWait();
-          if (kUseMagic) tc::TmemFill32(at, kMagicBits);  // ready for the buffer's next use
+        for (int c = 0; c < kChunks; ++c) {
+          tc::TmemLoadWait16(r[c & 1]);
+          if (c + 1 < kChunks) {
+            tc::TmemLoad16(at + ((c + 1) * kChunk), r[(c + 1) & 1]);
+          } else {
+            // every column of the buffer is in registers: the tensor core may reuse it
+            tc::TcFenceBefore();
+            __syncwarp();
+            if (lane == 0) tc::MbarArrive(&sh->tmem_empty[gl]);
+          }
 #pragma unroll
-          for (int v = 0; v < 8; ++v) {
-            const float4 x4 = *reinterpret_cast<const float4*>(bx + (part * 32) + (v * 4));
-            const float4 y4 = *reinterpret_cast<const float4*>(by + (part * 32) + (v * 4));
+          for (int v = 0; v < kChunk / 4; ++v) {
+            const float4 x4 = *reinterpret_cast<const float4*>(bx + (c * kChunk) + (v * 4));
+            const float4 y4 = *reinterpret_cast<const float4*>(by + (c * kChunk) + (v * 4));
             const float xs[4] = {x4.x, x4.y, x4.z, x4.w};
             const float ys[4] = {y4.x, y4.y, y4.z, y4.w};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              const int i = (part * 32) + (v * 4) + j;
-              // ax * C, rounded once: ax * (magic + C) - magic * ax
-              const float u = kUseMagic
-                                  ? fmaf(__uint_as_float(r[(v * 4) + j]), ax, cx)
-                                  : ax * static_cast<float>(static_cast<int>(r[(v * 4) + j]));
+              const int i = (c * kChunk) + (v * 4) + j;
+              const std::uint32_t bits = r[c & 1][(v * 4) + j];
+              // ax * C rounded once, either way: with the bias 12582912 + C is the
+              // float whose bits are 0x4B400000 + C, and ax * (bias + C) - bias * ax
+              // is one fused operation.
+              const float u = kRegMagic ? fmaf(__uint_as_float(bits + kMagicBits), ax, cx)
+                                        : ax * static_cast<float>(static_cast<int>(bits));
               acc[i] = fmaf(u, xs[j], acc[i]);
               acc[i] = fmaf(ay, ys[j], acc[i]);
             }
           }
         }
-        if (kUseMagic) tc::TmemStoreWait();
-        tc::TcFenceBefore();
-        __syncwarp();
-        if (lane == 0) tc::MbarArrive(&sh->tmem_empty[bb]);
       }
       __syncwarp();
       if (lane == 0 && ok) tc::MbarArrive(&sh->empty[s]);  // the stage's scales are consumed
     }
     if (ok && row0 + rt < a.nrows) {
-#pragma unroll 4
+#pragma unroll  // fully: a dynamic index would put acc[] in local memory
       for (int i = 0; i < kEpilogueCols; ++i) {
         const int c = col0 + (colgroup * kEpilogueCols) + i;
         if (c < c_end) {

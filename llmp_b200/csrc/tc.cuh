@@ -197,6 +197,26 @@ __device__ __forceinline__ void TmemLoad32(std::uint32_t taddr, std::uint32_t (&
         "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
 }
+// 16 columns; the load is asynchronous until TmemLoadWait16 names its registers.
+__device__ __forceinline__ void TmemLoad16(std::uint32_t taddr, std::uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+// Waits for this thread's tensor-memory loads; taking the registers as operands
+// keeps the compiler from using them before the wait when other loads are in flight.
+__device__ __forceinline__ void TmemLoadWait16(std::uint32_t (&r)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]),
+                 "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]),
+                 "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+               :
+               : "memory");
+}
 // The same 32 lanes x 32 columns written from registers.
 __device__ __forceinline__ void TmemStore32(std::uint32_t taddr, const std::uint32_t (&r)[32]) {
   asm volatile(
