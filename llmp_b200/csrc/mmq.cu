@@ -9,24 +9,31 @@
 //
 // The int8 contraction runs on tcgen05 (kind::i8, int32 accumulators in TMEM).
 // Q4_K's per-group scales forbid accumulating across groups in the tensor
-// core, so every 128x128x32 MMA lands in its own TMEM buffer (four of them, so
-// the tensor core runs up to four groups ahead) and a wide epilogue (8 warps)
-// folds each group's int32 tile into F32 register accumulators.  That fold is
-// CUDA-core work per output element per group and bounds the kernel.
+// core, so every 128x128x32 MMA lands in its own TMEM buffer (three of them, so
+// the tensor core runs ahead) and a wide epilogue (8 warps) folds each group's
+// int32 tile into F32 register accumulators: acc += ((d*sc) * C) * d8.  That
+// fold is CUDA-core work per output element per group, fed by one shared-memory
+// word (d8) per element, and bounds the kernel.  The min terms need no integer
+// product: sum over groups of (-dmin*m)_half * s8_half is a plain FP16
+// contraction over K = k / 32, which the tensor core takes (kind::f16, F32
+// accumulate, a fourth TMEM buffer) from two small K-major FP16 tiles that the
+// decode warps fill; the epilogue adds that buffer once at the end.
 //
 //   warp 0      TMA: activation int8 tiles (128 tokens x 128 K bytes) straight
 //               out of the [k/128][col] block array through a 3-D tensor map
 //               (row pitch 144 B, origin past the 16-byte block header);
 //   warps 1-4   decode: one weight row a thread; unpack the k-block's 128
 //               nibbles to int8 into the 128-byte-swizzled K-major tile the MMA
-//               reads, and the four groups' (d*sc, -dmin*m) half products;
-//               also stage the tokens' (d8, s8) as F32;
+//               reads, the four groups' d*sc as F32 and -dmin*m as FP16; also
+//               stage the tokens' d8 (F32) and s8 (FP16);
 //   warp 5      allocates TMEM and issues the MMAs;
-//   warps 6-13  epilogue: thread = (weight row, half of the token columns).
-// Two measured alternatives are kept behind build macros because both lost on
-// this part: 16 epilogue warps (LLMP_MMQ_EPILOGUE_WARPS=16: 100 against 122
-// TOP/s) and accumulating onto a preloaded bias 0x4B400000 so that the int32 sum
-// reads as the float 12582912 + C without a conversion (LLMP_MMQ_MAGIC=1: 82).
+//   warps 6-13  epilogue: thread = (weight row, half of the token columns);
+//               TMEM loads of 16 columns, the next in flight during a fold.
+// Measured on M 4096, K 4096, N 14336: 122 TOP/s with the min terms folded on
+// CUDA cores and unpipelined TMEM loads; pipelined loads 173.  Alternatives that
+// lost, behind build macros: 16 epilogue warps (LLMP_MMQ_EPILOGUE_WARPS=16) and
+// an integer add of 0x4B400000 in place of the int-to-float conversion
+// (LLMP_MMQ_MAGIC=1: 152 against 173).
 // Every wait is bounded; a wait that runs out raises the device fault counter.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -106,10 +113,15 @@ constexpr int kTileRows = 128;  // weight rows: the MMA's M, one TMEM lane each
 constexpr int kTileCols = 128;  // tokens: the MMA's N
 constexpr int kBK = 128;        // K bytes a stage: four 32-value groups
 constexpr int kStages = 4;
-constexpr int kBuffers = 4;     // TMEM group-result buffers of kTileCols columns
+constexpr int kBuffers = 3;     // TMEM group-result buffers of kTileCols columns
+constexpr int kMinColumn = kBuffers * kTileCols;  // TMEM: the F32 sum of the min terms
 constexpr int kWBytes = kTileRows * kBK, kYBytes = kTileCols * kBK;
 constexpr int kScaleBytes = 4 * 128 * 4;  // [group][row or col] F32
-constexpr int kStageBytes = kWBytes + kYBytes + (4 * kScaleBytes);
+constexpr int kStageBytes = kWBytes + kYBytes + (2 * kScaleBytes);
+// The min terms' operands: FP16 [128 rows][64 groups] K-major, 128-byte swizzled
+// like the int8 tiles; one tile holds 16 k-steps, two tiles alternate.
+constexpr int kMinTileBytes = 128 * 128;
+constexpr int kMinSteps = 16;  // k-steps a tile of min operands covers
 #ifndef LLMP_MMQ_EPILOGUE_WARPS
 #define LLMP_MMQ_EPILOGUE_WARPS 8
 #endif
@@ -126,7 +138,20 @@ constexpr int kChunks = kEpilogueCols / kChunk;
 // exactly (|C| < 2^22): an integer add in place of an integer-to-float conversion.
 constexpr std::uint32_t kMagicBits = 0x4B400000u;
 constexpr float kMagic = 12582912.0f;
-constexpr int kSmem = (kStages * kStageBytes) + 1024 + 512;
+constexpr int kSmem = (kStages * kStageBytes) + (4 * kMinTileBytes) + 1024 + 512;
+
+#ifdef LLMP_MMQ_TIMING
+// Build-time instrumentation: cycles each role spends in its waits, summed over
+// the grid.  [0] producer empty, [1] decode empty, [2] decode loop, [3] MMA
+// w_full, [4] MMA y_full, [5] MMA tmem_empty, [6] epilogue tmem_full,
+// [7] epilogue loop, [8] CTA lifetime, [9] CTAs.
+__device__ unsigned long long g_mmq_cycles[16];
+#define MMQ_T0() const long long t0_ = clock64()
+#define MMQ_T1(slot) local_cycles[slot] += clock64() - t0_
+#else
+#define MMQ_T0()
+#define MMQ_T1(slot)
+#endif
 
 struct Shared {
   std::uint64_t y_full[kStages];
@@ -134,6 +159,8 @@ struct Shared {
   std::uint64_t empty[kStages];
   std::uint64_t tmem_full[kBuffers];
   std::uint64_t tmem_empty[kBuffers];
+  std::uint64_t min_free[2];  // the tensor core has read a tile of min operands
+  std::uint64_t min_full;     // the min terms' sum is complete in tensor memory
   std::uint32_t tmem_base;
   std::uint32_t abort;
 };
@@ -146,15 +173,21 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const Desc a,
       (reinterpret_cast<std::uintptr_t>(raw_smem) + 1023) & ~static_cast<std::uintptr_t>(1023));
   unsigned char* w_tiles = smem;
   unsigned char* y_tiles = w_tiles + (kStages * kWBytes);
-  float* scales = reinterpret_cast<float*>(y_tiles + (kStages * kYBytes));
+  unsigned char* min_w = y_tiles + (kStages * kYBytes);  // [2] tiles: (-dmin * m) per weight row
+  unsigned char* min_y = min_w + (2 * kMinTileBytes);    // [2] tiles: s8 per token
+  float* scales = reinterpret_cast<float*>(min_y + (2 * kMinTileBytes));
   Shared* sh = reinterpret_cast<Shared*>(reinterpret_cast<unsigned char*>(scales) +
-                                         (kStages * 4 * kScaleBytes));
-  // scales of stage s: ax[4][128], ay[4][128] (weight rows), bx[4][128], by[4][128] (tokens)
-  auto stage_scales = [&](int s) { return scales + (static_cast<std::size_t>(s) * 4 * 512); };
+                                         (kStages * 2 * kScaleBytes));
+  // scales of stage s: ax[4][128] (weight rows, d * sc), bx[4][128] (tokens, d8)
+  auto stage_scales = [&](int s) { return scales + (static_cast<std::size_t>(s) * 2 * 512); };
 
   const int warp = static_cast<int>(threadIdx.x) >> 5;
   const int lane = static_cast<int>(threadIdx.x) & 31;
   const int ksteps = a.k / kBK;
+#ifdef LLMP_MMQ_TIMING
+  long long local_cycles[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+  const long long cta_start = clock64();
+#endif
 
   // The tile: weight rows [row0, row0 + 128) of expert e against sorted
   // columns [col0, col0 + 128) of that expert's range [c_begin, c_end).
@@ -184,6 +217,9 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const Desc a,
       tc::MbarInit(&sh->tmem_full[b], 1);
       tc::MbarInit(&sh->tmem_empty[b], kEpilogueWarps);
     }
+    tc::MbarInit(&sh->min_free[0], 1);
+    tc::MbarInit(&sh->min_free[1], 1);
+    tc::MbarInit(&sh->min_full, 1);
     sh->abort = 0;
     tc::MbarInitFence();
   }
@@ -207,10 +243,12 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const Desc a,
       tc::PrefetchMap(&map_y);
       for (int ks = 0; ks < ksteps && !*abort_flag; ++ks) {
         const int s = ks % kStages;
-        if (!tc::MbarWait(&sh->empty[s], ((ks / kStages) & 1) ^ 1)) {
+        MMQ_T0();
+        if (!tc::MbarWaitSleep(&sh->empty[s], ((ks / kStages) & 1) ^ 1, 256)) {
           give_up();
           break;
         }
+        MMQ_T1(0);
         tc::MbarExpectTx(&sh->y_full[s], kYBytes);
         asm volatile(
             "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
@@ -242,8 +280,10 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const Desc a,
       const uint4 ds = *reinterpret_cast<const uint4*>(
           ycol + (static_cast<std::size_t>(ks) * a.ncols * 144));
       bool ok = true;
-      if (lane == 0) ok = tc::MbarWait(&sh->empty[s], ((ks / kStages) & 1) ^ 1);
+      MMQ_T0();
+      if (lane == 0) ok = tc::MbarWaitSleep(&sh->empty[s], ((ks / kStages) & 1) ^ 1, 128);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      MMQ_T1(1);
       if (!ok) {
         if (lane == 0) give_up();
         break;
@@ -267,6 +307,17 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const Desc a,
         *reinterpret_cast<uint4*>(wt + (((j + 2) ^ (t & 7)) * 16)) = hi0;
         *reinterpret_cast<uint4*>(wt + (((j + 3) ^ (t & 7)) * 16)) = hi1;
       }
+      // The tile of min operands this k-step writes into, once the tensor core is
+      // done with its previous contents (32 k-steps ago).
+      const int mt = (ks / kMinSteps) & 1;
+      if (ks >= 2 * kMinSteps && ks % kMinSteps == 0) {
+        if (lane == 0) ok = tc::MbarWait(&sh->min_free[mt], ((ks / (2 * kMinSteps)) - 1) & 1);
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) {
+          if (lane == 0) give_up();
+          break;
+        }
+      }
       // The four groups' half products (d * sc, -dmin * m): GGML's tile loader
       // multiplies in half precision.
       float* sc = stage_scales(s);
@@ -274,6 +325,7 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const Desc a,
         const std::uint32_t s0 = head.y, s1 = head.z, s2 = head.w;
         const __half d = __ushort_as_half(static_cast<unsigned short>(head.x & 0xffffu));
         const __half dmin = __hneg(__ushort_as_half(static_cast<unsigned short>(head.x >> 16)));
+        std::uint32_t mins[4];
 #pragma unroll
         for (int gl = 0; gl < 4; ++gl) {
           int scv, mnv;
@@ -285,13 +337,29 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const Desc a,
             mnv = static_cast<int>(((s2 >> ((8 * gl) + 4)) & 15u) | (((s1 >> ((8 * gl) + 6)) & 3u) << 4));
           }
           sc[(gl * 128) + t] = row_live ? __half2float(__hmul(d, __int2half_rn(scv))) : 0.0f;
-          sc[512 + (gl * 128) + t] = row_live ? __half2float(__hmul(dmin, __int2half_rn(mnv))) : 0.0f;
+          mins[gl] = row_live ? __half_as_ushort(__hmul(dmin, __int2half_rn(mnv))) : 0u;
         }
         const std::uint32_t dsw[4] = {ds.x, ds.y, ds.z, ds.w};
 #pragma unroll
-        for (int gl = 0; gl < 4; ++gl) {
-          sc[1024 + (gl * 128) + t] = HalfBitsToFloat(dsw[gl] & 0xffffu);
-          sc[1536 + (gl * 128) + t] = HalfBitsToFloat(dsw[gl] >> 16);
+        for (int gl = 0; gl < 4; ++gl) sc[512 + (gl * 128) + t] = HalfBitsToFloat(dsw[gl] & 0xffffu);
+        // Row t of both min tiles, the four halves of this k-step: byte (ks % 16) * 8
+        // of the 128-byte row, 16-byte chunks swizzled like the int8 tiles.
+        const int kk = ks % kMinSteps;
+        const int at = ((t >> 3) * 1024) + ((t & 7) * 128) + ((((kk >> 1) ^ (t & 7))) * 16) +
+                       ((kk & 1) * 8);
+        *reinterpret_cast<uint2*>(min_w + (mt * kMinTileBytes) + at) =
+            make_uint2(mins[0] | (mins[1] << 16), mins[2] | (mins[3] << 16));
+        *reinterpret_cast<uint2*>(min_y + (mt * kMinTileBytes) + at) =
+            make_uint2((dsw[0] >> 16) | (dsw[1] & 0xffff0000u), (dsw[2] >> 16) | (dsw[3] & 0xffff0000u));
+        // The last FP16 MMA reads 16 groups: zero what the k range leaves unwritten.
+        if (ks == ksteps - 1) {
+          for (int pad = ks + 1; pad % 4 != 0; ++pad) {
+            const int pk = pad % kMinSteps;
+            const int pat = ((t >> 3) * 1024) + ((t & 7) * 128) + ((((pk >> 1) ^ (t & 7))) * 16) +
+                            ((pk & 1) * 8);
+            *reinterpret_cast<uint2*>(min_w + (mt * kMinTileBytes) + pat) = make_uint2(0u, 0u);
+            *reinterpret_cast<uint2*>(min_y + (mt * kMinTileBytes) + pat) = make_uint2(0u, 0u);
+          }
         }
       }
       tc::FenceProxyAsync();  // generic-proxy writes, read by the tensor core's proxy
@@ -305,23 +373,49 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const Desc a,
       std::uint32_t group = 0;
       for (int ks = 0; ks < ksteps && !*abort_flag; ++ks) {
         const int s = ks % kStages;
-        if (!tc::MbarWait(&sh->w_full[s], (ks / kStages) & 1) ||
-            !tc::MbarWait(&sh->y_full[s], (ks / kStages) & 1)) {
-          give_up();
-          break;
+        {
+          MMQ_T0();
+          const bool w_ok = tc::MbarWait(&sh->w_full[s], (ks / kStages) & 1);
+          MMQ_T1(3);
+          if (!w_ok) {
+            give_up();
+            break;
+          }
+        }
+        {
+          MMQ_T0();
+          const bool y_ok = tc::MbarWait(&sh->y_full[s], (ks / kStages) & 1);
+          MMQ_T1(4);
+          if (!y_ok) {
+            give_up();
+            break;
+          }
         }
         tc::TcFenceAfter();
         const std::uint64_t wdesc = tc::SmemDesc(w_tiles + (s * kWBytes), true, 1024);
         const std::uint64_t ydesc = tc::SmemDesc(y_tiles + (s * kYBytes), true, 1024);
         for (int gl = 0; gl < 4; ++gl, ++group) {
           const int b = static_cast<int>(group % kBuffers);
-          if (!tc::MbarWait(&sh->tmem_empty[b], ((group / kBuffers) & 1u) ^ 1u)) {
+          MMQ_T0();
+          if (!tc::MbarWaitSleep(&sh->tmem_empty[b], ((group / kBuffers) & 1u) ^ 1u, 32)) {
             give_up();
             break;
           }
+          MMQ_T1(5);
           tc::TcFenceAfter();
           tc::MmaI8(tmem + (b * kTileCols), wdesc + (gl * 2), ydesc + (gl * 2), idesc, false);
           tc::TcCommit(&sh->tmem_full[b]);
+        }
+        // Every fourth k-step completes 16 groups of min operands: one FP16 MMA
+        // (K 16) adds their products to the F32 sum.
+        if (ks % 4 == 3 || ks == ksteps - 1) {
+          const int mt = (ks / kMinSteps) & 1;
+          const int q = (ks % kMinSteps) / 4;  // 32 bytes along the swizzled row each
+          tc::MmaF16(tmem + kMinColumn, tc::SmemDesc(min_w + (mt * kMinTileBytes), true, 1024) + (q * 2),
+                     tc::SmemDesc(min_y + (mt * kMinTileBytes), true, 1024) + (q * 2),
+                     tc::IdescF16(kTileRows, kTileCols), ks >= 4);
+          if (ks % kMinSteps == kMinSteps - 1) tc::TcCommit(&sh->min_free[mt]);
+          if (ks == ksteps - 1) tc::TcCommit(&sh->min_full);
         }
       }
     }
@@ -336,47 +430,53 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const Desc a,
 #pragma unroll
     for (int i = 0; i < kEpilogueCols; ++i) acc[i] = 0.0f;
     bool ok = true;
+    int bb = 0;                  // the group's TMEM buffer and its use's parity
+    std::uint32_t parity = 0;
     for (int ks = 0; ks < ksteps && ok; ++ks) {
       const int s = ks % kStages;
       const float* sc = stage_scales(s);
-      static_assert(kBuffers == 4, "group gl of every k-step lands in buffer gl");
 #pragma unroll
       for (int gl = 0; gl < 4; ++gl) {
         if (!ok) break;
-        if (lane == 0) ok = tc::MbarWait(&sh->tmem_full[gl], static_cast<std::uint32_t>(ks) & 1u);
+        MMQ_T0();
+        if (lane == 0) ok = tc::MbarWait(&sh->tmem_full[bb], parity);
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        MMQ_T1(6);
         if (!ok || *abort_flag) {
           if (lane == 0 && !ok) give_up();
           ok = false;
           break;
         }
         tc::TcFenceAfter();
-        const std::uint32_t at = tmem + lane_base + (gl * kTileCols) + (colgroup * kEpilogueCols);
+        const std::uint32_t at = tmem + lane_base + (bb * kTileCols) + (colgroup * kEpilogueCols);
         // Two register buffers: chunk c + 1 is in flight while chunk c is folded.
         std::uint32_t r[2][kChunk];
         tc::TmemLoad16(at, r[0]);
         const float ax = sc[(gl * 128) + rt];
-        const float ay = sc[512 + (gl * 128) + rt];
         const float cx = -kMagic * ax;  // exact: a half-precision ax times 3 * 2^22
-        const float* bx = sc + 1024 + (gl * 128) + (colgroup * kEpilogueCols);
-        const float* by = sc + 1536 + (gl * 128) + (colgroup * kEpilogueCols);
+        const float* bx = sc + 512 + (gl * 128) + (colgroup * kEpilogueCols);
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) {
-          tc::TmemLoadWait16(r[c & 1]);
+          {
+            MMQ_T0();
+            tc::TmemLoadWait16(r[c & 1]);
+            MMQ_T1(10);
+          }
           if (c + 1 < kChunks) {
             tc::TmemLoad16(at + ((c + 1) * kChunk), r[(c + 1) & 1]);
           } else {
             // every column of the buffer is in registers: the tensor core may reuse it
             tc::TcFenceBefore();
             __syncwarp();
-            if (lane == 0) tc::MbarArrive(&sh->tmem_empty[gl]);
+            if (lane == 0) tc::MbarArrive(&sh->tmem_empty[bb]);
           }
+#ifdef LLMP_MMQ_TIMING
+          const long long fold0 = clock64();
+#endif
 #pragma unroll
           for (int v = 0; v < kChunk / 4; ++v) {
             const float4 x4 = *reinterpret_cast<const float4*>(bx + (c * kChunk) + (v * 4));
-            const float4 y4 = *reinterpret_cast<const float4*>(by + (c * kChunk) + (v * 4));
             const float xs[4] = {x4.x, x4.y, x4.z, x4.w};
-            const float ys[4] = {y4.x, y4.y, y4.z, y4.w};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const int i = (c * kChunk) + (v * 4) + j;
@@ -387,13 +487,37 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const Desc a,
               const float u = kRegMagic ? fmaf(__uint_as_float(bits + kMagicBits), ax, cx)
                                         : ax * static_cast<float>(static_cast<int>(bits));
               acc[i] = fmaf(u, xs[j], acc[i]);
-              acc[i] = fmaf(ay, ys[j], acc[i]);
             }
           }
+#ifdef LLMP_MMQ_TIMING
+          local_cycles[11] += clock64() - fold0;
+#endif
+        }
+        if (++bb == kBuffers) {
+          bb = 0;
+          parity ^= 1u;
         }
       }
       __syncwarp();
       if (lane == 0 && ok) tc::MbarArrive(&sh->empty[s]);  // the stage's scales are consumed
+    }
+    // The min terms: sum over the groups of (-dmin * m) * s8, taken by the tensor core.
+    if (ok) {
+      if (lane == 0) ok = tc::MbarWait(&sh->min_full, 0);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok && lane == 0) give_up();
+    }
+    if (ok) {
+      tc::TcFenceAfter();
+      const std::uint32_t at = tmem + lane_base + kMinColumn + (colgroup * kEpilogueCols);
+#pragma unroll
+      for (int c = 0; c < kChunks; ++c) {
+        std::uint32_t r[kChunk];
+        tc::TmemLoad16(at + (c * kChunk), r);
+        tc::TmemLoadWait16(r);
+#pragma unroll
+        for (int j = 0; j < kChunk; ++j) acc[(c * kChunk) + j] += __uint_as_float(r[j]);
+      }
     }
     if (ok && row0 + rt < a.nrows) {
 #pragma unroll  // fully: a dynamic index would put acc[] in local memory
@@ -407,6 +531,28 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const Desc a,
     }
   }
 
+#ifdef LLMP_MMQ_TIMING
+  if (lane == 0) {
+    const long long life = clock64() - cta_start;
+    if (warp == 0) {
+      atomicAdd(&g_mmq_cycles[0], static_cast<unsigned long long>(local_cycles[0]));
+      atomicAdd(&g_mmq_cycles[8], static_cast<unsigned long long>(life));
+      atomicAdd(&g_mmq_cycles[9], 1ull);
+    } else if (warp == 1) {
+      atomicAdd(&g_mmq_cycles[1], static_cast<unsigned long long>(local_cycles[1]));
+      atomicAdd(&g_mmq_cycles[2], static_cast<unsigned long long>(life));
+    } else if (warp == 5) {
+      for (int i = 3; i <= 5; ++i) {
+        atomicAdd(&g_mmq_cycles[i], static_cast<unsigned long long>(local_cycles[i]));
+      }
+    } else if (warp == 6) {
+      atomicAdd(&g_mmq_cycles[6], static_cast<unsigned long long>(local_cycles[6]));
+      atomicAdd(&g_mmq_cycles[7], static_cast<unsigned long long>(life));
+      atomicAdd(&g_mmq_cycles[10], static_cast<unsigned long long>(local_cycles[10]));
+      atomicAdd(&g_mmq_cycles[11], static_cast<unsigned long long>(local_cycles[11]));
+    }
+  }
+#endif
   tc::TcFenceBefore();
   __syncthreads();
   if (warp == 5) {
@@ -493,6 +639,18 @@ int LaunchMmq(const llmp_b200_mmq_desc& d, const std::int32_t* worklist, int max
 }
 
 }  // namespace llmp_b200
+
+#ifdef LLMP_MMQ_TIMING
+extern "C" int llmp_b200_mmq_debug_cycles(unsigned long long* out16, int reset) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out16, llmp_b200::g_mmq_cycles, sizeof(unsigned long long) * 16);
+  if (reset) {
+    unsigned long long zero[16] = {};
+    cudaMemcpyToSymbol(llmp_b200::g_mmq_cycles, zero, sizeof(zero));
+  }
+  return 0;
+}
+#endif
 
 extern "C" {
 

@@ -76,6 +76,27 @@ __device__ __forceinline__ bool MbarWait(std::uint64_t* bar, std::uint32_t parit
   }
   return false;
 }
+// The same with a sleep between polls: for a role that runs far ahead and whose
+// polling would take issue slots from the warps doing the work.
+__device__ __forceinline__ bool MbarWaitSleep(std::uint64_t* bar, std::uint32_t parity,
+                                              unsigned ns) {
+  const std::uint32_t addr = Smem(bar);
+  for (std::uint32_t i = 0; i < kSpinLimit; ++i) {
+    std::uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+    __nanosleep(ns);
+  }
+  return false;
+}
 
 // TMA: 2-D tile of a tensor map into shared memory (no multicast).
 __device__ __forceinline__ void TmaLoad2D(void* smem, const CUtensorMap* map, int c0, int c1,
@@ -146,6 +167,11 @@ __host__ __device__ constexpr std::uint32_t IdescI8(int m, int n, bool a_signed,
   return (2u << 4) | ((a_signed ? 1u : 0u) << 7) | ((b_signed ? 1u : 0u) << 10) |
          (static_cast<std::uint32_t>(n >> 3) << 17) | (static_cast<std::uint32_t>(m >> 4) << 24);
 }
+// kind::f16: A, B FP16 K-major, F32 accumulate.
+__host__ __device__ constexpr std::uint32_t IdescF16(int m, int n) {
+  return (1u << 4) | (static_cast<std::uint32_t>(n >> 3) << 17) |
+         (static_cast<std::uint32_t>(m >> 4) << 24);
+}
 // kind::mxf8f6f4.block_scale: E4M3 x E4M3, E8M0 scales per 32, F32 accumulate.
 __host__ __device__ constexpr std::uint32_t IdescMxf8(int m, int n, int a_sf_id, int b_sf_id) {
   return (static_cast<std::uint32_t>(b_sf_id) << 4) | (static_cast<std::uint32_t>(n >> 3) << 17) |
@@ -160,6 +186,17 @@ __device__ __forceinline__ void MmaI8(std::uint32_t tmem_d, std::uint64_t a, std
       ".reg .pred p;\n"
       "setp.ne.b32 p, %4, 0;\n"
       "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n"
+      "}\n"
+      ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate ? 1u : 0u)
+      : "memory");
+}
+__device__ __forceinline__ void MmaF16(std::uint32_t tmem_d, std::uint64_t a, std::uint64_t b,
+                                       std::uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
       "}\n"
       ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate ? 1u : 0u)
       : "memory");

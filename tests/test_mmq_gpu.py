@@ -49,7 +49,10 @@ def _check(got, want32, want64, what=""):
 
 
 @pytest.mark.parametrize("cols,n,k", [(128, 128, 256), (512, 256, 1024), (100, 200, 512),
-                                      (1, 1, 256), (129, 130, 768), (300, 384, 4096)])
+                                      (1, 1, 256), (129, 130, 768), (300, 384, 4096),
+                                      # k-steps 10 (a partial last group of 16 min terms) and
+                                      # 66 (both tiles of min operands reused)
+                                      (40, 136, 1280), (64, 128, 8448)])
 def test_dense_mmq_matches_the_oracle(cuda, orc, cols, n, k):
     torch = cuda
     ops = _ops()
