@@ -112,7 +112,7 @@ QuantizeMmqKernel(const void* __restrict__ x, std::int64_t row_stride, int k, st
 constexpr int kTileRows = 128;  // weight rows: the MMA's M, one TMEM lane each
 constexpr int kTileCols = 128;  // tokens: the MMA's N
 constexpr int kBK = 128;        // K bytes a stage: four 32-value groups
-constexpr int kStages = 4;
+constexpr int kStages = 3;
 constexpr int kBuffers = 3;     // TMEM group-result buffers of kTileCols columns
 constexpr int kMinColumn = kBuffers * kTileCols;  // TMEM: the F32 sum of the min terms
 constexpr int kWBytes = kTileRows * kBK, kYBytes = kTileCols * kBK;
@@ -122,6 +122,12 @@ constexpr int kStageBytes = kWBytes + kYBytes + (2 * kScaleBytes);
 // like the int8 tiles; one tile holds 16 k-steps, two tiles alternate.
 constexpr int kMinTileBytes = 128 * 128;
 constexpr int kMinSteps = 16;  // k-steps a tile of min operands covers
+// Raw stages: what TMA brings for one super-block column (two k-steps): the 128
+// weight rows' Q4_K blocks, then the 128 tokens' block headers of both k-steps.
+constexpr int kRawStages = 2;
+constexpr int kRawWBytes = 128 * 144;
+constexpr int kRawHBytes = 128 * 16;
+constexpr int kRawBytes = kRawWBytes + (2 * kRawHBytes);
 #ifndef LLMP_MMQ_EPILOGUE_WARPS
 #define LLMP_MMQ_EPILOGUE_WARPS 8
 #endif
@@ -138,7 +144,8 @@ constexpr int kChunks = kEpilogueCols / kChunk;
 // exactly (|C| < 2^22): an integer add in place of an integer-to-float conversion.
 constexpr std::uint32_t kMagicBits = 0x4B400000u;
 constexpr float kMagic = 12582912.0f;
-constexpr int kSmem = (kStages * kStageBytes) + (4 * kMinTileBytes) + 1024 + 512;
+constexpr int kSmem =
+    (kStages * kStageBytes) + (4 * kMinTileBytes) + (kRawStages * kRawBytes) + 1024 + 512;
 
 #ifdef LLMP_MMQ_TIMING
 // Build-time instrumentation: cycles each role spends in its waits, summed over
@@ -159,6 +166,8 @@ struct Shared {
   std::uint64_t empty[kStages];
   std::uint64_t tmem_full[kBuffers];
   std::uint64_t tmem_empty[kBuffers];
+  std::uint64_t raw_full[kRawStages];
+  std::uint64_t raw_empty[kRawStages];
   std::uint64_t min_free[2];  // the tensor core has read a tile of min operands
   std::uint64_t min_full;     // the min terms' sum is complete in tensor memory
   std::uint32_t tmem_base;
@@ -166,7 +175,8 @@ struct Shared {
 };
 
 __global__ void __launch_bounds__(kThreads, 1)
-MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const Desc a,
+MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ CUtensorMap map_w,
+             const __grid_constant__ CUtensorMap map_h, const Desc a,
              const std::int32_t* __restrict__ worklist, unsigned int* faults) {
   extern __shared__ unsigned char raw_smem[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
@@ -175,7 +185,8 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const Desc a,
   unsigned char* y_tiles = w_tiles + (kStages * kWBytes);
   unsigned char* min_w = y_tiles + (kStages * kYBytes);  // [2] tiles: (-dmin * m) per weight row
   unsigned char* min_y = min_w + (2 * kMinTileBytes);    // [2] tiles: s8 per token
-  float* scales = reinterpret_cast<float*>(min_y + (2 * kMinTileBytes));
+  unsigned char* raw = min_y + (2 * kMinTileBytes);      // [kRawStages] raw stages
+  float* scales = reinterpret_cast<float*>(raw + (kRawStages * kRawBytes));
   Shared* sh = reinterpret_cast<Shared*>(reinterpret_cast<unsigned char*>(scales) +
                                          (kStages * 2 * kScaleBytes));
   // scales of stage s: ax[4][128] (weight rows, d * sc), bx[4][128] (tokens, d8)
@@ -217,6 +228,10 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const Desc a,
       tc::MbarInit(&sh->tmem_full[b], 1);
       tc::MbarInit(&sh->tmem_empty[b], kEpilogueWarps);
     }
+    for (int r = 0; r < kRawStages; ++r) {
+      tc::MbarInit(&sh->raw_full[r], 1);
+      tc::MbarInit(&sh->raw_empty[r], 4);
+    }
     tc::MbarInit(&sh->min_free[0], 1);
     tc::MbarInit(&sh->min_free[1], 1);
     tc::MbarInit(&sh->min_full, 1);
@@ -241,7 +256,33 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const Desc a,
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       tc::PrefetchMap(&map_y);
+      tc::PrefetchMap(&map_w);
+      tc::PrefetchMap(&map_h);
       for (int ks = 0; ks < ksteps && !*abort_flag; ++ks) {
+        if ((ks & 1) == 0) {
+          // One super-block column (k-steps ks, ks + 1): the weight rows' blocks and
+          // the tokens' block headers, for the decode warps.
+          const int column = ks >> 1;
+          const int rs = column % kRawStages;
+          if (!tc::MbarWaitSleep(&sh->raw_empty[rs], ((column / kRawStages) & 1) ^ 1, 128)) {
+            give_up();
+            break;
+          }
+          unsigned char* stage = raw + (rs * kRawBytes);
+          tc::MbarExpectTx(&sh->raw_full[rs], kRawBytes);
+          asm volatile(
+              "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+              " [%0], [%1, {%3, %4, %5}], [%2];"
+              ::"r"(tc::Smem(stage)), "l"(&map_w), "r"(tc::Smem(&sh->raw_full[rs])),
+                "r"(column * 144), "r"(row0), "r"(expert)
+              : "memory");
+          asm volatile(
+              "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+              " [%0], [%1, {%3, %4, %5}], [%2];"
+              ::"r"(tc::Smem(stage + kRawWBytes)), "l"(&map_h), "r"(tc::Smem(&sh->raw_full[rs])),
+                "r"(0), "r"(col0), "r"(ks)
+              : "memory");
+        }
         const int s = ks % kStages;
         MMQ_T0();
         if (!tc::MbarWaitSleep(&sh->empty[s], ((ks / kStages) & 1) ^ 1, 256)) {
@@ -261,27 +302,35 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const Desc a,
   } else if (warp >= 1 && warp <= 4) {
     // ------------------------------------------------------------ decode
     const int t = (static_cast<int>(threadIdx.x) - 32);  // 0..127: weight row / token of the tile
-    const int row = min(row0 + t, a.nrows - 1);
-    const bool row_live = row0 + t < a.nrows;
-    const std::uint8_t* wrow = static_cast<const std::uint8_t*>(a.w) +
-                               ((static_cast<std::size_t>(expert) * a.stride_expert +
-                                 static_cast<std::size_t>(row) * a.stride_row) * 144);
-    const int col = min(col0 + t, a.ncols - 1);
-    const std::uint8_t* ycol = static_cast<const std::uint8_t*>(a.y) + (static_cast<std::size_t>(col) * 144);
+    // Rows past the matrix and tokens past the batch arrive as zero blocks (TMA's
+    // fill): zero scales, zero codes, nothing stored for them.
     for (int ks = 0; ks < ksteps && !*abort_flag; ++ks) {
       const int s = ks % kStages;
-      // Fetch before waiting for the stage: global latency overlaps the wait.
-      const std::uint8_t* sb = wrow + (static_cast<std::size_t>(ks >> 1) * 144);
       const int half = ks & 1;
-      const uint4 head = LoadStream16(sb);
+      const int column = ks >> 1;
+      const int rs = column % kRawStages;
+      bool ok = true;
+      if (half == 0) {
+        if (lane == 0) ok = tc::MbarWait(&sh->raw_full[rs], (column / kRawStages) & 1);
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) {
+          if (lane == 0) give_up();
+          break;
+        }
+      }
+      const unsigned char* stage = raw + (rs * kRawBytes);
+      const unsigned char* sb = stage + (t * 144);
+      const uint4 head = *reinterpret_cast<const uint4*>(sb);
       uint4 q[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) q[i] = LoadStream16(sb + 16 + (half * 64) + (i * 16));
-      const uint4 ds = *reinterpret_cast<const uint4*>(
-          ycol + (static_cast<std::size_t>(ks) * a.ncols * 144));
-      bool ok = true;
+      for (int i = 0; i < 4; ++i) q[i] = *reinterpret_cast<const uint4*>(sb + 16 + (half * 64) + (i * 16));
+      const uint4 ds = *reinterpret_cast<const uint4*>(stage + kRawWBytes + (half * kRawHBytes) + (t * 16));
+      if (half == 1) {  // this warp has read all it needs of the raw stage
+        __syncwarp();
+        if (lane == 0) tc::MbarArrive(&sh->raw_empty[rs]);
+      }
       MMQ_T0();
-      if (lane == 0) ok = tc::MbarWaitSleep(&sh->empty[s], ((ks / kStages) & 1) ^ 1, 128);
+      if (lane == 0) ok = tc::MbarWaitSleep(&sh->empty[s], ((ks / kStages) & 1) ^ 1, 64);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       MMQ_T1(1);
       if (!ok) {
@@ -290,17 +339,16 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const Desc a,
       }
       // int8 codes into the swizzled K-major tile: row t, 16-byte chunk j at j ^ (t % 8)
       unsigned char* wt = w_tiles + (s * kWBytes) + ((t >> 3) * 1024) + ((t & 7) * 128);
-      const std::uint32_t z = row_live ? 0xffffffffu : 0u;
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
-        const uint4 lo0 = make_uint4(q[2 * cc].x & 0x0f0f0f0fu & z, q[2 * cc].y & 0x0f0f0f0fu & z,
-                                     q[2 * cc].z & 0x0f0f0f0fu & z, q[2 * cc].w & 0x0f0f0f0fu & z);
-        const uint4 lo1 = make_uint4(q[2 * cc + 1].x & 0x0f0f0f0fu & z, q[2 * cc + 1].y & 0x0f0f0f0fu & z,
-                                     q[2 * cc + 1].z & 0x0f0f0f0fu & z, q[2 * cc + 1].w & 0x0f0f0f0fu & z);
-        const uint4 hi0 = make_uint4((q[2 * cc].x >> 4) & 0x0f0f0f0fu & z, (q[2 * cc].y >> 4) & 0x0f0f0f0fu & z,
-                                     (q[2 * cc].z >> 4) & 0x0f0f0f0fu & z, (q[2 * cc].w >> 4) & 0x0f0f0f0fu & z);
-        const uint4 hi1 = make_uint4((q[2 * cc + 1].x >> 4) & 0x0f0f0f0fu & z, (q[2 * cc + 1].y >> 4) & 0x0f0f0f0fu & z,
-                                     (q[2 * cc + 1].z >> 4) & 0x0f0f0f0fu & z, (q[2 * cc + 1].w >> 4) & 0x0f0f0f0fu & z);
+        const uint4 lo0 = make_uint4(q[2 * cc].x & 0x0f0f0f0fu, q[2 * cc].y & 0x0f0f0f0fu,
+                                     q[2 * cc].z & 0x0f0f0f0fu, q[2 * cc].w & 0x0f0f0f0fu);
+        const uint4 lo1 = make_uint4(q[2 * cc + 1].x & 0x0f0f0f0fu, q[2 * cc + 1].y & 0x0f0f0f0fu,
+                                     q[2 * cc + 1].z & 0x0f0f0f0fu, q[2 * cc + 1].w & 0x0f0f0f0fu);
+        const uint4 hi0 = make_uint4((q[2 * cc].x >> 4) & 0x0f0f0f0fu, (q[2 * cc].y >> 4) & 0x0f0f0f0fu,
+                                     (q[2 * cc].z >> 4) & 0x0f0f0f0fu, (q[2 * cc].w >> 4) & 0x0f0f0f0fu);
+        const uint4 hi1 = make_uint4((q[2 * cc + 1].x >> 4) & 0x0f0f0f0fu, (q[2 * cc + 1].y >> 4) & 0x0f0f0f0fu,
+                                     (q[2 * cc + 1].z >> 4) & 0x0f0f0f0fu, (q[2 * cc + 1].w >> 4) & 0x0f0f0f0fu);
         const int j = cc * 4;  // groups 2cc (chunks j, j+1) and 2cc+1 (chunks j+2, j+3)
         *reinterpret_cast<uint4*>(wt + (((j + 0) ^ (t & 7)) * 16)) = lo0;
         *reinterpret_cast<uint4*>(wt + (((j + 1) ^ (t & 7)) * 16)) = lo1;
@@ -336,8 +384,8 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const Desc a,
             scv = static_cast<int>(((s2 >> (8 * gl)) & 15u) | (((s0 >> ((8 * gl) + 6)) & 3u) << 4));
             mnv = static_cast<int>(((s2 >> ((8 * gl) + 4)) & 15u) | (((s1 >> ((8 * gl) + 6)) & 3u) << 4));
           }
-          sc[(gl * 128) + t] = row_live ? __half2float(__hmul(d, __int2half_rn(scv))) : 0.0f;
-          mins[gl] = row_live ? __half_as_ushort(__hmul(dmin, __int2half_rn(mnv))) : 0u;
+          sc[(gl * 128) + t] = __half2float(__hmul(d, __int2half_rn(scv)));
+          mins[gl] = __half_as_ushort(__hmul(dmin, __int2half_rn(mnv)));
         }
         const std::uint32_t dsw[4] = {ds.x, ds.y, ds.z, ds.w};
 #pragma unroll
@@ -608,6 +656,41 @@ int LaunchMmq(const llmp_b200_mmq_desc& d, const std::int32_t* worklist, int max
       return Reject("mmq: the driver refused a tensor map for the activation blocks");
     }
   }
+  // The weights as bytes [expert][row][k / 256 * 144]: a box is one block of 128 rows.
+  CUtensorMap map_w;
+  {
+    const int experts = d.expert_bounds != nullptr ? d.experts : 1;
+    const cuuint64_t row_pitch = static_cast<cuuint64_t>(d.stride_row) * 144;
+    const cuuint64_t expert_pitch =
+        experts > 1 ? static_cast<cuuint64_t>(d.stride_expert) * 144
+                    : row_pitch * static_cast<cuuint64_t>(d.nrows);
+    const cuuint64_t dims[3] = {static_cast<cuuint64_t>(d.k / 256) * 144,
+                                static_cast<cuuint64_t>(d.nrows), static_cast<cuuint64_t>(experts)};
+    const cuuint64_t strides[2] = {row_pitch, expert_pitch};
+    const cuuint32_t box[3] = {144, kTileRows, 1};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    if (encode(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(d.w), dims, strides,
+               box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+      return Reject("mmq: the driver refused a tensor map for the weight blocks");
+    }
+  }
+  // The activation blocks' 16-byte headers [k / 128][col]: a box is 128 tokens, two k-steps.
+  CUtensorMap map_h;
+  {
+    const cuuint64_t dims[3] = {16, static_cast<cuuint64_t>(d.ncols),
+                                static_cast<cuuint64_t>(d.k / 128)};
+    const cuuint64_t strides[2] = {144, static_cast<cuuint64_t>(d.ncols) * 144};
+    const cuuint32_t box[3] = {16, kTileCols, 2};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    if (encode(&map_h, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(d.y), dims, strides,
+               box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+               CU_TENSOR_MAP_L2_PROMOTION_NONE,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+      return Reject("mmq: the driver refused a tensor map for the activation headers");
+    }
+  }
   unsigned int* faults = FaultCounter();
   if (faults == nullptr) return Reject("mmq: no fault counter on this device");
   static thread_local int configured_device = -1;
@@ -631,8 +714,8 @@ int LaunchMmq(const llmp_b200_mmq_desc& d, const std::int32_t* worklist, int max
     grid.z = static_cast<unsigned>(experts);
   }
   if (grid.y > 65535u) return Reject("mmq: more column tiles than a grid holds");
-  MmqQ4KKernel<<<grid, kThreads, kSmem, static_cast<cudaStream_t>(stream)>>>(map_y, d, worklist,
-                                                                             faults);
+  MmqQ4KKernel<<<grid, kThreads, kSmem, static_cast<cudaStream_t>(stream)>>>(map_y, map_w, map_h, d,
+                                                                             worklist, faults);
   const cudaError_t e = cudaPeekAtLastError();
   if (e != cudaSuccess) return Failed(cudaGetLastError(), "mmq launch");
   return 0;
