@@ -131,14 +131,21 @@ constexpr int kRawBytes = kRawWBytes + (2 * kRawHBytes);
 #ifndef LLMP_MMQ_EPILOGUE_WARPS
 #define LLMP_MMQ_EPILOGUE_WARPS 8
 #endif
+#ifndef LLMP_MMQ_DECODE_WARPS
+#define LLMP_MMQ_DECODE_WARPS 2
+#endif
 #ifndef LLMP_MMQ_MAGIC
 #define LLMP_MMQ_MAGIC 0
 #endif
 constexpr int kEpilogueWarps = LLMP_MMQ_EPILOGUE_WARPS;
 constexpr bool kRegMagic = LLMP_MMQ_MAGIC != 0;
-constexpr int kThreads = (6 + kEpilogueWarps) * 32;
+constexpr int kDecodeWarps = LLMP_MMQ_DECODE_WARPS;  // warps 1 .. kDecodeWarps
+constexpr int kMmaWarp = kDecodeWarps + 1;
+constexpr int kFirstEpilogueWarp = kDecodeWarps + 2;  // a multiple of 4: warp % 4 is its TMEM quadrant
+constexpr int kThreads = (kFirstEpilogueWarp + kEpilogueWarps) * 32;
+static_assert(kFirstEpilogueWarp % 4 == 0, "epilogue warp e must sit in TMEM quadrant e % 4");
 constexpr int kEpilogueCols = kTileCols / (kEpilogueWarps / 4);  // columns a thread
-constexpr int kChunk = 16;                                       // columns a TMEM load
+constexpr int kChunk = 32;                                       // columns a TMEM load
 constexpr int kChunks = kEpilogueCols / kChunk;
 // An int32 sum C added to this bit pattern reads, as a float, 12582912 + C
 // exactly (|C| < 2^22): an integer add in place of an integer-to-float conversion.
@@ -221,7 +228,7 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       tc::MbarInit(&sh->y_full[s], 1);
-      tc::MbarInit(&sh->w_full[s], 4);
+      tc::MbarInit(&sh->w_full[s], kDecodeWarps);
       tc::MbarInit(&sh->empty[s], kEpilogueWarps);
     }
     for (int b = 0; b < kBuffers; ++b) {
@@ -230,7 +237,7 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
     }
     for (int r = 0; r < kRawStages; ++r) {
       tc::MbarInit(&sh->raw_full[r], 1);
-      tc::MbarInit(&sh->raw_empty[r], 4);
+      tc::MbarInit(&sh->raw_empty[r], kDecodeWarps);
     }
     tc::MbarInit(&sh->min_free[0], 1);
     tc::MbarInit(&sh->min_free[1], 1);
@@ -238,7 +245,7 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
     sh->abort = 0;
     tc::MbarInitFence();
   }
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tc::TmemAlloc(&sh->tmem_base, 512);
     tc::TmemRelinquish();
   }
@@ -299,9 +306,9 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
             : "memory");
       }
     }
-  } else if (warp >= 1 && warp <= 4) {
+  } else if (warp >= 1 && warp <= kDecodeWarps) {
     // ------------------------------------------------------------ decode
-    const int t = (static_cast<int>(threadIdx.x) - 32);  // 0..127: weight row / token of the tile
+    const int t0 = (static_cast<int>(threadIdx.x) - 32);  // first weight row / token of this thread
     // Rows past the matrix and tokens past the batch arrive as zero blocks (TMA's
     // fill): zero scales, zero codes, nothing stored for them.
     for (int ks = 0; ks < ksteps && !*abort_flag; ++ks) {
@@ -309,67 +316,56 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
       const int half = ks & 1;
       const int column = ks >> 1;
       const int rs = column % kRawStages;
+      const int mt = (ks / kMinSteps) & 1;  // the tile of min operands this k-step writes into
       bool ok = true;
-      if (half == 0) {
-        if (lane == 0) ok = tc::MbarWait(&sh->raw_full[rs], (column / kRawStages) & 1);
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        if (!ok) {
-          if (lane == 0) give_up();
-          break;
+      if (lane == 0) {
+        if (half == 0) ok = tc::MbarWait(&sh->raw_full[rs], (column / kRawStages) & 1);
+        MMQ_T0();
+        ok = ok && tc::MbarWaitSleep(&sh->empty[s], ((ks / kStages) & 1) ^ 1, 64);
+        MMQ_T1(1);
+        // ... and the tensor core is done with the min tile's contents of 32 k-steps ago
+        if (ks >= 2 * kMinSteps && ks % kMinSteps == 0) {
+          ok = ok && tc::MbarWait(&sh->min_free[mt], ((ks / (2 * kMinSteps)) - 1) & 1);
         }
       }
-      const unsigned char* stage = raw + (rs * kRawBytes);
-      const unsigned char* sb = stage + (t * 144);
-      const uint4 head = *reinterpret_cast<const uint4*>(sb);
-      uint4 q[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) q[i] = *reinterpret_cast<const uint4*>(sb + 16 + (half * 64) + (i * 16));
-      const uint4 ds = *reinterpret_cast<const uint4*>(stage + kRawWBytes + (half * kRawHBytes) + (t * 16));
-      if (half == 1) {  // this warp has read all it needs of the raw stage
-        __syncwarp();
-        if (lane == 0) tc::MbarArrive(&sh->raw_empty[rs]);
-      }
-      MMQ_T0();
-      if (lane == 0) ok = tc::MbarWaitSleep(&sh->empty[s], ((ks / kStages) & 1) ^ 1, 64);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      MMQ_T1(1);
       if (!ok) {
         if (lane == 0) give_up();
         break;
       }
-      // int8 codes into the swizzled K-major tile: row t, 16-byte chunk j at j ^ (t % 8)
-      unsigned char* wt = w_tiles + (s * kWBytes) + ((t >> 3) * 1024) + ((t & 7) * 128);
-#pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const uint4 lo0 = make_uint4(q[2 * cc].x & 0x0f0f0f0fu, q[2 * cc].y & 0x0f0f0f0fu,
-                                     q[2 * cc].z & 0x0f0f0f0fu, q[2 * cc].w & 0x0f0f0f0fu);
-        const uint4 lo1 = make_uint4(q[2 * cc + 1].x & 0x0f0f0f0fu, q[2 * cc + 1].y & 0x0f0f0f0fu,
-                                     q[2 * cc + 1].z & 0x0f0f0f0fu, q[2 * cc + 1].w & 0x0f0f0f0fu);
-        const uint4 hi0 = make_uint4((q[2 * cc].x >> 4) & 0x0f0f0f0fu, (q[2 * cc].y >> 4) & 0x0f0f0f0fu,
-                                     (q[2 * cc].z >> 4) & 0x0f0f0f0fu, (q[2 * cc].w >> 4) & 0x0f0f0f0fu);
-        const uint4 hi1 = make_uint4((q[2 * cc + 1].x >> 4) & 0x0f0f0f0fu, (q[2 * cc + 1].y >> 4) & 0x0f0f0f0fu,
-                                     (q[2 * cc + 1].z >> 4) & 0x0f0f0f0fu, (q[2 * cc + 1].w >> 4) & 0x0f0f0f0fu);
-        const int j = cc * 4;  // groups 2cc (chunks j, j+1) and 2cc+1 (chunks j+2, j+3)
-        *reinterpret_cast<uint4*>(wt + (((j + 0) ^ (t & 7)) * 16)) = lo0;
-        *reinterpret_cast<uint4*>(wt + (((j + 1) ^ (t & 7)) * 16)) = lo1;
-        *reinterpret_cast<uint4*>(wt + (((j + 2) ^ (t & 7)) * 16)) = hi0;
-        *reinterpret_cast<uint4*>(wt + (((j + 3) ^ (t & 7)) * 16)) = hi1;
-      }
-      // The tile of min operands this k-step writes into, once the tensor core is
-      // done with its previous contents (32 k-steps ago).
-      const int mt = (ks / kMinSteps) & 1;
-      if (ks >= 2 * kMinSteps && ks % kMinSteps == 0) {
-        if (lane == 0) ok = tc::MbarWait(&sh->min_free[mt], ((ks / (2 * kMinSteps)) - 1) & 1);
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        if (!ok) {
-          if (lane == 0) give_up();
-          break;
-        }
-      }
-      // The four groups' half products (d * sc, -dmin * m): GGML's tile loader
-      // multiplies in half precision.
+      const unsigned char* stage = raw + (rs * kRawBytes);
       float* sc = stage_scales(s);
-      {
+#pragma unroll  // the rows of a thread are independent: their latencies overlap
+      for (int t = t0; t < kTileRows; t += kDecodeWarps * 32) {
+        const unsigned char* sb = stage + (t * 144);
+        const uint4 head = *reinterpret_cast<const uint4*>(sb);
+        uint4 q[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          q[i] = *reinterpret_cast<const uint4*>(sb + 16 + (half * 64) + (i * 16));
+        }
+        const uint4 ds =
+            *reinterpret_cast<const uint4*>(stage + kRawWBytes + (half * kRawHBytes) + (t * 16));
+        // int8 codes into the swizzled K-major tile: row t, 16-byte chunk j at j ^ (t % 8)
+        unsigned char* wt = w_tiles + (s * kWBytes) + ((t >> 3) * 1024) + ((t & 7) * 128);
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          const uint4 lo0 = make_uint4(q[2 * cc].x & 0x0f0f0f0fu, q[2 * cc].y & 0x0f0f0f0fu,
+                                       q[2 * cc].z & 0x0f0f0f0fu, q[2 * cc].w & 0x0f0f0f0fu);
+          const uint4 lo1 = make_uint4(q[2 * cc + 1].x & 0x0f0f0f0fu, q[2 * cc + 1].y & 0x0f0f0f0fu,
+                                       q[2 * cc + 1].z & 0x0f0f0f0fu, q[2 * cc + 1].w & 0x0f0f0f0fu);
+          const uint4 hi0 = make_uint4((q[2 * cc].x >> 4) & 0x0f0f0f0fu, (q[2 * cc].y >> 4) & 0x0f0f0f0fu,
+                                       (q[2 * cc].z >> 4) & 0x0f0f0f0fu, (q[2 * cc].w >> 4) & 0x0f0f0f0fu);
+          const uint4 hi1 = make_uint4((q[2 * cc + 1].x >> 4) & 0x0f0f0f0fu, (q[2 * cc + 1].y >> 4) & 0x0f0f0f0fu,
+                                       (q[2 * cc + 1].z >> 4) & 0x0f0f0f0fu, (q[2 * cc + 1].w >> 4) & 0x0f0f0f0fu);
+          const int j = cc * 4;  // groups 2cc (chunks j, j+1) and 2cc+1 (chunks j+2, j+3)
+          *reinterpret_cast<uint4*>(wt + (((j + 0) ^ (t & 7)) * 16)) = lo0;
+          *reinterpret_cast<uint4*>(wt + (((j + 1) ^ (t & 7)) * 16)) = lo1;
+          *reinterpret_cast<uint4*>(wt + (((j + 2) ^ (t & 7)) * 16)) = hi0;
+          *reinterpret_cast<uint4*>(wt + (((j + 3) ^ (t & 7)) * 16)) = hi1;
+        }
+        // The four groups' half products (d * sc, -dmin * m): GGML's tile loader
+        // multiplies in half precision.
         const std::uint32_t s0 = head.y, s1 = head.z, s2 = head.w;
         const __half d = __ushort_as_half(static_cast<unsigned short>(head.x & 0xffffu));
         const __half dmin = __hneg(__ushort_as_half(static_cast<unsigned short>(head.x >> 16)));
@@ -412,9 +408,12 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
       }
       tc::FenceProxyAsync();  // generic-proxy writes, read by the tensor core's proxy
       __syncwarp();
-      if (lane == 0) tc::MbarArrive(&sh->w_full[s]);
+      if (lane == 0) {
+        if (half == 1) tc::MbarArrive(&sh->raw_empty[rs]);  // all of the raw stage is read
+        tc::MbarArrive(&sh->w_full[s]);
+      }
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const std::uint32_t idesc = tc::IdescI8(kTileRows, kTileCols, false, true);
@@ -445,7 +444,7 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
         for (int gl = 0; gl < 4; ++gl, ++group) {
           const int b = static_cast<int>(group % kBuffers);
           MMQ_T0();
-          if (!tc::MbarWaitSleep(&sh->tmem_empty[b], ((group / kBuffers) & 1u) ^ 1u, 32)) {
+          if (!tc::MbarWait(&sh->tmem_empty[b], ((group / kBuffers) & 1u) ^ 1u)) {
             give_up();
             break;
           }
@@ -469,7 +468,7 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
     }
   } else {
     // ------------------------------------------------------------ epilogue
-    const int ew = warp - 6;
+    const int ew = warp - kFirstEpilogueWarp;
     const int quadrant = warp & 3;          // TMEM lanes this warp may touch
     const int colgroup = ew >> 2;           // which kEpilogueCols columns
     const int rt = (quadrant * 32) + lane;  // weight row of the tile
@@ -480,47 +479,36 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
     bool ok = true;
     int bb = 0;                  // the group's TMEM buffer and its use's parity
     std::uint32_t parity = 0;
-    for (int ks = 0; ks < ksteps && ok; ++ks) {
+    for (int ks = 0; ks < ksteps && ok && !*abort_flag; ++ks) {
       const int s = ks % kStages;
       const float* sc = stage_scales(s);
 #pragma unroll
       for (int gl = 0; gl < 4; ++gl) {
         if (!ok) break;
         MMQ_T0();
-        if (lane == 0) ok = tc::MbarWait(&sh->tmem_full[bb], parity);
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        ok = tc::MbarWait(&sh->tmem_full[bb], parity);  // every lane polls: no shuffle after
         MMQ_T1(6);
-        if (!ok || *abort_flag) {
-          if (lane == 0 && !ok) give_up();
+        if (!__all_sync(0xffffffffu, ok)) {
+          if (lane == 0) give_up();
           ok = false;
           break;
         }
         tc::TcFenceAfter();
         const std::uint32_t at = tmem + lane_base + (bb * kTileCols) + (colgroup * kEpilogueCols);
-        // Two register buffers: chunk c + 1 is in flight while chunk c is folded.
-        std::uint32_t r[2][kChunk];
-        tc::TmemLoad16(at, r[0]);
+        // All of the thread's columns at once, then the buffer goes straight back to
+        // the tensor core: the fold below overlaps the next groups' MMAs.
+        std::uint32_t r[kChunks][kChunk];
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) tc::TmemLoad32(at + (c * kChunk), r[c]);
         const float ax = sc[(gl * 128) + rt];
         const float cx = -kMagic * ax;  // exact: a half-precision ax times 3 * 2^22
         const float* bx = sc + 512 + (gl * 128) + (colgroup * kEpilogueCols);
+        tc::TmemLoadWait();
+        tc::TcFenceBefore();
+        __syncwarp();
+        if (lane == 0) tc::MbarArrive(&sh->tmem_empty[bb]);
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) {
-          {
-            MMQ_T0();
-            tc::TmemLoadWait16(r[c & 1]);
-            MMQ_T1(10);
-          }
-          if (c + 1 < kChunks) {
-            tc::TmemLoad16(at + ((c + 1) * kChunk), r[(c + 1) & 1]);
-          } else {
-            // every column of the buffer is in registers: the tensor core may reuse it
-            tc::TcFenceBefore();
-            __syncwarp();
-            if (lane == 0) tc::MbarArrive(&sh->tmem_empty[bb]);
-          }
-#ifdef LLMP_MMQ_TIMING
-          const long long fold0 = clock64();
-#endif
 #pragma unroll
           for (int v = 0; v < kChunk / 4; ++v) {
             const float4 x4 = *reinterpret_cast<const float4*>(bx + (c * kChunk) + (v * 4));
@@ -528,7 +516,7 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const int i = (c * kChunk) + (v * 4) + j;
-              const std::uint32_t bits = r[c & 1][(v * 4) + j];
+              const std::uint32_t bits = r[c][(v * 4) + j];
               // ax * C rounded once, either way: with the bias 12582912 + C is the
               // float whose bits are 0x4B400000 + C, and ax * (bias + C) - bias * ax
               // is one fused operation.
@@ -537,9 +525,6 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
               acc[i] = fmaf(u, xs[j], acc[i]);
             }
           }
-#ifdef LLMP_MMQ_TIMING
-          local_cycles[11] += clock64() - fold0;
-#endif
         }
         if (++bb == kBuffers) {
           bb = 0;
@@ -561,8 +546,8 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
 #pragma unroll
       for (int c = 0; c < kChunks; ++c) {
         std::uint32_t r[kChunk];
-        tc::TmemLoad16(at + (c * kChunk), r);
-        tc::TmemLoadWait16(r);
+        tc::TmemLoad32(at + (c * kChunk), r);
+        tc::TmemLoadWait();
 #pragma unroll
         for (int j = 0; j < kChunk; ++j) acc[(c * kChunk) + j] += __uint_as_float(r[j]);
       }
@@ -589,11 +574,11 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
     } else if (warp == 1) {
       atomicAdd(&g_mmq_cycles[1], static_cast<unsigned long long>(local_cycles[1]));
       atomicAdd(&g_mmq_cycles[2], static_cast<unsigned long long>(life));
-    } else if (warp == 5) {
+    } else if (warp == kMmaWarp) {
       for (int i = 3; i <= 5; ++i) {
         atomicAdd(&g_mmq_cycles[i], static_cast<unsigned long long>(local_cycles[i]));
       }
-    } else if (warp == 6) {
+    } else if (warp == kFirstEpilogueWarp) {
       atomicAdd(&g_mmq_cycles[6], static_cast<unsigned long long>(local_cycles[6]));
       atomicAdd(&g_mmq_cycles[7], static_cast<unsigned long long>(life));
       atomicAdd(&g_mmq_cycles[10], static_cast<unsigned long long>(local_cycles[10]));
@@ -603,7 +588,7 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
 #endif
   tc::TcFenceBefore();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tc::TcFenceAfter();
     tc::TmemDealloc(tmem, 512);
   }
