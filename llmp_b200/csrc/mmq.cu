@@ -10,7 +10,7 @@
 // The int8 contraction runs on tcgen05 (kind::i8, int32 accumulators in TMEM).
 // Q4_K's per-group scales forbid accumulating across groups in the tensor
 // core, so every 128x128x32 MMA lands in its own TMEM buffer (three of them, so
-// the tensor core runs ahead) and a wide epilogue (8 warps) folds each group's
+// the tensor core runs ahead) and a wide epilogue (16 warps) folds each group's
 // int32 tile into F32 register accumulators: acc += ((d*sc) * C) * d8.  That
 // fold is CUDA-core work per output element per group, fed by one shared-memory
 // word (d8) per element, and bounds the kernel.  The min terms need no integer
@@ -19,21 +19,30 @@
 // accumulate, a fourth TMEM buffer) from two small K-major FP16 tiles that the
 // decode warps fill; the epilogue adds that buffer once at the end.
 //
-//   warp 0      TMA: activation int8 tiles (128 tokens x 128 K bytes) straight
-//               out of the [k/128][col] block array through a 3-D tensor map
-//               (row pitch 144 B, origin past the 16-byte block header);
-//   warps 1-4   decode: one weight row a thread; unpack the k-block's 128
-//               nibbles to int8 into the 128-byte-swizzled K-major tile the MMA
-//               reads, the four groups' d*sc as F32 and -dmin*m as FP16; also
-//               stage the tokens' d8 (F32) and s8 (FP16);
-//   warp 5      allocates TMEM and issues the MMAs;
-//   warps 6-13  epilogue: thread = (weight row, half of the token columns);
-//               TMEM loads of 16 columns, the next in flight during a fold.
-// Measured on M 4096, K 4096, N 14336: 122 TOP/s with the min terms folded on
-// CUDA cores and unpipelined TMEM loads; pipelined loads 173.  Alternatives that
-// lost, behind build macros: 16 epilogue warps (LLMP_MMQ_EPILOGUE_WARPS=16) and
-// an integer add of 0x4B400000 in place of the int-to-float conversion
-// (LLMP_MMQ_MAGIC=1: 152 against 173).
+//   warp 0       TMA: per k-step the activation int8 tile (128 tokens x 128 K
+//                bytes) straight out of the [k/128][col] block array through a
+//                3-D tensor map (row pitch 144 B, origin past the 16-byte block
+//                header) into the 128-byte-swizzled layout the MMA reads; per
+//                super-block column (two k-steps) the 128 weight rows' raw
+//                Q4_K blocks and the tokens' block headers into a raw stage;
+//   warps 1-2    decode, two weight rows a thread, from the raw stage: unpack
+//                the k-step's 128 nibbles to int8 into the swizzled K-major
+//                tile, the four groups' d*sc as F32 and -dmin*m as FP16, the
+//                tokens' d8 (F32) and s8 (FP16);
+//   warp 3       allocates TMEM and issues the MMAs;
+//   warps 4-19   epilogue: thread = (weight row, a quarter of the token
+//                columns): loads its 32 columns, hands the buffer back to the
+//                tensor core at once, then folds.
+// Rows past the matrix and tokens past the batch are TMA's zero fill.
+// Measured on M 4096, K 4096, N 14336 (TOP/s): min terms folded on CUDA cores
+// and the decode warps fetching weights with uncoalesced global loads 122-173;
+// min terms on the tensor core and TMA-fed decode 229; every lane polling its
+// barrier (no shuffle) 245; 16 epilogue warps of 32 columns 267; the fold in
+// packed F32x2 arithmetic 270.  With the
+// epilogue only handing buffers back the kernel runs at 425, with the tensor
+// core free-running at 555: one tcgen05.commit per 32-value group costs about
+// 335 cycles of tensor-pipe time whatever else happens.  The integer-add
+// variant of the conversion (LLMP_MMQ_MAGIC=1) measured slower (242).
 // Every wait is bounded; a wait that runs out raises the device fault counter.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -129,7 +138,7 @@ constexpr int kRawWBytes = 128 * 144;
 constexpr int kRawHBytes = 128 * 16;
 constexpr int kRawBytes = kRawWBytes + (2 * kRawHBytes);
 #ifndef LLMP_MMQ_EPILOGUE_WARPS
-#define LLMP_MMQ_EPILOGUE_WARPS 8
+#define LLMP_MMQ_EPILOGUE_WARPS 16
 #endif
 #ifndef LLMP_MMQ_DECODE_WARPS
 #define LLMP_MMQ_DECODE_WARPS 2
@@ -166,6 +175,27 @@ __device__ unsigned long long g_mmq_cycles[16];
 #define MMQ_T0()
 #define MMQ_T1(slot)
 #endif
+
+// Two F32 lanes in one 64-bit register: sm_100's packed F32 arithmetic does two
+// roundings-to-nearest per instruction, the same results as two scalar ones.
+__device__ __forceinline__ std::uint64_t Pack2(float lo, float hi) {
+  std::uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void Unpack2(std::uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ std::uint64_t Mul2(std::uint64_t a, std::uint64_t b) {
+  std::uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ std::uint64_t Fma2(std::uint64_t a, std::uint64_t b, std::uint64_t c) {
+  std::uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
 
 struct Shared {
   std::uint64_t y_full[kStages];
@@ -473,9 +503,9 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
     const int colgroup = ew >> 2;           // which kEpilogueCols columns
     const int rt = (quadrant * 32) + lane;  // weight row of the tile
     const std::uint32_t lane_base = static_cast<std::uint32_t>(quadrant * 32) << 16;
-    float acc[kEpilogueCols];
+    std::uint64_t acc2[kEpilogueCols / 2];  // columns 2i, 2i + 1
 #pragma unroll
-    for (int i = 0; i < kEpilogueCols; ++i) acc[i] = 0.0f;
+    for (int i = 0; i < kEpilogueCols / 2; ++i) acc2[i] = 0ull;
     bool ok = true;
     int bb = 0;                  // the group's TMEM buffer and its use's parity
     std::uint32_t parity = 0;
@@ -507,6 +537,8 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
         tc::TcFenceBefore();
         __syncwarp();
         if (lane == 0) tc::MbarArrive(&sh->tmem_empty[bb]);
+        const std::uint64_t ax2 = Pack2(ax, ax);
+        const std::uint64_t cx2 = Pack2(cx, cx);
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) {
 #pragma unroll
@@ -514,15 +546,23 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
             const float4 x4 = *reinterpret_cast<const float4*>(bx + (c * kChunk) + (v * 4));
             const float xs[4] = {x4.x, x4.y, x4.z, x4.w};
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int i = (c * kChunk) + (v * 4) + j;
-              const std::uint32_t bits = r[c][(v * 4) + j];
-              // ax * C rounded once, either way: with the bias 12582912 + C is the
-              // float whose bits are 0x4B400000 + C, and ax * (bias + C) - bias * ax
-              // is one fused operation.
-              const float u = kRegMagic ? fmaf(__uint_as_float(bits + kMagicBits), ax, cx)
-                                        : ax * static_cast<float>(static_cast<int>(bits));
-              acc[i] = fmaf(u, xs[j], acc[i]);
+            for (int j = 0; j < 4; j += 2) {
+              const int i = ((c * kChunk) + (v * 4) + j) / 2;
+              // (ax * C) rounded, times d8, added: as the scalar sequence, two columns at once
+              std::uint64_t u2;
+              if (kRegMagic) {
+                // 0x4B400000 + C are the bits of the float 12582912 + C (|C| < 2^22), and
+                // ax * (12582912 + C) - 12582912 * ax is one fused operation: ax * C
+                // rounded once, as the conversion gives.
+                u2 = Fma2(Pack2(__uint_as_float(r[c][(v * 4) + j] + kMagicBits),
+                                __uint_as_float(r[c][(v * 4) + j + 1] + kMagicBits)),
+                          ax2, cx2);
+              } else {
+                u2 = Mul2(Pack2(static_cast<float>(static_cast<int>(r[c][(v * 4) + j])),
+                                static_cast<float>(static_cast<int>(r[c][(v * 4) + j + 1]))),
+                          ax2);
+              }
+              acc2[i] = Fma2(u2, Pack2(xs[j], xs[j + 1]), acc2[i]);
             }
           }
         }
@@ -540,6 +580,7 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok && lane == 0) give_up();
     }
+    float acc[kEpilogueCols];  // the min terms first, then plus the folded groups
     if (ok) {
       tc::TcFenceAfter();
       const std::uint32_t at = tmem + lane_base + kMinColumn + (colgroup * kEpilogueCols);
@@ -549,8 +590,15 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
         tc::TmemLoad32(at + (c * kChunk), r);
         tc::TmemLoadWait();
 #pragma unroll
-        for (int j = 0; j < kChunk; ++j) acc[(c * kChunk) + j] += __uint_as_float(r[j]);
+        for (int j = 0; j < kChunk; ++j) acc[(c * kChunk) + j] = __uint_as_float(r[j]);
       }
+    }
+#pragma unroll
+    for (int i = 0; i < kEpilogueCols / 2; ++i) {
+      float lo, hi;
+      Unpack2(acc2[i], lo, hi);
+      acc[2 * i] += lo;
+      acc[(2 * i) + 1] += hi;
     }
     if (ok && row0 + rt < a.nrows) {
 #pragma unroll  // fully: a dynamic index would put acc[] in local memory
