@@ -194,9 +194,16 @@ def make_q4k_device(torch, rows: int, k: int, gen):
 class FfnStep:
     """The step's device state and launches, for one rank's shard."""
 
-    def __init__(self, torch, ops, batch: int, world: int, rank: int, dist, fused: bool = False):
+    def __init__(self, torch, ops, batch: int, world: int, rank: int, dist, fused: bool = False,
+                 q8_out: bool = False):
         self.torch, self.ops, self.batch, self.world, self.dist = torch, ops, batch, world, dist
         self.fused = fused
+        # Opt-in (one GPU): the gate/up product writes its output's Q8_1 blocks
+        # itself (llmp_b200_vecq_q8), so the down product needs no quantize
+        # launch.  Bit-identical; measured slower (0.61 against 0.57 ms a step: the
+        # count-and-quantize tail costs the product more than the launch it saves).
+        self.q8_out = q8_out and world == 1 and not fused
+        self.rows_done = ops.vecq_q8_scratch(INTER, batch, "cuda")
         gen = torch.Generator(device="cuda")
         gen.manual_seed(1234 + rank)
         self.n_glu = INTER // world
@@ -220,7 +227,9 @@ class FfnStep:
         self.h_rows = torch.empty((batch, INTER), device="cuda")
         self.y_shard = torch.empty((batch, self.n_down), device="cuda")
         self.y_full = torch.empty((LAYERS, world, batch, self.n_down), device="cuda")
-        self.launches_per_step = LAYERS * (2 if (world == 1 and fused) else 4 + (1 if world > 1 else 0))
+        self.launches_per_layer = (2 if (world == 1 and fused) else 3 if self.q8_out
+                                   else 4 + (1 if world > 1 else 0))
+        self.launches_per_step = LAYERS * self.launches_per_layer
 
     def layer(self, l: int, x):
         ops, T = self.ops, self.ops.TYPE_Q4_K
@@ -233,6 +242,11 @@ class FfnStep:
             ops.vecq_f32(down, T, INTER, self.n_down, self.h_shard, out=self.y_full[l, 0])
             return
         ops.quantize_q8(x, out=self.q8x)
+        if self.q8_out:
+            ops.vecq_q8(up, T, HIDDEN, self.n_glu, self.q8x, self.batch, rows_done=self.rows_done,
+                        gate=gate, glu=ops.GLU_GEGLU, out=self.h_shard, q8_dst=self.q8h)
+            ops.vecq(down, T, INTER, self.n_down, self.q8h, self.batch, out=self.y_full[l, 0])
+            return
         ops.vecq(up, T, HIDDEN, self.n_glu, self.q8x, self.batch, gate=gate, glu=ops.GLU_GEGLU,
                  out=self.h_shard)
         if self.world > 1:
@@ -262,8 +276,13 @@ class FfnStep:
                              out=self.h_shard)
             return
         for gate, up, _ in self.layers:
-            ops.vecq(up, T, HIDDEN, self.n_glu, self.q8x, self.batch, gate=gate,
-                     glu=ops.GLU_GEGLU, out=self.h_shard)
+            if self.q8_out:
+                ops.vecq_q8(up, T, HIDDEN, self.n_glu, self.q8x, self.batch,
+                            rows_done=self.rows_done, gate=gate, glu=ops.GLU_GEGLU,
+                            out=self.h_shard, q8_dst=self.q8h)
+            else:
+                ops.vecq(up, T, HIDDEN, self.n_glu, self.q8x, self.batch, gate=gate,
+                         glu=ops.GLU_GEGLU, out=self.h_shard)
 
 
 def run_gpu(args, rank: int, world: int, local_rank: int):
@@ -281,7 +300,7 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
         raise SystemExit("bench.py: no B200 / native library: " + ops._native.last_error())
 
     batch = args.batch
-    st = FfnStep(torch, ops, batch, world, rank, dist, fused=args.fused)
+    st = FfnStep(torch, ops, batch, world, rank, dist, fused=args.fused, q8_out=args.q8_out)
     stream = torch.cuda.Stream()
     sync = torch.cuda.synchronize
 
@@ -417,7 +436,7 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
                 "l2": f"inputs larger than L2: {LAYERS} distinct layer copies, "
                       f"{LAYERS * 44.2e-3:.2f} GB, streamed in order",
                 "launch": "cuda graph replay" if graph is not None else "stream launches",
-                "launches_per_layer": 2 if (world == 1 and args.fused) else 4,
+                "launches_per_layer": st.launches_per_layer,
                 "parallelism": "single GPU" if world == 1 else f"N-column shards x{world}, "
                                "NCCL all-gather of the GLU output and of the layer output",
                 "step_bytes": sb,
@@ -626,6 +645,9 @@ def main():
                     help="ffn_q4k is the bench line; the others time the other configs' kernels")
     ap.add_argument("--tokens", type=int, default=0,
                     help="tokens / rows of the other workloads")
+    ap.add_argument("--q8-out", action="store_true",
+                    help="the gate/up product also writes its output's Q8_1 blocks "
+                         "(llmp_b200_vecq_q8): one launch fewer a layer, measured slower")
     ap.add_argument("--fused", action="store_true",
                     help="llmp_b200_vecq_f32: each product quantizes its F32 input itself (two "
                          "launches a layer instead of four; measured slower: 2,200 against 2,717 "

@@ -116,6 +116,24 @@ int llmp_b200_vecq(int type, const llmp_b200_vecq_desc* desc, int variant, void*
  * blocks of each token's row, rows llmp_b200_q8_1_row_blocks(k) blocks apart. */
 int llmp_b200_vecq_f32(int type, const llmp_b200_vecq_desc* desc, void* q8_out, void* stream);
 
+/* The product with the quantization of its OUTPUT fused: in the decode graph a
+ * product's F32 result usually feeds the QuantizeQ8 node of the next product
+ * (src/kernels/ggml/vecq.cu:1095-1111 after :1168; shared_q8.h:20-47).  This
+ * entry writes desc->dst as llmp_b200_vecq does and, besides, the Q8_1 blocks of
+ * every token's output row into q8_dst ([tokens][nrows / 32] blocks of 36 bytes):
+ * the warp that completes a 32-row block quantizes it with the quantizer's
+ * arithmetic, so the blocks equal llmp_b200_q8_1_quantize(dst) bit for bit and
+ * one launch is saved (on B200 the counting tail costs the product about what
+ * the launch costs: measure before preferring it).  Taken for dense Q4_K
+ * products of up to 8 tokens whose nrows is a multiple of 512 (others:
+ * status > 0, use the two calls).
+ * rows_done: llmp_b200_vecq_q8_scratch(nrows, tokens) bytes of device memory,
+ * zero before the first call; every call leaves them zero.  Calls that share
+ * rows_done must be ordered on a stream. */
+size_t llmp_b200_vecq_q8_scratch(int nrows, int tokens);
+int llmp_b200_vecq_q8(int type, const llmp_b200_vecq_desc* desc, void* q8_dst, uint32_t* rows_done,
+                      void* stream);
+
 /* Verification entry with no reference counterpart as a separate call: the
  * int32 per-block sums the product kernels form (the quantity the reference
  * checks bit for bit, tests/unit/dsv4_fast_test.cc:511-540), for nrows weight

@@ -165,16 +165,29 @@ const char* llmp_b200_vecq_variant_name(int variant) {
 namespace llmp_b200 {
 namespace {
 int LaunchVecQ(int type, const llmp_b200_vecq_desc* desc, int variant, bool f32_input, void* q8_out,
-               void* stream);
+               void* q8_dst, unsigned int* rows_done, void* stream);
 }  // namespace
 }  // namespace llmp_b200
 
 int llmp_b200_vecq(int type, const llmp_b200_vecq_desc* desc, int variant, void* stream) {
-  return llmp_b200::LaunchVecQ(type, desc, variant, false, nullptr, stream);
+  return llmp_b200::LaunchVecQ(type, desc, variant, false, nullptr, nullptr, nullptr, stream);
 }
 
 int llmp_b200_vecq_f32(int type, const llmp_b200_vecq_desc* desc, void* q8_out, void* stream) {
-  return llmp_b200::LaunchVecQ(type, desc, -1, true, q8_out, stream);
+  return llmp_b200::LaunchVecQ(type, desc, -1, true, q8_out, nullptr, nullptr, stream);
+}
+
+int llmp_b200_vecq_q8(int type, const llmp_b200_vecq_desc* desc, void* q8_dst, uint32_t* rows_done,
+                      void* stream) {
+  if (q8_dst == nullptr || rows_done == nullptr) {
+    return llmp_b200::Reject("vecq_q8: the output blocks and the row counters");
+  }
+  return llmp_b200::LaunchVecQ(type, desc, -1, false, nullptr, q8_dst, rows_done, stream);
+}
+
+size_t llmp_b200_vecq_q8_scratch(int nrows, int tokens) {
+  if (nrows < 1 || tokens < 1) return 0;
+  return static_cast<size_t>(tokens) * static_cast<size_t>((nrows + 31) / 32) * sizeof(uint32_t);
 }
 
 }  // extern "C"
@@ -182,7 +195,7 @@ int llmp_b200_vecq_f32(int type, const llmp_b200_vecq_desc* desc, void* q8_out, 
 namespace llmp_b200 {
 namespace {
 int LaunchVecQ(int type, const llmp_b200_vecq_desc* desc, int variant, bool f32_input, void* q8_out,
-               void* stream) {
+               void* q8_dst, unsigned int* rows_done, void* stream) {
   if (desc == nullptr) return Reject("vecq: null descriptor");
   bool q8_fast = false;
   if (const int status = Check(type, *desc, &q8_fast); status != 0) return status;
@@ -243,6 +256,15 @@ int LaunchVecQ(int type, const llmp_b200_vecq_desc* desc, int variant, bool f32_
     lanes.f32_input = 1;
     lanes.q8_out = static_cast<std::uint8_t*>(q8_out);
     lanes.q8_row_blocks = (d.ncols_x + 511) / 512 * 512 / 32;
+  }
+  if (q8_dst != nullptr) {
+    // The quantized output exists in the rowlane kernel only, for rows of whole
+    // 512-value groups (a token's blocks then have no padding to fill).
+    if (!rowlane_ok || d.nrows % 512 != 0 || !Aligned(q8_dst, 4) || !Aligned(rows_done, 4)) {
+      return Reject("vecq_q8: dense Q4_K products of up to 8 tokens with nrows a multiple of 512");
+    }
+    lanes.q8_dst = static_cast<std::uint8_t*>(q8_dst);
+    lanes.q8_rows_done = rows_done;
   }
   if (rowlane_ok && (wants_rowlane || variant < 0)) {
     e = LaunchRowLane(d, p, lanes, s);

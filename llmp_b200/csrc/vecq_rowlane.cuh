@@ -54,6 +54,10 @@ struct RowLanePlan {
   int f32_input;     // activations are F32: quantize to Q8_1 while staging
   int q8_row_blocks; // Q8_1 blocks between tokens' rows in q8_out
   std::uint8_t* q8_out;  // optional: the Q8_1 blocks, written by CTA 0
+  // Optional: the OUTPUT's Q8_1 blocks (what the next product reads).  The warp
+  // that completes a 32-row block of a token's output quantizes it.
+  std::uint8_t* q8_dst;
+  unsigned int* q8_rows_done;  // [tokens][nrows / 32] counters, zero between launches
   unsigned int* faults;
 };
 
@@ -336,6 +340,54 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
       }
     }
   }
+
+  // The output as Q8_1 blocks too: every warp counts its rows into the 32-row
+  // blocks they fall in (at most two: R <= 32); the warp whose count completes a
+  // block reads the block's 32 values back from L2 and quantizes them with the
+  // Q8_1 quantizer's arithmetic (d = amax / 127 as FP16, q = roundf(x / d), the sum
+  // a butterfly over indices 16, 8, 4, 2, 1 apart), so the blocks are the ones the
+  // separate quantizer writes, bit for bit.  nrows is a multiple of 512 here, so
+  // a token's row of blocks has no padding.
+  if (plan.q8_dst != nullptr) {
+    __threadfence();  // this warp's rows are visible before they are counted
+    __syncwarp();
+    const int row_blocks = a.nrows >> 5;
+    const int b0 = row_begin >> 5, b1 = (row_end - 1) >> 5;
+    const int t = lane >> 1;
+    const int blk = (lane & 1) ? b1 : b0;
+    bool mine = false;
+    if (t < a.tokens && ((lane & 1) == 0 || b1 != b0)) {
+      const int lo = max(row_begin, blk << 5), hi = min(row_end, (blk << 5) + 32);
+      const unsigned int count = static_cast<unsigned int>(hi - lo);
+      unsigned int* counter = plan.q8_rows_done + (static_cast<std::size_t>(t) * row_blocks) + blk;
+      mine = atomicAdd(counter, count) + count == 32u;
+      if (mine) *counter = 0u;  // as the next launch expects it
+    }
+    unsigned int done = __ballot_sync(0xffffffffu, mine);
+    if (done != 0u) __threadfence();
+    while (done != 0u) {
+      const int src = __ffs(static_cast<int>(done)) - 1;
+      done &= done - 1u;
+      const int tt = src >> 1;
+      const int bb = (src & 1) ? b1 : b0;
+      const float x = __ldcg(a.dst + (static_cast<std::size_t>(tt) * a.dst_token) + (bb << 5) + lane);
+      float amax = fabsf(x), sum = x;
+#pragma unroll
+      for (int offset = 16; offset > 0; offset >>= 1) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
+        sum = sum + __shfl_xor_sync(0xffffffffu, sum, offset);
+      }
+      const float df = amax / 127.0f;
+      const int q = amax != 0.0f ? static_cast<int>(roundf(x / df)) : 0;
+      std::uint8_t* out = plan.q8_dst + ((static_cast<std::size_t>(tt) * row_blocks + bb) * 36);
+      reinterpret_cast<signed char*>(out + 4)[lane] = static_cast<signed char>(q);
+      if (lane == 0) {
+        *reinterpret_cast<std::uint32_t*>(out) =
+            static_cast<std::uint32_t>(__half_as_ushort(__float2half_rn(df))) |
+            (static_cast<std::uint32_t>(__half_as_ushort(__float2half_rn(sum))) << 16);
+      }
+    }
+  }
 }
 
 // Host: the geometry for a dense Q4_K product, or false if it does not fit.
@@ -411,6 +463,8 @@ inline bool PlanRowLane(const Desc& d, int p, int sms, int force_rows, bool half
       best.f32_input = 0;
       best.q8_row_blocks = 0;
       best.q8_out = nullptr;
+      best.q8_dst = nullptr;
+      best.q8_rows_done = nullptr;
     }
     }
   }

@@ -16,7 +16,7 @@ from ._native import (GLU_GEGLU, GLU_NONE, GLU_SWIGLU, GLU_SWIGLU_CLAMP, TYPE_Q4
                       LaunchFailed, Rejected)
 
 __all__ = ["available", "sm_count", "device_faults", "block_bytes", "block_elems", "q8_1_row_blocks",
-           "quantize_q8", "vecq", "vecq_f32", "vecq_variants", "vecq_block_sums", "mxfp8_padded_rows",
+           "quantize_q8", "vecq", "vecq_f32", "vecq_q8", "vecq_q8_scratch", "vecq_variants", "vecq_block_sums", "mxfp8_padded_rows",
            "mxfp8_quantize", "mxfp8_swizzle", "mxfp8_gemm", "mxfp8_mul_mat_vec", "mmq_quantize", "mmq", "moe_route", "grouped_gemm",
            "moe_glu_quantize", "moe_combine", "moe_ffn", "TYPE_Q8_0", "TYPE_Q4_K",
            "GLU_NONE", "GLU_SWIGLU", "GLU_SWIGLU_CLAMP", "GLU_GEGLU", "Rejected", "LaunchFailed"]
@@ -162,6 +162,45 @@ def vecq_f32(weights: torch.Tensor, wtype: int, k: int, n: int, x: torch.Tensor,
                                        q8_out.data_ptr() if q8_out is not None else None,
                                        _stream()), "llmp_b200_vecq_f32")
     return out
+
+
+def vecq_q8_scratch(n: int, tokens: int, device) -> torch.Tensor:
+    """Zeroed row counters for vecq_q8 (every call leaves them zero)."""
+    nbytes = int(N.lib().llmp_b200_vecq_q8_scratch(n, tokens))
+    return torch.zeros(nbytes // 4, dtype=torch.int32, device=device)
+
+
+def vecq_q8(weights: torch.Tensor, wtype: int, k: int, n: int, q8: torch.Tensor, tokens: int, *,
+            rows_done: torch.Tensor, gate: torch.Tensor | None = None, glu: int = GLU_NONE,
+            limit: float = 0.0, out: torch.Tensor | None = None,
+            q8_dst: torch.Tensor | None = None):
+    """VecQ + QuantizeQ8 of its output in one launch: dense Q4_K weights [n, k] (n a multiple
+    of 512), q8 of [tokens <= 8, k] -> (F32 [tokens, n], its Q8_1 blocks uint8 [tokens, n/32*36])."""
+    _need(weights, torch.uint8, "vecq_q8 weights")
+    _need(q8, torch.uint8, "vecq_q8 q8")
+    _need(rows_done, torch.int32, "vecq_q8 counters")
+    d = N.VecQDesc()
+    d.w = weights.data_ptr()
+    d.g = gate.data_ptr() if gate is not None else None
+    d.y = q8.data_ptr()
+    d.ncols_x, d.nrows = k, n
+    d.stride_row = k // _BLOCK[wtype][0]
+    d.y_token = q8_1_row_blocks(k)
+    d.used, d.tokens = 1, tokens
+    if out is None:
+        out = torch.empty((tokens, n), dtype=torch.float32, device=weights.device)
+    if q8_dst is None:
+        q8_dst = torch.empty((tokens, q8_1_row_blocks(n) * 36), dtype=torch.uint8,
+                             device=weights.device)
+    _need(out, torch.float32, "vecq_q8 output")
+    _need(q8_dst, torch.uint8, "vecq_q8 output blocks")
+    if rows_done.numel() * 4 < int(N.lib().llmp_b200_vecq_q8_scratch(n, tokens)):
+        raise Rejected("vecq_q8: counters of llmp_b200_vecq_q8_scratch(n, tokens) bytes")
+    d.dst, d.dst_token = out.data_ptr(), n
+    d.glu, d.limit = glu, limit
+    N.check(N.lib().llmp_b200_vecq_q8(wtype, C.byref(d), q8_dst.data_ptr(), rows_done.data_ptr(),
+                                      _stream()), "llmp_b200_vecq_q8")
+    return out, q8_dst
 
 
 def vecq_block_sums(weights: torch.Tensor, wtype: int, k: int, n: int, q8_row: torch.Tensor):

@@ -274,6 +274,36 @@ def test_fused_quantization_gives_the_two_call_bits(cuda, orc, n, k, tokens, glu
                           orc.quantize_q8_1(x)[:, :blocks * 36])
 
 
+@pytest.mark.parametrize("n,k,tokens,glu", [(10240, 2560, 1, 3), (2560, 10240, 1, 0),
+                                            (2560, 10240, 8, 0), (1024, 512, 3, 1),
+                                            (512, 256, 2, 0)])
+def test_fused_output_quantization_gives_the_two_call_bits(cuda, orc, n, k, tokens, glu):
+    """llmp_b200_vecq_q8 also writes its output as Q8_1 blocks: the F32 output is the plain
+    product's and the blocks are the quantizer's over that output, bit for bit; the row
+    counters come back zero, so a second call gives the same again."""
+    torch = cuda
+    ops = _ops()
+    rng = np.random.default_rng(n + k + tokens)
+    w = to_dev(torch, synth.q4_k_weights(rng, n, k))
+    g = to_dev(torch, synth.q4_k_weights(rng, n, k)) if glu else None
+    x = rng.normal(0, 1, size=(tokens, k)).astype(np.float32)
+    q8 = ops.quantize_q8(to_dev(torch, x))
+    want = ops.vecq(w, orc.Q4_K, k, n, q8, tokens, gate=g, glu=glu)
+    want_q8 = ops.quantize_q8(want)
+    rows_done = ops.vecq_q8_scratch(n, tokens, "cuda")
+    for _ in range(2):
+        q8_dst = torch.full_like(want_q8, 0x5a)
+        got, blocks = ops.vecq_q8(w, orc.Q4_K, k, n, q8, tokens, rows_done=rows_done, gate=g,
+                                  glu=glu, q8_dst=q8_dst)
+        assert torch.equal(got, want)
+        assert torch.equal(blocks, want_q8)
+        assert int(rows_done.abs().sum()) == 0
+    assert np.array_equal(want_q8.cpu().numpy(), orc.quantize_q8_1(want.cpu().numpy()))
+    with pytest.raises(ops.Rejected):                       # rows not whole 512-value groups
+        ops.vecq_q8(w[:480].contiguous(), orc.Q4_K, k, 480, q8, tokens,
+                    rows_done=rows_done)
+
+
 def test_no_bounded_wait_ran_out(cuda):
     """Collected after the product tests of this file: the TMA-fed kernels'
     bounded mbarrier waits never expired."""
