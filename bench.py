@@ -300,7 +300,13 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
         raise SystemExit("bench.py: no B200 / native library: " + ops._native.last_error())
 
     batch = args.batch
-    st = FfnStep(torch, ops, batch, world, rank, dist, fused=args.fused, q8_out=args.q8_out)
+    # N > 1: by default every rank runs the whole step on its own batch (replicas of
+    # the data-parallel decode path: no collective, weak scaling).  --shard columns
+    # splits every matrix's rows over the ranks and all-gathers the outputs (strong
+    # scaling; at decode sizes the all-gathers' latency dominates).
+    sharded = world > 1 and args.shard == "columns"
+    parts = world if sharded else 1
+    st = FfnStep(torch, ops, batch, parts, rank, dist, fused=args.fused, q8_out=args.q8_out)
     stream = torch.cuda.Stream()
     sync = torch.cuda.synchronize
 
@@ -313,12 +319,13 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
         st.step()       # warm: module load, attributes
         sync()
         graph = None
-        # Graph replay on one GPU only: a step with NCCL collectives is queued as
-        # plain stream launches.
-        if world == 1 and not args.no_graph:
+        # Graph replay only for steps without NCCL collectives (one GPU, replicas): a
+        # sharded step is queued as plain stream launches.
+        graph_kw = {"capture_error_mode": "thread_local"} if world > 1 else {}
+        if parts == 1 and not args.no_graph:
             try:
                 graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph, stream=stream):
+                with torch.cuda.graph(graph, stream=stream, **graph_kw):
                     st.step()
             except Exception as e:  # capture refused: time plain launches
                 print(f"bench.py: graph capture unavailable ({e}); timing plain launches",
@@ -346,10 +353,10 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
         st.glu_only()
         sync()
         glu_graph = None
-        if world == 1 and not args.no_graph:
+        if parts == 1 and not args.no_graph:
             try:
                 glu_graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(glu_graph, stream=stream):
+                with torch.cuda.graph(glu_graph, stream=stream, **graph_kw):
                     st.glu_only()
             except Exception:
                 glu_graph = None
@@ -367,7 +374,7 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
         glu_us = 1e3 * k0.elapsed_time(k1) / (reps * LAYERS)
         # ---- end to end through the C ABI from host buffers
         hx = torch.randn((LAYERS, batch, HIDDEN)).pin_memory()
-        hy = torch.empty((LAYERS, world, batch, st.n_down)).pin_memory()
+        hy = torch.empty((LAYERS, parts, batch, st.n_down)).pin_memory()
         dx = torch.empty_like(st.x)
 
         def e2e_body():
@@ -380,12 +387,12 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
         # launches, pinned-host output copy, all captured once and replayed (the
         # reference replays captured steps too, src/engine/step_runs.cc:323).
         e2e_graph = None
-        if world == 1 and not args.no_graph:
+        if parts == 1 and not args.no_graph:
             try:
                 e2e_body()
                 sync()
                 e2e_graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(e2e_graph, stream=stream):
+                with torch.cuda.graph(e2e_graph, stream=stream, **graph_kw):
                     e2e_body()
             except Exception as e:
                 print(f"bench.py: e2e graph capture unavailable ({e})", file=sys.stderr)
@@ -414,7 +421,8 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_ms, glu_us = (float(v) for v in t.tolist())
     if rank == 0:
-        sb = step_bytes(batch)
+        replicas = world if not sharded else 1
+        sb = step_bytes(batch) * replicas      # what all ranks streamed in a step
         value = sb / (ms * 1e-3) / 1e9
         peaks = {}
         try:
@@ -422,12 +430,13 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
         except OSError:
             pass
         peak = float(peaks.get("hbm_gbs", 6650.0))
-        glu_b = glu_launch_bytes(batch, world)
+        glu_b = glu_launch_bytes(batch, parts)
         achieved = glu_b / (glu_us * 1e-6) / 1e9
         line = {
             "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 5),
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "higher_is_better": True, "scaling": "strong" if sharded or world == 1 else "weak",
+            "vs_baseline": None,
             "dtype": "int8 dp4a -> int32 per block, f32 sums", "data": "synthetic",
             "config": {
                 "workload": f"Gemma-3-4B FFN decode products, Q4_K, {LAYERS} layers, batch {batch}",
@@ -437,8 +446,10 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
                       f"{LAYERS * 44.2e-3:.2f} GB, streamed in order",
                 "launch": "cuda graph replay" if graph is not None else "stream launches",
                 "launches_per_layer": st.launches_per_layer,
-                "parallelism": "single GPU" if world == 1 else f"N-column shards x{world}, "
-                               "NCCL all-gather of the GLU output and of the layer output",
+                "parallelism": "single GPU" if world == 1 else
+                               (f"N-column shards x{world}, NCCL all-gather of the GLU output and of "
+                                "the layer output" if sharded else
+                                f"{world} replicas, one batch a GPU, no collective in the step"),
                 "step_bytes": sb,
             },
             "e2e": {"value": round(sb / (e2e_ms * 1e-3) / 1e9, 2), "unit": UNIT,
@@ -446,9 +457,9 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
                     "how": "host wall clock around pinned H2D of x, the step's C-ABI launches and "
                            "pinned D2H of y, with a stream synchronize per step"
                            + (" (captured once, replayed)" if e2e_graph is not None else ""),
-                    "h2d_bytes_per_step": LAYERS * batch * HIDDEN * 4,
-                    "d2h_bytes_per_step": LAYERS * batch * HIDDEN * 4},
-            "gpu_launches": st.launches_per_step * args.steps,
+                    "h2d_bytes_per_step": LAYERS * batch * HIDDEN * 4 * replicas,
+                    "d2h_bytes_per_step": LAYERS * batch * HIDDEN * 4 * replicas},
+            "gpu_launches": st.launches_per_step * args.steps * world,
             "roofline": {"bound": "hbm", "kernel": "VecQKernel<Q4_K, GLU> (fused gate/up)",
                          "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4),
@@ -485,7 +496,7 @@ def run_other(args):
         raise SystemExit("bench.py: no B200 / native library: " + ops._native.last_error())
     gen = torch.Generator(device="cuda")
     gen.manual_seed(0)
-    peaks = {"mxf8f6f4": 4466.5, "i8": 4567.3}  # profiles/tcgen05_issue_peaks.md
+    peaks = {"mxf8f6f4": 4466.5, "i8": 4567.3}  # profiles/tcgen05_microbenchmarks.md
 
     def timed(fns, steps, warmup):
         for i in range(max(warmup, 3)):
@@ -518,7 +529,7 @@ def run_other(args):
                              "peak": peaks["mxf8f6f4"], "unit": "TFLOP/s",
                              "frac": round(rate / peaks["mxf8f6f4"], 4),
                              "peak_source": "bare tcgen05.mma loop on this pool "
-                                            "(profiles/tcgen05_issue_peaks.md)"}}
+                                            "(profiles/tcgen05_microbenchmarks.md)"}}
     elif args.workload == "mmq_q4k":
         m, n, k = args.tokens or 4096, 14336, 4096
         x = torch.randn((m, k), device="cuda", generator=gen).bfloat16()
@@ -534,7 +545,7 @@ def run_other(args):
                 "roofline": {"bound": "tensor", "achieved": round(rate, 1), "peak": peaks["i8"],
                              "unit": "TOP/s", "frac": round(rate / peaks["i8"], 4),
                              "peak_source": "bare tcgen05.mma loop on this pool "
-                                            "(profiles/tcgen05_issue_peaks.md)"}}
+                                            "(profiles/tcgen05_microbenchmarks.md)"}}
     else:  # moe
         import numpy as np
 
@@ -565,6 +576,73 @@ def run_other(args):
                  "higher_is_better": True, "data": "synthetic", "vs_baseline": None,
                  "faults": ops.device_faults()})
     print(json.dumps(line), flush=True)
+
+
+def run_mmq_sharded(args, rank: int, world: int, local_rank: int):
+    """The prefill GEMM N-column sharded (BASELINE configs[2]): every rank holds the weight
+    rows [rank * n / world, +n / world) and the whole activation batch, computes its slice
+    D[:, slice] and the slices are all-gathered over NVLink (NCCL) into [world, m, n / world]
+    on every rank.  Strong scaling: the product is the same at every N."""
+    import torch
+    import torch.distributed as dist
+
+    torch.cuda.set_device(local_rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    import llmp_b200 as ops
+    from llmp_b200 import shard
+    m, n, k = args.tokens or 4096, 14336, 4096
+    lo, hi = shard.row_shard(n, world, rank, multiple=128)
+    width = shard.row_shard(n, world, 0, multiple=128)
+    width = width[1] - width[0]                      # the widest slice; others pad to it
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(7)                               # the same activations on every rank
+    x = torch.randn((m, k), device="cuda", generator=gen).bfloat16()
+    gen.manual_seed(100 + rank)
+    if hi - lo != width:
+        raise SystemExit("bench.py: N-column shards of unequal width are not benchmarked")
+    sets = [(make_q4k_device(torch, width, k, gen), torch.empty((m, width), device="cuda"),
+             torch.empty((world, m, width), device="cuda")) for _ in range(2)]
+
+    def step(i):
+        w, mine, full = sets[i % 2]
+        yq = ops.mmq_quantize(x)
+        ops.mmq(w, yq, k, width, out=mine)
+        dist.all_gather_into_tensor(full, mine)
+        return full
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        out = step(i)
+    e1.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ok = torch.tensor([float(torch.isfinite(out).all())], device="cuda")
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        ms = float(t.item())
+        rate = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+        print(json.dumps({
+            "metric": "mmq_q4k_int8_gemm_throughput", "value": round(rate, 1), "unit": "TOP/s",
+            "ms_per_step": round(ms, 5), "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "higher_is_better": True, "scaling": "strong",
+            "data": "synthetic", "vs_baseline": None, "finite": bool(ok.item()),
+            "faults": ops.device_faults(),
+            "config": {"workload": f"Q4_K x Q8_1-MMQ int8 GEMM M {m} K {k} N {n}",
+                       "parallelism": f"N-column shards x{world} (slices of {width} columns), "
+                                      "activation quantizer on every rank, NCCL all-gather of "
+                                      f"the F32 output ({m * n * 4 / 1e6:.0f} MB)"},
+            "roofline": {"bound": "tensor", "achieved": round(rate, 1), "peak": 4567.3 * world,
+                         "unit": "TOP/s", "frac": round(rate / (4567.3 * world), 4),
+                         "peak_source": "bare tcgen05.mma loop on this pool "
+                                        "(profiles/tcgen05_microbenchmarks.md) x N"}}), flush=True)
+    dist.destroy_process_group()
 
 
 def run_moe_ep(args, rank: int, world: int, local_rank: int):
@@ -652,6 +730,9 @@ def main():
                     help="llmp_b200_vecq_f32: each product quantizes its F32 input itself (two "
                          "launches a layer instead of four; measured slower: 2,200 against 2,717 "
                          "GB/s, the per-CTA quantization sits on the critical path)")
+    ap.add_argument("--shard", default="replicas", choices=["replicas", "columns"],
+                    help="N > 1: replicas (each GPU its own batch, weak scaling) or columns "
+                         "(rows of every matrix split, NCCL all-gather, strong scaling)")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--traffic", type=float, default=None,
@@ -667,6 +748,9 @@ def main():
         return
     if args.workload == "moe" and world > 1:
         run_moe_ep(args, rank, world, local_rank)
+        return
+    if args.workload == "mmq_q4k" and world > 1:
+        run_mmq_sharded(args, rank, world, local_rank)
         return
     if args.workload != "ffn_q4k":
         if rank == 0:
