@@ -147,75 +147,66 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
       const int token = min(t, a.tokens - 1);
       uint4* q = reinterpret_cast<uint4*>(acts + (static_cast<std::size_t>(t) * plan.acts_bytes));
       float* sc = reinterpret_cast<float*>(q + (16 * UR));
-      if (plan.f32_input) {
-        // Eight lanes a block, four values a lane, as the quantizer does it: amax by
-        // xor-shuffles, the sum as the butterfly over value indices 16, 8, 4 (lanes
-        // 4, 2, 1 apart) then 2 and 1 (inside the lane).
-        const float* row = static_cast<const float*>(a.y) + (static_cast<std::size_t>(token) * a.y_token);
-        const int lanes = blocks * 8;
-        for (int base = 0; base < lanes; base += static_cast<int>(blockDim.x)) {
-          const int i = base + tid;
-          const bool live = i < lanes;
-          const int b = (live ? i : 0) >> 3, part = i & 7;
-          float4 f = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-          if (live) f = *reinterpret_cast<const float4*>(row + (b * 32) + (part * 4));
-          float amax = fmaxf(fmaxf(fabsf(f.x), fabsf(f.y)), fmaxf(fabsf(f.z), fabsf(f.w)));
-          float s4[4] = {f.x, f.y, f.z, f.w};
-#pragma unroll
-          for (int offset = 4; offset > 0; offset >>= 1) {
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
-#pragma unroll
-            for (int c4 = 0; c4 < 4; ++c4) s4[c4] = s4[c4] + __shfl_xor_sync(0xffffffffu, s4[c4], offset);
-          }
-          const float sum = (s4[0] + s4[2]) + (s4[1] + s4[3]);
-          const float df = amax / 127.0f;
-          std::uint32_t packed = 0;
-          if (amax != 0.0f) {
-            const float xs[4] = {f.x, f.y, f.z, f.w};
-#pragma unroll
-            for (int c4 = 0; c4 < 4; ++c4) {
-              const int qi = static_cast<int>(roundf(xs[c4] / df));
-              packed |= (static_cast<std::uint32_t>(qi) & 0xffu) << (8 * c4);
-            }
-          }
-          int isum = Dp4a(0x01010101, static_cast<int>(packed), 0);
-#pragma unroll
-          for (int offset = 4; offset > 0; offset >>= 1) isum += __shfl_xor_sync(0xffffffffu, isum, offset);
-          if (live) {
-            const __half dh = __float2half_rn(df);
-            const float d = __half2float(dh);
-            const int c = b >> 3, g = b & 7;
-            // word `part` of the block: the first four words are chunk 2g, the rest chunk 2g + 1
-            reinterpret_cast<std::uint32_t*>(q + (((2 * g) + (part >> 2)) * UR) + c)[part & 3] = packed;
-            if (part == 0) {
-              sc[((((g >> 2)) * UR + c) * 4) + (g & 3)] = d;
-              sc[((((2 + (g >> 2))) * UR + c) * 4) + (g & 3)] = d * static_cast<float>(isum);
-            }
-            if (plan.q8_out != nullptr && blockIdx.x == 0 && t < a.tokens) {
-              auto* out = reinterpret_cast<std::uint32_t*>(
-                  plan.q8_out + ((static_cast<std::size_t>(t) * plan.q8_row_blocks + b) * 36));
-              out[1 + part] = packed;
-              if (part == 0) {
-                out[0] = static_cast<std::uint32_t>(__half_as_ushort(dh)) |
-                         (static_cast<std::uint32_t>(__half_as_ushort(__float2half_rn(sum))) << 16);
-              }
-            }
-          }
-        }
-        continue;
-      }
       for (int b = tid; b < blocks; b += static_cast<int>(blockDim.x)) {
         std::uint32_t v[8];
         int isum = 0;
-        const auto* src = reinterpret_cast<const std::uint32_t*>(
-            static_cast<const std::uint8_t*>(a.y) +
-            ((static_cast<std::size_t>(token) * a.y_token + b) * 36));
+        float d;
+        if (plan.f32_input) {
+          const float4* src = reinterpret_cast<const float4*>(
+              static_cast<const float*>(a.y) + (static_cast<std::size_t>(token) * a.y_token) +
+              (static_cast<std::size_t>(b) * 32));
+          float x[32], sum[32];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          v[i] = src[1 + i];
-          isum = Dp4a(0x01010101, static_cast<int>(v[i]), isum);
+          for (int i = 0; i < 8; ++i) {
+            const float4 f = src[i];
+            x[4 * i] = f.x; x[4 * i + 1] = f.y; x[4 * i + 2] = f.z; x[4 * i + 3] = f.w;
+          }
+          float amax = 0.0f;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            amax = fmaxf(amax, fabsf(x[i]));
+            sum[i] = x[i];
+          }
+#pragma unroll
+          for (int offset = 16; offset > 0; offset >>= 1) {
+#pragma unroll
+            for (int i = 0; i < offset; ++i) sum[i] = sum[i] + sum[i + offset];
+          }
+          const float df = amax / 127.0f;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            std::uint32_t packed = 0;
+            if (amax != 0.0f) {
+#pragma unroll
+              for (int c4 = 0; c4 < 4; ++c4) {
+                const int qi = static_cast<int>(roundf(x[(4 * i) + c4] / df));
+                packed |= (static_cast<std::uint32_t>(qi) & 0xffu) << (8 * c4);
+              }
+            }
+            v[i] = packed;
+            isum = Dp4a(0x01010101, static_cast<int>(packed), isum);
+          }
+          const __half dh = __float2half_rn(df);
+          d = __half2float(dh);
+          if (plan.q8_out != nullptr && blockIdx.x == 0 && t < a.tokens) {
+            auto* out = reinterpret_cast<std::uint32_t*>(
+                plan.q8_out + ((static_cast<std::size_t>(t) * plan.q8_row_blocks + b) * 36));
+            out[0] = static_cast<std::uint32_t>(__half_as_ushort(dh)) |
+                     (static_cast<std::uint32_t>(__half_as_ushort(__float2half_rn(sum[0]))) << 16);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) out[1 + i] = v[i];
+          }
+        } else {
+          const auto* src = reinterpret_cast<const std::uint32_t*>(
+              static_cast<const std::uint8_t*>(a.y) +
+              ((static_cast<std::size_t>(token) * a.y_token + b) * 36));
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            v[i] = src[1 + i];
+            isum = Dp4a(0x01010101, static_cast<int>(v[i]), isum);
+          }
+          d = HalfBitsToFloat(src[0] & 0xffffu);
         }
-        const float d = HalfBitsToFloat(src[0] & 0xffffu);
         const int c = b >> 3, g = b & 7;
         q[((2 * g) * UR) + c] = make_uint4(v[0], v[1], v[2], v[3]);
         q[((2 * g + 1) * UR) + c] = make_uint4(v[4], v[5], v[6], v[7]);
