@@ -22,6 +22,9 @@ __all__ = ["available", "sm_count", "device_faults", "block_bytes", "block_elems
            "GLU_NONE", "GLU_SWIGLU", "GLU_SWIGLU_CLAMP", "GLU_GEGLU", "Rejected", "LaunchFailed"]
 
 _BLOCK = {TYPE_Q8_0: (32, 34), TYPE_Q4_K: (256, 144), N.TYPE_Q8_1: (32, 36)}
+# moe_ffn: up to this many tokens take the routed decode products (measured on B200 against the
+# grouped tensor-core GEMM for 128 experts, top-8, hidden 2048, intermediate 768).
+DECODE_TOKENS = 96
 
 
 def available() -> bool:
@@ -394,27 +397,41 @@ def moe_combine(rows: torch.Tensor, position: torch.Tensor, weights: torch.Tenso
 
 
 def moe_ffn(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, gate_up: torch.Tensor,
-            down: torch.Tensor, hidden: int, inter: int, glu: int = GLU_SWIGLU) -> torch.Tensor:
+            down: torch.Tensor, hidden: int, inter: int, glu: int = GLU_SWIGLU,
+            decode_tokens: int | None = None) -> torch.Tensor:
     """The routed-expert block as the reference wires it (tests/unit/qwen38_moe_test.cc:487-497):
     route -> quantize (scattered to expert-sorted rows) -> grouped GEMM gate|up -> GLU +
     requantize -> grouped GEMM down -> ordered weighted combine.  x F32/BF16 [tokens, hidden];
     ids I32 [tokens, used]; weights F32 [tokens, used]; gate_up Q4_K [experts, 2 inter, hidden]
-    (gate rows then up rows); down Q4_K [experts, hidden, inter].  Tokens of up to 16 take the
-    decode products (llmp.vecq routed) instead of the tensor-core GEMM."""
+    (gate rows then up rows); down Q4_K [experts, hidden, inter].  Up to DECODE_TOKENS tokens
+    take the decode products (llmp.vecq routed) instead of the tensor-core GEMM."""
     tokens, used = ids.shape
     experts = gate_up.shape[0]
-    if tokens <= 16 and tokens * used <= 128:
-        q8 = quantize_q8(x.float())
+    # Few tokens: the decode products (routed llmp.vecq), which stream each named expert's
+    # weights once per call, in calls of at most 16 tokens and 128 (token, slot) pairs (the
+    # operator's limits).  Up to DECODE_TOKENS tokens that beats the tensor-core GEMM, whose
+    # 128-row tiles are nearly empty when an expert sees a handful of rows.
+    chunk = min(16, max(1, 128 // used))
+    if tokens <= (DECODE_TOKENS if decode_tokens is None else decode_tokens) and used <= 128:
         gate_w = gate_up[:, :inter]
         up_w = gate_up[:, inter:]
         bpr = hidden // 256
-        h = vecq(up_w, TYPE_Q4_K, hidden, inter, q8, tokens, ids=ids, gate=gate_w, glu=glu,
-                 stride_row=bpr, stride_expert=2 * inter * bpr)
-        q8h = quantize_q8(h.view(tokens * used, inter))
-        y = vecq(down, TYPE_Q4_K, inter, hidden, q8h, tokens, ids=ids, per_slot=True)
-        position = torch.arange(tokens * used, dtype=torch.int32, device=x.device)
-        return moe_combine(y.view(tokens * used, hidden), position, weights.contiguous(), tokens,
-                           used)
+        xf = x.float()
+        weights = weights.contiguous()
+        out = torch.empty((tokens, hidden), dtype=torch.float32, device=x.device)
+        for t0 in range(0, tokens, chunk):
+            t1 = min(tokens, t0 + chunk)
+            n = t1 - t0
+            part_ids = ids[t0:t1].contiguous()
+            q8 = quantize_q8(xf[t0:t1])
+            h = vecq(up_w, TYPE_Q4_K, hidden, inter, q8, n, ids=part_ids, gate=gate_w, glu=glu,
+                     stride_row=bpr, stride_expert=2 * inter * bpr)
+            q8h = quantize_q8(h.view(n * used, inter))
+            y = vecq(down, TYPE_Q4_K, inter, hidden, q8h, n, ids=part_ids, per_slot=True)
+            position = torch.arange(n * used, dtype=torch.int32, device=x.device)
+            out[t0:t1] = moe_combine(y.view(n * used, hidden), position, weights[t0:t1].contiguous(),
+                                     n, used)
+        return out
     route = moe_route(ids, experts)
     slots = tokens * used
     aq = mmq_quantize(x, ids_src=route["token"], cols=slots)

@@ -125,7 +125,8 @@ def test_routed_expert_block_matches_the_oracle(cuda, orc, tokens):
     x = rng.normal(0, 1, size=(tokens, hidden)).astype(np.float32)
     ids, w = synth.topk_route(rng, tokens, experts, used)
     got = ops.moe_ffn(to_dev(torch, x), to_dev(torch, ids), to_dev(torch, w),
-                      to_dev(torch, gate_up), to_dev(torch, down), hidden, inter).cpu().numpy()
+                      to_dev(torch, gate_up), to_dev(torch, down), hidden, inter,
+                      decode_tokens=16).cpu().numpy()      # the tensor-core path
     assert ops.device_faults() == 0
     want = _oracle_moe(orc, x, ids, w, gate_up, down, hidden, inter, experts)
     assert np.isfinite(got).all()
@@ -133,14 +134,16 @@ def test_routed_expert_block_matches_the_oracle(cuda, orc, tokens):
     assert nmse <= 1e-5, nmse
 
 
-def test_decode_tokens_take_the_vecq_products(cuda, orc):
-    """Up to 16 tokens: routed llmp.vecq with a fused GLU, per-slot down products, combine.
-    Q8_1 activations instead of Q8_1-MMQ ones: compared with the double product of the
-    dequantized weights at the bound the reference uses across formats (NMSE 3e-2)."""
+@pytest.mark.parametrize("tokens", [1, 40])
+def test_decode_tokens_take_the_vecq_products(cuda, orc, tokens):
+    """Few tokens: routed llmp.vecq with a fused GLU, per-slot down products, combine, in calls
+    of at most 16 tokens.  Q8_1 activations instead of Q8_1-MMQ ones: compared with the double
+    product of the dequantized weights at the bound the reference uses across formats (NMSE
+    3e-2), and with the tensor-core path on the same inputs."""
     torch = cuda
     ops = _ops()
     rng = np.random.default_rng(3)
-    experts, used, hidden, inter, tokens = 128, 8, 2048, 768, 1
+    experts, used, hidden, inter = 128, 8, 2048, 768
     gate_up = synth.q4_k_weights(rng, experts * 2 * inter, hidden).reshape(experts, 2 * inter, -1)
     down = synth.q4_k_weights(rng, experts * hidden, inter).reshape(experts, hidden, -1)
     x = rng.normal(0, 1, size=(tokens, hidden)).astype(np.float32)
@@ -156,3 +159,11 @@ def test_decode_tokens_take_the_vecq_products(cuda, orc):
             g, u = gu[:inter] @ x[t], gu[inter:] @ x[t]
             ref[t] += w[t, j] * (dn @ (g / (1 + np.exp(-g)) * u))
     assert ((got - ref) ** 2).sum() / (ref ** 2).sum() <= 3e-2
+    if tokens > 16:
+        gemm = ops.moe_ffn(to_dev(torch, x), to_dev(torch, ids), to_dev(torch, w),
+                           to_dev(torch, gate_up), to_dev(torch, down), hidden, inter,
+                           decode_tokens=0).cpu().numpy()
+        # The two paths are GGML's two conventions: the decode product multiplies Q4_K's minima
+        # by d8 * (sum of the int8 codes), the GEMM by the block's stored FP16 sum of the
+        # original inputs; they differ by the codes' rounding (measured NMSE 1.9e-4).
+        assert ((got - gemm) ** 2).sum() / (gemm ** 2).sum() <= 1e-3
