@@ -90,7 +90,7 @@ typedef struct llmp_b200_vecq_desc {
   int y_slot;        /* between slots' rows (per-slot activations), else 0 */
   int ids_stride;    /* ids between tokens */
   int used;          /* slots a token (1 when dense) */
-  int tokens;        /* 1..16; used * tokens <= 128 */
+  int tokens;        /* 1..16 (the reference's bound); routed: up to 128, used * tokens <= 1024 */
   int dst_token;     /* floats */
   int dst_slot;
   int glu;           /* LLMP_B200_GLU_* */

@@ -94,9 +94,9 @@ int Check(int type, const Desc& d, bool* q8_fast) {
   if (d.w == nullptr || d.y == nullptr || d.dst == nullptr) {
     return Reject("vecq: quantized weights, a llmp.q8_1 input and an F32 output");
   }
-  if (d.tokens < 1 || d.tokens > 16 || d.glu < 0 || d.glu > 3 ||
-      ((d.glu != 0) != (d.g != nullptr))) {
-    return Reject("vecq: 1 to 16 tokens, and gate weights exactly with a GLU");
+  if (d.tokens < 1 || d.tokens > (d.ids != nullptr ? kMaxRoutedTokens : 16) || d.glu < 0 ||
+      d.glu > 3 || ((d.glu != 0) != (d.g != nullptr))) {
+    return Reject("vecq: 1 to 16 tokens (128 routed), and gate weights exactly with a GLU");
   }
   if (d.glu == LLMP_B200_GLU_GEGLU && d.limit != 0.0f) {
     return Reject("vecq: GeGLU uses GELU-tanh without a clamp limit");
@@ -106,7 +106,7 @@ int Check(int type, const Desc& d, bool* q8_fast) {
     return Reject("vecq: k a positive multiple of the block's %d values, n >= 1", elems);
   }
   if (d.used < 1 || d.used > 256 || d.used * d.tokens > (d.ids != nullptr ? kMaxPairs : 256 * 16)) {
-    return Reject("vecq: used * tokens <= 128 routed; at most 256 groups");
+    return Reject("vecq: used * tokens <= 1024 routed; at most 256 groups");
   }
   if (d.ids == nullptr && d.tokens > kMaxPairs) return Reject("vecq: tokens");
   if (d.stride_row < d.ncols_x / elems || d.stride_expert < 0 || d.y_token < 0 || d.y_slot < 0 ||

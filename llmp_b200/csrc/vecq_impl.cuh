@@ -32,7 +32,11 @@
 namespace llmp_b200 {
 namespace vecq {
 
-constexpr int kMaxPairs = 128;  // used * tokens <= 128 (llmp_ops.cc:2950)
+// Routed (token, slot) pairs a launch.  The reference's operator stops at 128 pairs of 16
+// tokens (llmp_ops.cc:2932, 2950); this kernel's pair lists take eight times that, so a
+// routed block of up to 128 tokens reads every named expert's weights once.
+constexpr int kMaxPairs = 1024;
+constexpr int kMaxRoutedTokens = 128;
 constexpr int kMaxThreads = 256;
 
 using Desc = llmp_b200_vecq_desc;

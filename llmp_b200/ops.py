@@ -408,10 +408,10 @@ def moe_ffn(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, gate_up: 
     tokens, used = ids.shape
     experts = gate_up.shape[0]
     # Few tokens: the decode products (routed llmp.vecq), which stream each named expert's
-    # weights once per call, in calls of at most 16 tokens and 128 (token, slot) pairs (the
-    # operator's limits).  Up to DECODE_TOKENS tokens that beats the tensor-core GEMM, whose
+    # weights once per call, in calls of at most 128 tokens and 1,024 (token, slot) pairs (the
+    # kernel's limits).  Up to DECODE_TOKENS tokens that beats the tensor-core GEMM, whose
     # 128-row tiles are nearly empty when an expert sees a handful of rows.
-    chunk = min(16, max(1, 128 // used))
+    chunk = min(128, max(1, 1024 // used))
     if tokens <= (DECODE_TOKENS if decode_tokens is None else decode_tokens) and used <= 128:
         gate_w = gate_up[:, :inter]
         up_w = gate_up[:, inter:]
