@@ -194,6 +194,23 @@ size_t llmp_b200_vecq_q8_scratch(int nrows, int tokens) {
 
 namespace llmp_b200 {
 namespace {
+// The rowlane geometry a default launch takes for p tokens a pass.  By default a
+// CTA owns its SM, unless half an SM holds the CTA's whole row range at no worse
+// a lane use: then the next kernel on the stream, a programmatic dependent,
+// becomes resident and fetches early.  (A looser rule sped the down projection up
+// alone, 5.6 against 6.8 us, but slowed the FFN chain it sits in, 2,377 against
+// 2,742 GB/s.)
+bool ChooseRowLane(const Desc& d, int p, RowLanePlan* lanes) {
+  RowLanePlan half;
+  bool ok = PlanRowLane(d, p, SmCount(), 0, false, lanes);
+  if (PlanRowLane(d, p, SmCount(), 0, true, &half) && half.stages == half.steps &&
+      (!ok || half.score >= 0.95 * lanes->score)) {
+    *lanes = half;
+    ok = true;
+  }
+  return ok;
+}
+
 int LaunchVecQ(int type, const llmp_b200_vecq_desc* desc, int variant, bool f32_input, void* q8_out,
                void* q8_dst, unsigned int* rows_done, void* stream) {
   if (desc == nullptr) return Reject("vecq: null descriptor");
@@ -230,17 +247,19 @@ int LaunchVecQ(int type, const llmp_b200_vecq_desc* desc, int variant, bool f32_
       rowlane_ok = PlanRowLane(d, p, SmCount(), kVariants[variant].r, kVariants[variant].u == 1,
                                &lanes);
     } else {
-      // By default a CTA owns its SM, unless half an SM holds the CTA's whole row
-      // range at no worse a lane use: then the next kernel on the stream, a
-      // programmatic dependent, becomes resident and fetches early.  (A looser
-      // rule sped the down projection up alone, 5.6 against 6.8 us, but slowed the
-      // FFN chain it sits in, 2,377 against 2,742 GB/s.)
-      RowLanePlan half;
-      rowlane_ok = PlanRowLane(d, p, SmCount(), 0, false, &lanes);
-      if (PlanRowLane(d, p, SmCount(), 0, true, &half) && half.stages == half.steps &&
-          (!rowlane_ok || half.score >= 0.95 * lanes.score)) {
-        lanes = half;
-        rowlane_ok = true;
+      // A row's sum adds its super-blocks up in an order the geometry (rows and phases
+      // a warp) fixes.  So that a token gives the same bits alone or in company, more
+      // tokens keep the one-token geometry and only the ring depth adapts; if that
+      // does not fit, the geometry is planned afresh (and the bits may differ).
+      rowlane_ok = ChooseRowLane(d, 1, &lanes);
+      if (rowlane_ok && p > 1) {
+        RowLanePlan more;
+        if (PlanRowLane(d, p, SmCount(), lanes.rows, lanes.half != 0, &more, lanes.phases) ||
+            PlanRowLane(d, p, SmCount(), lanes.rows, false, &more, lanes.phases)) {
+          lanes = more;
+        } else {
+          rowlane_ok = ChooseRowLane(d, p, &lanes);
+        }
       }
     }
   }

@@ -392,7 +392,7 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
 
 // Host: the geometry for a dense Q4_K product, or false if it does not fit.
 inline bool PlanRowLane(const Desc& d, int p, int sms, int force_rows, bool half,
-                        RowLanePlan* plan) {
+                        RowLanePlan* plan, int force_phases = 0) {
   const int mats = d.glu != LLMP_B200_GLU_NONE ? 2 : 1;
   const int ur = d.ncols_x / 256;
   if (ur < 1) return false;
@@ -409,6 +409,7 @@ inline bool PlanRowLane(const Desc& d, int p, int sms, int force_rows, bool half
     const int warps = (cta_rows + rows - 1) / rows;
     if (warps < 1 || warps > max_warps) continue;
     for (int phases = 1; phases <= 32 / rows; ++phases) {
+    if (force_phases > 0 && phases != force_phases) continue;
     const int steps = (ur + phases - 1) / phases;
     // The pitch between a stage's rows: the pad (in 16-byte units) that leaves the
     // fewest quarter-warp bank-group collisions for 128-bit loads, lane (r, ph)
@@ -437,7 +438,8 @@ inline bool PlanRowLane(const Desc& d, int p, int sms, int force_rows, bool half
     const int stage_bytes = rows * pitch * mats;
     int stages = std::min({steps, kRowLaneMaxStages, budget / (warps * stage_bytes)});
     if (stages < 1) continue;
-    if (stages < steps && stages < 2) continue;
+    // (a forced geometry may run on a one-stage ring: slower, but the sums keep their order)
+    if (stages < steps && stages < 2 && force_phases == 0) continue;
     // Lane utilization, with a preference for more warps and for a ring that
     // holds the whole range.
     // (all 32 lanes of every warp count: lanes past R * PH idle)

@@ -126,18 +126,26 @@ def test_q8_0_two_byte_aligned_weights_take_the_fallback(cuda, orc):
     assert_close_to_f64(out.cpu().numpy(), f32[:, 0, :], s64[:, 0, :], a64[:, 0, :])
 
 
-def test_a_token_alone_gives_the_same_bits(cuda, orc):
+@pytest.mark.parametrize("n,k,tokens,glu", [(300, 2560, 8, 0), (1000, 2560, 3, 3), (2560, 10240, 8, 0),
+                                            (10240, 2560, 5, 1), (77, 512, 2, 0)])
+def test_a_token_alone_gives_the_same_bits(cuda, orc, n, k, tokens, glu):
+    """A token's sums are the same bits alone or in a batch (the reference's row_invariant
+    capability): more tokens keep the one-token launch geometry."""
     torch = cuda
     ops = _ops()
-    rng = np.random.default_rng(21)
-    n, k = 300, 2560
+    rng = np.random.default_rng(21 + n)
     w = to_dev(torch, synth.q4_k_weights(rng, n, k))
-    x = to_dev(torch, rng.normal(0, 1, size=(8, k)).astype(np.float32))
+    g = to_dev(torch, synth.q4_k_weights(rng, n, k)) if glu else None
+    x = to_dev(torch, rng.normal(0, 1, size=(tokens, k)).astype(np.float32))
     q8 = ops.quantize_q8(x)
-    together = ops.vecq(w, orc.Q4_K, k, n, q8, 8)
-    for j in (0, 3, 7):
-        alone = ops.vecq(w, orc.Q4_K, k, n, ops.quantize_q8(x[j:j + 1]), 1)
-        assert torch.equal(alone[0], together[j])
+    buf = torch.full((tokens * n + 32,), float("nan"), device="cuda")
+    together = buf[: tokens * n].view(tokens, n)
+    ops.vecq(w, orc.Q4_K, k, n, q8, tokens, gate=g, glu=glu, out=together)
+    assert torch.isnan(buf[tokens * n:]).all() and torch.isfinite(together).all()
+    for j in sorted({0, tokens // 2, tokens - 1}):
+        alone = ops.vecq(w, orc.Q4_K, k, n, ops.quantize_q8(x[j:j + 1]), 1, gate=g, glu=glu)
+        assert torch.equal(alone[0], together[j]), (j, (alone[0] != together[j]).sum().item())
+    assert ops.device_faults() == 0
 
 
 @pytest.mark.parametrize("glu,limit", [(1, 0.0), (2, 7.0), (3, 0.0)])
