@@ -159,13 +159,21 @@ __device__ __forceinline__ void Q4KBlockDots(const Q4KBlockUnit& w, const int* a
 }
 
 __device__ __forceinline__ void Q4KBlockScales(const Q4KBlockUnit& w, int sc[8], int mn[8]) {
+  // The twelve bytes hold 6-bit fields: scales 0..3 and minima 0..3 in the low six
+  // bits of bytes 0..3 and 4..7; scales / minima 4..7 as the low / high nibbles of
+  // bytes 8..11 with their top two bits in bits 6..7 of bytes 0..3 / 4..7.  Unpacked
+  // four at a time as packed bytes, then one extract a value.
   const std::uint32_t s0 = w.head.y, s1 = w.head.z, s2 = w.head.w;
+  const std::uint32_t sc_lo = s0 & 0x3f3f3f3fu;
+  const std::uint32_t mn_lo = s1 & 0x3f3f3f3fu;
+  const std::uint32_t sc_hi = (s2 & 0x0f0f0f0fu) | ((s0 >> 2) & 0x30303030u);
+  const std::uint32_t mn_hi = ((s2 >> 4) & 0x0f0f0f0fu) | ((s1 >> 2) & 0x30303030u);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    sc[i] = static_cast<int>((s0 >> (8 * i)) & 63u);
-    mn[i] = static_cast<int>((s1 >> (8 * i)) & 63u);
-    sc[4 + i] = static_cast<int>(((s2 >> (8 * i)) & 15u) | (((s0 >> ((8 * i) + 6)) & 3u) << 4));
-    mn[4 + i] = static_cast<int>(((s2 >> ((8 * i) + 4)) & 15u) | (((s1 >> ((8 * i) + 6)) & 3u) << 4));
+    sc[i] = static_cast<int>((sc_lo >> (8 * i)) & 0xffu);
+    mn[i] = static_cast<int>((mn_lo >> (8 * i)) & 0xffu);
+    sc[4 + i] = static_cast<int>((sc_hi >> (8 * i)) & 0xffu);
+    mn[4 + i] = static_cast<int>((mn_hi >> (8 * i)) & 0xffu);
   }
 }
 
