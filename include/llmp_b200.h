@@ -280,6 +280,55 @@ int llmp_b200_mxfp8_mul_mat_vec(const void* codes, const void* scales, const flo
                                 int64_t x_stride, float* y, int64_t y_stride, int n, int k,
                                 int columns, void* stream);
 
+/* ---- The decode module's vector products (F32 activations, no Q8_1) ----
+ * Replace decode::RunVector and decode::RunVectorGlu (src/kernels/decode/products.h:96-147;
+ * kernels templates.cuh:116-186) for the decoders this build has: Q8_0 blocks
+ * (decoders.cuh:106-125) and MXFP8 with row-major scales or scale atoms (:193-220).
+ * The operand has the fields of decode::Operand (operand.h:71-93) those decoders read.
+ * y[t * y_stride + j] = tensor_scale(row) * sum_k W[first + j, k] * x[t * x_stride + k] for
+ * t < rows (1..16) and j < outputs, summed in the reference's order (a warp a row, lane l the
+ * 16-value segments l, l + 32, ..., a butterfly over the lanes), so the F32 results are the
+ * reference's bit for bit.  decode::RunMatrix and RunGrouped are not part of this build. */
+#define LLMP_B200_DECODER_Q8_0_BLOCKS 0
+#define LLMP_B200_DECODER_MXFP8_SPLIT 1  /* scales [rows, k / 32] row-major */
+#define LLMP_B200_DECODER_MXFP8_ATOMS 2  /* scales in 128 x 4 scale atoms */
+typedef struct llmp_b200_decode_operand {
+  const void* data;           /* Q8_0 blocks, or E4M3 codes */
+  const void* scales;         /* MXFP8: E8M0 scales; Q8_0: unused */
+  const float* tensor_scale;  /* or NULL: row r takes tensor_scale[r / rows_per_scale] */
+  uint32_t k;                 /* values a row */
+  uint32_t rows;              /* rows of the matrix */
+  uint32_t rows_per_scale;
+  uint32_t decoder;           /* LLMP_B200_DECODER_* */
+  uint64_t row_bytes;         /* bytes of a row of data */
+} llmp_b200_decode_operand;
+typedef struct llmp_b200_decode_product {
+  llmp_b200_decode_operand w;
+  uint64_t first, outputs;
+  const float* x;
+  uint64_t rows, x_stride;    /* strides in floats */
+  float* y;
+  uint64_t y_stride;
+} llmp_b200_decode_product;
+int llmp_b200_decode_vector(const llmp_b200_decode_product* product, void* stream);
+/* out[t, j] = glu(gate[t, j], up[t, j]) of rows gate_first + j and up_first + j; glu is
+ * LLMP_B200_GLU_SWIGLU, _SWIGLU_CLAMP (limit) or _GEGLU (tanh): ir::GluKind 0, 3 and 2 of
+ * templates.cuh:75-95; the erf GeGLU (1) is refused. */
+typedef struct llmp_b200_decode_glu_product {
+  llmp_b200_decode_operand gate;
+  uint64_t gate_first;
+  llmp_b200_decode_operand up;
+  uint64_t up_first;
+  uint64_t outputs;
+  int glu;
+  float limit;
+  const float* x;
+  uint64_t rows, x_stride;
+  float* y;
+  uint64_t y_stride;
+} llmp_b200_decode_glu_product;
+int llmp_b200_decode_vector_glu(const llmp_b200_decode_glu_product* product, void* stream);
+
 /* Field for field mxfp8::Gemm (src/kernels/ggml/mxfp8_cutlass.h:56-68). */
 typedef struct llmp_b200_mxfp8_gemm_desc {
   int m, n, k;

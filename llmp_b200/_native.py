@@ -34,6 +34,25 @@ class VecQDesc(C.Structure):
                         ("limit", C.c_float)]
 
 
+class DecodeOperand(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("scales", C.c_void_p), ("tensor_scale", C.c_void_p),
+                ("k", C.c_uint32), ("rows", C.c_uint32), ("rows_per_scale", C.c_uint32),
+                ("decoder", C.c_uint32), ("row_bytes", C.c_uint64)]
+
+
+class DecodeProduct(C.Structure):
+    _fields_ = [("w", DecodeOperand), ("first", C.c_uint64), ("outputs", C.c_uint64),
+                ("x", C.c_void_p), ("rows", C.c_uint64), ("x_stride", C.c_uint64),
+                ("y", C.c_void_p), ("y_stride", C.c_uint64)]
+
+
+class DecodeGluProduct(C.Structure):
+    _fields_ = [("gate", DecodeOperand), ("gate_first", C.c_uint64), ("up", DecodeOperand),
+                ("up_first", C.c_uint64), ("outputs", C.c_uint64), ("glu", C.c_int),
+                ("limit", C.c_float), ("x", C.c_void_p), ("rows", C.c_uint64),
+                ("x_stride", C.c_uint64), ("y", C.c_void_p), ("y_stride", C.c_uint64)]
+
+
 class Mxfp8GemmDesc(C.Structure):
     """llmp_b200_mxfp8_gemm_desc (include/llmp_b200.h)."""
     _fields_ = [("m", C.c_int), ("n", C.c_int), ("k", C.c_int), ("a", C.c_void_p),
@@ -96,6 +115,8 @@ SIGNATURES = {
     "llmp_b200_mxfp8_gemm_available": (C.c_int, []),
     "llmp_b200_mxfp8_gemm_scratch": (C.c_size_t, [C.POINTER(Mxfp8GemmDesc), C.c_int]),
     "llmp_b200_mxfp8_gemm": (C.c_int, [C.POINTER(Mxfp8GemmDesc), C.c_int, C.c_void_p]),
+    "llmp_b200_decode_vector": (C.c_int, [C.POINTER(DecodeProduct), C.c_void_p]),
+    "llmp_b200_decode_vector_glu": (C.c_int, [C.POINTER(DecodeGluProduct), C.c_void_p]),
     "llmp_b200_vecq_f32": (C.c_int, [C.c_int, C.POINTER(VecQDesc), C.c_void_p, C.c_void_p]),
     "llmp_b200_vecq_q8_scratch": (C.c_size_t, [C.c_int, C.c_int]),
     "llmp_b200_vecq_q8": (C.c_int, [C.c_int, C.POINTER(VecQDesc), C.c_void_p, C.c_void_p,

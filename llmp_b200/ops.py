@@ -17,7 +17,8 @@ from ._native import (GLU_GEGLU, GLU_NONE, GLU_SWIGLU, GLU_SWIGLU_CLAMP, TYPE_Q4
 
 __all__ = ["available", "sm_count", "device_faults", "block_bytes", "block_elems", "q8_1_row_blocks",
            "quantize_q8", "vecq", "vecq_f32", "vecq_q8", "vecq_q8_scratch", "vecq_variants", "vecq_block_sums", "mxfp8_padded_rows",
-           "mxfp8_quantize", "mxfp8_swizzle", "mxfp8_gemm", "mxfp8_mul_mat_vec", "mmq_quantize", "mmq", "moe_route", "grouped_gemm",
+           "mxfp8_quantize", "mxfp8_swizzle", "mxfp8_gemm", "mxfp8_mul_mat_vec", "decode_vector", "DECODER_Q8_0", "DECODER_MXFP8_SPLIT",
+           "DECODER_MXFP8_ATOMS", "mmq_quantize", "mmq", "moe_route", "grouped_gemm",
            "moe_glu_quantize", "moe_combine", "moe_ffn", "TYPE_Q8_0", "TYPE_Q4_K",
            "GLU_NONE", "GLU_SWIGLU", "GLU_SWIGLU_CLAMP", "GLU_GEGLU", "Rejected", "LaunchFailed"]
 
@@ -456,3 +457,56 @@ def mxfp8_mul_mat_vec(codes: torch.Tensor, scales: torch.Tensor, x: torch.Tensor
                                                 x.stride(0), y.data_ptr(), y.stride(0), n, k, cols,
                                                 _stream()), "llmp_b200_mxfp8_mul_mat_vec")
     return y
+
+
+# ------------------------------------------------------ decode module (F32 x)
+DECODER_Q8_0, DECODER_MXFP8_SPLIT, DECODER_MXFP8_ATOMS = 0, 1, 2
+
+
+def _decode_operand(decoder: int, data: torch.Tensor, scales: torch.Tensor | None, k: int,
+                    tensor_scale: torch.Tensor | None, rows_per_scale: int) -> "N.DecodeOperand":
+    _need(data, torch.uint8, "decode_vector data")
+    if data.dim() != 2 or data.stride(1) != 1:
+        raise Rejected("decode_vector: data uint8 [rows, row_bytes]")
+    op = N.DecodeOperand()
+    op.data = data.data_ptr()
+    op.scales = scales.data_ptr() if scales is not None else None
+    op.tensor_scale = tensor_scale.data_ptr() if tensor_scale is not None else None
+    op.k, op.rows, op.rows_per_scale, op.decoder = k, data.shape[0], rows_per_scale, decoder
+    op.row_bytes = data.stride(0)
+    return op
+
+
+def decode_vector(decoder: int, data: torch.Tensor, x: torch.Tensor, k: int, outputs: int, *,
+                  scales: torch.Tensor | None = None, first: int = 0,
+                  up: torch.Tensor | None = None, up_scales: torch.Tensor | None = None,
+                  up_first: int = 0, glu: int = GLU_NONE, limit: float = 0.0,
+                  tensor_scale: torch.Tensor | None = None, rows_per_scale: int = 1,
+                  out: torch.Tensor | None = None) -> torch.Tensor:
+    """decode::RunVector / RunVectorGlu: data uint8 [n, row_bytes] (Q8_0 blocks or E4M3 codes
+    with E8M0 scales), x F32 [rows <= 16, k] -> F32 [rows, outputs]; with `up` the GLU of the
+    gate product (data) and the up product."""
+    _need(x, torch.float32, "decode_vector x")
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise Rejected("decode_vector: x F32 [rows, k], k contiguous")
+    rows = x.shape[0]
+    if out is None:
+        out = torch.empty((rows, outputs), dtype=torch.float32, device=x.device)
+    _need(out, torch.float32, "decode_vector output")
+    gate_op = _decode_operand(decoder, data, scales, k, tensor_scale, rows_per_scale)
+    if up is None:
+        p = N.DecodeProduct()
+        p.w, p.first, p.outputs = gate_op, first, outputs
+        p.x, p.rows, p.x_stride = x.data_ptr(), rows, x.stride(0)
+        p.y, p.y_stride = out.data_ptr(), out.stride(0)
+        N.check(N.lib().llmp_b200_decode_vector(C.byref(p), _stream()), "llmp_b200_decode_vector")
+        return out
+    g = N.DecodeGluProduct()
+    g.gate, g.gate_first = gate_op, first
+    g.up = _decode_operand(decoder, up, up_scales, k, tensor_scale, rows_per_scale)
+    g.up_first, g.outputs, g.glu, g.limit = up_first, outputs, glu, limit
+    g.x, g.rows, g.x_stride = x.data_ptr(), rows, x.stride(0)
+    g.y, g.y_stride = out.data_ptr(), out.stride(0)
+    N.check(N.lib().llmp_b200_decode_vector_glu(C.byref(g), _stream()),
+            "llmp_b200_decode_vector_glu")
+    return out

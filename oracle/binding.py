@@ -99,6 +99,10 @@ def lib():
             "orc_mxfp8_dequant": [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p],
             "orc_mxfp8_gemm": [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
                                C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int],
+            "orc_decode_vector": [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p,
+                                  C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
+                                  C.c_int, C.c_float, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p,
+                                  C.c_int64],
             "orc_moe_route": [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p],
             "orc_moe_combine": [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                 C.c_void_p],
@@ -294,3 +298,25 @@ def moe_combine(rows, position, weights, tokens, used):
     lib().orc_moe_combine(_p(rows), _p(_c(position, np.int32)), _p(_c(weights, np.float32)), used,
                           tokens, width, _p(dst))
     return dst
+
+
+DECODER_Q8_0, DECODER_MXFP8_SPLIT, DECODER_MXFP8_ATOMS = 0, 1, 2
+
+
+def decode_vector(decoder, data, x, k, outputs, *, scales=None, first=0, up=None, up_scales=None,
+                  up_first=0, glu=-1, limit=0.0, tensor_scale=None, rows_per_scale=1):
+    """The decode module's vector product (or GLU product with `up`): data uint8 [n, row_bytes],
+    x F32 [rows, k] -> F32 [rows, outputs]."""
+    data = np.ascontiguousarray(data, dtype=np.uint8)
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    rows = x.shape[0]
+    y = np.empty((rows, outputs), np.float32)
+    hold = [None if a is None else np.ascontiguousarray(a, dtype=np.uint8)
+            for a in (scales, up, up_scales)]
+    ts = None if tensor_scale is None else np.ascontiguousarray(tensor_scale, dtype=np.float32)
+    lib().orc_decode_vector(decoder, _p(data), _p(hold[0]) if hold[0] is not None else None,
+                            data.shape[1], _p(hold[1]) if hold[1] is not None else None,
+                            _p(hold[2]) if hold[2] is not None else None, k,
+                            _p(ts) if ts is not None else None, rows_per_scale, first, up_first,
+                            outputs, glu, limit, _p(x), rows, x.shape[1], _p(y), outputs)
+    return y

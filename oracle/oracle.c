@@ -537,6 +537,72 @@ uint32_t orc_mxfp8_scale_code(float amax) {
   return e > 253u ? 253u : e;
 }
 
+/* ------------------------------------------------------------------------- */
+/* Decode module, vector products (templates.cuh:83-186).                      */
+/* ------------------------------------------------------------------------- */
+uint64_t orc_scale_atom_offset(uint64_t row, uint64_t block, uint64_t blocks);
+
+/* decoders.cuh:106-125 (Q8_0: half a block a segment), 193-220 (MXFP8). */
+static void decode_segment(int decoder, const uint8_t* data, const uint8_t* scales,
+                           int64_t row_bytes, int64_t k, int64_t row, int64_t seg, float v[16]) {
+  if (decoder == 0) {
+    const uint8_t* block = data + row * row_bytes + (seg / 2) * ORC_Q8_0_BYTES;
+    const float d = orc_f16_to_f32(load_u16(block));
+    const int8_t* q = (const int8_t*)(block + 2 + (seg & 1) * 16);
+    for (int i = 0; i < 16; ++i) v[i] = d * (float)q[i];
+    return;
+  }
+  const uint8_t e = decoder == 1
+                        ? scales[row * (k / 32) + seg / 2]
+                        : scales[orc_scale_atom_offset((uint64_t)row, (uint64_t)(seg / 2),
+                                                       (uint64_t)(k / 32))];
+  const float s = orc_e8m0_to_f32(e);
+  const uint8_t* c = data + row * row_bytes + seg * 16;
+  for (int i = 0; i < 16; ++i) v[i] = orc_e4m3_to_f32(c[i]) * s;
+}
+
+static float decode_row_dot(int decoder, const uint8_t* data, const uint8_t* scales,
+                            int64_t row_bytes, int64_t k, int64_t row, const float* x) {
+  float lane[32];
+  const int64_t segs = k / 16;
+  for (int l = 0; l < 32; ++l) {
+    float acc = 0.0f;
+    for (int64_t seg = l; seg < segs; seg += 32) {
+      float v[16];
+      decode_segment(decoder, data, scales, row_bytes, k, row, seg, v);
+      for (int i = 0; i < 16; ++i) acc = fmaf(v[i], x[seg * 16 + i], acc);
+    }
+    lane[l] = acc;
+  }
+  for (int offset = 16; offset > 0; offset >>= 1) {
+    float next[32];
+    for (int l = 0; l < 32; ++l) next[l] = lane[l] + lane[l ^ offset];
+    memcpy(lane, next, sizeof(lane));
+  }
+  return lane[0];
+}
+
+void orc_decode_vector(int decoder, const uint8_t* data, const uint8_t* scales, int64_t row_bytes,
+                       const uint8_t* data2, const uint8_t* scales2, int64_t k,
+                       const float* tensor_scale, int64_t rows_per_scale, int64_t first,
+                       int64_t first2, int64_t outputs, int glu, float limit, const float* x,
+                       int64_t rows, int64_t x_stride, float* y, int64_t y_stride) {
+  for (int64_t j = 0; j < outputs; ++j) {
+    const float scale = tensor_scale ? tensor_scale[(first + j) / rows_per_scale] : 1.0f;
+    const float scale2 = tensor_scale ? tensor_scale[(first2 + j) / rows_per_scale] : 1.0f;
+    for (int64_t t = 0; t < rows; ++t) {
+      const float* xt = x + t * x_stride;
+      const float a = decode_row_dot(decoder, data, scales, row_bytes, k, first + j, xt) * scale;
+      if (glu < 0) {
+        y[t * y_stride + j] = a;
+      } else {
+        const float u = decode_row_dot(decoder, data2, scales2, row_bytes, k, first2 + j, xt) * scale2;
+        y[t * y_stride + j] = orc_glu(glu, a, u, limit);
+      }
+    }
+  }
+}
+
 uint64_t orc_scale_atom_offset(uint64_t row, uint64_t block, uint64_t blocks) {
   return (((row / 128) * (blocks / 4) + (block / 4)) * 512) + ((row % 32) * 16) +
          (((row % 128) / 32) * 4) + (block % 4);

@@ -114,6 +114,22 @@ void orc_mxfp8_gemm(int m, int n, int k, const uint8_t* a, const uint8_t* a_scal
                     int threads);
 
 /* ---- MoE route / combine (src/kernels/ggml/moe_layout.h:47-83, llmp_moe.cu:81-160, 393-435) ---- */
+/* The decode module's vector products with F32 activations
+ * (src/kernels/decode/templates.cuh:83-186, decoders.cuh:106-125, 193-220,
+ * products.h:96-147): a warp a weight row, lane l takes the 16-value segments l,
+ * l + 32, ... with one fused multiply-add a value in order, the lanes meet in a
+ * butterfly over lanes 16, 8, 4, 2, 1 apart, the sum times the row's tensor scale.
+ * decoder: 0 Q8_0 blocks (v = d * q), 1 MXFP8 with row-major scales, 2 MXFP8 with
+ * scale atoms (v = e4m3 * 2^(e - 127)).  y[t * y_stride + j] for t < rows, j <
+ * outputs.  glu < 0: plain product of (data, scales); else the GLU of the gate
+ * operand (data, scales, row first) and the up operand (data2, scales2, row
+ * first2), kinds as orc_glu. */
+void orc_decode_vector(int decoder, const uint8_t* data, const uint8_t* scales, int64_t row_bytes,
+                       const uint8_t* data2, const uint8_t* scales2, int64_t k,
+                       const float* tensor_scale, int64_t rows_per_scale, int64_t first,
+                       int64_t first2, int64_t outputs, int glu, float limit, const float* x,
+                       int64_t rows, int64_t x_stride, float* y, int64_t y_stride);
+
 int64_t orc_moe_route_ints(int64_t experts, int64_t used, int64_t tokens);
 void orc_moe_route(const int32_t* ids, int ids_stride, int experts, int used, int tokens,
                    int32_t* out);

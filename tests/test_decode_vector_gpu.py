@@ -1,0 +1,111 @@
+"""GPU parity of the decode module's vector products (F32 activations; Q8_0 blocks and MXFP8
+weights) against the CPU oracle, through the C ABI.  The oracle restates the reference's
+summation order (src/kernels/decode/templates.cuh:83-145), so plain products are compared
+bit for bit; GLU products to a few ulp of the factors (two exponential implementations)."""
+import numpy as np
+import pytest
+
+from helpers import to_dev
+from llmp_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def _ops():
+    import llmp_b200
+    return llmp_b200
+
+
+def _mxfp8(ops, torch, rng, n, k):
+    w = rng.normal(0, 0.02, size=(n, k)).astype(np.float32)
+    codes, atoms = ops.mxfp8_quantize(to_dev(torch, w))
+    return codes, atoms
+
+
+@pytest.mark.parametrize("n,k,rows", [(64, 256, 1), (300, 4096, 1), (100, 1024, 5), (40, 96, 16),
+                                      (7, 32, 2)])
+def test_q8_0_vector_products_are_the_reference_bits(cuda, orc, n, k, rows):
+    torch = cuda
+    ops = _ops()
+    rng = np.random.default_rng(n + k + rows)
+    w = synth.q8_0_weights(rng, n, k)
+    x = rng.normal(0, 1, size=(rows, k)).astype(np.float32)
+    first, outputs = (3, n - 5) if n > 8 else (0, n)
+    buf = torch.full((rows * outputs + 16,), float("nan"), device="cuda")
+    out = buf[: rows * outputs].view(rows, outputs)
+    ops.decode_vector(ops.DECODER_Q8_0, to_dev(torch, w), to_dev(torch, x), k, outputs, first=first,
+                      out=out)
+    torch.cuda.synchronize()
+    assert torch.isnan(buf[rows * outputs:]).all()
+    want = orc.decode_vector(orc.DECODER_Q8_0, w, x, k, outputs, first=first)
+    assert np.array_equal(out.cpu().numpy(), want)
+    # and the values are the product of the dequantized weights
+    ref = x.astype(np.float64) @ orc.dequant(orc.Q8_0, w).reshape(n, k).astype(np.float64)[first:first + outputs].T
+    assert np.abs(want - ref).max() <= 1e-5 * max(np.abs(ref).max(), 1e-30)
+
+
+@pytest.mark.parametrize("atoms", [False, True])
+@pytest.mark.parametrize("n,k,rows", [(256, 512, 1), (130, 4096, 3), (12288, 4096, 1), (64, 128, 16)])
+def test_mxfp8_vector_products_are_the_reference_bits(cuda, orc, n, k, rows, atoms):
+    torch = cuda
+    ops = _ops()
+    rng = np.random.default_rng(n + k + rows)
+    codes, scale_atoms = _mxfp8(ops, torch, rng, n, k)
+    x = rng.normal(0, 1, size=(rows, k)).astype(np.float32)
+    codes_h, atoms_h = codes.cpu().numpy(), scale_atoms.cpu().numpy()
+    if atoms:
+        scales_h, decoder, odec = atoms_h, ops.DECODER_MXFP8_ATOMS, orc.DECODER_MXFP8_ATOMS
+    else:
+        # the same scales row-major: atom (row, block) -> [row, block]
+        blocks = k // 32
+        r = np.arange(n)[:, None]
+        b = np.arange(blocks)[None, :]
+        at = (((r // 128) * (blocks // 4) + (b // 4)) * 512) + ((r % 32) * 16) + (((r % 128) // 32) * 4) + (b % 4)
+        scales_h, decoder, odec = atoms_h.reshape(-1)[at].astype(np.uint8), ops.DECODER_MXFP8_SPLIT, \
+            orc.DECODER_MXFP8_SPLIT
+    got = ops.decode_vector(decoder, codes, to_dev(torch, x), k, n, scales=to_dev(torch, scales_h))
+    want = orc.decode_vector(odec, codes_h, x, k, n, scales=scales_h)
+    assert np.array_equal(got.cpu().numpy(), want)
+    deq = orc.mxfp8_dequant(codes_h, atoms_h)[:n].astype(np.float64)
+    ref = x.astype(np.float64) @ deq.T
+    assert np.abs(want - ref).max() <= 1e-5 * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("glu,limit", [(1, 0.0), (2, 5.0), (3, 0.0)])
+def test_vector_glu_and_tensor_scales(cuda, orc, glu, limit):
+    torch = cuda
+    ops = _ops()
+    rng = np.random.default_rng(glu)
+    n, k, rows = 96, 1024, 4
+    w = synth.q8_0_weights(rng, 2 * n, k)            # a stacked gate and up
+    x = rng.normal(0, 3, size=(rows, k)).astype(np.float32)
+    ts = np.array([0.5, 1.75], np.float32)            # one tensor scale per stacked matrix
+    wd = to_dev(torch, w)
+    got = ops.decode_vector(ops.DECODER_Q8_0, wd, to_dev(torch, x), k, n, up=wd, up_first=n, glu=glu,
+                            limit=limit, tensor_scale=to_dev(torch, ts), rows_per_scale=n)
+    want = orc.decode_vector(orc.DECODER_Q8_0, w, x, k, n, up=w, up_first=n, glu=glu, limit=limit,
+                             tensor_scale=ts, rows_per_scale=n)
+    got = got.cpu().numpy()
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() <= 4e-6 * np.abs(want).max()
+    # the plain products under the GLU are the oracle's bits, scales included
+    g = ops.decode_vector(ops.DECODER_Q8_0, wd, to_dev(torch, x), k, n, tensor_scale=to_dev(torch, ts),
+                          rows_per_scale=n)
+    assert np.array_equal(g.cpu().numpy(), orc.decode_vector(orc.DECODER_Q8_0, w, x, k, n,
+                                                              tensor_scale=ts, rows_per_scale=n))
+
+
+def test_vector_products_refuse_what_they_do_not_take(cuda, orc):
+    torch = cuda
+    ops = _ops()
+    w = to_dev(torch, synth.q8_0_weights(np.random.default_rng(0), 8, 64))
+    x = torch.zeros((17, 64), device="cuda")
+    with pytest.raises(ops.Rejected):
+        ops.decode_vector(ops.DECODER_Q8_0, w, x, 64, 8)                       # 17 rows
+    with pytest.raises(ops.Rejected):
+        ops.decode_vector(ops.DECODER_Q8_0, w, x[:1], 64, 9)                   # past the matrix
+    with pytest.raises(ops.Rejected):
+        ops.decode_vector(ops.DECODER_MXFP8_SPLIT, w, x[:1], 64, 8)            # MXFP8 without scales
+    with pytest.raises(ops.Rejected):
+        ops.decode_vector(7, w, x[:1], 64, 8)                                  # no such decoder
+    torch.cuda.synchronize()

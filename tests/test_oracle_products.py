@@ -103,3 +103,35 @@ def test_route_is_a_stable_counting_sort(orc):
     assert np.array_equal(r["token"][:valid.sum()], order // used)
     assert np.array_equal(r["expert"][:valid.sum()], flat[order])
     assert np.allclose(w.sum(axis=1), 1.0, atol=1e-6)
+
+
+def test_decode_module_vector_product_follows_the_lane_order():
+    """orc_decode_vector against an independent numpy statement of the reference's order
+    (src/kernels/decode/templates.cuh:83-145): lane l sums segments l, l + 32, ... with one
+    fused multiply-add a value, then a butterfly over lanes 16, 8, 4, 2, 1 apart."""
+    import math
+    from llmp_b200 import synth
+    from oracle import binding as orc
+    rng = np.random.default_rng(5)
+    n, k = 6, 1056                      # 66 segments: lanes 0 and 1 take three, the rest two
+    w = synth.q8_0_weights(rng, n, k)
+    x = rng.normal(0, 1, size=(2, k)).astype(np.float32)
+    got = orc.decode_vector(orc.DECODER_Q8_0, w, x, k, n)
+    vals = orc.dequant(orc.Q8_0, w).reshape(n, k)          # d * q, one F32 rounding each
+    for t in range(2):
+        for r in range(n):
+            lanes = []
+            for lane in range(32):
+                acc = np.float32(0.0)
+                for seg in range(lane, k // 16, 32):
+                    for i in range(16):
+                        j = seg * 16 + i
+                        acc = np.float32(math.fma(float(vals[r, j]), float(x[t, j]), float(acc))) \
+                            if hasattr(math, "fma") else np.float32(
+                                np.float64(vals[r, j]) * np.float64(x[t, j]) + np.float64(acc))
+                lanes.append(acc)
+            for offset in (16, 8, 4, 2, 1):
+                lanes = [np.float32(lanes[i] + lanes[i ^ offset]) for i in range(32)]
+            assert got[t, r] == lanes[0]
+    ref = x.astype(np.float64) @ vals.astype(np.float64).T
+    assert np.abs(got - ref).max() <= 1e-5 * np.abs(ref).max()
