@@ -288,7 +288,7 @@ int llmp_b200_mxfp8_mul_mat_vec(const void* codes, const void* scales, const flo
  * y[t * y_stride + j] = tensor_scale(row) * sum_k W[first + j, k] * x[t * x_stride + k] for
  * t < rows (1..16) and j < outputs, summed in the reference's order (a warp a row, lane l the
  * 16-value segments l, l + 32, ..., a butterfly over the lanes), so the F32 results are the
- * reference's bit for bit.  decode::RunMatrix and RunGrouped are not part of this build. */
+ * reference's bit for bit.  decode::RunGrouped is not part of this build. */
 #define LLMP_B200_DECODER_Q8_0_BLOCKS 0
 #define LLMP_B200_DECODER_MXFP8_SPLIT 1  /* scales [rows, k / 32] row-major */
 #define LLMP_B200_DECODER_MXFP8_ATOMS 2  /* scales in 128 x 4 scale atoms */
@@ -311,6 +311,13 @@ typedef struct llmp_b200_decode_product {
   uint64_t y_stride;
 } llmp_b200_decode_product;
 int llmp_b200_decode_vector(const llmp_b200_decode_product* product, void* stream);
+/* decode::RunMatrix with MatrixPath::kMma (products.h:116-120; tile kernel templates.cuh:
+ * 236-440): any number of activation rows; weights and activations are rounded to the
+ * decoder's MMA element (FP16 for Q8_0 blocks, BF16 for MXFP8: DecoderMmaElement) and
+ * multiplied on the tensor cores with F32 accumulation, here tcgen05 kind::f16 over the whole
+ * K in tensor memory.  Results agree with the reference's mma.sync tiles to F32 summation
+ * order.  The FMA path (MatrixPath::kFma, for devices without tensor cores) is not provided. */
+int llmp_b200_decode_matrix(const llmp_b200_decode_product* product, void* stream);
 /* out[t, j] = glu(gate[t, j], up[t, j]) of rows gate_first + j and up_first + j; glu is
  * LLMP_B200_GLU_SWIGLU, _SWIGLU_CLAMP (limit) or _GEGLU (tanh): ir::GluKind 0, 3 and 2 of
  * templates.cuh:75-95; the erf GeGLU (1) is refused. */

@@ -117,6 +117,7 @@ SIGNATURES = {
     "llmp_b200_mxfp8_gemm": (C.c_int, [C.POINTER(Mxfp8GemmDesc), C.c_int, C.c_void_p]),
     "llmp_b200_decode_vector": (C.c_int, [C.POINTER(DecodeProduct), C.c_void_p]),
     "llmp_b200_decode_vector_glu": (C.c_int, [C.POINTER(DecodeGluProduct), C.c_void_p]),
+    "llmp_b200_decode_matrix": (C.c_int, [C.POINTER(DecodeProduct), C.c_void_p]),
     "llmp_b200_vecq_f32": (C.c_int, [C.c_int, C.POINTER(VecQDesc), C.c_void_p, C.c_void_p]),
     "llmp_b200_vecq_q8_scratch": (C.c_size_t, [C.c_int, C.c_int]),
     "llmp_b200_vecq_q8": (C.c_int, [C.c_int, C.POINTER(VecQDesc), C.c_void_p, C.c_void_p,

@@ -1,0 +1,340 @@
+// The decode module's matrix product on B200: y = W x for any number of F32
+// activation rows, the weight decoded on the fly and both operands rounded to
+// the decoder's 16-bit MMA element (FP16 for Q8_0 blocks, BF16 for MXFP8), F32
+// accumulation.  Interface and numerics follow decode::RunMatrix with
+// MatrixPath::kMma (src/kernels/decode/products.h:96-120; tile kernel
+// templates.cuh:236-440, which decodes to D::Mma and runs mma.sync tiles); the
+// structure is B200's: tcgen05.mma kind::f16 with the whole K accumulated in
+// tensor memory, operands written by decode warps straight into the
+// 128-byte-swizzled K-major tiles the MMA reads.
+//
+//   warp 0       allocates TMEM, issues four MMAs (128 x 128 x 16) a k-step of 64
+//                values, commits each stage back to the writers;
+//   warps 1-4    weights: a thread a weight row, 64 values a k-step decoded
+//                (d * q, or e4m3 * 2^(e-127)), rounded to the MMA element;
+//   warps 5-8    activations: a thread an activation row, 64 floats a k-step
+//                rounded to the MMA element;
+//   warps 9-12   epilogue: the tile out of tensor memory, times the row's tensor
+//                scale, to y.
+// Rows past the matrix or the batch are written as zeros.  Every wait is bounded.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
+#include "common.cuh"
+#include "tc.cuh"
+
+namespace llmp_b200 {
+namespace {
+
+using Operand = llmp_b200_decode_operand;
+
+constexpr int kTile = 128;     // weight rows (TMEM lanes) and activation rows (columns) a tile
+constexpr int kStepK = 64;     // values a k-step: one 128-byte swizzle row of 16-bit elements
+constexpr int kStages = 4;
+constexpr int kTileBytes = kTile * 128;
+constexpr int kThreads = 13 * 32;
+constexpr int kSmem = (kStages * 2 * kTileBytes) + 1024 + 256;
+
+struct Shared {
+  std::uint64_t full[kStages];   // eight writer warps have filled the stage
+  std::uint64_t empty[kStages];  // the tensor core has read it
+  std::uint64_t done;            // the tile's sum is complete
+  std::uint32_t tmem_base;
+  std::uint32_t abort;
+};
+
+struct Args {
+  Operand w;
+  std::uint32_t first, outputs, rows;
+  const float* x;
+  std::uint64_t x_stride;
+  float* y;
+  std::uint64_t y_stride;
+};
+
+__device__ __forceinline__ float E8m0(std::uint32_t e) {
+  return e == 0 ? __uint_as_float(0x00400000u) : e == 255 ? __uint_as_float(0x7fffffffu)
+                                                           : __uint_as_float(e << 23);
+}
+
+template <bool kBf16>
+__device__ __forceinline__ std::uint32_t Pack(float lo, float hi) {
+  if constexpr (kBf16) {
+    const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const std::uint32_t*>(&p);
+  } else {
+    const __half2 p = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const std::uint32_t*>(&p);
+  }
+}
+
+// 64 values of row `row` from value k0 on, as 32 packed pairs.
+template <int kDecoder>
+__device__ __forceinline__ void DecodeRow(const Operand& p, std::uint32_t row, std::uint32_t k0,
+                                          std::uint32_t (&out)[32]) {
+  constexpr bool kBf16 = kDecoder != LLMP_B200_DECODER_Q8_0_BLOCKS;
+  const auto* data = static_cast<const std::uint8_t*>(p.data);
+#pragma unroll
+  for (int b = 0; b < 2; ++b) {
+    const std::uint32_t kb = k0 + (b * 32);
+    if (kb >= p.k) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) out[(16 * b) + i] = 0u;
+      continue;
+    }
+    if constexpr (kDecoder == LLMP_B200_DECODER_Q8_0_BLOCKS) {
+      const std::uint8_t* block = data + (row * p.row_bytes) + (static_cast<std::uint64_t>(kb / 32) * 34);
+      const auto* h = reinterpret_cast<const unsigned short*>(block);
+      const float d = HalfBitsToFloat(__ldg(h));
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const std::uint32_t pair = __ldg(h + 1 + i);
+        out[(16 * b) + i] = Pack<kBf16>(d * static_cast<float>(static_cast<std::int8_t>(pair & 0xffu)),
+                                        d * static_cast<float>(static_cast<std::int8_t>(pair >> 8)));
+      }
+    } else {
+      const auto* scales = static_cast<const std::uint8_t*>(p.scales);
+      const std::uint32_t blocks = p.k / 32, block = kb / 32;
+      const std::uint64_t at =
+          kDecoder == LLMP_B200_DECODER_MXFP8_SPLIT
+              ? (static_cast<std::uint64_t>(row) * blocks) + block
+              : ((((static_cast<std::uint64_t>(row) / 128) * (blocks / 4)) + (block / 4)) * 512) +
+                    ((row % 32) * 16) + (((row % 128) / 32) * 4) + (block % 4);
+      const float s = E8m0(__ldg(scales + at));
+      const auto* codes = reinterpret_cast<const uint4*>(data + (row * p.row_bytes) + kb);
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const uint4 c = __ldg(codes + q);
+        const std::uint32_t w[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const __half2_raw hh = __nv_cvt_fp8x2_to_halfraw2(
+              static_cast<__nv_fp8x2_storage_t>((w[i / 2] >> (16 * (i % 2))) & 0xffffu), __NV_E4M3);
+          out[(16 * b) + (8 * q) + i] = Pack<kBf16>(__half2float(__ushort_as_half(hh.x)) * s,
+                                                    __half2float(__ushort_as_half(hh.y)) * s);
+        }
+      }
+    }
+  }
+}
+
+// Row t's 128 bytes into the swizzled tile: 16-byte chunk j at j ^ (t % 8).
+__device__ __forceinline__ void StoreRow(unsigned char* tile, int t, const std::uint32_t (&v)[32]) {
+  unsigned char* row = tile + ((t >> 3) * 1024) + ((t & 7) * 128);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    *reinterpret_cast<uint4*>(row + ((j ^ (t & 7)) * 16)) =
+        make_uint4(v[4 * j], v[(4 * j) + 1], v[(4 * j) + 2], v[(4 * j) + 3]);
+  }
+}
+
+template <int kDecoder>
+__global__ void __launch_bounds__(kThreads, 1) DecodeMatrixKernel(const Args a, unsigned int* faults) {
+  constexpr bool kBf16 = kDecoder != LLMP_B200_DECODER_Q8_0_BLOCKS;
+  extern __shared__ unsigned char raw_smem[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<std::uintptr_t>(raw_smem) + 1023) & ~static_cast<std::uintptr_t>(1023));
+  unsigned char* w_tiles = smem;
+  unsigned char* x_tiles = smem + (kStages * kTileBytes);
+  Shared* sh = reinterpret_cast<Shared*>(x_tiles + (kStages * kTileBytes));
+
+  const int warp = static_cast<int>(threadIdx.x) >> 5;
+  const int lane = static_cast<int>(threadIdx.x) & 31;
+  const std::uint32_t n0 = blockIdx.x * kTile;  // first output (weight row first + n0)
+  const std::uint32_t m0 = blockIdx.y * kTile;  // first activation row
+  const int ksteps = static_cast<int>((a.w.k + kStepK - 1) / kStepK);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      tc::MbarInit(&sh->full[s], 8);
+      tc::MbarInit(&sh->empty[s], 1);
+    }
+    tc::MbarInit(&sh->done, 1);
+    sh->abort = 0;
+    tc::MbarInitFence();
+  }
+  if (warp == 0) {
+    tc::TmemAlloc(&sh->tmem_base, 128);
+    tc::TmemRelinquish();
+  }
+  tc::TcFenceBefore();
+  __syncthreads();
+  tc::TcFenceAfter();
+  const std::uint32_t tmem = sh->tmem_base;
+  volatile std::uint32_t* abort_flag = &sh->abort;
+  auto give_up = [&]() {
+    *abort_flag = 1;
+    atomicAdd(faults, 1u);
+  };
+
+  GridDependencyWait();  // the activations may be the kernel before's output
+  if (warp == 0) {
+    if (lane == 0) {
+      const std::uint32_t idesc = tc::IdescF16(kTile, kTile, kBf16);
+      for (int ks = 0; ks < ksteps && !*abort_flag; ++ks) {
+        const int s = ks % kStages;
+        if (!tc::MbarWait(&sh->full[s], (ks / kStages) & 1)) {
+          give_up();
+          break;
+        }
+        tc::TcFenceAfter();
+        const std::uint64_t wdesc = tc::SmemDesc(w_tiles + (s * kTileBytes), true, 1024);
+        const std::uint64_t xdesc = tc::SmemDesc(x_tiles + (s * kTileBytes), true, 1024);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {  // 16 values = 32 bytes along the swizzled row
+          tc::MmaF16(tmem, wdesc + (kk * 2), xdesc + (kk * 2), idesc, ks > 0 || kk > 0);
+        }
+        tc::TcCommit(&sh->empty[s]);
+      }
+      tc::TcCommit(&sh->done);
+    }
+  } else if (warp <= 8) {
+    const bool weights = warp <= 4;
+    const int t = (static_cast<int>(threadIdx.x) - (weights ? 32 : 160));  // 0..127
+    for (int ks = 0; ks < ksteps && !*abort_flag; ++ks) {
+      const int s = ks % kStages;
+      std::uint32_t v[32];
+      if (weights) {
+        if (n0 + t < a.outputs) {
+          DecodeRow<kDecoder>(a.w, a.first + n0 + t, static_cast<std::uint32_t>(ks) * kStepK, v);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0u;
+        }
+      } else {
+        const std::uint32_t k0 = static_cast<std::uint32_t>(ks) * kStepK;
+        if (m0 + t < a.rows) {
+          const auto* xp = reinterpret_cast<const float4*>(a.x + (static_cast<std::uint64_t>(m0 + t) * a.x_stride) + k0);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float4 f = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (k0 + (4 * i) < a.w.k) f = __ldg(xp + i);   // k is a multiple of 32: whole float4s
+            v[2 * i] = Pack<kBf16>(f.x, f.y);
+            v[(2 * i) + 1] = Pack<kBf16>(f.z, f.w);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0u;
+        }
+      }
+      bool ok = true;
+      if (lane == 0) ok = tc::MbarWait(&sh->empty[s], ((ks / kStages) & 1) ^ 1);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) {
+        if (lane == 0) give_up();
+        break;
+      }
+      StoreRow((weights ? w_tiles : x_tiles) + (s * kTileBytes), t, v);
+      tc::FenceProxyAsync();  // generic-proxy writes, read by the tensor core's proxy
+      __syncwarp();
+      if (lane == 0) tc::MbarArrive(&sh->full[s]);
+    }
+  } else {
+    const int quadrant = warp & 3;  // the TMEM lanes this warp may read
+    bool ok = true;
+    if (lane == 0) ok = tc::MbarWait(&sh->done, 0);
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    if (!ok) {
+      if (lane == 0) give_up();
+    } else {
+      tc::TcFenceAfter();
+      const std::uint32_t n = n0 + (quadrant * 32) + lane;  // this thread's output
+      const float scale = (n < a.outputs && a.w.tensor_scale != nullptr)
+                              ? __ldg(a.w.tensor_scale + ((a.first + n) / a.w.rows_per_scale))
+                              : 1.0f;
+#pragma unroll 1
+      for (int c = 0; c < kTile / 32; ++c) {
+        std::uint32_t r[32];
+        tc::TmemLoad32(tmem + (static_cast<std::uint32_t>(quadrant * 32) << 16) + (c * 32), r);
+        tc::TmemLoadWait();
+        if (n < a.outputs) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const std::uint32_t m = m0 + (c * 32) + j;
+            if (m < a.rows) a.y[(static_cast<std::uint64_t>(m) * a.y_stride) + n] = __uint_as_float(r[j]) * scale;
+          }
+        }
+      }
+    }
+  }
+
+  tc::TcFenceBefore();
+  __syncthreads();
+  if (warp == 0) {
+    tc::TcFenceAfter();
+    tc::TmemDealloc(tmem, 128);
+  }
+}
+
+template <int kDecoder>
+cudaError_t Launch(const Args& a, unsigned int* faults, cudaStream_t s) {
+  static thread_local int configured_device = -1;
+  int device = -1;
+  cudaGetDevice(&device);
+  if (configured_device != device) {
+    const cudaError_t e = cudaFuncSetAttribute(DecodeMatrixKernel<kDecoder>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    if (e != cudaSuccess) return e;
+    configured_device = device;
+  }
+  const dim3 grid((a.outputs + kTile - 1) / kTile, (a.rows + kTile - 1) / kTile);
+  return LaunchPdl(DecodeMatrixKernel<kDecoder>, grid, dim3(kThreads), static_cast<std::size_t>(kSmem), s,
+                   a, faults);
+}
+
+}  // namespace
+}  // namespace llmp_b200
+
+extern "C" {
+
+int llmp_b200_decode_matrix(const llmp_b200_decode_product* product, void* stream) {
+  using namespace llmp_b200;
+  if (product == nullptr) return Reject("decode.matrix: null product");
+  const Operand& w = product->w;
+  if (w.decoder > LLMP_B200_DECODER_MXFP8_ATOMS) {
+    return Reject("decode.matrix: decoder %u is not one this build has (Q8_0 blocks, MXFP8)", w.decoder);
+  }
+  const bool q8 = w.decoder == LLMP_B200_DECODER_Q8_0_BLOCKS;
+  if (w.data == nullptr || w.k < 32 || w.k % 32 != 0 || w.rows < 1 ||
+      w.row_bytes < (q8 ? (w.k / 32) * 34ull : w.k) ||
+      (q8 ? (!Aligned(w.data, 2) || w.row_bytes % 2 != 0)
+          : (!Aligned(w.data, 16) || w.row_bytes % 16 != 0 || w.scales == nullptr)) ||
+      (w.decoder == LLMP_B200_DECODER_MXFP8_ATOMS && w.k % 128 != 0) ||
+      (w.tensor_scale != nullptr && w.rows_per_scale < 1)) {
+    return Reject("decode.matrix: a Q8_0 (2-byte aligned) or MXFP8 (16-byte aligned, with scales) weight "
+                  "of k a positive multiple of 32");
+  }
+  if (product->outputs < 1 || product->rows < 1 || product->x == nullptr || product->y == nullptr ||
+      product->first + product->outputs > w.rows || product->rows > 0x7fffff80ull ||
+      product->outputs > 0x7fffff80ull) {
+    return Reject("decode.matrix: at least one activation row and output, rows inside the matrix");
+  }
+  if (product->x_stride < w.k || product->y_stride < product->outputs || !Aligned(product->x, 16) ||
+      product->x_stride % 4 != 0 || !Aligned(product->y, 4)) {
+    return Reject("decode.matrix: activation rows of k floats, 16-byte aligned; output rows of "
+                  "`outputs` floats");
+  }
+  if ((product->rows + 127) / 128 > 65535) return Reject("decode.matrix: more row tiles than a grid holds");
+  if (const int status = DeviceStatus(); status != 0) return status;
+  unsigned int* faults = FaultCounter();
+  if (faults == nullptr) return Reject("decode.matrix: no fault counter on this device");
+  Args a{};
+  a.w = w;
+  a.first = static_cast<std::uint32_t>(product->first);
+  a.outputs = static_cast<std::uint32_t>(product->outputs);
+  a.rows = static_cast<std::uint32_t>(product->rows);
+  a.x = product->x;
+  a.x_stride = product->x_stride;
+  a.y = product->y;
+  a.y_stride = product->y_stride;
+  auto* s = static_cast<cudaStream_t>(stream);
+  const cudaError_t e =
+      w.decoder == LLMP_B200_DECODER_Q8_0_BLOCKS   ? Launch<LLMP_B200_DECODER_Q8_0_BLOCKS>(a, faults, s)
+      : w.decoder == LLMP_B200_DECODER_MXFP8_SPLIT ? Launch<LLMP_B200_DECODER_MXFP8_SPLIT>(a, faults, s)
+                                                   : Launch<LLMP_B200_DECODER_MXFP8_ATOMS>(a, faults, s);
+  if (e != cudaSuccess) return Failed(e, "decode.matrix launch");
+  return 0;
+}
+
+}  // extern "C"

@@ -167,10 +167,10 @@ __host__ __device__ constexpr std::uint32_t IdescI8(int m, int n, bool a_signed,
   return (2u << 4) | ((a_signed ? 1u : 0u) << 7) | ((b_signed ? 1u : 0u) << 10) |
          (static_cast<std::uint32_t>(n >> 3) << 17) | (static_cast<std::uint32_t>(m >> 4) << 24);
 }
-// kind::f16: A, B FP16 K-major, F32 accumulate.
-__host__ __device__ constexpr std::uint32_t IdescF16(int m, int n) {
-  return (1u << 4) | (static_cast<std::uint32_t>(n >> 3) << 17) |
-         (static_cast<std::uint32_t>(m >> 4) << 24);
+// kind::f16: A, B FP16 (or both BF16) K-major, F32 accumulate.
+__host__ __device__ constexpr std::uint32_t IdescF16(int m, int n, bool bf16 = false) {
+  return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) |
+         (static_cast<std::uint32_t>(n >> 3) << 17) | (static_cast<std::uint32_t>(m >> 4) << 24);
 }
 // kind::mxf8f6f4.block_scale: E4M3 x E4M3, E8M0 scales per 32, F32 accumulate.
 __host__ __device__ constexpr std::uint32_t IdescMxf8(int m, int n, int a_sf_id, int b_sf_id) {

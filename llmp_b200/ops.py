@@ -17,7 +17,7 @@ from ._native import (GLU_GEGLU, GLU_NONE, GLU_SWIGLU, GLU_SWIGLU_CLAMP, TYPE_Q4
 
 __all__ = ["available", "sm_count", "device_faults", "block_bytes", "block_elems", "q8_1_row_blocks",
            "quantize_q8", "vecq", "vecq_f32", "vecq_q8", "vecq_q8_scratch", "vecq_variants", "vecq_block_sums", "mxfp8_padded_rows",
-           "mxfp8_quantize", "mxfp8_swizzle", "mxfp8_gemm", "mxfp8_mul_mat_vec", "decode_vector", "DECODER_Q8_0", "DECODER_MXFP8_SPLIT",
+           "mxfp8_quantize", "mxfp8_swizzle", "mxfp8_gemm", "mxfp8_mul_mat_vec", "decode_vector", "decode_matrix", "DECODER_Q8_0", "DECODER_MXFP8_SPLIT",
            "DECODER_MXFP8_ATOMS", "mmq_quantize", "mmq", "moe_route", "grouped_gemm",
            "moe_glu_quantize", "moe_combine", "moe_ffn", "TYPE_Q8_0", "TYPE_Q4_K",
            "GLU_NONE", "GLU_SWIGLU", "GLU_SWIGLU_CLAMP", "GLU_GEGLU", "Rejected", "LaunchFailed"]
@@ -509,4 +509,26 @@ def decode_vector(decoder: int, data: torch.Tensor, x: torch.Tensor, k: int, out
     g.y, g.y_stride = out.data_ptr(), out.stride(0)
     N.check(N.lib().llmp_b200_decode_vector_glu(C.byref(g), _stream()),
             "llmp_b200_decode_vector_glu")
+    return out
+
+
+def decode_matrix(decoder: int, data: torch.Tensor, x: torch.Tensor, k: int, outputs: int, *,
+                  scales: torch.Tensor | None = None, first: int = 0,
+                  tensor_scale: torch.Tensor | None = None, rows_per_scale: int = 1,
+                  out: torch.Tensor | None = None) -> torch.Tensor:
+    """decode::RunMatrix (MMA path): data uint8 [n, row_bytes], x F32 [rows, k] (any rows) ->
+    F32 [rows, outputs]; operands rounded to FP16 (Q8_0) or BF16 (MXFP8), F32 accumulation."""
+    _need(x, torch.float32, "decode_matrix x")
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise Rejected("decode_matrix: x F32 [rows, k], k contiguous")
+    rows = x.shape[0]
+    if out is None:
+        out = torch.empty((rows, outputs), dtype=torch.float32, device=x.device)
+    _need(out, torch.float32, "decode_matrix output")
+    p = N.DecodeProduct()
+    p.w = _decode_operand(decoder, data, scales, k, tensor_scale, rows_per_scale)
+    p.first, p.outputs = first, outputs
+    p.x, p.rows, p.x_stride = x.data_ptr(), rows, x.stride(0)
+    p.y, p.y_stride = out.data_ptr(), out.stride(0)
+    N.check(N.lib().llmp_b200_decode_matrix(C.byref(p), _stream()), "llmp_b200_decode_matrix")
     return out

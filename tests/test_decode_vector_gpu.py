@@ -109,3 +109,53 @@ def test_vector_products_refuse_what_they_do_not_take(cuda, orc):
     with pytest.raises(ops.Rejected):
         ops.decode_vector(7, w, x[:1], 64, 8)                                  # no such decoder
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("decoder", ["q8_0", "mxfp8_split", "mxfp8_atoms"])
+@pytest.mark.parametrize("n,k,rows", [(128, 256, 128), (300, 1024, 77), (64, 96, 5), (640, 4096, 513)])
+def test_matrix_product_matches_the_double_product_of_the_rounded_operands(cuda, orc, decoder, n, k,
+                                                                            rows):
+    """decode::RunMatrix (MMA path): weights decoded and rounded to FP16 (Q8_0) or BF16 (MXFP8),
+    activations rounded likewise, F32 accumulation: NMSE 1e-10 against the double product of
+    the rounded operands, 1e-5 of the output scale element by element."""
+    torch = cuda
+    ops = _ops()
+    if decoder != "q8_0" and k % 128 != 0:
+        pytest.skip("this build's MXFP8 quantizer (the weights' source here) takes k % 128 == 0")
+    rng = np.random.default_rng(n + k + rows)
+    x = rng.normal(0, 1, size=(rows, k)).astype(np.float32)
+    first = 7 if n > 64 else 0
+    outputs = n - first - (3 if n > 64 else 0)
+    buf = torch.full((rows * outputs + 32,), float("nan"), device="cuda")
+    out = buf[: rows * outputs].view(rows, outputs)
+    if decoder == "q8_0":
+        w = synth.q8_0_weights(rng, n, k)
+        ops.decode_matrix(ops.DECODER_Q8_0, to_dev(torch, w), to_dev(torch, x), k, outputs, first=first,
+                          out=out)
+        wv = orc.dequant(orc.Q8_0, w).reshape(n, k).astype(np.float16).astype(np.float64)
+        xv = x.astype(np.float16).astype(np.float64)
+    else:
+        wf = rng.normal(0, 0.02, size=(n, k)).astype(np.float32)
+        codes, atoms = ops.mxfp8_quantize(to_dev(torch, wf))
+        atoms_h = atoms.cpu().numpy()
+        if decoder == "mxfp8_atoms":
+            scales, dec = atoms, ops.DECODER_MXFP8_ATOMS
+        else:
+            blocks = k // 32
+            r = np.arange(n)[:, None]
+            b = np.arange(blocks)[None, :]
+            at = (((r // 128) * (blocks // 4) + (b // 4)) * 512) + ((r % 32) * 16) + \
+                (((r % 128) // 32) * 4) + (b % 4)
+            scales, dec = to_dev(torch, atoms_h.reshape(-1)[at].astype(np.uint8)), ops.DECODER_MXFP8_SPLIT
+        ops.decode_matrix(dec, codes, to_dev(torch, x), k, outputs, scales=scales, first=first, out=out)
+        deq = orc.mxfp8_dequant(codes.cpu().numpy(), atoms_h)[:n]
+        wv = torch.from_numpy(deq).to(torch.bfloat16).double().numpy()
+        xv = torch.from_numpy(x).to(torch.bfloat16).double().numpy()
+    torch.cuda.synchronize()
+    assert ops.device_faults() == 0
+    assert torch.isnan(buf[rows * outputs:]).all()
+    got = out.cpu().numpy().astype(np.float64)
+    want = xv @ wv[first:first + outputs].T
+    assert np.isfinite(got).all()
+    assert ((got - want) ** 2).sum() / (want ** 2).sum() <= 1e-10
+    assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()
