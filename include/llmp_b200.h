@@ -288,7 +288,7 @@ int llmp_b200_mxfp8_mul_mat_vec(const void* codes, const void* scales, const flo
  * y[t * y_stride + j] = tensor_scale(row) * sum_k W[first + j, k] * x[t * x_stride + k] for
  * t < rows (1..16) and j < outputs, summed in the reference's order (a warp a row, lane l the
  * 16-value segments l, l + 32, ..., a butterfly over the lanes), so the F32 results are the
- * reference's bit for bit.  decode::RunGrouped is not part of this build. */
+ * reference's bit for bit. */
 #define LLMP_B200_DECODER_Q8_0_BLOCKS 0
 #define LLMP_B200_DECODER_MXFP8_SPLIT 1  /* scales [rows, k / 32] row-major */
 #define LLMP_B200_DECODER_MXFP8_ATOMS 2  /* scales in 128 x 4 scale atoms */
@@ -318,6 +318,28 @@ int llmp_b200_decode_vector(const llmp_b200_decode_product* product, void* strea
  * K in tensor memory.  Results agree with the reference's mma.sync tiles to F32 summation
  * order.  The FMA path (MatrixPath::kFma, for devices without tensor cores) is not provided. */
 int llmp_b200_decode_matrix(const llmp_b200_decode_product* product, void* stream);
+/* decode::RunGrouped (products.h:149-168): for each expert e, its pairs p in [offsets[e],
+ * offsets[e + 1]) compute y[pair_out[p] (or p), j] = sum_k W_e[first + j, k] * x[pair_rows[p], k]
+ * with the matrix product's numerics.  `format` gives the experts' decoder, k and rows (its
+ * pointers are unused); `experts` is a DEVICE array of experts_count operands; offsets,
+ * pair_rows and pair_out (or NULL) are device I32 arrays.  As in the reference the device
+ * skips an expert whose operand is not of the format, a pair past `pairs`, and one naming a
+ * row past x_rows or y_rows.  The reference's rows_hint (its tile choice) has no use here. */
+typedef struct llmp_b200_decode_grouped_product {
+  llmp_b200_decode_operand format;
+  const llmp_b200_decode_operand* experts;
+  uint64_t experts_count;
+  uint64_t first, outputs;
+  const int32_t* offsets;
+  const int32_t* pair_rows;
+  const int32_t* pair_out;
+  uint64_t pairs;
+  const float* x;
+  uint64_t x_rows, x_stride;
+  float* y;
+  uint64_t y_rows, y_stride;
+} llmp_b200_decode_grouped_product;
+int llmp_b200_decode_grouped(const llmp_b200_decode_grouped_product* product, void* stream);
 /* out[t, j] = glu(gate[t, j], up[t, j]) of rows gate_first + j and up_first + j; glu is
  * LLMP_B200_GLU_SWIGLU, _SWIGLU_CLAMP (limit) or _GEGLU (tanh): ir::GluKind 0, 3 and 2 of
  * templates.cuh:75-95; the erf GeGLU (1) is refused. */

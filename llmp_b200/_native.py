@@ -46,6 +46,14 @@ class DecodeProduct(C.Structure):
                 ("y", C.c_void_p), ("y_stride", C.c_uint64)]
 
 
+class DecodeGroupedProduct(C.Structure):
+    _fields_ = [("format", DecodeOperand), ("experts", C.c_void_p), ("experts_count", C.c_uint64),
+                ("first", C.c_uint64), ("outputs", C.c_uint64), ("offsets", C.c_void_p),
+                ("pair_rows", C.c_void_p), ("pair_out", C.c_void_p), ("pairs", C.c_uint64),
+                ("x", C.c_void_p), ("x_rows", C.c_uint64), ("x_stride", C.c_uint64),
+                ("y", C.c_void_p), ("y_rows", C.c_uint64), ("y_stride", C.c_uint64)]
+
+
 class DecodeGluProduct(C.Structure):
     _fields_ = [("gate", DecodeOperand), ("gate_first", C.c_uint64), ("up", DecodeOperand),
                 ("up_first", C.c_uint64), ("outputs", C.c_uint64), ("glu", C.c_int),
@@ -118,6 +126,7 @@ SIGNATURES = {
     "llmp_b200_decode_vector": (C.c_int, [C.POINTER(DecodeProduct), C.c_void_p]),
     "llmp_b200_decode_vector_glu": (C.c_int, [C.POINTER(DecodeGluProduct), C.c_void_p]),
     "llmp_b200_decode_matrix": (C.c_int, [C.POINTER(DecodeProduct), C.c_void_p]),
+    "llmp_b200_decode_grouped": (C.c_int, [C.POINTER(DecodeGroupedProduct), C.c_void_p]),
     "llmp_b200_vecq_f32": (C.c_int, [C.c_int, C.POINTER(VecQDesc), C.c_void_p, C.c_void_p]),
     "llmp_b200_vecq_q8_scratch": (C.c_size_t, [C.c_int, C.c_int]),
     "llmp_b200_vecq_q8": (C.c_int, [C.c_int, C.POINTER(VecQDesc), C.c_void_p, C.c_void_p,

@@ -51,6 +51,14 @@ struct Args {
   std::uint64_t x_stride;
   float* y;
   std::uint64_t y_stride;
+  // Grouped (decode::RunGrouped): grid z names the expert; its pairs [offsets[e],
+  // offsets[e + 1]) are the tile's activation rows, x rows pair_rows[p], y rows
+  // pair_out[p] (or p).  `w` then carries the format's k, rows and decoder.
+  const Operand* experts;
+  const std::int32_t* offsets;
+  const std::int32_t* pair_rows;
+  const std::int32_t* pair_out;
+  std::uint32_t pairs, x_rows, y_rows;
 };
 
 __device__ __forceinline__ float E8m0(std::uint32_t e) {
@@ -129,9 +137,21 @@ __device__ __forceinline__ void StoreRow(unsigned char* tile, int t, const std::
   }
 }
 
-template <int kDecoder>
+template <int kDecoder, bool kGrouped>
 __global__ void __launch_bounds__(kThreads, 1) DecodeMatrixKernel(const Args a, unsigned int* faults) {
   constexpr bool kBf16 = kDecoder != LLMP_B200_DECODER_Q8_0_BLOCKS;
+  // The tile's weight and its activation rows [begin + m0, end).
+  Operand w = a.w;
+  std::uint32_t begin = 0, end = a.rows;
+  if constexpr (kGrouped) {
+    const std::uint32_t e = blockIdx.z;
+    const std::int32_t lo = __ldg(a.offsets + e), hi = __ldg(a.offsets + e + 1);
+    begin = lo < 0 ? 0u : min(static_cast<std::uint32_t>(lo), a.pairs);
+    end = hi < 0 ? begin : max(begin, min(static_cast<std::uint32_t>(hi), a.pairs));
+    if (begin + (blockIdx.y * kTile) >= end) return;  // uniform: before any barrier
+    w = a.experts[e];
+    if (w.k != a.w.k || w.rows != a.w.rows || w.decoder != a.w.decoder) return;  // not of the format
+  }
   extern __shared__ unsigned char raw_smem[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<std::uintptr_t>(raw_smem) + 1023) & ~static_cast<std::uintptr_t>(1023));
@@ -142,8 +162,8 @@ __global__ void __launch_bounds__(kThreads, 1) DecodeMatrixKernel(const Args a, 
   const int warp = static_cast<int>(threadIdx.x) >> 5;
   const int lane = static_cast<int>(threadIdx.x) & 31;
   const std::uint32_t n0 = blockIdx.x * kTile;  // first output (weight row first + n0)
-  const std::uint32_t m0 = blockIdx.y * kTile;  // first activation row
-  const int ksteps = static_cast<int>((a.w.k + kStepK - 1) / kStepK);
+  const std::uint32_t m0 = begin + (blockIdx.y * kTile);  // first activation row (pair)
+  const int ksteps = static_cast<int>((w.k + kStepK - 1) / kStepK);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -192,24 +212,35 @@ __global__ void __launch_bounds__(kThreads, 1) DecodeMatrixKernel(const Args a, 
   } else if (warp <= 8) {
     const bool weights = warp <= 4;
     const int t = (static_cast<int>(threadIdx.x) - (weights ? 32 : 160));  // 0..127
+    // The activation row this thread converts (grouped: the pair's x row; a pair naming a
+    // row past x is computed as zeros and never stored).
+    std::uint32_t x_row = m0 + t;
+    bool x_live = m0 + t < end;
+    if constexpr (kGrouped) {
+      if (!weights && x_live) {
+        const std::int32_t pr = __ldg(a.pair_rows + m0 + t);
+        x_live = pr >= 0 && static_cast<std::uint32_t>(pr) < a.x_rows;
+        x_row = static_cast<std::uint32_t>(pr);
+      }
+    }
     for (int ks = 0; ks < ksteps && !*abort_flag; ++ks) {
       const int s = ks % kStages;
       std::uint32_t v[32];
       if (weights) {
         if (n0 + t < a.outputs) {
-          DecodeRow<kDecoder>(a.w, a.first + n0 + t, static_cast<std::uint32_t>(ks) * kStepK, v);
+          DecodeRow<kDecoder>(w, a.first + n0 + t, static_cast<std::uint32_t>(ks) * kStepK, v);
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = 0u;
         }
       } else {
         const std::uint32_t k0 = static_cast<std::uint32_t>(ks) * kStepK;
-        if (m0 + t < a.rows) {
-          const auto* xp = reinterpret_cast<const float4*>(a.x + (static_cast<std::uint64_t>(m0 + t) * a.x_stride) + k0);
+        if (x_live) {
+          const auto* xp = reinterpret_cast<const float4*>(a.x + (static_cast<std::uint64_t>(x_row) * a.x_stride) + k0);
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             float4 f = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            if (k0 + (4 * i) < a.w.k) f = __ldg(xp + i);   // k is a multiple of 32: whole float4s
+            if (k0 + (4 * i) < w.k) f = __ldg(xp + i);   // k is a multiple of 32: whole float4s
             v[2 * i] = Pack<kBf16>(f.x, f.y);
             v[(2 * i) + 1] = Pack<kBf16>(f.z, f.w);
           }
@@ -240,8 +271,8 @@ __global__ void __launch_bounds__(kThreads, 1) DecodeMatrixKernel(const Args a, 
     } else {
       tc::TcFenceAfter();
       const std::uint32_t n = n0 + (quadrant * 32) + lane;  // this thread's output
-      const float scale = (n < a.outputs && a.w.tensor_scale != nullptr)
-                              ? __ldg(a.w.tensor_scale + ((a.first + n) / a.w.rows_per_scale))
+      const float scale = (n < a.outputs && w.tensor_scale != nullptr)
+                              ? __ldg(w.tensor_scale + ((a.first + n) / w.rows_per_scale))
                               : 1.0f;
 #pragma unroll 1
       for (int c = 0; c < kTile / 32; ++c) {
@@ -252,7 +283,19 @@ __global__ void __launch_bounds__(kThreads, 1) DecodeMatrixKernel(const Args a, 
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const std::uint32_t m = m0 + (c * 32) + j;
-            if (m < a.rows) a.y[(static_cast<std::uint64_t>(m) * a.y_stride) + n] = __uint_as_float(r[j]) * scale;
+            if (m >= end) continue;
+            std::uint32_t out = m;
+            if constexpr (kGrouped) {
+              const std::int32_t pr = __ldg(a.pair_rows + m);
+              if (pr < 0 || static_cast<std::uint32_t>(pr) >= a.x_rows) continue;
+              if (a.pair_out != nullptr) {
+                const std::int32_t po = __ldg(a.pair_out + m);
+                if (po < 0) continue;
+                out = static_cast<std::uint32_t>(po);
+              }
+              if (out >= a.y_rows) continue;
+            }
+            a.y[(static_cast<std::uint64_t>(out) * a.y_stride) + n] = __uint_as_float(r[j]) * scale;
           }
         }
       }
@@ -267,20 +310,43 @@ __global__ void __launch_bounds__(kThreads, 1) DecodeMatrixKernel(const Args a, 
   }
 }
 
-template <int kDecoder>
-cudaError_t Launch(const Args& a, unsigned int* faults, cudaStream_t s) {
+template <int kDecoder, bool kGrouped>
+cudaError_t Launch(const Args& a, unsigned int groups, unsigned int* faults, cudaStream_t s) {
   static thread_local int configured_device = -1;
   int device = -1;
   cudaGetDevice(&device);
   if (configured_device != device) {
-    const cudaError_t e = cudaFuncSetAttribute(DecodeMatrixKernel<kDecoder>,
+    const cudaError_t e = cudaFuncSetAttribute(DecodeMatrixKernel<kDecoder, kGrouped>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
     if (e != cudaSuccess) return e;
     configured_device = device;
   }
-  const dim3 grid((a.outputs + kTile - 1) / kTile, (a.rows + kTile - 1) / kTile);
-  return LaunchPdl(DecodeMatrixKernel<kDecoder>, grid, dim3(kThreads), static_cast<std::size_t>(kSmem), s,
-                   a, faults);
+  // Grouped: every expert gets the row tiles its pairs could need at most; a CTA whose
+  // tile lies past the expert's pairs leaves at once.
+  const std::uint32_t rows = kGrouped ? a.pairs : a.rows;
+  const dim3 grid((a.outputs + kTile - 1) / kTile, (rows + kTile - 1) / kTile, groups);
+  return LaunchPdl(DecodeMatrixKernel<kDecoder, kGrouped>, grid, dim3(kThreads),
+                   static_cast<std::size_t>(kSmem), s, a, faults);
+}
+
+int CheckFormat(const Operand& w, const char* what) {
+  if (w.decoder > LLMP_B200_DECODER_MXFP8_ATOMS) {
+    return Reject("%s: decoder %u is not one this build has (Q8_0 blocks, MXFP8)", what, w.decoder);
+  }
+  if (w.k < 32 || w.k % 32 != 0 || w.rows < 1 ||
+      (w.decoder == LLMP_B200_DECODER_MXFP8_ATOMS && w.k % 128 != 0)) {
+    return Reject("%s: k a positive multiple of 32 (128 with scale atoms), at least one row", what);
+  }
+  return 0;
+}
+
+template <bool kGrouped>
+cudaError_t LaunchDecoder(const Args& a, unsigned int groups, unsigned int* faults, cudaStream_t s) {
+  return a.w.decoder == LLMP_B200_DECODER_Q8_0_BLOCKS
+             ? Launch<LLMP_B200_DECODER_Q8_0_BLOCKS, kGrouped>(a, groups, faults, s)
+         : a.w.decoder == LLMP_B200_DECODER_MXFP8_SPLIT
+             ? Launch<LLMP_B200_DECODER_MXFP8_SPLIT, kGrouped>(a, groups, faults, s)
+             : Launch<LLMP_B200_DECODER_MXFP8_ATOMS, kGrouped>(a, groups, faults, s);
 }
 
 }  // namespace
@@ -328,12 +394,50 @@ int llmp_b200_decode_matrix(const llmp_b200_decode_product* product, void* strea
   a.x_stride = product->x_stride;
   a.y = product->y;
   a.y_stride = product->y_stride;
-  auto* s = static_cast<cudaStream_t>(stream);
-  const cudaError_t e =
-      w.decoder == LLMP_B200_DECODER_Q8_0_BLOCKS   ? Launch<LLMP_B200_DECODER_Q8_0_BLOCKS>(a, faults, s)
-      : w.decoder == LLMP_B200_DECODER_MXFP8_SPLIT ? Launch<LLMP_B200_DECODER_MXFP8_SPLIT>(a, faults, s)
-                                                   : Launch<LLMP_B200_DECODER_MXFP8_ATOMS>(a, faults, s);
+  const cudaError_t e = LaunchDecoder<false>(a, 1, faults, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return Failed(e, "decode.matrix launch");
+  return 0;
+}
+
+int llmp_b200_decode_grouped(const llmp_b200_decode_grouped_product* g, void* stream) {
+  using namespace llmp_b200;
+  if (g == nullptr) return Reject("decode.grouped: null product");
+  if (const int status = CheckFormat(g->format, "decode.grouped"); status != 0) return status;
+  if (g->experts == nullptr || g->experts_count < 1 || g->experts_count > 65535 ||
+      g->offsets == nullptr || g->pair_rows == nullptr || g->x == nullptr || g->y == nullptr) {
+    return Reject("decode.grouped: 1 to 65535 expert operands, offsets, pair rows, x and y");
+  }
+  if (g->outputs < 1 || g->first + g->outputs > g->format.rows || g->pairs < 1 ||
+      g->pairs > 0x7fffff80ull || (g->pairs + 127) / 128 > 65535 || g->x_rows < 1 || g->y_rows < 1) {
+    return Reject("decode.grouped: outputs inside the matrices; 1 .. 8,388,480 pairs");
+  }
+  if (g->x_stride < g->format.k || g->y_stride < g->outputs || !Aligned(g->x, 16) ||
+      g->x_stride % 4 != 0 || !Aligned(g->y, 4) || !Aligned(g->experts, 8)) {
+    return Reject("decode.grouped: activation rows of k floats, 16-byte aligned; output rows of "
+                  "`outputs` floats");
+  }
+  if (const int status = DeviceStatus(); status != 0) return status;
+  unsigned int* faults = FaultCounter();
+  if (faults == nullptr) return Reject("decode.grouped: no fault counter on this device");
+  Args a{};
+  a.w = g->format;
+  a.first = static_cast<std::uint32_t>(g->first);
+  a.outputs = static_cast<std::uint32_t>(g->outputs);
+  a.rows = 0;
+  a.x = g->x;
+  a.x_stride = g->x_stride;
+  a.y = g->y;
+  a.y_stride = g->y_stride;
+  a.experts = g->experts;
+  a.offsets = g->offsets;
+  a.pair_rows = g->pair_rows;
+  a.pair_out = g->pair_out;
+  a.pairs = static_cast<std::uint32_t>(g->pairs);
+  a.x_rows = static_cast<std::uint32_t>(g->x_rows);
+  a.y_rows = static_cast<std::uint32_t>(g->y_rows);
+  const cudaError_t e = LaunchDecoder<true>(a, static_cast<unsigned int>(g->experts_count), faults,
+                                            static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return Failed(e, "decode.grouped launch");
   return 0;
 }
 

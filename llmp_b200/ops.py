@@ -17,7 +17,7 @@ from ._native import (GLU_GEGLU, GLU_NONE, GLU_SWIGLU, GLU_SWIGLU_CLAMP, TYPE_Q4
 
 __all__ = ["available", "sm_count", "device_faults", "block_bytes", "block_elems", "q8_1_row_blocks",
            "quantize_q8", "vecq", "vecq_f32", "vecq_q8", "vecq_q8_scratch", "vecq_variants", "vecq_block_sums", "mxfp8_padded_rows",
-           "mxfp8_quantize", "mxfp8_swizzle", "mxfp8_gemm", "mxfp8_mul_mat_vec", "decode_vector", "decode_matrix", "DECODER_Q8_0", "DECODER_MXFP8_SPLIT",
+           "mxfp8_quantize", "mxfp8_swizzle", "mxfp8_gemm", "mxfp8_mul_mat_vec", "decode_vector", "decode_matrix", "decode_grouped", "DECODER_Q8_0", "DECODER_MXFP8_SPLIT",
            "DECODER_MXFP8_ATOMS", "mmq_quantize", "mmq", "moe_route", "grouped_gemm",
            "moe_glu_quantize", "moe_combine", "moe_ffn", "TYPE_Q8_0", "TYPE_Q4_K",
            "GLU_NONE", "GLU_SWIGLU", "GLU_SWIGLU_CLAMP", "GLU_GEGLU", "Rejected", "LaunchFailed"]
@@ -531,4 +531,42 @@ def decode_matrix(decoder: int, data: torch.Tensor, x: torch.Tensor, k: int, out
     p.x, p.rows, p.x_stride = x.data_ptr(), rows, x.stride(0)
     p.y, p.y_stride = out.data_ptr(), out.stride(0)
     N.check(N.lib().llmp_b200_decode_matrix(C.byref(p), _stream()), "llmp_b200_decode_matrix")
+    return out
+
+
+def decode_grouped(decoder: int, data: torch.Tensor, x: torch.Tensor, k: int, outputs: int,
+                   offsets: torch.Tensor, pair_rows: torch.Tensor, y_rows: int, *,
+                   scales: torch.Tensor | None = None, pair_out: torch.Tensor | None = None,
+                   first: int = 0) -> torch.Tensor:
+    """decode::RunGrouped: data uint8 [experts, n, row_bytes] (scales [experts, ...] likewise),
+    offsets I32 [experts + 1] over the pairs, pair_rows I32 [pairs] naming x rows, pair_out I32
+    [pairs] naming y rows (or the pair index) -> F32 [y_rows, outputs] (rows no pair writes stay
+    zero)."""
+    import numpy as np
+    _need(data, torch.uint8, "decode_grouped data")
+    _need(x, torch.float32, "decode_grouped x")
+    _need(offsets, torch.int32, "decode_grouped offsets")
+    _need(pair_rows, torch.int32, "decode_grouped pair_rows")
+    experts, n = data.shape[0], data.shape[1]
+    table = np.zeros((experts, 6), np.uint64)     # llmp_b200_decode_operand, 48 bytes each
+    for e in range(experts):
+        table[e, 0] = data[e].data_ptr()
+        table[e, 1] = scales[e].data_ptr() if scales is not None else 0
+        table[e, 3] = k | (n << 32)
+        table[e, 4] = 1 | (decoder << 32)
+        table[e, 5] = data.stride(1)
+    operands = torch.from_numpy(table.view(np.uint8).reshape(-1)).to(x.device)
+    out = torch.zeros((y_rows, outputs), dtype=torch.float32, device=x.device)
+    g = N.DecodeGroupedProduct()
+    g.format.k, g.format.rows, g.format.rows_per_scale, g.format.decoder = k, n, 1, decoder
+    g.format.row_bytes = data.stride(1)
+    g.experts, g.experts_count = operands.data_ptr(), experts
+    g.first, g.outputs = first, outputs
+    g.offsets, g.pair_rows = offsets.data_ptr(), pair_rows.data_ptr()
+    g.pair_out = pair_out.data_ptr() if pair_out is not None else None
+    g.pairs = pair_rows.numel()
+    g.x, g.x_rows, g.x_stride = x.data_ptr(), x.shape[0], x.stride(0)
+    g.y, g.y_rows, g.y_stride = out.data_ptr(), y_rows, out.stride(0)
+    N.check(N.lib().llmp_b200_decode_grouped(C.byref(g), _stream()), "llmp_b200_decode_grouped")
+    torch.cuda.current_stream().synchronize()     # the operand table lives until here
     return out

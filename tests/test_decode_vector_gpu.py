@@ -159,3 +159,35 @@ def test_matrix_product_matches_the_double_product_of_the_rounded_operands(cuda,
     assert np.isfinite(got).all()
     assert ((got - want) ** 2).sum() / (want ** 2).sum() <= 1e-10
     assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()
+
+
+def test_grouped_product_over_an_expert_worklist(cuda, orc):
+    """decode::RunGrouped: each expert's pairs gather x rows and scatter y rows; an empty expert,
+    a pair naming a row past x and one whose output is -1 are skipped."""
+    torch = cuda
+    ops = _ops()
+    rng = np.random.default_rng(11)
+    experts, n, k, tokens = 5, 200, 512, 40
+    w = np.stack([synth.q8_0_weights(rng, n, k) for _ in range(experts)])
+    x = rng.normal(0, 1, size=(tokens, k)).astype(np.float32)
+    counts = [150, 0, 3, 131, 17]                       # one expert spans two tiles, one is empty
+    offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    pairs = int(offsets[-1])
+    pair_rows = rng.integers(0, tokens, size=pairs).astype(np.int32)
+    pair_out = rng.permutation(pairs).astype(np.int32)
+    pair_rows[5] = tokens + 3                            # past x: skipped
+    pair_out[9] = -1                                     # no output: skipped
+    got = ops.decode_grouped(ops.DECODER_Q8_0, to_dev(torch, w), to_dev(torch, x), k, n,
+                             to_dev(torch, offsets), to_dev(torch, pair_rows), pairs,
+                             pair_out=to_dev(torch, pair_out)).cpu().numpy().astype(np.float64)
+    assert ops.device_faults() == 0
+    want = np.zeros((pairs, n))
+    xv = x.astype(np.float16).astype(np.float64)
+    for e in range(experts):
+        wv = orc.dequant(orc.Q8_0, w[e]).reshape(n, k).astype(np.float16).astype(np.float64)
+        for p in range(offsets[e], offsets[e + 1]):
+            if pair_rows[p] >= tokens or pair_out[p] < 0:
+                continue
+            want[pair_out[p]] = wv @ xv[pair_rows[p]]
+    assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()
+    assert (got[want.any(axis=1) == False] == 0).all()  # noqa: E712  untouched rows stay zero
