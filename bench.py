@@ -460,7 +460,7 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
                     "h2d_bytes_per_step": LAYERS * batch * HIDDEN * 4 * replicas,
                     "d2h_bytes_per_step": LAYERS * batch * HIDDEN * 4 * replicas},
             "gpu_launches": st.launches_per_step * args.steps * world,
-            "roofline": {"bound": "hbm", "kernel": "VecQKernel<Q4_K, GLU> (fused gate/up)",
+            "roofline": {"bound": "hbm", "kernel": "VecQRowLaneKernel<P, GLU> (fused gate/up, Q4_K)",
                          "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4),
                          "peak_source": "measured (MEASURED_PEAKS.json hbm_gbs)" if peaks
