@@ -1,5 +1,5 @@
-"""Builds libllmp_b200.so and the tensor-core microbenchmark (tc_probe) in-tree with nvcc for
-sm_100a (llmp_b200/csrc/Makefile)."""
+"""Builds libllmp_b200.so in-tree with nvcc for sm_100a (llmp_b200/csrc/Makefile).  The
+tensor-core microbenchmark is a separate target: make -C llmp_b200/csrc probe."""
 import os
 import subprocess
 
@@ -8,7 +8,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 
 def build(jobs: int | None = None, verbose: bool = False) -> str:
     jobs = jobs or min(16, os.cpu_count() or 4)
-    r = subprocess.run(["make", "-C", os.path.join(_HERE, "csrc"), f"-j{jobs}", "all", "probe"],
+    r = subprocess.run(["make", "-C", os.path.join(_HERE, "csrc"), f"-j{jobs}", "all"],
                        capture_output=not verbose, text=True)
     if r.returncode != 0:
         raise RuntimeError("nvcc build failed:\n" + (r.stdout or "")[-4000:] + (r.stderr or "")[-4000:])

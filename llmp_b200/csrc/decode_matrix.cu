@@ -144,13 +144,28 @@ __global__ void __launch_bounds__(kThreads, 1) DecodeMatrixKernel(const Args a, 
   Operand w = a.w;
   std::uint32_t begin = 0, end = a.rows;
   if constexpr (kGrouped) {
+    // The worklist and the operand table may be the kernel before's output.
+    GridDependencyWait();
     const std::uint32_t e = blockIdx.z;
-    const std::int32_t lo = __ldg(a.offsets + e), hi = __ldg(a.offsets + e + 1);
+    const std::int32_t lo = a.offsets[e], hi = a.offsets[e + 1];
     begin = lo < 0 ? 0u : min(static_cast<std::uint32_t>(lo), a.pairs);
     end = hi < 0 ? begin : max(begin, min(static_cast<std::uint32_t>(hi), a.pairs));
     if (begin + (blockIdx.y * kTile) >= end) return;  // uniform: before any barrier
     w = a.experts[e];
     if (w.k != a.w.k || w.rows != a.w.rows || w.decoder != a.w.decoder) return;  // not of the format
+    // The host never sees these device-resident operands: an expert whose pointers
+    // or pitch the loads below could not take is skipped and counted, not read.
+    const bool q8 = kDecoder == LLMP_B200_DECODER_Q8_0_BLOCKS;
+    const std::uintptr_t where = reinterpret_cast<std::uintptr_t>(w.data);
+    const bool usable =
+        w.data != nullptr &&
+        (q8 ? ((where | w.row_bytes) % 2 == 0 && w.row_bytes >= (w.k / 32) * 34ull)
+            : ((where | w.row_bytes) % 16 == 0 && w.row_bytes >= w.k && w.scales != nullptr)) &&
+        (w.tensor_scale == nullptr || w.rows_per_scale >= 1);
+    if (!usable) {
+      if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) atomicAdd(faults, 1u);
+      return;
+    }
   }
   extern __shared__ unsigned char raw_smem[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(

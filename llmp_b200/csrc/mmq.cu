@@ -41,8 +41,8 @@
 // packed F32x2 arithmetic 270.  With the
 // epilogue only handing buffers back the kernel runs at 425, with the tensor
 // core free-running at 555: one tcgen05.commit per 32-value group costs about
-// 335 cycles of tensor-pipe time whatever else happens.  The integer-add
-// variant of the conversion (LLMP_MMQ_MAGIC=1) measured slower (242).
+// 335 cycles of tensor-pipe time whatever else happens.  Replacing the
+// integer-to-float conversion by an integer add onto a magic exponent measured slower (242).
 // Every wait is bounded; a wait that runs out raises the device fault counter.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -137,18 +137,8 @@ constexpr int kRawStages = 2;
 constexpr int kRawWBytes = 128 * 144;
 constexpr int kRawHBytes = 128 * 16;
 constexpr int kRawBytes = kRawWBytes + (2 * kRawHBytes);
-#ifndef LLMP_MMQ_EPILOGUE_WARPS
-#define LLMP_MMQ_EPILOGUE_WARPS 16
-#endif
-#ifndef LLMP_MMQ_DECODE_WARPS
-#define LLMP_MMQ_DECODE_WARPS 2
-#endif
-#ifndef LLMP_MMQ_MAGIC
-#define LLMP_MMQ_MAGIC 0
-#endif
-constexpr int kEpilogueWarps = LLMP_MMQ_EPILOGUE_WARPS;
-constexpr bool kRegMagic = LLMP_MMQ_MAGIC != 0;
-constexpr int kDecodeWarps = LLMP_MMQ_DECODE_WARPS;  // warps 1 .. kDecodeWarps
+constexpr int kEpilogueWarps = 16;
+constexpr int kDecodeWarps = 2;  // warps 1 .. kDecodeWarps
 constexpr int kMmaWarp = kDecodeWarps + 1;
 constexpr int kFirstEpilogueWarp = kDecodeWarps + 2;  // a multiple of 4: warp % 4 is its TMEM quadrant
 constexpr int kThreads = (kFirstEpilogueWarp + kEpilogueWarps) * 32;
@@ -156,25 +146,8 @@ static_assert(kFirstEpilogueWarp % 4 == 0, "epilogue warp e must sit in TMEM qua
 constexpr int kEpilogueCols = kTileCols / (kEpilogueWarps / 4);  // columns a thread
 constexpr int kChunk = 32;                                       // columns a TMEM load
 constexpr int kChunks = kEpilogueCols / kChunk;
-// An int32 sum C added to this bit pattern reads, as a float, 12582912 + C
-// exactly (|C| < 2^22): an integer add in place of an integer-to-float conversion.
-constexpr std::uint32_t kMagicBits = 0x4B400000u;
-constexpr float kMagic = 12582912.0f;
 constexpr int kSmem =
     (kStages * kStageBytes) + (4 * kMinTileBytes) + (kRawStages * kRawBytes) + 1024 + 512;
-
-#ifdef LLMP_MMQ_TIMING
-// Build-time instrumentation: cycles each role spends in its waits, summed over
-// the grid.  [0] producer empty, [1] decode empty, [2] decode loop, [3] MMA
-// w_full, [4] MMA y_full, [5] MMA tmem_empty, [6] epilogue tmem_full,
-// [7] epilogue loop, [8] CTA lifetime, [9] CTAs.
-__device__ unsigned long long g_mmq_cycles[16];
-#define MMQ_T0() const long long t0_ = clock64()
-#define MMQ_T1(slot) local_cycles[slot] += clock64() - t0_
-#else
-#define MMQ_T0()
-#define MMQ_T1(slot)
-#endif
 
 // Two F32 lanes in one 64-bit register: sm_100's packed F32 arithmetic does two
 // roundings-to-nearest per instruction, the same results as two scalar ones.
@@ -232,10 +205,6 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
   const int warp = static_cast<int>(threadIdx.x) >> 5;
   const int lane = static_cast<int>(threadIdx.x) & 31;
   const int ksteps = a.k / kBK;
-#ifdef LLMP_MMQ_TIMING
-  long long local_cycles[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-  const long long cta_start = clock64();
-#endif
 
   // The tile: weight rows [row0, row0 + 128) of expert e against sorted
   // columns [col0, col0 + 128) of that expert's range [c_begin, c_end).
@@ -321,12 +290,10 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
               : "memory");
         }
         const int s = ks % kStages;
-        MMQ_T0();
         if (!tc::MbarWaitSleep(&sh->empty[s], ((ks / kStages) & 1) ^ 1, 256)) {
           give_up();
           break;
         }
-        MMQ_T1(0);
         tc::MbarExpectTx(&sh->y_full[s], kYBytes);
         asm volatile(
             "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
@@ -350,9 +317,7 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
       bool ok = true;
       if (lane == 0) {
         if (half == 0) ok = tc::MbarWait(&sh->raw_full[rs], (column / kRawStages) & 1);
-        MMQ_T0();
         ok = ok && tc::MbarWaitSleep(&sh->empty[s], ((ks / kStages) & 1) ^ 1, 64);
-        MMQ_T1(1);
         // ... and the tensor core is done with the min tile's contents of 32 k-steps ago
         if (ks >= 2 * kMinSteps && ks % kMinSteps == 0) {
           ok = ok && tc::MbarWait(&sh->min_free[mt], ((ks / (2 * kMinSteps)) - 1) & 1);
@@ -451,18 +416,14 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
       for (int ks = 0; ks < ksteps && !*abort_flag; ++ks) {
         const int s = ks % kStages;
         {
-          MMQ_T0();
           const bool w_ok = tc::MbarWait(&sh->w_full[s], (ks / kStages) & 1);
-          MMQ_T1(3);
           if (!w_ok) {
             give_up();
             break;
           }
         }
         {
-          MMQ_T0();
           const bool y_ok = tc::MbarWait(&sh->y_full[s], (ks / kStages) & 1);
-          MMQ_T1(4);
           if (!y_ok) {
             give_up();
             break;
@@ -473,12 +434,10 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
         const std::uint64_t ydesc = tc::SmemDesc(y_tiles + (s * kYBytes), true, 1024);
         for (int gl = 0; gl < 4; ++gl, ++group) {
           const int b = static_cast<int>(group % kBuffers);
-          MMQ_T0();
           if (!tc::MbarWait(&sh->tmem_empty[b], ((group / kBuffers) & 1u) ^ 1u)) {
             give_up();
             break;
           }
-          MMQ_T1(5);
           tc::TcFenceAfter();
           tc::MmaI8(tmem + (b * kTileCols), wdesc + (gl * 2), ydesc + (gl * 2), idesc, false);
           tc::TcCommit(&sh->tmem_full[b]);
@@ -515,9 +474,7 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
 #pragma unroll
       for (int gl = 0; gl < 4; ++gl) {
         if (!ok) break;
-        MMQ_T0();
         ok = tc::MbarWait(&sh->tmem_full[bb], parity);  // every lane polls: no shuffle after
-        MMQ_T1(6);
         if (!__all_sync(0xffffffffu, ok)) {
           if (lane == 0) give_up();
           ok = false;
@@ -531,14 +488,12 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) tc::TmemLoad32(at + (c * kChunk), r[c]);
         const float ax = sc[(gl * 128) + rt];
-        const float cx = -kMagic * ax;  // exact: a half-precision ax times 3 * 2^22
         const float* bx = sc + 512 + (gl * 128) + (colgroup * kEpilogueCols);
         tc::TmemLoadWait();
         tc::TcFenceBefore();
         __syncwarp();
         if (lane == 0) tc::MbarArrive(&sh->tmem_empty[bb]);
         const std::uint64_t ax2 = Pack2(ax, ax);
-        const std::uint64_t cx2 = Pack2(cx, cx);
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) {
 #pragma unroll
@@ -550,18 +505,9 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
               const int i = ((c * kChunk) + (v * 4) + j) / 2;
               // (ax * C) rounded, times d8, added: as the scalar sequence, two columns at once
               std::uint64_t u2;
-              if (kRegMagic) {
-                // 0x4B400000 + C are the bits of the float 12582912 + C (|C| < 2^22), and
-                // ax * (12582912 + C) - 12582912 * ax is one fused operation: ax * C
-                // rounded once, as the conversion gives.
-                u2 = Fma2(Pack2(__uint_as_float(r[c][(v * 4) + j] + kMagicBits),
-                                __uint_as_float(r[c][(v * 4) + j + 1] + kMagicBits)),
-                          ax2, cx2);
-              } else {
-                u2 = Mul2(Pack2(static_cast<float>(static_cast<int>(r[c][(v * 4) + j])),
-                                static_cast<float>(static_cast<int>(r[c][(v * 4) + j + 1]))),
-                          ax2);
-              }
+              u2 = Mul2(Pack2(static_cast<float>(static_cast<int>(r[c][(v * 4) + j])),
+                              static_cast<float>(static_cast<int>(r[c][(v * 4) + j + 1]))),
+                        ax2);
               acc2[i] = Fma2(u2, Pack2(xs[j], xs[j + 1]), acc2[i]);
             }
           }
@@ -612,28 +558,6 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
     }
   }
 
-#ifdef LLMP_MMQ_TIMING
-  if (lane == 0) {
-    const long long life = clock64() - cta_start;
-    if (warp == 0) {
-      atomicAdd(&g_mmq_cycles[0], static_cast<unsigned long long>(local_cycles[0]));
-      atomicAdd(&g_mmq_cycles[8], static_cast<unsigned long long>(life));
-      atomicAdd(&g_mmq_cycles[9], 1ull);
-    } else if (warp == 1) {
-      atomicAdd(&g_mmq_cycles[1], static_cast<unsigned long long>(local_cycles[1]));
-      atomicAdd(&g_mmq_cycles[2], static_cast<unsigned long long>(life));
-    } else if (warp == kMmaWarp) {
-      for (int i = 3; i <= 5; ++i) {
-        atomicAdd(&g_mmq_cycles[i], static_cast<unsigned long long>(local_cycles[i]));
-      }
-    } else if (warp == kFirstEpilogueWarp) {
-      atomicAdd(&g_mmq_cycles[6], static_cast<unsigned long long>(local_cycles[6]));
-      atomicAdd(&g_mmq_cycles[7], static_cast<unsigned long long>(life));
-      atomicAdd(&g_mmq_cycles[10], static_cast<unsigned long long>(local_cycles[10]));
-      atomicAdd(&g_mmq_cycles[11], static_cast<unsigned long long>(local_cycles[11]));
-    }
-  }
-#endif
   tc::TcFenceBefore();
   __syncthreads();
   if (warp == kMmaWarp) {
@@ -755,18 +679,6 @@ int LaunchMmq(const llmp_b200_mmq_desc& d, const std::int32_t* worklist, int max
 }
 
 }  // namespace llmp_b200
-
-#ifdef LLMP_MMQ_TIMING
-extern "C" int llmp_b200_mmq_debug_cycles(unsigned long long* out16, int reset) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out16, llmp_b200::g_mmq_cycles, sizeof(unsigned long long) * 16);
-  if (reset) {
-    unsigned long long zero[16] = {};
-    cudaMemcpyToSymbol(llmp_b200::g_mmq_cycles, zero, sizeof(zero));
-  }
-  return 0;
-}
-#endif
 
 extern "C" {
 

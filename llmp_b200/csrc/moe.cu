@@ -45,32 +45,92 @@ __host__ Route RouteOf(std::int32_t* base, int experts, int used, int tokens) {
   return r;
 }
 
-// Each block counts its chunk's ids per expert (llmp_moe.cu:81-106).
-__global__ void RouteCount(const std::int32_t* __restrict__ ids, int ids_stride, Route r) {
-  extern __shared__ int hist[];
-  for (int e = threadIdx.x; e < r.experts; e += blockDim.x) hist[e] = 0;
-  __syncthreads();
-  const int c = blockIdx.x;
-  const int t0 = c * kRouteChunk;
-  const int t1 = min(t0 + kRouteChunk, r.tokens);
-  const int n = (t1 - t0) * r.used;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const int t = t0 + (i / r.used);
-    const int e = ids[(static_cast<std::int64_t>(t) * ids_stride) + (i % r.used)];
-    if (e >= 0 && e < r.experts) atomicAdd(&hist[e], 1);  // integer counts: order-free
-  }
-  __syncthreads();
-  for (int e = threadIdx.x; e < r.experts; e += blockDim.x) {
-    r.counts[(static_cast<std::int64_t>(c) * r.experts) + e] = hist[e];
-  }
+// The whole counting sort in ONE launch (the reference queues three kernels,
+// llmp_moe.cu:81-160; the blob they leave, moe_layout.h:47-83, is reproduced
+// word for word).  A thread-block cluster of 1 to 8 CTAs, sized by the chunk
+// count, walks four phases separated by cluster barriers:
+//   1. a warp owns whole 64-token chunks.  It clears its chunk's row of
+//      `counts`, then takes the chunk's slots 32 at a time in slot order:
+//      lanes naming the same expert find each other with match.any, the first
+//      of them bumps the chunk's count for that expert (a plain read-modify-
+//      write: the row is the warp's own) and every lane learns its ordinal
+//      within (chunk, expert), parked in position[slot];
+//   2. a thread an expert turns its column of `counts` into the exclusive
+//      prefix over the chunks and leaves the expert's total in offsets[e + 1];
+//   3. every CTA scans the totals into its own shared copy of the offsets
+//      (CTA 0 also writes offsets and scale_rows out, after a barrier that
+//      lets the others finish reading the totals);
+//   4. a thread a slot: row = offsets[e] + counts[chunk][e] + ordinal.
+// No atomics, and rows keep token order within an expert by construction.
+constexpr int kRouteThreads = 1024;
+
+__device__ __forceinline__ void ClusterSync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n"
+               "barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ unsigned ClusterRank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ unsigned ClusterSize() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
 }
 
-// One block: chunk counts -> chunk bases, expert offsets and scale rows
-// (llmp_moe.cu:108-133); also clears the sorted rows' token / expert so that
-// rows no slot reaches read as row 0 of expert 0.
-__global__ void RouteScan(Route r) {
-  extern __shared__ int total[];
-  for (int e = threadIdx.x; e < r.experts; e += blockDim.x) {
+__global__ void __launch_bounds__(kRouteThreads, 1)
+RouteKernel(const std::int32_t* __restrict__ ids, int ids_stride, Route r) {
+  __shared__ int base[kMaxExperts + 1];   // this CTA's copy of the offsets
+  __shared__ int warp_sums[2][32];
+  const int tid = static_cast<int>(threadIdx.x);
+  const int lane = tid & 31;
+  const int ctas = static_cast<int>(ClusterSize());
+  const int cta = static_cast<int>(ClusterRank());
+  const int gthread = (cta * kRouteThreads) + tid;
+  const int gthreads = ctas * kRouteThreads;
+  const int gwarp = gthread >> 5;
+  const int gwarps = gthreads >> 5;
+  const std::int64_t slots = static_cast<std::int64_t>(r.used) * r.tokens;
+
+  // Rows no slot reaches read as row 0 of expert 0.
+  for (std::int64_t i = gthread; i < slots; i += gthreads) {
+    r.token[i] = 0;
+    r.expert[i] = 0;
+  }
+  // ---- 1: per-chunk counts and each slot's ordinal within (chunk, expert)
+  for (int c = gwarp; c < r.chunks; c += gwarps) {
+    std::int32_t* row = r.counts + (static_cast<std::int64_t>(c) * r.experts);
+    for (int e = lane; e < r.experts; e += 32) row[e] = 0;
+    __syncwarp();
+    const int t0 = c * kRouteChunk;
+    const int n = (min(t0 + kRouteChunk, r.tokens) - t0) * r.used;
+    for (int i0 = 0; i0 < n; i0 += 32) {
+      const int i = i0 + lane;
+      int e = -1;
+      if (i < n) {
+        e = ids[(static_cast<std::int64_t>(t0 + (i / r.used)) * ids_stride) + (i % r.used)];
+        if (e < 0 || e >= r.experts) e = -1;
+      }
+      // lanes without a valid id all fall in the -1 group and write nothing
+      const unsigned same = __match_any_sync(0xffffffffu, e);
+      const int first = __ffs(static_cast<int>(same)) - 1;
+      int seen = 0;
+      if (e >= 0 && lane == first) {
+        seen = row[e];
+        row[e] = seen + __popc(same);
+      }
+      seen = __shfl_sync(0xffffffffu, seen, first);
+      if (i < n) {
+        r.position[(static_cast<std::int64_t>(t0) * r.used) + i] =
+            e < 0 ? -1 : seen + __popc(same & ((1u << lane) - 1u));
+      }
+      __syncwarp();  // the next batch's leaders read what this batch's wrote
+    }
+  }
+  ClusterSync();
+  // ---- 2: counts -> exclusive prefix over the chunks; totals into offsets[e + 1]
+  for (int e = gthread; e < r.experts; e += gthreads) {
     int running = 0;
     for (int c = 0; c < r.chunks; ++c) {
       std::int32_t* at = r.counts + (static_cast<std::int64_t>(c) * r.experts) + e;
@@ -78,52 +138,65 @@ __global__ void RouteScan(Route r) {
       *at = running;
       running += v;
     }
-    total[e] = running;
+    r.offsets[e + 1] = running;
   }
-  const std::int64_t slots = static_cast<std::int64_t>(r.used) * r.tokens;
-  for (std::int64_t i = threadIdx.x; i < slots; i += blockDim.x) {
-    r.token[i] = 0;
-    r.expert[i] = 0;
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    r.offsets[0] = 0;
-    r.scale_rows[0] = 0;
-    for (int e = 0; e < r.experts; ++e) {
-      r.offsets[e + 1] = r.offsets[e] + total[e];
-      r.scale_rows[e + 1] = r.scale_rows[e] + ((total[e] + kScaleRows - 1) / kScaleRows * kScaleRows);
+  ClusterSync();
+  // ---- 3: the offsets (and the rows rounded up to 128 per expert): a block scan
+  // of up to 1024 totals, one a thread, kept in shared memory by every CTA.
+  {
+    const int total = tid < r.experts ? r.offsets[tid + 1] : 0;
+    int v[2] = {total, (total + kScaleRows - 1) / kScaleRows * kScaleRows};
+#pragma unroll
+    for (int w = 0; w < 2; ++w) {
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, v[w], d);
+        if (lane >= d) v[w] += up;
+      }
+      if (lane == 31) warp_sums[w][tid >> 5] = v[w];
     }
-  }
-}
-
-// Places a chunk's slots in token order within each expert.  One thread an
-// expert walks the chunk's ids (staged in shared memory) in slot order: the
-// same placement as the reference's one-thread loop (llmp_moe.cu:135-160),
-// every expert at once, no atomics.
-__global__ void RouteAssign(const std::int32_t* __restrict__ ids, int ids_stride, Route r) {
-  extern __shared__ int chunk_ids[];
-  const int c = blockIdx.x;
-  const int t0 = c * kRouteChunk;
-  const int t1 = min(t0 + kRouteChunk, r.tokens);
-  const int n = (t1 - t0) * r.used;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const int t = t0 + (i / r.used);
-    const int e = ids[(static_cast<std::int64_t>(t) * ids_stride) + (i % r.used)];
-    chunk_ids[i] = e;
-    if (e < 0 || e >= r.experts) r.position[(static_cast<std::int64_t>(t0) * r.used) + i] = -1;
-  }
-  __syncthreads();
-  for (int e = threadIdx.x; e < r.experts; e += blockDim.x) {
-    int row = r.offsets[e] + r.counts[(static_cast<std::int64_t>(c) * r.experts) + e];
-    for (int i = 0; i < n; ++i) {
-      if (chunk_ids[i] == e) {
-        const std::int64_t slot = (static_cast<std::int64_t>(t0) * r.used) + i;
-        r.position[slot] = row;
-        r.token[row] = t0 + (i / r.used);
-        r.expert[row] = e;
-        ++row;
+    __syncthreads();
+    if (tid < 32) {
+#pragma unroll
+      for (int w = 0; w < 2; ++w) {
+        int x = warp_sums[w][tid];
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const int up = __shfl_up_sync(0xffffffffu, x, d);
+          if (lane >= d) x += up;
+        }
+        warp_sums[w][tid] = x;  // inclusive over the warps
       }
     }
+    __syncthreads();
+    const int before0 = (tid >> 5) > 0 ? warp_sums[0][(tid >> 5) - 1] : 0;
+    const int before1 = (tid >> 5) > 0 ? warp_sums[1][(tid >> 5) - 1] : 0;
+    if (tid == 0) base[0] = 0;
+    if (tid < r.experts) base[tid + 1] = before0 + v[0];
+    ClusterSync();  // every CTA has read the totals: CTA 0 may overwrite them
+    if (cta == 0) {
+      if (tid == 0) {
+        r.offsets[0] = 0;
+        r.scale_rows[0] = 0;
+      }
+      if (tid < r.experts) {
+        r.offsets[tid + 1] = before0 + v[0];
+        r.scale_rows[tid + 1] = before1 + v[1];
+      }
+    }
+  }
+  __syncthreads();
+  // ---- 4: each slot's sorted row; each row's token and expert
+  for (std::int64_t slot = gthread; slot < slots; slot += gthreads) {
+    const int ordinal = r.position[slot];
+    if (ordinal < 0) continue;
+    const int t = static_cast<int>(slot / r.used);
+    const int e = ids[(static_cast<std::int64_t>(t) * ids_stride) + (slot % r.used)];
+    const int row = base[e] + r.counts[(static_cast<std::int64_t>(t / kRouteChunk) * r.experts) + e] +
+                    ordinal;
+    r.position[slot] = row;
+    r.token[row] = t;
+    r.expert[row] = e;
   }
 }
 
@@ -321,9 +394,22 @@ int llmp_b200_moe_route(const int32_t* ids, int ids_stride, int experts, int use
   if (const int status = DeviceStatus(); status != 0) return status;
   auto* s = static_cast<cudaStream_t>(stream);
   const Route r = RouteOf(out, experts, used, tokens);
-  RouteCount<<<r.chunks, 256, experts * sizeof(int), s>>>(ids, ids_stride, r);
-  RouteScan<<<1, 256, experts * sizeof(int), s>>>(r);
-  RouteAssign<<<r.chunks, 256, used * kRouteChunk * sizeof(int), s>>>(ids, ids_stride, r);
+  // A cluster of 1 to 8 CTAs: 32 warps each, a warp a chunk at a time.
+  int ctas = (r.chunks + 31) / 32;
+  ctas = ctas < 1 ? 1 : ctas > 8 ? 8 : ctas;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(static_cast<unsigned>(ctas));
+  config.blockDim = dim3(kRouteThreads);
+  config.stream = s;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeClusterDimension;
+  attribute[0].val.clusterDim.x = static_cast<unsigned>(ctas);
+  attribute[0].val.clusterDim.y = 1;
+  attribute[0].val.clusterDim.z = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&config, RouteKernel, ids, ids_stride, r);
+  if (e != cudaSuccess) return Failed(e, "moe.route launch");
   return Launched("moe.route launch");
 }
 

@@ -308,26 +308,49 @@ VecQKernel(const Desc a) {
   }
   GridDependencyWait();
   if (routed) {
-    // One CTA row per distinct expert (vecq.cu:514-546): grid row y is a
-    // (token, slot) pair; the first pair naming an expert computes every pair
-    // that names it, in pair order.
+    // One CTA row per distinct expert (the ownership rule of vecq.cu:514-546): grid
+    // row y is a (token, slot) pair, and the CTA whose pair is the FIRST to name an
+    // expert computes every pair that names it, in pair order; the others leave.
+    // The list is built by the whole CTA: a thread takes a contiguous run of
+    // pairs and counts its matches, the counts are scanned across the CTA, and
+    // each thread drops its matches at its offset.
     const int s = static_cast<int>(blockIdx.y);
     expert = a.ids[((s / a.used) * a.ids_stride) + (s % a.used)];
-    if (warp == 0) {
-      const int total = a.tokens * a.used;
-      int n = 0;
-      bool owner = true;
-      for (int base = 0; base < total && owner; base += 32) {
-        const int s2 = base + lane;
-        const int t = s2 / a.used;
-        const int j = s2 % a.used;
-        const bool match = s2 < total && a.ids[(t * a.ids_stride) + j] == expert;
-        const unsigned ballot = __ballot_sync(0xffffffffu, match);
-        if (n == 0 && ballot != 0) owner = base + __ffs(static_cast<int>(ballot)) - 1 == s;
-        if (owner && match) pairs[n + __popc(ballot & ((1u << lane) - 1u))] = (t << 8) | j;
-        n += __popc(ballot);
+    const int total = a.tokens * a.used;
+    const int run = (total + threads - 1) / threads;
+    const int lo = min(tid * run, total), hi = min(lo + run, total);
+    int mine = 0;
+    for (int q = lo; q < hi; ++q) {
+      mine += a.ids[((q / a.used) * a.ids_stride) + (q % a.used)] == expert ? 1 : 0;
+    }
+    // exclusive scan of `mine` over the CTA (at most eight warps)
+    __shared__ int warp_total[kMaxThreads / 32];
+    int before = mine;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, before, d);
+      if (lane >= d) before += up;
+    }
+    if (lane == 31) warp_total[warp] = before;
+    __syncthreads();
+    int earlier = 0;
+    for (int w = 0; w < warp; ++w) earlier += warp_total[w];
+    before += earlier - mine;
+    // The pair in front of every other match decides the ownership; exactly one
+    // thread holds it (this CTA's own pair matches, so there is one).
+    if (mine > 0 && before == 0) {
+      int q = lo;
+      while (a.ids[((q / a.used) * a.ids_stride) + (q % a.used)] != expert) ++q;
+      int all = 0;
+      for (int w = 0; w < (threads >> 5); ++w) all += warp_total[w];
+      count = q == s ? all : 0;
+    }
+    __syncthreads();
+    if (count != 0) {
+      for (int q = lo; q < hi; ++q) {
+        const int t = q / a.used, j = q % a.used;
+        if (a.ids[(t * a.ids_stride) + j] == expert) pairs[before++] = (t << 8) | j;
       }
-      if (lane == 0) count = owner ? n : 0;
     }
     set_rows(expert);
   }

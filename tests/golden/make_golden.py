@@ -24,7 +24,8 @@ from llmp_b200 import synth  # noqa: E402
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get(
+        "LLMP_REFERENCE_ROOT", os.path.join(os.path.dirname(ROOT), "reference"))
     subprocess.run(["make", "-C", os.path.join(ROOT, "oracle"), "ref", "CXX=g++",
                     f"REFERENCE={ref_root}"], check=True)
     R = C.CDLL(os.path.join(ROOT, "oracle", "_ref", "libref.so"))
