@@ -57,8 +57,10 @@ int llmp_b200_sm_count(void);
 const char* llmp_b200_last_error(void);
 
 /* Diagnostics, no reference counterpart: how many bounded device-side waits
- * (an mbarrier that a bulk copy should have completed) ran out since the
- * library was loaded.  0 on a healthy device; synchronizes the device, so it
+ * (an mbarrier that a bulk copy should have completed) ran out, plus how many
+ * device-resident operands a kernel refused to read (a grouped product's
+ * expert whose pointers or pitch its loads could not take), since the library
+ * was loaded.  0 on a healthy device with well-formed operands; synchronizes the device, so it
  * is for tests and post-mortems, never for the launch path.  -1: unreadable. */
 int llmp_b200_device_faults(void);
 
@@ -133,6 +135,41 @@ int llmp_b200_vecq_f32(int type, const llmp_b200_vecq_desc* desc, void* q8_out, 
 size_t llmp_b200_vecq_q8_scratch(int nrows, int tokens);
 int llmp_b200_vecq_q8(int type, const llmp_b200_vecq_desc* desc, void* q8_dst, uint32_t* rows_done,
                       void* stream);
+
+/* ------------------------------------------------------------------ MMVQ */
+/* The operands of the reference's MMVQ calls (GGML's mul_mat_vec_q as
+ * src/kernels/ggml/mul_mat_q.cu:407-451, 502-515 reaches it): dense weights [n][k] in
+ * blocks, F32 activation columns (or their prepared Q8_1 rows), F32 output columns. */
+typedef struct llmp_b200_mmvq_desc {
+  int type;                /* LLMP_B200_TYPE_Q8_0 / _Q4_K */
+  const void* w;           /* weight blocks; with a GLU the up projection */
+  const void* gate;        /* MulMatVecQGlu: the gate's blocks (same shape), else NULL */
+  int glu;                 /* LLMP_B200_GLU_* */
+  float limit;
+  const float* x;          /* F32 [k, cols]: columns x_col_stride floats apart, 16-byte aligned */
+  int64_t x_col_stride;
+  const void* q8;          /* prepared Q8_1 rows (llmp_b200_q8_1_row_blocks(k) blocks a column), or NULL */
+  float* dst;              /* F32 [n, cols]: columns dst_col_stride floats apart */
+  int64_t dst_col_stride;
+  int k, n, cols;
+  int stride_row;          /* weight blocks between rows */
+  void* scratch;           /* llmp_b200_mmvq_scratch(k, cols) bytes, 256-byte aligned (unused when prepared) */
+} llmp_b200_mmvq_desc;
+/* Replaces PlanMulMatVecQ's draw (mul_mat_q.cu:308-312): the Q8_1 rows of cols columns. */
+size_t llmp_b200_mmvq_scratch(int k, int cols);
+/* Replaces MulMatVecQ and, with `gate`, MulMatVecQGlu (mul_mat_q.cu:407-416, 502-515): quantize
+ * the 1 to 8 columns of x into scratch, then dst[:, c] = W . x[:, c] (or the GLU of the gate and
+ * up products).  Two launches: the Q8_1 quantizer and the llmp.vecq product. */
+int llmp_b200_mmvq(const llmp_b200_mmvq_desc* desc, void* stream);
+/* Replaces RunMmvqPrepared (mul_mat_q.cu:431-451): the same product over prepared rows
+ * (desc->q8), which another product may share; nothing is quantized, scratch is unused. */
+int llmp_b200_mmvq_prepared(const llmp_b200_mmvq_desc* desc, void* stream);
+/* Replaces MulMatVecQRows (src/kernels/ggml/mmvq_rows.cu:825; kernel :319-452): every column's
+ * F32 result is the one-column product's, bit for bit, whatever the column count (a
+ * speculative verify's rows equal the decode steps they stand for).  Takes any column
+ * count up to 4096 (the reference: 8) in passes that keep the one-column launch geometry;
+ * x or prepared q8.  No fused GLU. */
+int llmp_b200_mmvq_rows(const llmp_b200_mmvq_desc* desc, void* stream);
 
 /* Verification entry with no reference counterpart as a separate call: the
  * int32 per-block sums the product kernels form (the quantity the reference
@@ -292,6 +329,13 @@ int llmp_b200_mxfp8_mul_mat_vec(const void* codes, const void* scales, const flo
 #define LLMP_B200_DECODER_Q8_0_BLOCKS 0
 #define LLMP_B200_DECODER_MXFP8_SPLIT 1  /* scales [rows, k / 32] row-major */
 #define LLMP_B200_DECODER_MXFP8_ATOMS 2  /* scales in 128 x 4 scale atoms */
+/* The vector and row products also take (decoders.cuh:73-103, 125-150, 222-239): */
+#define LLMP_B200_DECODER_BF16_DENSE 3
+#define LLMP_B200_DECODER_F16_DENSE 4
+#define LLMP_B200_DECODER_NVFP4_SPLIT 5  /* E2M1 codes k / 2 bytes a row, UE4M3 scales k / 16 a row */
+#define LLMP_B200_DECODER_NVFP4_ATOMS 6  /* the same scales in scale atoms (k % 64 == 0) */
+#define LLMP_B200_DECODER_MXFP4_SPLIT 7  /* E2M1 codes, E8M0 scales k / 32 a row */
+#define LLMP_B200_DECODER_MXFP4_ATOMS 8  /* the same scales in scale atoms (k % 128 == 0) */
 typedef struct llmp_b200_decode_operand {
   const void* data;           /* Q8_0 blocks, or E4M3 codes */
   const void* scales;         /* MXFP8: E8M0 scales; Q8_0: unused */
@@ -311,6 +355,12 @@ typedef struct llmp_b200_decode_product {
   uint64_t y_stride;
 } llmp_b200_decode_product;
 int llmp_b200_decode_vector(const llmp_b200_decode_product* product, void* stream);
+/* decode::RunRows (products.h:170-186; kernel templates.cuh:441-466): y[i, 0..k) = the decoded
+ * row ids[i] of the weight times its tensor scale, for i < count (an embedding lookup).  An id
+ * outside the matrix gives a zero row and sets *bad (a device int, or NULL) to 1.  y rows are
+ * y_stride floats apart, 16-byte aligned. */
+int llmp_b200_decode_rows(const llmp_b200_decode_operand* weight, const int32_t* ids, uint64_t count,
+                          float* y, uint64_t y_stride, int32_t* bad, void* stream);
 /* decode::RunMatrix with MatrixPath::kMma (products.h:116-120; tile kernel templates.cuh:
  * 236-440): any number of activation rows; weights and activations are rounded to the
  * decoder's MMA element (FP16 for Q8_0 blocks, BF16 for MXFP8: DecoderMmaElement) and

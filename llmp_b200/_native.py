@@ -34,6 +34,15 @@ class VecQDesc(C.Structure):
                         ("limit", C.c_float)]
 
 
+class MmvqDesc(C.Structure):
+    """llmp_b200_mmvq_desc (include/llmp_b200.h)."""
+    _fields_ = [("type", C.c_int), ("w", C.c_void_p), ("gate", C.c_void_p), ("glu", C.c_int),
+                ("limit", C.c_float), ("x", C.c_void_p), ("x_col_stride", C.c_int64),
+                ("q8", C.c_void_p), ("dst", C.c_void_p), ("dst_col_stride", C.c_int64),
+                ("k", C.c_int), ("n", C.c_int), ("cols", C.c_int), ("stride_row", C.c_int),
+                ("scratch", C.c_void_p)]
+
+
 class DecodeOperand(C.Structure):
     _fields_ = [("data", C.c_void_p), ("scales", C.c_void_p), ("tensor_scale", C.c_void_p),
                 ("k", C.c_uint32), ("rows", C.c_uint32), ("rows_per_scale", C.c_uint32),
@@ -125,8 +134,14 @@ SIGNATURES = {
     "llmp_b200_mxfp8_gemm": (C.c_int, [C.POINTER(Mxfp8GemmDesc), C.c_int, C.c_void_p]),
     "llmp_b200_decode_vector": (C.c_int, [C.POINTER(DecodeProduct), C.c_void_p]),
     "llmp_b200_decode_vector_glu": (C.c_int, [C.POINTER(DecodeGluProduct), C.c_void_p]),
+    "llmp_b200_decode_rows": (C.c_int, [C.POINTER(DecodeOperand), C.c_void_p, C.c_uint64,
+                                        C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p]),
     "llmp_b200_decode_matrix": (C.c_int, [C.POINTER(DecodeProduct), C.c_void_p]),
     "llmp_b200_decode_grouped": (C.c_int, [C.POINTER(DecodeGroupedProduct), C.c_void_p]),
+    "llmp_b200_mmvq_scratch": (C.c_size_t, [C.c_int, C.c_int]),
+    "llmp_b200_mmvq": (C.c_int, [C.POINTER(MmvqDesc), C.c_void_p]),
+    "llmp_b200_mmvq_prepared": (C.c_int, [C.POINTER(MmvqDesc), C.c_void_p]),
+    "llmp_b200_mmvq_rows": (C.c_int, [C.POINTER(MmvqDesc), C.c_void_p]),
     "llmp_b200_vecq_f32": (C.c_int, [C.c_int, C.POINTER(VecQDesc), C.c_void_p, C.c_void_p]),
     "llmp_b200_vecq_q8_scratch": (C.c_size_t, [C.c_int, C.c_int]),
     "llmp_b200_vecq_q8": (C.c_int, [C.c_int, C.POINTER(VecQDesc), C.c_void_p, C.c_void_p,

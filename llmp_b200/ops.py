@@ -16,9 +16,10 @@ from ._native import (GLU_GEGLU, GLU_NONE, GLU_SWIGLU, GLU_SWIGLU_CLAMP, TYPE_Q4
                       LaunchFailed, Rejected)
 
 __all__ = ["available", "sm_count", "device_faults", "block_bytes", "block_elems", "q8_1_row_blocks",
-           "quantize_q8", "vecq", "vecq_f32", "vecq_q8", "vecq_q8_scratch", "vecq_variants", "vecq_block_sums", "mxfp8_padded_rows",
-           "mxfp8_quantize", "mxfp8_swizzle", "mxfp8_gemm", "mxfp8_mul_mat_vec", "decode_vector", "decode_matrix", "decode_grouped", "DECODER_Q8_0", "DECODER_MXFP8_SPLIT",
-           "DECODER_MXFP8_ATOMS", "mmq_quantize", "mmq", "moe_route", "grouped_gemm",
+           "quantize_q8", "vecq", "mmvq", "vecq_f32", "vecq_q8", "vecq_q8_scratch", "vecq_variants", "vecq_block_sums", "mxfp8_padded_rows",
+           "mxfp8_quantize", "mxfp8_swizzle", "mxfp8_gemm", "mxfp8_mul_mat_vec", "decode_vector", "decode_rows", "decode_matrix", "decode_grouped", "DECODER_Q8_0", "DECODER_MXFP8_SPLIT",
+           "DECODER_MXFP8_ATOMS", "DECODER_BF16", "DECODER_F16", "DECODER_NVFP4_SPLIT", "DECODER_NVFP4_ATOMS",
+           "DECODER_MXFP4_SPLIT", "DECODER_MXFP4_ATOMS", "mmq_quantize", "mmq", "moe_route", "grouped_gemm",
            "moe_glu_quantize", "moe_combine", "moe_ffn", "TYPE_Q8_0", "TYPE_Q4_K",
            "GLU_NONE", "GLU_SWIGLU", "GLU_SWIGLU_CLAMP", "GLU_GEGLU", "Rejected", "LaunchFailed"]
 
@@ -136,6 +137,44 @@ def vecq(weights: torch.Tensor, wtype: int, k: int, n: int, q8: torch.Tensor, to
     d.dst_slot = n if slotted else 0
     d.glu, d.limit = glu, limit
     N.check(N.lib().llmp_b200_vecq(wtype, C.byref(d), variant, _stream()), "llmp_b200_vecq")
+    return out
+
+
+def mmvq(weights: torch.Tensor, wtype: int, k: int, n: int, x: torch.Tensor | None = None, *,
+         q8: torch.Tensor | None = None, gate: torch.Tensor | None = None, glu: int = GLU_NONE,
+         limit: float = 0.0, rows: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
+    """The reference's MMVQ calls.  x F32 [cols, k] -> F32 [cols, n]: MulMatVecQ (with `gate`,
+    MulMatVecQGlu); q8 (prepared Q8_1 rows of the columns) instead of x: RunMmvqPrepared;
+    rows=True: MulMatVecQRows, every column's bits the one-column product's, any column
+    count."""
+    _need(weights, torch.uint8, "mmvq weights")
+    d = N.MmvqDesc()
+    d.type, d.w, d.k, d.n = wtype, weights.data_ptr(), k, n
+    d.gate = gate.data_ptr() if gate is not None else None
+    d.glu, d.limit = glu, limit
+    d.stride_row = k // _BLOCK[wtype][0]
+    if q8 is not None:
+        _need(q8, torch.uint8, "mmvq q8")
+        cols = q8.shape[0]
+        d.q8 = q8.data_ptr()
+        scratch = None
+    else:
+        _need(x, torch.float32, "mmvq x")
+        if x.dim() != 2 or x.stride(1) != 1:
+            raise Rejected("mmvq: x F32 [cols, k], k contiguous")
+        cols = x.shape[0]
+        d.x, d.x_col_stride = x.data_ptr(), x.stride(0)
+        scratch = torch.empty((int(N.lib().llmp_b200_mmvq_scratch(k, cols)),), dtype=torch.uint8,
+                              device=weights.device)
+        d.scratch = scratch.data_ptr()
+    d.cols = cols
+    if out is None:
+        out = torch.empty((cols, n), dtype=torch.float32, device=weights.device)
+    d.dst, d.dst_col_stride = out.data_ptr(), out.stride(0)
+    L = N.lib()
+    fn = L.llmp_b200_mmvq_rows if rows else (L.llmp_b200_mmvq_prepared if q8 is not None
+                                             else L.llmp_b200_mmvq)
+    N.check(fn(C.byref(d), _stream()), "llmp_b200_mmvq")
     return out
 
 
@@ -461,6 +500,8 @@ def mxfp8_mul_mat_vec(codes: torch.Tensor, scales: torch.Tensor, x: torch.Tensor
 
 # ------------------------------------------------------ decode module (F32 x)
 DECODER_Q8_0, DECODER_MXFP8_SPLIT, DECODER_MXFP8_ATOMS = 0, 1, 2
+DECODER_BF16, DECODER_F16, DECODER_NVFP4_SPLIT, DECODER_NVFP4_ATOMS = 3, 4, 5, 6
+DECODER_MXFP4_SPLIT, DECODER_MXFP4_ATOMS = 7, 8
 
 
 def _decode_operand(decoder: int, data: torch.Tensor, scales: torch.Tensor | None, k: int,
@@ -509,6 +550,22 @@ def decode_vector(decoder: int, data: torch.Tensor, x: torch.Tensor, k: int, out
     g.y, g.y_stride = out.data_ptr(), out.stride(0)
     N.check(N.lib().llmp_b200_decode_vector_glu(C.byref(g), _stream()),
             "llmp_b200_decode_vector_glu")
+    return out
+
+
+def decode_rows(decoder: int, data: torch.Tensor, ids: torch.Tensor, k: int, *,
+                scales: torch.Tensor | None = None, tensor_scale: torch.Tensor | None = None,
+                rows_per_scale: int = 1, bad: torch.Tensor | None = None) -> torch.Tensor:
+    """decode::RunRows: the decoded rows ids[i] of data uint8 [n, row_bytes] -> F32 [count, k]
+    (an id outside the matrix gives a zero row and sets bad[0], an I32 tensor, to 1)."""
+    _need(ids, torch.int32, "decode_rows ids")
+    op = _decode_operand(decoder, data, scales, k, tensor_scale, rows_per_scale)
+    out = torch.empty((ids.numel(), k), dtype=torch.float32, device=data.device)
+    if bad is not None:
+        _need(bad, torch.int32, "decode_rows bad flag")
+    N.check(N.lib().llmp_b200_decode_rows(C.byref(op), ids.data_ptr(), ids.numel(), out.data_ptr(),
+                                          out.stride(0), bad.data_ptr() if bad is not None else None,
+                                          _stream()), "llmp_b200_decode_rows")
     return out
 
 

@@ -103,6 +103,8 @@ def lib():
                                   C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
                                   C.c_int, C.c_float, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p,
                                   C.c_int64],
+            "orc_decode_rows": [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
+                                C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p],
             "orc_moe_route": [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p],
             "orc_moe_combine": [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                 C.c_void_p],
@@ -320,3 +322,18 @@ def decode_vector(decoder, data, x, k, outputs, *, scales=None, first=0, up=None
                             _p(ts) if ts is not None else None, rows_per_scale, first, up_first,
                             outputs, glu, limit, _p(x), rows, x.shape[1], _p(y), outputs)
     return y
+
+
+def decode_rows(decoder, data, ids, k, *, scales=None, tensor_scale=None, rows_per_scale=1):
+    """decode::RunRows: the decoded rows ids[i] of data uint8 [n, row_bytes] -> (F32 [count, k],
+    bad flag)."""
+    data = np.ascontiguousarray(data, dtype=np.uint8)
+    ids = np.ascontiguousarray(ids, dtype=np.int32)
+    sc = None if scales is None else np.ascontiguousarray(scales, dtype=np.uint8)
+    ts = None if tensor_scale is None else np.ascontiguousarray(tensor_scale, dtype=np.float32)
+    y = np.empty((ids.size, k), np.float32)
+    bad = np.zeros(1, np.int32)
+    lib().orc_decode_rows(decoder, _p(data), _p(sc) if sc is not None else None, data.shape[1], k,
+                          data.shape[0], _p(ts) if ts is not None else None, rows_per_scale,
+                          _p(ids), ids.size, _p(y), _p(bad))
+    return y, int(bad[0])

@@ -541,6 +541,8 @@ uint32_t orc_mxfp8_scale_code(float amax) {
 /* Decode module, vector products (templates.cuh:83-186).                      */
 /* ------------------------------------------------------------------------- */
 uint64_t orc_scale_atom_offset(uint64_t row, uint64_t block, uint64_t blocks);
+float orc_e2m1_to_f32(uint8_t code);
+float orc_ue4m3_to_f32(uint8_t bits);
 
 /* decoders.cuh:106-125 (Q8_0: half a block a segment), 193-220 (MXFP8). */
 static void decode_segment(int decoder, const uint8_t* data, const uint8_t* scales,
@@ -552,13 +554,71 @@ static void decode_segment(int decoder, const uint8_t* data, const uint8_t* scal
     for (int i = 0; i < 16; ++i) v[i] = d * (float)q[i];
     return;
   }
-  const uint8_t e = decoder == 1
-                        ? scales[row * (k / 32) + seg / 2]
-                        : scales[orc_scale_atom_offset((uint64_t)row, (uint64_t)(seg / 2),
-                                                       (uint64_t)(k / 32))];
-  const float s = orc_e8m0_to_f32(e);
-  const uint8_t* c = data + row * row_bytes + seg * 16;
-  for (int i = 0; i < 16; ++i) v[i] = orc_e4m3_to_f32(c[i]) * s;
+  if (decoder == 1 || decoder == 2) {
+    const uint8_t e = decoder == 1
+                          ? scales[row * (k / 32) + seg / 2]
+                          : scales[orc_scale_atom_offset((uint64_t)row, (uint64_t)(seg / 2),
+                                                         (uint64_t)(k / 32))];
+    const float s = orc_e8m0_to_f32(e);
+    const uint8_t* c = data + row * row_bytes + seg * 16;
+    for (int i = 0; i < 16; ++i) v[i] = orc_e4m3_to_f32(c[i]) * s;
+    return;
+  }
+  if (decoder == 3 || decoder == 4) { /* dense BF16 / F16 (decoders.cuh:73-103) */
+    const uint8_t* c = data + row * row_bytes + seg * 32;
+    for (int i = 0; i < 16; ++i) {
+      const uint16_t bits = load_u16(c + 2 * i);
+      v[i] = decoder == 3 ? orc_bf16_to_f32(bits) : orc_f16_to_f32(bits);
+    }
+    return;
+  }
+  /* E2M1 codes, value 2 i in byte i's low nibble; NVFP4 (5 split, 6 atoms): a UE4M3 scale
+   * per 16; MXFP4 (7 split, 8 atoms): an E8M0 scale per 32 (decoders.cuh:57-71, 125-150,
+   * 222-239). */
+  const int nv = decoder == 5 || decoder == 6, atoms = decoder == 6 || decoder == 8;
+  const int64_t blocks = nv ? k / 16 : k / 32, block = nv ? seg : seg / 2;
+  const uint8_t code = atoms ? scales[orc_scale_atom_offset((uint64_t)row, (uint64_t)block,
+                                                            (uint64_t)blocks)]
+                             : scales[row * blocks + block];
+  const float s = nv ? orc_ue4m3_to_f32(code) : orc_e8m0_to_f32(code);
+  const uint8_t* c = data + row * row_bytes + seg * 8;
+  for (int i = 0; i < 8; ++i) {
+    v[2 * i] = orc_e2m1_to_f32(c[i] & 15u) * s;
+    v[2 * i + 1] = orc_e2m1_to_f32(c[i] >> 4) * s;
+  }
+}
+
+/* E2M1: sign, two exponent bits (bias 1), one mantissa bit: +-{0, .5, 1, 1.5, 2, 3, 4, 6}
+ * (src/kernels/device/float_formats.cuh:12-15). */
+float orc_e2m1_to_f32(uint8_t code) {
+  static const float magnitude[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
+  const float m = magnitude[code & 7u];
+  return (code & 8u) ? -m : m;
+}
+/* NVFP4's block scale: E4M3's value for 0x00-0x7E, NaN from 0x7F up (float_formats.cuh:30-35). */
+float orc_ue4m3_to_f32(uint8_t bits) {
+  return bits >= 0x7Fu ? bits_f32(0x7fc00000u) : orc_e4m3_to_f32(bits);
+}
+
+/* decode::RunRows (templates.cuh:441-466): the decoded rows ids[i] times the tensor scale; an
+ * id outside the matrix gives zeros and sets *bad. */
+void orc_decode_rows(int decoder, const uint8_t* data, const uint8_t* scales, int64_t row_bytes,
+                     int64_t k, int64_t n, const float* tensor_scale, int64_t rows_per_scale,
+                     const int32_t* ids, int64_t count, float* y, int32_t* bad) {
+  for (int64_t i = 0; i < count; ++i) {
+    float* out = y + i * k;
+    if (ids[i] < 0 || ids[i] >= n) {
+      memset(out, 0, (size_t)k * sizeof(float));
+      if (bad) *bad = 1;
+      continue;
+    }
+    const float scale = tensor_scale ? tensor_scale[ids[i] / rows_per_scale] : 1.0f;
+    for (int64_t seg = 0; seg < k / 16; ++seg) {
+      float v[16];
+      decode_segment(decoder, data, scales, row_bytes, k, ids[i], seg, v);
+      for (int j = 0; j < 16; ++j) out[seg * 16 + j] = v[j] * scale;
+    }
+  }
 }
 
 static float decode_row_dot(int decoder, const uint8_t* data, const uint8_t* scales,

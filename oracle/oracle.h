@@ -38,6 +38,8 @@ float orc_bf16_to_f32(uint16_t bits);
 uint16_t orc_f32_to_bf16(float value);
 float orc_e4m3_to_f32(uint8_t bits);
 float orc_e8m0_to_f32(uint8_t bits);
+float orc_e2m1_to_f32(uint8_t code);   /* low nibble */
+float orc_ue4m3_to_f32(uint8_t bits);  /* NVFP4 block scale: NaN from 0x7F up */
 uint8_t orc_f32_to_e4m3_satfinite(float value);
 
 /* ---- block geometry ---- */
@@ -120,7 +122,9 @@ void orc_mxfp8_gemm(int m, int n, int k, const uint8_t* a, const uint8_t* a_scal
  * l + 32, ... with one fused multiply-add a value in order, the lanes meet in a
  * butterfly over lanes 16, 8, 4, 2, 1 apart, the sum times the row's tensor scale.
  * decoder: 0 Q8_0 blocks (v = d * q), 1 MXFP8 with row-major scales, 2 MXFP8 with
- * scale atoms (v = e4m3 * 2^(e - 127)).  y[t * y_stride + j] for t < rows, j <
+ * scale atoms (v = e4m3 * 2^(e - 127)), 3 dense BF16, 4 dense F16, 5 / 6 NVFP4 (E2M1 codes, a
+ * UE4M3 scale per 16) with row-major scales / scale atoms, 7 / 8 MXFP4 (E2M1 codes, an E8M0
+ * scale per 32) likewise.  y[t * y_stride + j] for t < rows, j <
  * outputs.  glu < 0: plain product of (data, scales); else the GLU of the gate
  * operand (data, scales, row first) and the up operand (data2, scales2, row
  * first2), kinds as orc_glu. */
@@ -129,6 +133,12 @@ void orc_decode_vector(int decoder, const uint8_t* data, const uint8_t* scales, 
                        const float* tensor_scale, int64_t rows_per_scale, int64_t first,
                        int64_t first2, int64_t outputs, int glu, float limit, const float* x,
                        int64_t rows, int64_t x_stride, float* y, int64_t y_stride);
+
+/* decode::RunRows: y[i][0..k) = decoded row ids[i] times its tensor scale (zeros and *bad = 1
+ * for an id outside the n rows). */
+void orc_decode_rows(int decoder, const uint8_t* data, const uint8_t* scales, int64_t row_bytes,
+                     int64_t k, int64_t n, const float* tensor_scale, int64_t rows_per_scale,
+                     const int32_t* ids, int64_t count, float* y, int32_t* bad);
 
 int64_t orc_moe_route_ints(int64_t experts, int64_t used, int64_t tokens);
 void orc_moe_route(const int32_t* ids, int ids_stride, int experts, int used, int tokens,

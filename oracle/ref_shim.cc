@@ -67,7 +67,8 @@ int ref_block_geometry(int ggml_type_number, uint64_t* elements, uint64_t* bytes
 }
 
 // DecodeRows of an [n, k] matrix.  kind 0: MXFP8 codes + scale atoms; 1: MXFP8
-// split (scales [n, k/32]); 2: Q8_1 blocks; 3: Q8_0 blocks; 4: Q4_K blocks.
+// split (scales [n, k/32]); 2: Q8_1 blocks; 3: Q8_0 blocks; 4: Q4_K blocks; 5 / 6: NVFP4
+// split / scale atoms; 7 / 8: MXFP4 split / scale atoms; 9: dense BF16; 10: dense F16.
 int ref_decode_rows(int kind, const uint8_t* data, uint64_t data_bytes, const uint8_t* scales,
                     uint64_t scale_bytes, uint64_t n, uint64_t k, float* out) {
   fmt::TensorFormat f;
@@ -77,12 +78,18 @@ int ref_decode_rows(int kind, const uint8_t* data, uint64_t data_bytes, const ui
     case 2: f.encoding = fmt::Encoding::kQ8_1; f.layout = fmt::Layout::kGgmlBlocks; break;
     case 3: f.encoding = fmt::Encoding::kQ8_0; f.layout = fmt::Layout::kGgmlBlocks; break;
     case 4: f.encoding = fmt::Encoding::kQ4_K; f.layout = fmt::Layout::kGgmlBlocks; break;
+    case 5: f.encoding = fmt::Encoding::kNvfp4; f.layout = fmt::Layout::kSplit; break;
+    case 6: f.encoding = fmt::Encoding::kNvfp4; f.layout = fmt::Layout::kScaleAtoms; break;
+    case 7: f.encoding = fmt::Encoding::kMxfp4; f.layout = fmt::Layout::kSplit; break;
+    case 8: f.encoding = fmt::Encoding::kMxfp4; f.layout = fmt::Layout::kScaleAtoms; break;
+    case 9: f.encoding = fmt::Encoding::kBF16; f.layout = fmt::Layout::kDense; break;
+    case 10: f.encoding = fmt::Encoding::kF16; f.layout = fmt::Layout::kDense; break;
     default: return 100;
   }
   f.shape = {.ne = {k, n, 1, 1}, .rank = 2};
   std::vector<ref::PartView> parts;
   const auto* d = reinterpret_cast<const std::byte*>(data);
-  if (kind <= 1) {
+  if (kind <= 1 || (kind >= 5 && kind <= 8)) {
     parts.push_back({fmt::PartRole::kCodes, std::span<const std::byte>(d, data_bytes)});
     parts.push_back({fmt::PartRole::kBlockScales,
                      std::span<const std::byte>(reinterpret_cast<const std::byte*>(scales),

@@ -108,6 +108,41 @@ def main():
     d81 = np.empty((4, 512), np.float32)
     assert R.ref_decode_rows(2, q81.ctypes.data, q81.size, None, 0, 4, 512, d81.ctypes.data) == 0
     out["q8_1_blocks"], out["q8_1_decoded_bits"] = q81, d81.view(np.uint32)
+    # ---- NVFP4 / MXFP4 (E2M1 codes; split scales and scale atoms) and dense BF16 / F16
+    n, k = 20, 256
+    fp4 = rng.integers(0, 256, size=(n, k // 2), dtype=np.uint8)
+    nv_scales = rng.integers(0x20, 0x60, size=(n, k // 16), dtype=np.uint8)
+    nv_scales[0, 1], nv_scales[1, 2], nv_scales[2, 0] = 0x7F, 0x80, 0x00
+    mx_scales = (118 + (np.arange(n * (k // 32)) % 18)).astype(np.uint8).reshape(n, k // 32)
+    mx_scales[3, 1] = 0xFF
+
+    def atoms_of(scales):
+        blocks = scales.shape[1]
+        a = np.zeros(128 * blocks, np.uint8)
+        for r in range(scales.shape[0]):
+            for b in range(blocks):
+                a[int(R.ref_scale_atom_offset(r, b, blocks))] = scales[r, b]
+        return a
+
+    for name, kind, sc in (("nvfp4", 5, nv_scales), ("mxfp4", 7, mx_scales)):
+        dec = np.empty((n, k), np.float32)
+        assert R.ref_decode_rows(kind, fp4.ctypes.data, fp4.size, sc.ctypes.data, sc.size, n, k,
+                                 dec.ctypes.data) == 0, name
+        at = atoms_of(sc)
+        dec2 = np.empty((n, k), np.float32)
+        assert R.ref_decode_rows(kind + 1, fp4.ctypes.data, fp4.size, at.ctypes.data, at.size, n, k,
+                                 dec2.ctypes.data) == 0, name
+        assert np.array_equal(dec.view(np.uint32), dec2.view(np.uint32))
+        out[name + "_scales"], out[name + "_atoms"] = sc, at
+        out[name + "_decoded_bits"] = dec.view(np.uint32)
+    out["fp4_codes"] = fp4
+    half = rng.integers(0, 65536, size=(6, 64), dtype=np.uint16)
+    for name, kind in (("bf16", 9), ("f16", 10)):
+        dec = np.empty((6, 64), np.float32)
+        assert R.ref_decode_rows(kind, half.ctypes.data, half.size * 2, None, 0, 6, 64,
+                                 dec.ctypes.data) == 0, name
+        out[name + "_decoded_bits"] = dec.view(np.uint32)
+    out["dense16_bits"] = half
     # ---- gguf: Q8_0 quantize/dequantize, Q4_K dequantize
     import gguf
     from gguf import quants

@@ -107,7 +107,7 @@ def test_vector_products_refuse_what_they_do_not_take(cuda, orc):
     with pytest.raises(ops.Rejected):
         ops.decode_vector(ops.DECODER_MXFP8_SPLIT, w, x[:1], 64, 8)            # MXFP8 without scales
     with pytest.raises(ops.Rejected):
-        ops.decode_vector(7, w, x[:1], 64, 8)                                  # no such decoder
+        ops.decode_vector(99, w, x[:1], 64, 8)                                 # no such decoder
     torch.cuda.synchronize()
 
 
@@ -191,3 +191,83 @@ def test_grouped_product_over_an_expert_worklist(cuda, orc):
             want[pair_out[p]] = wv @ xv[pair_rows[p]]
     assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()
     assert (got[want.any(axis=1) == False] == 0).all()  # noqa: E712  untouched rows stay zero
+
+
+def _fp4_operands(rng, n, k, nv):
+    codes = rng.integers(0, 256, size=(n, k // 2), dtype=np.uint8)
+    if nv:
+        scales = rng.integers(0x28, 0x58, size=(n, k // 16), dtype=np.uint8)   # UE4M3, finite
+    else:
+        scales = rng.integers(118, 132, size=(n, k // 32), dtype=np.uint8)     # E8M0
+    blocks = scales.shape[1]
+    r = np.arange(n)[:, None]
+    b = np.arange(blocks)[None, :]
+    at = (((r // 128) * (blocks // 4) + (b // 4)) * 512) + ((r % 32) * 16) + (((r % 128) // 32) * 4) + (b % 4)
+    atoms = np.zeros(((n + 127) // 128) * 128 * blocks, np.uint8)
+    atoms[at] = scales
+    return codes, scales, atoms
+
+
+@pytest.mark.parametrize("kind", ["nvfp4", "mxfp4"])
+@pytest.mark.parametrize("n,k,rows", [(200, 512, 1), (130, 4096, 3), (64, 128, 16)])
+def test_fp4_vector_products_are_the_reference_bits(cuda, orc, kind, n, k, rows):
+    """NVFP4 and MXFP4 weights (decoders.cuh:125-150, 222-239), scales row-major and in scale
+    atoms: the oracle restates the decoders (pinned to the reference's DecodeRows) and the
+    summation order, so the products are compared bit for bit."""
+    torch = cuda
+    ops = _ops()
+    rng = np.random.default_rng(n + k + rows)
+    nv = kind == "nvfp4"
+    codes, scales, atoms = _fp4_operands(rng, n, k, nv)
+    x = rng.normal(0, 1, size=(rows, k)).astype(np.float32)
+    split, atom = (ops.DECODER_NVFP4_SPLIT, ops.DECODER_NVFP4_ATOMS) if nv else \
+        (ops.DECODER_MXFP4_SPLIT, ops.DECODER_MXFP4_ATOMS)
+    want = orc.decode_vector(split, codes, x, k, n, scales=scales)
+    got = ops.decode_vector(split, to_dev(torch, codes), to_dev(torch, x), k, n,
+                            scales=to_dev(torch, scales))
+    assert np.array_equal(got.cpu().numpy(), want)
+    got = ops.decode_vector(atom, to_dev(torch, codes), to_dev(torch, x), k, n,
+                            scales=to_dev(torch, atoms))
+    assert np.array_equal(got.cpu().numpy(), want)
+    assert np.array_equal(orc.decode_vector(atom, codes, x, k, n, scales=atoms), want)
+    assert ops.device_faults() == 0
+
+
+@pytest.mark.parametrize("decoder", ["bf16", "f16"])
+def test_dense16_vector_products_are_the_reference_bits(cuda, orc, decoder):
+    torch = cuda
+    ops = _ops()
+    rng = np.random.default_rng(5)
+    n, k, rows = 150, 1024, 4
+    w = rng.normal(0, 0.05, size=(n, k)).astype(np.float32)
+    tw = torch.from_numpy(w)
+    bits = (tw.to(torch.bfloat16) if decoder == "bf16" else tw.to(torch.float16)).view(torch.uint8)
+    raw = bits.numpy().reshape(n, 2 * k)
+    x = rng.normal(0, 1, size=(rows, k)).astype(np.float32)
+    dec = ops.DECODER_BF16 if decoder == "bf16" else ops.DECODER_F16
+    got = ops.decode_vector(dec, to_dev(torch, raw), to_dev(torch, x), k, n - 6, first=6)
+    want = orc.decode_vector(dec, raw, x, k, n - 6, first=6)
+    assert np.array_equal(got.cpu().numpy(), want)
+
+
+def test_decoded_rows_lookup(cuda, orc):
+    """decode::RunRows: rows by id, times the tensor scale; an id outside the matrix gives a
+    zero row and raises the flag."""
+    torch = cuda
+    ops = _ops()
+    rng = np.random.default_rng(12)
+    n, k = 90, 512
+    ids = np.array([3, 89, 0, 90, 17, -2, 3], np.int32)
+    ts = np.array([0.5, 2.0, 1.25], np.float32)
+    w = synth.q8_0_weights(rng, n, k)
+    bad = torch.zeros(1, dtype=torch.int32, device="cuda")
+    got = ops.decode_rows(ops.DECODER_Q8_0, to_dev(torch, w), to_dev(torch, ids), k,
+                          tensor_scale=to_dev(torch, ts), rows_per_scale=30, bad=bad)
+    want, flag = orc.decode_rows(orc.DECODER_Q8_0, w, ids, k, tensor_scale=ts, rows_per_scale=30)
+    assert np.array_equal(got.cpu().numpy(), want) and flag == 1 and int(bad.item()) == 1
+    codes, scales, atoms = _fp4_operands(rng, n, k, True)
+    good = np.array([5, 88, 64], np.int32)
+    got = ops.decode_rows(ops.DECODER_NVFP4_ATOMS, to_dev(torch, codes), to_dev(torch, good), k,
+                          scales=to_dev(torch, atoms))
+    want, flag = orc.decode_rows(6, codes, good, k, scales=atoms)
+    assert np.array_equal(got.cpu().numpy(), want) and flag == 0

@@ -144,3 +144,32 @@ def test_q4_k_block_product_is_the_reference_scalar_statement(orc):
         orc.lib().orc_q4_k_scales(blk.ctypes.data_as(C.c_void_p), a.ctypes.data_as(C.c_void_p),
                                   b.ctypes.data_as(C.c_void_p))
         assert np.array_equal(a, sc[i]) and np.array_equal(b, mn[i])
+
+
+def _same_values(got, want_bits):
+    want = want_bits.view(np.float32)
+    assert np.array_equal(np.isnan(got), np.isnan(want))
+    ok = ~np.isnan(want)
+    assert np.array_equal(got[ok].view(np.uint32), want[ok].view(np.uint32))
+
+
+def test_fp4_and_dense16_decoders_match_reference_decode_rows(orc, pins):
+    """The decode module's E2M1 decoders (NVFP4: UE4M3 scale per 16; MXFP4: E8M0 scale per 32;
+    row-major scales and scale atoms) and its dense BF16 / F16 decoders, against the
+    reference's own DecodeRows (src/kernels/reference/decode.cc) run on the same bytes."""
+    codes = pins["fp4_codes"]
+    n, k = codes.shape[0], codes.shape[1] * 2
+    ids = np.arange(n, dtype=np.int32)
+    for name, split, atoms in (("nvfp4", 5, 6), ("mxfp4", 7, 8)):
+        got, bad = orc.decode_rows(split, codes, ids, k, scales=pins[name + "_scales"])
+        assert bad == 0
+        _same_values(got, pins[name + "_decoded_bits"])
+        got, _ = orc.decode_rows(atoms, codes, ids, k, scales=pins[name + "_atoms"])
+        _same_values(got, pins[name + "_decoded_bits"])
+    raw = pins["dense16_bits"].view(np.uint8).reshape(6, 128)
+    for name, decoder in (("bf16", 3), ("f16", 4)):
+        got, _ = orc.decode_rows(decoder, raw, np.arange(6, dtype=np.int32), 64)
+        _same_values(got, pins[name + "_decoded_bits"])
+    # an id outside the matrix: a zero row and the flag
+    got, bad = orc.decode_rows(3, raw, np.array([1, 6, -1], np.int32), 64)
+    assert bad == 1 and not got[1].any() and not got[2].any() and got[0].any()
