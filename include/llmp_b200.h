@@ -206,14 +206,40 @@ typedef struct llmp_b200_mmq_desc {
   int dst_col_stride;
   int experts;                  /* with expert_bounds */
   int max_cols_per_expert;      /* host-known bound on an expert's columns (<= ncols) */
+  const void* w_slab;           /* the weights as llmp_b200_q4k_relayout left them, or NULL
+                                   (then `w` is read; with a slab `w` may be NULL) */
+  void* scratch;                /* llmp_b200_mmq_scratch() bytes, 256-byte aligned, or NULL */
 } llmp_b200_mmq_desc;
+
+/* The reference's import-time expert relayout (src/import/expert_relayout.h,
+ * src/kernels/ggml/moe_layout.h:8-24, src/engine/expert_slab.h:22-36: GGML blocks to the
+ * tensor core's layout, once at load time), for Q4_K and tcgen05: per expert the 4-bit codes
+ * as int8 rows K-major (what kind::i8 reads through a swizzled tensor map), the groups'
+ * (d * sc)_half as F32 in [128 rows][k-step] tiles, the groups' (-dmin * m)_half as FP16
+ * K-major.  Lossless: every value of the blocks is kept, only rearranged and widened
+ * (1.19 bytes a weight against 0.56).  w: Q4_K blocks [experts][nrows][k / 256], stride_row
+ * blocks between rows, stride_expert blocks between experts.  slab: llmp_b200_q4k_slab_bytes
+ * bytes, 256-byte aligned.  One launch; nothing else is allocated or synchronized. */
+size_t llmp_b200_q4k_slab_bytes(int nrows, int k, int experts);
+int llmp_b200_q4k_relayout(const void* w, int nrows, int k, int stride_row, int64_t stride_expert,
+                           int experts, void* slab, void* stream);
 
 /* Replace PlanMulMatQ's scratch sizing and MulMatQ / RunExpertProducts
  * (src/kernels/ggml/mul_mat_q.cu:317-397, 453-462, 551-737): D[col][row] =
  * W[row] . Y[col] with exact int32 group sums on tcgen05 (kind::i8) and the
- * F32 scale fold of GGML's MMQ.  No stream-k fixup: scratch is 0 bytes. */
+ * F32 scale fold of GGML's MMQ.  The weights are read from desc->w_slab when given;
+ * else they are relaid into desc->scratch first (llmp_b200_mmq_scratch bytes: the slab's
+ * size; one more launch); with neither, the kernel unpacks the raw blocks itself, k-step
+ * by k-step, which is the slowest of the three and needs no memory.  There is no stream-k
+ * fixup pass. */
 size_t llmp_b200_mmq_scratch(const llmp_b200_mmq_desc* desc, int sms);
 int llmp_b200_mmq(const llmp_b200_mmq_desc* desc, int sms, void* stream);
+/* Verification entry with no reference counterpart as a separate call: the dense product as
+ * llmp_b200_mmq queues it and, besides, the exact int32 sums C = sum code * q of every
+ * (column, weight row, 32-value group), read out of tensor memory before the fold:
+ * sums[(col * nrows + row) * (k / 32) + group] (the quantity the reference checks bit for
+ * bit against GGML, tests/unit/dsv4_fast_test.cc:511-540). */
+int llmp_b200_mmq_block_sums(const llmp_b200_mmq_desc* desc, int32_t* sums, void* stream);
 
 /* ------------------------------------------------------------------ MoE */
 /* Replaces RunMoeRoute (src/kernels/ggml/llmp_moe.cu:760; kernels :81-160).
@@ -246,6 +272,9 @@ typedef struct llmp_b200_grouped_gemm_desc {
   uint64_t expert_stride;   /* bytes, a multiple of 144 */
   void* d;                  /* F32 [rows][n] */
   void* scratch;            /* llmp_b200_grouped_gemm_scratch() bytes, 256-byte aligned */
+  const void* weights_slab; /* the experts as llmp_b200_q4k_relayout(weights, n, k, k / 256,
+                               expert_stride / 144, groups) left them, or NULL: then the
+                               kernel unpacks `weights` itself (slower) */
 } llmp_b200_grouped_gemm_desc;
 
 /* Replace moe::GroupedGemmAvailable / GroupedGemmScratch / RunGroupedGemm

@@ -83,14 +83,15 @@ class MmqDesc(C.Structure):
                 ("expert_bounds", C.c_void_p), ("dst", C.c_void_p), ("k", C.c_int),
                 ("nrows", C.c_int), ("ncols", C.c_int), ("stride_row", C.c_int),
                 ("stride_expert", C.c_int), ("dst_col_stride", C.c_int), ("experts", C.c_int),
-                ("max_cols_per_expert", C.c_int)]
+                ("max_cols_per_expert", C.c_int), ("w_slab", C.c_void_p), ("scratch", C.c_void_p)]
 
 
 class GroupedGemmDesc(C.Structure):
     """llmp_b200_grouped_gemm_desc (include/llmp_b200.h)."""
     _fields_ = [("groups", C.c_int), ("n", C.c_int), ("k", C.c_int), ("rows", C.c_int),
                 ("offsets", C.c_void_p), ("a", C.c_void_p), ("weights", C.c_void_p),
-                ("expert_stride", C.c_uint64), ("d", C.c_void_p), ("scratch", C.c_void_p)]
+                ("expert_stride", C.c_uint64), ("d", C.c_void_p), ("scratch", C.c_void_p),
+                ("weights_slab", C.c_void_p)]
 
 
 # name -> (restype, argtypes): every symbol include/llmp_b200.h declares.
@@ -110,6 +111,10 @@ SIGNATURES = {
                                          C.c_void_p, C.c_void_p, C.c_void_p]),
     "llmp_b200_mmq_scratch": (C.c_size_t, [C.POINTER(MmqDesc), C.c_int]),
     "llmp_b200_mmq": (C.c_int, [C.POINTER(MmqDesc), C.c_int, C.c_void_p]),
+    "llmp_b200_mmq_block_sums": (C.c_int, [C.POINTER(MmqDesc), C.c_void_p, C.c_void_p]),
+    "llmp_b200_q4k_slab_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
+    "llmp_b200_q4k_relayout": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int,
+                                         C.c_void_p, C.c_void_p]),
     "llmp_b200_moe_route_ints": (C.c_int64, [C.c_int, C.c_int, C.c_int]),
     "llmp_b200_moe_route": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
                                       C.c_void_p]),

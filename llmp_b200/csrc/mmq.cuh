@@ -13,8 +13,9 @@ constexpr int kMmqTileCols = 128;  // token columns a tile
 
 // worklist (device, or null): int32 {count, (expert, first column) x count};
 // grid row y takes entry y and exits when y >= count.  max_tiles: its capacity.
+// sums (device, or null): verification output, the int32 group sums [col][row][k / 32].
 int LaunchMmq(const llmp_b200_mmq_desc& d, const std::int32_t* worklist, int max_tiles,
-              void* stream);
+              void* stream, std::int32_t* sums = nullptr);
 
 }  // namespace llmp_b200
 

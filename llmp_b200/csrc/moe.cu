@@ -311,8 +311,9 @@ int CheckGrouped(const llmp_b200_grouped_gemm_desc& g) {
       g.rows < 1) {
     return Reject("grouped_gemm: 1..1024 groups, n >= 1, k a positive multiple of 256, rows >= 1");
   }
-  if (g.offsets == nullptr || g.a == nullptr || g.weights == nullptr || g.d == nullptr) {
-    return Reject("grouped_gemm: offsets, activation blocks, weights and an output");
+  if (g.offsets == nullptr || g.a == nullptr || (g.weights == nullptr && g.weights_slab == nullptr) ||
+      g.d == nullptr) {
+    return Reject("grouped_gemm: offsets, activation blocks, weights (blocks or slab) and an output");
   }
   if (g.expert_stride % 144 != 0 || g.expert_stride < static_cast<std::uint64_t>(g.n) * (g.k / 256) * 144) {
     return Reject("grouped_gemm: expert stride a whole number of Q4_K blocks covering n rows");
@@ -336,6 +337,8 @@ llmp_b200_mmq_desc MmqOf(const llmp_b200_grouped_gemm_desc& g) {
   d.dst_col_stride = g.n;
   d.experts = g.groups;
   d.max_cols_per_expert = g.rows;
+  d.w_slab = g.weights_slab;
+  d.scratch = nullptr;
   return d;
 }
 

@@ -19,7 +19,7 @@ __all__ = ["available", "sm_count", "device_faults", "block_bytes", "block_elems
            "quantize_q8", "vecq", "mmvq", "vecq_f32", "vecq_q8", "vecq_q8_scratch", "vecq_variants", "vecq_block_sums", "mxfp8_padded_rows",
            "mxfp8_quantize", "mxfp8_swizzle", "mxfp8_gemm", "mxfp8_mul_mat_vec", "decode_vector", "decode_rows", "decode_matrix", "decode_grouped", "DECODER_Q8_0", "DECODER_MXFP8_SPLIT",
            "DECODER_MXFP8_ATOMS", "DECODER_BF16", "DECODER_F16", "DECODER_NVFP4_SPLIT", "DECODER_NVFP4_ATOMS",
-           "DECODER_MXFP4_SPLIT", "DECODER_MXFP4_ATOMS", "mmq_quantize", "mmq", "moe_route", "grouped_gemm",
+           "DECODER_MXFP4_SPLIT", "DECODER_MXFP4_ATOMS", "mmq_quantize", "mmq", "mmq_scratch", "mmq_block_sums", "q4k_relayout", "moe_route", "grouped_gemm",
            "moe_glu_quantize", "moe_combine", "moe_ffn", "TYPE_Q8_0", "TYPE_Q4_K",
            "GLU_NONE", "GLU_SWIGLU", "GLU_SWIGLU_CLAMP", "GLU_GEGLU", "Rejected", "LaunchFailed"]
 
@@ -338,22 +338,34 @@ def mmq_quantize(x: torch.Tensor, ids_src: torch.Tensor | None = None,
     return out
 
 
-def mmq(weights: torch.Tensor, yq: torch.Tensor, k: int, n: int, *, wtype: int = TYPE_Q4_K,
-        ids_dst: torch.Tensor | None = None, expert_bounds: torch.Tensor | None = None,
-        out_cols: int | None = None, max_cols_per_expert: int | None = None,
-        stride_row: int | None = None, stride_expert: int | None = None,
-        out: torch.Tensor | None = None) -> torch.Tensor:
-    """MulMatQ: weights Q4_K [n, k] (or [experts, n, k] with expert_bounds over the sorted
-    columns of yq) x Q8_1-MMQ activations -> F32 [out_cols, n]."""
-    _need(weights, torch.uint8, "mmq weights")
+def q4k_relayout(weights: torch.Tensor, k: int, n: int) -> torch.Tensor:
+    """The load-time relayout of Q4_K weights [n, k blocks] or experts [experts, n, k blocks]
+    into the tensor core's slab (llmp_b200_q4k_relayout): a uint8 tensor to pass as `slab`."""
+    _need(weights, torch.uint8, "q4k_relayout weights")
+    experts = weights.shape[0] if weights.dim() == 3 else 1
+    stride_row = weights.stride(-2) // 144
+    stride_expert = weights.stride(0) // 144 if weights.dim() == 3 else n * stride_row
+    slab = torch.empty((int(N.lib().llmp_b200_q4k_slab_bytes(n, k, experts)),), dtype=torch.uint8,
+                       device=weights.device)
+    N.check(N.lib().llmp_b200_q4k_relayout(weights.data_ptr(), n, k, stride_row, stride_expert,
+                                           experts, slab.data_ptr(), _stream()),
+            "llmp_b200_q4k_relayout")
+    return slab
+
+
+def _mmq_desc(weights, yq, k, n, wtype, ids_dst, expert_bounds, out_cols, max_cols_per_expert,
+              stride_row, stride_expert, out, slab, scratch):
     _need(yq, torch.uint8, "mmq activations")
     ncols = yq.shape[1]
     out_cols = ncols if out_cols is None else out_cols
     if out is None:
-        out = torch.empty((out_cols, n), dtype=torch.float32, device=weights.device)
+        out = torch.empty((out_cols, n), dtype=torch.float32, device=yq.device)
     _need(out, torch.float32, "mmq output")
     d = N.MmqDesc()
-    d.type, d.w, d.y, d.dst = wtype, weights.data_ptr(), yq.data_ptr(), out.data_ptr()
+    d.type, d.y, d.dst = wtype, yq.data_ptr(), out.data_ptr()
+    if weights is not None:
+        _need(weights, torch.uint8, "mmq weights")
+        d.w = weights.data_ptr()
     d.ids_dst = ids_dst.data_ptr() if ids_dst is not None else None
     d.expert_bounds = expert_bounds.data_ptr() if expert_bounds is not None else None
     d.k, d.nrows, d.ncols = k, n, ncols
@@ -363,8 +375,43 @@ def mmq(weights: torch.Tensor, yq: torch.Tensor, k: int, n: int, *, wtype: int =
     d.dst_col_stride = out.stride(0)
     d.experts = expert_bounds.numel() - 1 if expert_bounds is not None else 1
     d.max_cols_per_expert = ncols if max_cols_per_expert is None else max_cols_per_expert
+    d.w_slab = slab.data_ptr() if slab is not None else None
+    d.scratch = scratch.data_ptr() if scratch is not None else None
+    return d, out
+
+
+def mmq_scratch(k: int, n: int, experts: int = 1, device="cuda") -> torch.Tensor:
+    """Scratch for mmq(..., scratch=...): room for the weights' slab."""
+    return torch.empty((int(N.lib().llmp_b200_q4k_slab_bytes(n, k, experts)),), dtype=torch.uint8,
+                       device=device)
+
+
+def mmq(weights: torch.Tensor | None, yq: torch.Tensor, k: int, n: int, *, wtype: int = TYPE_Q4_K,
+        ids_dst: torch.Tensor | None = None, expert_bounds: torch.Tensor | None = None,
+        out_cols: int | None = None, max_cols_per_expert: int | None = None,
+        stride_row: int | None = None, stride_expert: int | None = None,
+        out: torch.Tensor | None = None, slab: torch.Tensor | None = None,
+        scratch: torch.Tensor | None = None) -> torch.Tensor:
+    """MulMatQ: weights Q4_K [n, k] (or [experts, n, k] with expert_bounds over the sorted
+    columns of yq) x Q8_1-MMQ activations -> F32 [out_cols, n].  slab: the weights as
+    q4k_relayout left them (then weights may be None); scratch (mmq_scratch): the call relays
+    the weights there first; neither: the kernel unpacks the raw blocks itself."""
+    d, out = _mmq_desc(weights, yq, k, n, wtype, ids_dst, expert_bounds, out_cols,
+                       max_cols_per_expert, stride_row, stride_expert, out, slab, scratch)
     N.check(N.lib().llmp_b200_mmq(C.byref(d), 0, _stream()), "llmp_b200_mmq")
     return out
+
+
+def mmq_block_sums(weights: torch.Tensor | None, yq: torch.Tensor, k: int, n: int, *,
+                   slab: torch.Tensor | None = None, scratch: torch.Tensor | None = None):
+    """The dense product and the exact int32 group sums it folds: (F32 [cols, n], I32
+    [cols, n, k / 32])."""
+    d, out = _mmq_desc(weights, yq, k, n, TYPE_Q4_K, None, None, None, None, None, None, None, slab,
+                       scratch)
+    sums = torch.empty((yq.shape[1], n, k // 32), dtype=torch.int32, device=yq.device)
+    N.check(N.lib().llmp_b200_mmq_block_sums(C.byref(d), sums.data_ptr(), _stream()),
+            "llmp_b200_mmq_block_sums")
+    return out, sums
 
 
 # ----------------------------------------------------------------------- MoE
@@ -387,24 +434,29 @@ def moe_route(ids: torch.Tensor, experts: int) -> dict:
             "tokens": tokens}
 
 
-def grouped_gemm(weights: torch.Tensor, a: torch.Tensor, offsets: torch.Tensor, k: int, n: int,
-                 *, out: torch.Tensor | None = None,
-                 scratch: torch.Tensor | None = None) -> torch.Tensor:
-    """MoeGemm: weights Q4_K [groups, n, k]; a Q8_1-MMQ blocks [k / 128, rows, 144] of
-    expert-sorted rows; offsets I32 [groups + 1] -> F32 [rows, n]."""
-    _need(weights, torch.uint8, "grouped_gemm weights")
+def grouped_gemm(weights: torch.Tensor | None, a: torch.Tensor, offsets: torch.Tensor, k: int, n: int,
+                 *, out: torch.Tensor | None = None, scratch: torch.Tensor | None = None,
+                 slab: torch.Tensor | None = None) -> torch.Tensor:
+    """MoeGemm: weights Q4_K [groups, n, k] (or their slab from q4k_relayout); a Q8_1-MMQ blocks
+    [k / 128, rows, 144] of expert-sorted rows; offsets I32 [groups + 1] -> F32 [rows, n]."""
     _need(a, torch.uint8, "grouped_gemm activations")
     _need(offsets, torch.int32, "grouped_gemm offsets")
     groups, rows = offsets.numel() - 1, a.shape[1]
     if out is None:
-        out = torch.empty((rows, n), dtype=torch.float32, device=weights.device)
+        out = torch.empty((rows, n), dtype=torch.float32, device=a.device)
     need = int(N.lib().llmp_b200_grouped_gemm_scratch(groups, rows, 0))
     if scratch is None:
-        scratch = torch.empty((need,), dtype=torch.uint8, device=weights.device)
+        scratch = torch.empty((need,), dtype=torch.uint8, device=a.device)
     g = N.GroupedGemmDesc()
     g.groups, g.n, g.k, g.rows = groups, n, k, rows
-    g.offsets, g.a, g.weights = offsets.data_ptr(), a.data_ptr(), weights.data_ptr()
-    g.expert_stride = weights.stride(0) if weights.dim() == 3 else n * (k // 256) * 144
+    g.offsets, g.a = offsets.data_ptr(), a.data_ptr()
+    g.expert_stride = n * (k // 256) * 144
+    if weights is not None:
+        _need(weights, torch.uint8, "grouped_gemm weights")
+        g.weights = weights.data_ptr()
+        if weights.dim() == 3:
+            g.expert_stride = weights.stride(0)
+    g.weights_slab = slab.data_ptr() if slab is not None else None
     g.d, g.scratch = out.data_ptr(), scratch.data_ptr()
     N.check(N.lib().llmp_b200_grouped_gemm(C.byref(g), 0, _stream()), "llmp_b200_grouped_gemm")
     return out
@@ -438,13 +490,14 @@ def moe_combine(rows: torch.Tensor, position: torch.Tensor, weights: torch.Tenso
 
 def moe_ffn(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, gate_up: torch.Tensor,
             down: torch.Tensor, hidden: int, inter: int, glu: int = GLU_SWIGLU,
-            decode_tokens: int | None = None) -> torch.Tensor:
+            decode_tokens: int | None = None, slabs: tuple | None = None) -> torch.Tensor:
     """The routed-expert block as the reference wires it (tests/unit/qwen38_moe_test.cc:487-497):
     route -> quantize (scattered to expert-sorted rows) -> grouped GEMM gate|up -> GLU +
     requantize -> grouped GEMM down -> ordered weighted combine.  x F32/BF16 [tokens, hidden];
     ids I32 [tokens, used]; weights F32 [tokens, used]; gate_up Q4_K [experts, 2 inter, hidden]
     (gate rows then up rows); down Q4_K [experts, hidden, inter].  Up to DECODE_TOKENS tokens
-    take the decode products (llmp.vecq routed) instead of the tensor-core GEMM."""
+    take the decode products (llmp.vecq routed) instead of the tensor-core GEMM.  slabs: the
+    experts' (gate_up, down) weights as q4k_relayout left them at load time, for the GEMM path."""
     tokens, used = ids.shape
     experts = gate_up.shape[0]
     # Few tokens: the decode products (routed llmp.vecq), which stream each named expert's
@@ -475,9 +528,11 @@ def moe_ffn(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, gate_up: 
     route = moe_route(ids, experts)
     slots = tokens * used
     aq = mmq_quantize(x, ids_src=route["token"], cols=slots)
-    gu = grouped_gemm(gate_up, aq, route["offsets"], hidden, 2 * inter)
+    gu = grouped_gemm(gate_up, aq, route["offsets"], hidden, 2 * inter,
+                      slab=slabs[0] if slabs is not None else None)
     hq = moe_glu_quantize(gu, inter, glu)
-    y = grouped_gemm(down, hq, route["offsets"], inter, hidden)
+    y = grouped_gemm(down, hq, route["offsets"], inter, hidden,
+                     slab=slabs[1] if slabs is not None else None)
     return moe_combine(y, route["position"], weights.contiguous(), tokens, used)
 
 

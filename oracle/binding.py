@@ -103,6 +103,8 @@ def lib():
                                   C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
                                   C.c_int, C.c_float, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p,
                                   C.c_int64],
+            "orc_mmq_block_sums": [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
+                                   C.c_void_p],
             "orc_decode_rows": [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
                                 C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p],
             "orc_moe_route": [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p],
@@ -337,3 +339,13 @@ def decode_rows(decoder, data, ids, k, *, scales=None, tensor_scale=None, rows_p
                           data.shape[0], _p(ts) if ts is not None else None, rows_per_scale,
                           _p(ids), ids.size, _p(y), _p(bad))
     return y, int(bad[0])
+
+
+def mmq_block_sums(w, yq, k, n):
+    """The exact int32 group sums of the dense MMQ: I32 [cols, n, k / 32]."""
+    w = np.ascontiguousarray(w, dtype=np.uint8)
+    yq = np.ascontiguousarray(yq, dtype=np.uint8)
+    cols = yq.shape[1]
+    sums = np.empty((cols, n, k // 32), np.int32)
+    lib().orc_mmq_block_sums(_p(w), k // 256, _p(yq), cols, k, n, _p(sums))
+    return sums

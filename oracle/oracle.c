@@ -509,6 +509,25 @@ static void mmq_range(int64_t begin, int64_t end, void* ctxp) {
   }
 }
 
+/* The exact int32 sums the MMQ folds: sums[(col * n + row) * (k / 32) + group] =
+ * sum over the group's 32 values of code * q (the quantity the reference checks bit for bit
+ * against GGML, tests/unit/dsv4_fast_test.cc:511-540). */
+void orc_mmq_block_sums(const uint8_t* w, int64_t stride_row_blocks, const uint8_t* yq,
+                        int64_t ncols, int64_t k, int64_t n, int32_t* sums) {
+  const int64_t groups = k / 32;
+  for (int64_t c = 0; c < ncols; ++c)
+    for (int64_t row = 0; row < n; ++row)
+      for (int64_t g = 0; g < groups; ++g) {
+        const uint8_t* wb = w + (row * stride_row_blocks + g / 8) * ORC_Q4_K_BYTES;
+        const uint8_t* codes = wb + 16 + ((g % 8) / 2) * 32;
+        const uint8_t* yb = yq + ((g / 4) * ncols + c) * ORC_Q8_1_MMQ_BYTES;
+        const int8_t* q = (const int8_t*)(yb + 16 + (g % 4) * 32);
+        int32_t C = 0;
+        for (int i = 0; i < 32; ++i) C += ((codes[i] >> ((g % 2) * 4)) & 15) * (int32_t)q[i];
+        sums[(c * n + row) * groups + g] = C;
+      }
+}
+
 void orc_mmq_q4_k(const uint8_t* w, int64_t stride_row_blocks, int64_t stride_expert_blocks,
                   const uint8_t* yq, int64_t ncols_y, const int32_t* ids_dst,
                   const int32_t* expert_bounds, int experts, float* dst, int64_t dst_col_stride,

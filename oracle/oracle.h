@@ -94,6 +94,9 @@ void orc_quantize_mmq_q8_1_ds4(const float* x, int64_t k, int64_t cols, int64_t 
                                const int32_t* ids_src, uint8_t* out);
 /* D[col][n] = W_q4k[n][k] . X_q8mmq[col][k]; dst column stride in floats.
  * ids_dst / expert_bounds NULL: dense. */
+/* sums[(col * n + row) * (k / 32) + group]: the exact int32 group sums of the dense product. */
+void orc_mmq_block_sums(const uint8_t* w, int64_t stride_row_blocks, const uint8_t* yq,
+                        int64_t ncols, int64_t k, int64_t n, int32_t* sums);
 void orc_mmq_q4_k(const uint8_t* w, int64_t stride_row_blocks, int64_t stride_expert_blocks,
                   const uint8_t* yq, int64_t ncols_y, const int32_t* ids_dst,
                   const int32_t* expert_bounds, int experts, float* dst, int64_t dst_col_stride,

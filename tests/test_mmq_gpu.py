@@ -53,7 +53,10 @@ def _check(got, want32, want64, what=""):
                                       # k-steps 10 (a partial last group of 16 min terms) and
                                       # 66 (both tiles of min operands reused)
                                       (40, 136, 1280), (64, 128, 8448)])
-def test_dense_mmq_matches_the_oracle(cuda, orc, cols, n, k):
+@pytest.mark.parametrize("mode", ["raw", "scratch", "slab"])
+def test_dense_mmq_matches_the_oracle(cuda, orc, cols, n, k, mode):
+    """The three ways the weights reach the tensor core: unpacked in the kernel (raw), relaid
+    into caller scratch by the call, relaid once beforehand (slab)."""
     torch = cuda
     ops = _ops()
     rng = np.random.default_rng(cols + n + k)
@@ -62,7 +65,13 @@ def test_dense_mmq_matches_the_oracle(cuda, orc, cols, n, k):
     yq = ops.mmq_quantize(to_dev(torch, x))
     buf = torch.full((cols * n + 64,), float("nan"), device="cuda")
     out = buf[: cols * n].view(cols, n)
-    ops.mmq(to_dev(torch, w), yq, k, n, out=out)
+    wd = to_dev(torch, w)
+    if mode == "raw":
+        ops.mmq(wd, yq, k, n, out=out)
+    elif mode == "scratch":
+        ops.mmq(wd, yq, k, n, out=out, scratch=ops.mmq_scratch(k, n))
+    else:
+        ops.mmq(None, yq, k, n, out=out, slab=ops.q4k_relayout(wd, k, n))
     torch.cuda.synchronize()
     assert ops.device_faults() == 0
     assert torch.isnan(buf[cols * n:]).all()
@@ -112,3 +121,75 @@ def test_mmq_refuses_what_it_does_not_take(cuda):
     with pytest.raises(ops.Rejected):
         ops.mmq(w, y, 128, 4)
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("mode", ["raw", "slab"])
+@pytest.mark.parametrize("cols,n,k", [(128, 128, 256), (70, 200, 1024), (260, 130, 768)])
+def test_mmq_group_sums_are_bit_exact(cuda, orc, cols, n, k, mode):
+    """The int32 sums C = sum code * q of every (column, row, 32-value group), read out of
+    tensor memory before the fold, against the oracle's integer loop: bit for bit."""
+    torch = cuda
+    ops = _ops()
+    rng = np.random.default_rng(cols * 7 + n + k)
+    w = synth.q4_k_weights(rng, n, k)
+    x = rng.normal(0, 1, size=(cols, k)).astype(np.float32)
+    yq = ops.mmq_quantize(to_dev(torch, x))
+    wd = to_dev(torch, w)
+    slab = ops.q4k_relayout(wd, k, n) if mode == "slab" else None
+    out, sums = ops.mmq_block_sums(wd, yq, k, n, slab=slab)
+    torch.cuda.synchronize()
+    assert ops.device_faults() == 0
+    want = orc.mmq_block_sums(w, yq.cpu().numpy(), k, n)
+    assert np.array_equal(sums.cpu().numpy(), want)
+    want32, want64 = orc.mmq_q4_k(w, yq.cpu().numpy(), k, n, want64=True)
+    _check(out.cpu().numpy(), want32, want64)
+
+
+@pytest.mark.parametrize("m", [512, 4096])
+def test_prefill_gemm_at_the_benchmark_shape_by_slabs(cuda, orc, m):
+    """The prefill config's own shape (K 4096, N 14336, M tokens): the whole product on the
+    device, slabs of it (first / middle / last row tile x first / last column tile) against the
+    oracle."""
+    torch = cuda
+    ops = _ops()
+    n, k = 14336, 4096
+    rng = np.random.default_rng(m)
+    w = synth.q4_k_weights(rng, n, k)
+    x = rng.normal(0, 1, size=(m, k)).astype(np.float32)
+    xd = torch.from_numpy(x).to(torch.bfloat16).cuda()
+    yq = ops.mmq_quantize(xd)
+    wd = to_dev(torch, w)
+    out = ops.mmq(wd, yq, k, n, scratch=ops.mmq_scratch(k, n))
+    torch.cuda.synchronize()
+    assert ops.device_faults() == 0 and torch.isfinite(out).all()
+    yh = yq.cpu().numpy()
+    got = out.cpu().numpy()
+    for r0 in (0, 56 * 128, n - 128):
+        for c0 in (0, m - 128):
+            want32, want64 = orc.mmq_q4_k(w[r0:r0 + 128], np.ascontiguousarray(yh[:, c0:c0 + 128]), k,
+                                          128, want64=True)
+            _check(got[c0:c0 + 128, r0:r0 + 128], want32, want64, f"slab rows {r0} cols {c0}")
+
+
+def test_routed_mmq_takes_a_slab_of_experts(cuda, orc):
+    torch = cuda
+    ops = _ops()
+    rng = np.random.default_rng(6)
+    experts, used, tokens, n, k = 6, 2, 200, 384, 768
+    w = synth.q4_k_weights(rng, experts * n, k).reshape(experts, n, -1)
+    ids, _ = synth.topk_route(rng, tokens, experts, used)
+    route = orc.moe_route(ids, experts)
+    slots = tokens * used
+    x = rng.normal(0, 1, size=(tokens, k)).astype(np.float32)
+    ids_src = route["token"][:slots].astype(np.int32)
+    bounds = route["offsets"].astype(np.int32)
+    yq = ops.mmq_quantize(to_dev(torch, x), ids_src=to_dev(torch, ids_src))
+    wd = to_dev(torch, w)
+    raw = ops.grouped_gemm(wd, yq, to_dev(torch, bounds), k, n)
+    slab = ops.grouped_gemm(None, yq, to_dev(torch, bounds), k, n, slab=ops.q4k_relayout(wd, k, n))
+    torch.cuda.synchronize()
+    assert ops.device_faults() == 0
+    assert torch.equal(raw, slab)          # the same arithmetic either way
+    want32, want64 = orc.mmq_q4_k(w, yq.cpu().numpy(), k, n, expert_bounds=bounds,
+                                  stride_expert=n * (k // 256), want64=True)
+    _check(slab.cpu().numpy(), want32, want64)
