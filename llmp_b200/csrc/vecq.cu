@@ -244,8 +244,9 @@ int LaunchVecQ(int type, const llmp_b200_vecq_desc* desc, int variant, bool f32_
   bool rowlane_ok = false;
   if (dense && q4 && Aligned(d.w, 16) && (d.g == nullptr || Aligned(d.g, 16))) {
     if (wants_rowlane) {
-      rowlane_ok = PlanRowLane(d, p, SmCount(), kVariants[variant].r, kVariants[variant].u == 1,
-                               &lanes);
+      const Variant& forced = kVariants[variant];
+      rowlane_ok = PlanRowLane(d, p, SmCount(), forced.r, forced.u == 1, &lanes, 0, forced.u == 2,
+                               forced.warps > 0 ? forced.warps : kRowLaneWarps);
     } else {
       // A row's sum adds its super-blocks up in an order the geometry (rows and phases
       // a warp) fixes.  So that a token gives the same bits alone or in company, more

@@ -509,10 +509,17 @@ constexpr Variant kVariants[] = {
     {"rowlane.r32", 0, 32, 0, 0},
     // Half an SM a CTA (u field = 1), so consecutive kernels overlap.
     {"rowlane.half", 0, 0, 1, 0},
+    // Whole rows in one bulk copy a warp and matrix (u field = 2); up to 16 or 24 warps a
+    // CTA (warps field; 24 for one token a pass only); both.
+    {"rowlane.packed", 0, 0, 2, 0},
+    {"rowlane.w16", 0, 0, 0, 16},
+    {"rowlane.packed.w16", 0, 0, 2, 16},
+    {"rowlane.w24", 0, 0, 0, 24},
+    {"rowlane.packed.w24", 0, 0, 2, 24},
 };
 constexpr int kVariantCount = static_cast<int>(sizeof(kVariants) / sizeof(kVariants[0]));
-constexpr int kStreamVariant = kVariantCount - 9;
-constexpr int kRowLaneVariant = kVariantCount - 8;  // and its seven forced forms after it
+constexpr int kStreamVariant = kVariantCount - 14;
+constexpr int kRowLaneVariant = kVariantCount - 13;  // and its twelve forced forms after it
 
 template <typename Unit, int P, int LPR, int R, int U, bool kGlu>
 cudaError_t LaunchOne(const Desc& d, int warps, cudaStream_t stream) {

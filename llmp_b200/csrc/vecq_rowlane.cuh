@@ -33,9 +33,13 @@
 namespace llmp_b200 {
 namespace vecq {
 
-constexpr int kRowLaneMaxWarps = 12;      // a CTA that owns its SM
+constexpr int kRowLaneMaxWarps = 24;      // a CTA that owns its SM: 24 warps of 85 registers for one
+                                          // token a pass, 16 of 128 up to four, 12 of 168 for eight
+constexpr int kRowLaneWarps = 12;         // ... by default
 constexpr int kRowLaneHalfWarps = 9;      // a CTA that shares its SM with the next kernel's
 constexpr int kRowLaneMaxStages = 8;
+
+__host__ __device__ constexpr int RowLaneWarpLimit(int p) { return p == 1 ? 24 : p <= 4 ? 16 : 12; }
 
 struct RowLanePlan {
   int warps;         // W
@@ -50,6 +54,8 @@ struct RowLanePlan {
   int smem_bytes;
   int grid;
   int half;          // the kHalf instantiation
+  int packed;        // whole rows, all steps, in ONE bulk copy a warp and matrix (rows contiguous
+                     // in memory, ring depth = steps): pitch = a row's bytes
   double score;      // the planner's figure of merit (lane use x warps x ring depth)
   int f32_input;     // activations are F32: quantize to Q8_1 while staging
   int q8_row_blocks; // Q8_1 blocks between tokens' rows in q8_out
@@ -65,7 +71,7 @@ struct RowLanePlan {
 // after this one (launched as a programmatic dependent) becomes resident and
 // requests its weights while this one still computes.
 template <int P, bool kGlu, bool kHalf>
-__global__ void __launch_bounds__(kHalf ? kRowLaneHalfWarps * 32 : kRowLaneMaxWarps * 32,
+__global__ void __launch_bounds__(kHalf ? kRowLaneHalfWarps * 32 : RowLaneWarpLimit(P) * 32,
                                   kHalf ? 2 : 1)
 VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
   constexpr int kMats = kGlu ? 2 : 1;
@@ -129,7 +135,19 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
 
   GridLaunchDependents();
   if (my_rows > 0) {
-    for (int j = 0; j < min(S, J); ++j) request(j);
+    if (plan.packed) {
+      // The warp's rows are one contiguous run of the matrix: a single copy a matrix.
+      const std::uint32_t bytes = static_cast<std::uint32_t>(my_rows) * static_cast<std::uint32_t>(UR) * 144u;
+      if (lane == 0) MbarExpectTx(&full[warp][0], bytes * kMats);
+      __syncwarp();
+      if (lane < kMats) {
+        BulkLoad(ring + (static_cast<std::size_t>(lane) * R * plan.pitch),
+                 mats[lane] + (static_cast<std::size_t>(row_begin) * a.stride_row * 144), bytes,
+                 &full[warp][0]);
+      }
+    } else {
+      for (int j = 0; j < min(S, J); ++j) request(j);
+    }
   }
   GridDependencyWait();
 
@@ -226,13 +244,14 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
 
   bool healthy = true;
   for (int j = 0; j < J; ++j) {
-    const int s = j % S;
-    if (healthy && lane == 0 &&
-        !MbarWait(&full[warp][s], static_cast<std::uint32_t>((j / S) & 1))) {
+    const int s = plan.packed ? 0 : j % S;
+    if (healthy && lane == 0 && (j == 0 || !plan.packed) &&
+        !MbarWait(&full[warp][s], plan.packed ? 0u : static_cast<std::uint32_t>((j / S) & 1))) {
       healthy = false;
       atomicAdd(plan.faults, 1u);
     }
-    __syncwarp();
+    healthy = __shfl_sync(0xffffffffu, healthy ? 1 : 0, 0) != 0;
+    if (!healthy) return;  // nothing of an incomplete stage is summed or stored
     const int c = (j * PH) + ph;
     if (ph < PH && c < UR && r < my_rows) {
       const unsigned char* base = ring + (static_cast<std::size_t>(s) * plan.stage_bytes);
@@ -244,7 +263,8 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
 #pragma unroll
       for (int m = 0; m < kMats; ++m) {
         Q4KBlockUnit raw;
-        raw.LoadShared(base + ((static_cast<std::size_t>(m) * R + r) * plan.pitch), ph);
+        raw.LoadShared(base + ((static_cast<std::size_t>(m) * R + r) * plan.pitch),
+                       plan.packed ? c : ph);
         int sc[8], mn[8];
         Q4KBlockScales(raw, sc, mn);
         float fmn[8];
@@ -314,7 +334,7 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
       }
     }
     __syncwarp();
-    if (j + S < J) {
+    if (!plan.packed && j + S < J) {
       FenceProxyAsync();
       request(j + S);
     }
@@ -392,7 +412,8 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
 
 // Host: the geometry for a dense Q4_K product, or false if it does not fit.
 inline bool PlanRowLane(const Desc& d, int p, int sms, int force_rows, bool half,
-                        RowLanePlan* plan, int force_phases = 0) {
+                        RowLanePlan* plan, int force_phases = 0, bool packed = false,
+                        int warps_limit = kRowLaneWarps) {
   const int mats = d.glu != LLMP_B200_GLU_NONE ? 2 : 1;
   const int ur = d.ncols_x / 256;
   if (ur < 1) return false;
@@ -400,8 +421,9 @@ inline bool PlanRowLane(const Desc& d, int p, int sms, int force_rows, bool half
   const int cta_rows = (d.nrows + grid - 1) / grid;
   const int acts_bytes = (ur * 256) + (ur * 64);
   const int budget = (half ? 110 : 220) * 1024 - (p * acts_bytes) - 1024;
-  const int max_warps = half ? kRowLaneHalfWarps : kRowLaneMaxWarps;
+  const int max_warps = half ? kRowLaneHalfWarps : std::min(warps_limit, RowLaneWarpLimit(p));
   if (budget <= 0) return false;
+  if (packed && d.stride_row != ur) return false;  // rows must follow one another in memory
   double best_score = -1.0;
   RowLanePlan best{};
   for (int rows = 1; rows <= 32; ++rows) {
@@ -434,19 +456,24 @@ inline bool PlanRowLane(const Desc& d, int p, int sms, int force_rows, bool half
       }
       pitch16 += best_pad;
     }
-    const int pitch = pitch16 * 16;
+    const int pitch = packed ? ur * 144 : pitch16 * 16;
     const int stage_bytes = rows * pitch * mats;
     int stages = std::min({steps, kRowLaneMaxStages, budget / (warps * stage_bytes)});
+    if (packed) {
+      // one stage holds every step: the whole of the warp's rows
+      if (warps * stage_bytes > budget) continue;
+      stages = 1;
+    }
     if (stages < 1) continue;
     // (a forced geometry may run on a one-stage ring: slower, but the sums keep their order)
-    if (stages < steps && stages < 2 && force_phases == 0) continue;
+    if (!packed && stages < steps && stages < 2 && force_phases == 0) continue;
     // Lane utilization, with a preference for more warps and for a ring that
     // holds the whole range.
     // (all 32 lanes of every warp count: lanes past R * PH idle)
     const double lanes = static_cast<double>(cta_rows) * ur /
                          (static_cast<double>(warps) * 32 * steps);
     const double score = lanes * (0.6 + 0.4 * std::min(1.0, warps / 8.0)) *
-                         (0.7 + 0.3 * static_cast<double>(stages) / steps);
+                         (0.7 + 0.3 * (packed ? 1.0 : static_cast<double>(stages) / steps));
     if (score > best_score) {
       best_score = score;
       best.warps = warps;
@@ -461,6 +488,7 @@ inline bool PlanRowLane(const Desc& d, int p, int sms, int force_rows, bool half
       best.smem_bytes = (p * acts_bytes) + (warps * stages * stage_bytes);
       best.grid = grid;
       best.half = half ? 1 : 0;
+      best.packed = packed ? 1 : 0;
       best.score = score;
       best.f32_input = 0;
       best.q8_row_blocks = 0;
@@ -480,9 +508,16 @@ inline bool PlanRowLane(const Desc& d, int p, int sms, int force_rows, bool half
 template <int P, bool kGlu, bool kHalf>
 cudaError_t LaunchRowLaneOne(const Desc& d, const RowLanePlan& plan, cudaStream_t stream) {
   auto* kernel = VecQRowLaneKernel<P, kGlu, kHalf>;
-  const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             plan.smem_bytes);
-  if (e != cudaSuccess) return e;
+  // Once a device (and host thread): the most any plan asks for.
+  static thread_local int configured_device = -1;
+  int device = -1;
+  cudaGetDevice(&device);
+  if (configured_device != device) {
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (kHalf ? 110 : 220) * 1024);
+    if (e != cudaSuccess) return e;
+    configured_device = device;
+  }
   return LaunchPdl(kernel, dim3(static_cast<unsigned>(plan.grid)),
                    dim3(static_cast<unsigned>(plan.warps * 32)),
                    static_cast<std::size_t>(plan.smem_bytes), stream, d, plan);

@@ -167,3 +167,56 @@ def test_decode_tokens_take_the_vecq_products(cuda, orc, tokens):
         # by d8 * (sum of the int8 codes), the GEMM by the block's stored FP16 sum of the
         # original inputs; they differ by the codes' rounding (measured NMSE 1.9e-4).
         assert ((got - gemm) ** 2).sum() / (gemm ** 2).sum() <= 1e-3
+
+
+def test_routed_expert_block_at_4096_tokens_stage_by_stage(cuda, orc):
+    """The MoE config at its largest size (4096 tokens, 32,768 routed rows): the block's stages
+    run on the device as moe_ffn queues them (experts relaid into slabs at load time) and, for
+    32 sampled tokens (rows are independent), every stage is compared with the oracle on the
+    device's own input to that stage: the gate|up GEMM and the down GEMM to 1e-5 of their
+    scale, GLU + requantization to one code (two exponential implementations), the combine
+    bit for bit."""
+    torch = cuda
+    ops = _ops()
+    rng = np.random.default_rng(4096)
+    tokens, experts, used, hidden, inter = 4096, 128, 8, 2048, 768
+    gate_up = synth.q4_k_weights(rng, experts * 2 * inter, hidden).reshape(experts, 2 * inter, -1)
+    down = synth.q4_k_weights(rng, experts * hidden, inter).reshape(experts, hidden, -1)
+    x = rng.normal(0, 1, size=(tokens, hidden)).astype(np.float32)
+    ids, w = synth.topk_route(rng, tokens, experts, used)
+    gu_d, dn_d = to_dev(torch, gate_up), to_dev(torch, down)
+    slabs = (ops.q4k_relayout(gu_d, hidden, 2 * inter), ops.q4k_relayout(dn_d, inter, hidden))
+    xd, ids_d, w_d = to_dev(torch, x), to_dev(torch, ids), to_dev(torch, w)
+    route = ops.moe_route(ids_d, experts)
+    slots = tokens * used
+    aq = ops.mmq_quantize(xd, ids_src=route["token"], cols=slots)
+    gu = ops.grouped_gemm(None, aq, route["offsets"], hidden, 2 * inter, slab=slabs[0])
+    hq = ops.moe_glu_quantize(gu, inter, ops.GLU_SWIGLU)
+    y = ops.grouped_gemm(None, hq, route["offsets"], inter, hidden, slab=slabs[1])
+    out = ops.moe_combine(y, route["position"], w_d, tokens, used)
+    whole = ops.moe_ffn(xd, ids_d, w_d, gu_d, dn_d, hidden, inter, slabs=slabs)
+    torch.cuda.synchronize()
+    assert ops.device_faults() == 0
+    assert torch.equal(whole, out) and torch.isfinite(out).all()
+    want_route = orc.moe_route(ids, experts)
+    assert np.array_equal(route["position"].cpu().numpy(), want_route["position"])
+    position = want_route["position"]
+    sample = rng.choice(tokens, size=32, replace=False)
+    aq_h, gu_h, hq_h, y_h = (t.cpu().numpy() for t in (aq, gu, hq, y))
+    for t in sample:
+        for j in range(used):
+            r, e = int(position[t * used + j]), int(ids[t, j])
+            col = np.ascontiguousarray(aq_h[:, r:r + 1])
+            want = orc.mmq_q4_k(gate_up[e], col, hidden, 2 * inter)[0]
+            assert np.abs(gu_h[r] - want).max() <= 1e-5 * np.abs(want).max(), (t, j, "gate|up")
+            h = np.array([orc.glu(orc.GLU_SWIGLU, gu_h[r, i], gu_h[r, inter + i])
+                          for i in range(inter)], np.float32)[None, :]
+            want_q = orc.quantize_mmq_q8_1(h)
+            got_q = hq_h[:, r:r + 1]
+            dq = got_q[:, :, 16:].view(np.int8).astype(int) - want_q[:, :, 16:].view(np.int8).astype(int)
+            assert np.abs(dq).max() <= 1, (t, j, "requantized codes")
+            want = orc.mmq_q4_k(down[e], np.ascontiguousarray(got_q), inter, hidden)[0]
+            assert np.abs(y_h[r] - want).max() <= 1e-5 * np.abs(want).max(), (t, j, "down")
+    rows = np.concatenate([position[t * used:(t + 1) * used] for t in sample])
+    want = orc.moe_combine(y_h[rows], np.arange(rows.size, dtype=np.int32), w[sample], 32, used)
+    assert np.array_equal(out.cpu().numpy()[sample], want)
