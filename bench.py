@@ -1,25 +1,32 @@
 #!/usr/bin/env python
 """Benchmark of the decode hot path: Q4_K GEMV over Q8_1 activations.
 
-Workload (N=1): the FFN products of one Gemma-3-4B-shaped decode step, all 34
-layers, Q4_K weights: per layer  x[b,2560] -> Q8_1 -> fused gate/up GeGLU
-product (two 10240x2560 matrices) -> Q8_1 -> down product (2560x10240).
-Each layer has its own weight copy (34 x 44.2 MB = 1.5 GB, far beyond the
-126 MB L2), so every launch streams its weights from HBM, the rotation the
-reference's own benchmark uses (benchmarks/vecq_bench.cc:119-121).
+Workload: the FFN products of one Gemma-3-4B-shaped decode step, all 34 layers,
+Q4_K weights: per layer  x[b,2560] -> Q8_1 -> fused gate/up GeGLU product (two
+10240x2560 matrices) -> Q8_1 -> down product (2560x10240).  Each layer has its
+own weight copy (34 x 44.2 MB = 1.5 GB, far beyond the 126 MB L2), so every
+launch streams its weights from HBM, the rotation the reference's own benchmark
+uses (benchmarks/vecq_bench.cc:119-121).
 
 One step = that whole pass for one batch.  `value` = algorithmic bytes of the
-step / device time (GB/s), inputs resident in HBM, the step replayed as one
-CUDA graph.  `e2e` = the same step driven through the C ABI from HOST buffers:
-pinned x copied in, y copied back, inside the timed region.
+step / device time (GB/s), inputs resident in HBM, the step replayed as one CUDA
+graph; the timed block of K steps is repeated and the median reported.  `e2e` =
+the same step driven through the C ABI from HOST buffers: pinned x copied in, y
+copied back, inside the timed region.  `roofline` = the fused gate/up launch
+alone; `roofline.others` = the down product and the Q8_0 4096 x 4096 product.
 
-N>1 (torchrun): N-column sharding.  Each rank owns 1/N of every matrix's
-output rows; the GLU output and the layer output are all-gathered with NCCL.
-Total work is fixed ("strong" scaling).
+N > 1 (torchrun): every rank runs the whole step on its own batch (replicas of
+the data-parallel decode path, no collective in the step: `value`, weak
+scaling), and then, in the same run, the sharded forms the path has, each with
+its own timing and a parity flag against the unsharded result (`sharded`):
+the prefill GEMM N-column sharded with its all-gather pipelined behind the
+next chunk's product, the expert-parallel MoE block with all-to-alls of fixed
+size, and the decode step N-column sharded.
 
 --impl reference: the CPU arm.  GGML's CPU vec_dot is not part of the
 reference build, so the arm times the oracle's restatement of the same
-products on the host cores (kind "port").
+products on the host cores (kind "port"); a step of the arm is a bounded
+sample of the 34-layer pass (4 layers, scaled: every layer is the same work).
 """
 from __future__ import annotations
 
@@ -39,8 +46,8 @@ if ROOT not in sys.path:
 LAYERS = 34
 HIDDEN, INTER = 2560, 10240
 SB = 144  # Q4_K super-block bytes
-# dram__bytes_read.sum + dram__bytes_write.sum of one fused gate/up launch at batch 1
-# (profiles/vecq_rowlane_glu_b1.md): the matrices' 29,491,200 bytes plus activations.
+# dram__bytes_read.sum + dram__bytes_write.sum of one fused gate/up launch at batch 1, from an
+# ncu capture of this kernel: the matrices' 29,491,200 bytes plus activations.
 NCU_GLU_DRAM_BYTES_B1 = 29532928
 METRIC = "q4k_decode_gemv_hbm_throughput"
 UNIT = "GB/s"
@@ -51,6 +58,18 @@ def step_bytes(batch: int, layers: int | None = None) -> int:
     glu = 2 * INTER * (HIDDEN // 256) * SB + batch * (HIDDEN // 32 * 36) + batch * INTER * 4
     down = HIDDEN * (INTER // 256) * SB + batch * (INTER // 32 * 36) + batch * HIDDEN * 4
     return (LAYERS if layers is None else layers) * (glu + down)
+
+
+def down_launch_bytes(batch: int) -> int:
+    return HIDDEN * (INTER // 256) * SB + batch * (INTER // 32 * 36) + batch * HIDDEN * 4
+
+
+def workload_config(batch: int) -> dict:
+    """What both arms run, key for key."""
+    return {"workload": f"Gemma-3-4B FFN decode products, Q4_K, {LAYERS} layers, batch {batch}",
+            "batch": batch, "layers": LAYERS, "gate_up": [INTER, HIDDEN], "down": [HIDDEN, INTER],
+            "l2": "inputs larger than the last-level cache: distinct layer copies streamed in order",
+            "step_bytes": step_bytes(batch)}
 
 
 def glu_launch_bytes(batch: int, shard: int = 1) -> int:
@@ -129,10 +148,12 @@ def run_reference(args, rank: int):
         "impl": "reference", "metric": METRIC, "value": round(value, 3), "unit": UNIT,
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(1e3 * statistics.mean(per_step), 3), "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "int8 dp4a -> int32 per block, f32 sums",
-        "data": "synthetic",
-        "config": {"workload": f"Gemma-3-4B FFN decode products, Q4_K, {LAYERS} layers, batch {batch}",
-                   "batch": batch, "timing": "host wall clock; weights beyond the CPU cache"},
+        "scaling": "weak", "vs_baseline": None, "dtype": "int8 dp4a -> int32 per block, f32 sums",
+        "data": "synthetic", "config": workload_config(batch),
+        "arm": {"timing": "host wall clock; a step is a bounded sample: "
+                          f"{sample_layers} of the {LAYERS} layer passes, scaled to {LAYERS} "
+                          "(every layer is the same work); 8 distinct layer copies, beyond the "
+                          "host's last-level cache"},
         "cpu_baseline": {"value": round(value, 3), "unit": UNIT, "cores": threads, "kind": "port",
                          "sample": text},
         "e2e": {"value": round(value, 3), "unit": UNIT, "h2d_bytes_per_step": 0,
@@ -227,9 +248,12 @@ class FfnStep:
         self.h_rows = torch.empty((batch, INTER), device="cuda")
         self.y_shard = torch.empty((batch, self.n_down), device="cuda")
         self.y_full = torch.empty((LAYERS, world, batch, self.n_down), device="cuda")
-        self.launches_per_layer = (2 if (world == 1 and fused) else 3 if self.q8_out
-                                   else 4 + (1 if world > 1 else 0))
+        self.launches_per_layer = self.launches_per_layer_of(world, fused, self.q8_out)
         self.launches_per_step = LAYERS * self.launches_per_layer
+
+    @staticmethod
+    def launches_per_layer_of(world: int, fused: bool, q8_out: bool) -> int:
+        return 2 if (world == 1 and fused) else 3 if q8_out else 4 + (1 if world > 1 else 0)
 
     def layer(self, l: int, x):
         ops, T = self.ops, self.ops.TYPE_Q4_K
@@ -267,6 +291,12 @@ class FfnStep:
         for l in range(LAYERS):
             self.layer(l, x_all[l])
 
+    def down_only(self):
+        """The down product alone, one launch per layer copy."""
+        ops, T = self.ops, self.ops.TYPE_Q4_K
+        for _, _, down in self.layers:
+            ops.vecq(down, T, INTER, self.n_down, self.q8h, self.batch, out=self.y_shard)
+
     def glu_only(self):
         """The dominant kernel alone, one launch per layer copy."""
         ops, T = self.ops, self.ops.TYPE_Q4_K
@@ -285,6 +315,39 @@ class FfnStep:
                          glu=ops.GLU_GEGLU, out=self.h_shard)
 
 
+def _median_ms(run, stream, steps, repeats, barrier, torch):
+    """The block of `steps` runs, timed `repeats` times with CUDA events on the launching
+    stream between barriers; the median per-step time."""
+    times = []
+    for _ in range(repeats):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record(stream)
+        for _ in range(steps):
+            run()
+        e1.record(stream)
+        barrier()
+        times.append(e0.elapsed_time(e1) / steps)
+    return statistics.median(times)
+
+
+def _graphed(torch, fn, stream, enabled, **kw):
+    """fn captured once as a CUDA graph (None when capture is off or refused)."""
+    if not enabled:
+        return None
+    try:
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream, **kw):
+            fn()
+        return graph
+    except Exception as e:  # capture refused: time plain launches
+        print(f"bench.py: graph capture unavailable ({e}); timing plain launches", file=sys.stderr)
+        torch.cuda.synchronize()
+        return None
+
+
 def run_gpu(args, rank: int, world: int, local_rank: int):
     import torch
 
@@ -300,15 +363,15 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
         raise SystemExit("bench.py: no B200 / native library: " + ops._native.last_error())
 
     batch = args.batch
-    # N > 1: by default every rank runs the whole step on its own batch (replicas of
-    # the data-parallel decode path: no collective, weak scaling).  --shard columns
-    # splits every matrix's rows over the ranks and all-gathers the outputs (strong
-    # scaling; at decode sizes the all-gathers' latency dominates).
+    # N > 1: every rank runs the whole step on its own batch (replicas of the data-parallel
+    # decode path: no collective, weak scaling); the sharded forms are timed after it.
+    # --shard columns makes the N-column form the headline instead (strong scaling).
     sharded = world > 1 and args.shard == "columns"
     parts = world if sharded else 1
     st = FfnStep(torch, ops, batch, parts, rank, dist, fused=args.fused, q8_out=args.q8_out)
     stream = torch.cuda.Stream()
     sync = torch.cuda.synchronize
+    repeats = max(1, args.repeats)
 
     def barrier():
         if world > 1:
@@ -318,20 +381,11 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
     with torch.cuda.stream(stream):
         st.step()       # warm: module load, attributes
         sync()
-        graph = None
         # Graph replay only for steps without NCCL collectives (one GPU, replicas): a
         # sharded step is queued as plain stream launches.
         graph_kw = {"capture_error_mode": "thread_local"} if world > 1 else {}
-        if parts == 1 and not args.no_graph:
-            try:
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph, stream=stream, **graph_kw):
-                    st.step()
-            except Exception as e:  # capture refused: time plain launches
-                print(f"bench.py: graph capture unavailable ({e}); timing plain launches",
-                      file=sys.stderr)
-                graph = None
-                sync()
+        use_graph = parts == 1 and not args.no_graph
+        graph = _graphed(torch, st.step, stream, use_graph, **graph_kw)
         run = graph.replay if graph is not None else st.step
         for _ in range(max(args.warmup, 3)):
             run()
@@ -339,39 +393,18 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
         sampler = ClockSampler(local_rank)
         if rank == 0:
             sampler.start()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        e0.record(stream)
-        for _ in range(args.steps):
-            run()
-        e1.record(stream)
-        barrier()
-        ms = e0.elapsed_time(e1) / args.steps
-        # ---- the dominant kernel alone (roofline): one launch per layer copy, replayed
-        # as a CUDA graph so the host's launch rate is not what is timed; CUDA events
-        # on the launching stream around the replays
-        st.glu_only()
-        sync()
-        glu_graph = None
-        if parts == 1 and not args.no_graph:
-            try:
-                glu_graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(glu_graph, stream=stream, **graph_kw):
-                    st.glu_only()
-            except Exception:
-                glu_graph = None
-                sync()
+        ms = _median_ms(run, stream, args.steps, repeats, barrier, torch)
+        # ---- the dominant kernel alone (roofline): one launch per layer copy, replayed as a
+        # CUDA graph so the host's launch rate is not what is timed; CUDA events on the
+        # launching stream around the replays.  The down product likewise.
+        glu_graph = _graphed(torch, st.glu_only, stream, use_graph, **graph_kw)
         run_glu = glu_graph.replay if glu_graph is not None else st.glu_only
         run_glu()
-        sync()
-        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        reps = 10
-        k0.record(stream)
-        for _ in range(reps):
-            run_glu()
-        k1.record(stream)
-        sync()
-        glu_us = 1e3 * k0.elapsed_time(k1) / (reps * LAYERS)
+        glu_us = 1e3 * _median_ms(run_glu, stream, 5, repeats, sync, torch) / LAYERS
+        down_graph = _graphed(torch, st.down_only, stream, use_graph, **graph_kw)
+        run_down = down_graph.replay if down_graph is not None else st.down_only
+        run_down()
+        down_us = 1e3 * _median_ms(run_down, stream, 5, repeats, sync, torch) / LAYERS
         # ---- end to end through the C ABI from host buffers
         hx = torch.randn((LAYERS, batch, HIDDEN)).pin_memory()
         hy = torch.empty((LAYERS, parts, batch, st.n_down)).pin_memory()
@@ -386,18 +419,7 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
         # The step as a caller would queue it: pinned-host input copy, the C-ABI
         # launches, pinned-host output copy, all captured once and replayed (the
         # reference replays captured steps too, src/engine/step_runs.cc:323).
-        e2e_graph = None
-        if parts == 1 and not args.no_graph:
-            try:
-                e2e_body()
-                sync()
-                e2e_graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(e2e_graph, stream=stream, **graph_kw):
-                    e2e_body()
-            except Exception as e:
-                print(f"bench.py: e2e graph capture unavailable ({e})", file=sys.stderr)
-                e2e_graph = None
-                sync()
+        e2e_graph = _graphed(torch, e2e_body, stream, use_graph, **graph_kw)
 
         def e2e_step():
             if e2e_graph is not None:
@@ -408,18 +430,35 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
 
         for _ in range(3):
             e2e_step()
-        barrier()
-        t0 = time.perf_counter()
-        for _ in range(args.steps):
-            e2e_step()
-        barrier()
-        e2e_ms = 1e3 * (time.perf_counter() - t0) / args.steps
+        e2e_times = []
+        for _ in range(repeats):
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(args.steps):
+                e2e_step()
+            barrier()
+            e2e_times.append(1e3 * (time.perf_counter() - t0) / args.steps)
+        e2e_ms = statistics.median(e2e_times)
         clocks = sampler.stop() if rank == 0 else None
+        # ---- the Q8_0 4096 x 4096 product (the reference's CPU-runnable config), one GPU
+        q80 = _q8_0_roofline(torch, ops, stream, use_graph, repeats) if world == 1 else None
 
     if world > 1:
-        t = torch.tensor([ms, e2e_ms, glu_us], device="cuda", dtype=torch.float64)
+        t = torch.tensor([ms, e2e_ms, glu_us, down_us], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms, glu_us = (float(v) for v in t.tolist())
+        ms, e2e_ms, glu_us, down_us = (float(v) for v in t.tolist())
+    launches = st.launches_per_step * (args.steps * repeats + max(args.warmup, 3) + 1) * world
+    del graph, glu_graph, down_graph, e2e_graph
+    st = None
+    torch.cuda.empty_cache()
+    # ---- the sharded forms, in the same run, each with its parity flag
+    sharded_lines = None
+    if world > 1 and args.shard != "columns" and not args.no_sharded:
+        sharded_lines = {
+            "mmq_q4k": bench_mmq_sharded(torch, dist, ops, rank, world, tokens=4096, steps=10, warmup=3),
+            "moe_ep": bench_moe_ep(torch, dist, ops, rank, world, tokens=1024, steps=10, warmup=3),
+            "ffn_columns": bench_ffn_columns(torch, dist, ops, rank, world, batch, steps=5, warmup=2),
+        }
     if rank == 0:
         replicas = world if not sharded else 1
         sb = step_bytes(batch) * replicas      # what all ranks streamed in a step
@@ -430,47 +469,59 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
         except OSError:
             pass
         peak = float(peaks.get("hbm_gbs", 6650.0))
+        source = "measured (MEASURED_PEAKS.json hbm_gbs)" if peaks else "fallback 6650"
         glu_b = glu_launch_bytes(batch, parts)
         achieved = glu_b / (glu_us * 1e-6) / 1e9
+        down_b = down_launch_bytes(batch) if parts == 1 else None
+        others = []
+        if down_b is not None:
+            rate = down_b / (down_us * 1e-6) / 1e9
+            others.append({"kernel": "down product 2560 x 10240, Q4_K", "bound": "hbm",
+                           "achieved": round(rate, 1), "peak": peak, "unit": "GB/s",
+                           "frac": round(rate / peak, 4), "us_per_launch": round(down_us, 3),
+                           "bytes_per_launch": down_b})
+        if q80 is not None:
+            q80.update({"peak": peak, "frac": round(q80["achieved"] / peak, 4)})
+            others.append(q80)
+        config = workload_config(batch)
+        config["step_bytes"] = sb
         line = {
             "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 5),
-            "higher_is_better": True, "scaling": "strong" if sharded or world == 1 else "weak",
+            "higher_is_better": True, "scaling": "strong" if sharded else "weak",
             "vs_baseline": None,
             "dtype": "int8 dp4a -> int32 per block, f32 sums", "data": "synthetic",
-            "config": {
-                "workload": f"Gemma-3-4B FFN decode products, Q4_K, {LAYERS} layers, batch {batch}",
-                "batch": batch, "layers": LAYERS, "gate_up": [INTER, HIDDEN],
-                "down": [HIDDEN, INTER],
-                "l2": f"inputs larger than L2: {LAYERS} distinct layer copies, "
-                      f"{LAYERS * 44.2e-3:.2f} GB, streamed in order",
-                "launch": "cuda graph replay" if graph is not None else "stream launches",
-                "launches_per_layer": st.launches_per_layer,
+            "config": config,
+            "arm": {
+                "launch": "cuda graph replay" if use_graph else "stream launches",
+                "timing": f"median of {repeats} blocks of {args.steps} steps, CUDA events on the "
+                          "launching stream, max over ranks",
+                "launches_per_layer": FfnStep.launches_per_layer_of(world, args.fused, args.q8_out),
                 "parallelism": "single GPU" if world == 1 else
                                (f"N-column shards x{world}, NCCL all-gather of the GLU output and of "
                                 "the layer output" if sharded else
                                 f"{world} replicas, one batch a GPU, no collective in the step"),
-                "step_bytes": sb,
             },
             "e2e": {"value": round(sb / (e2e_ms * 1e-3) / 1e9, 2), "unit": UNIT,
                     "ms_per_step": round(e2e_ms, 4),
                     "how": "host wall clock around pinned H2D of x, the step's C-ABI launches and "
                            "pinned D2H of y, with a stream synchronize per step"
-                           + (" (captured once, replayed)" if e2e_graph is not None else ""),
+                           + (" (captured once, replayed)" if use_graph else ""),
                     "h2d_bytes_per_step": LAYERS * batch * HIDDEN * 4 * replicas,
                     "d2h_bytes_per_step": LAYERS * batch * HIDDEN * 4 * replicas},
-            "gpu_launches": st.launches_per_step * args.steps * world,
-            "roofline": {"bound": "hbm", "kernel": "VecQRowLaneKernel<P, GLU> (fused gate/up, Q4_K)",
+            "gpu_launches": launches,
+            "roofline": {"bound": "hbm", "kernel": "fused gate/up GeGLU product 2 x (10240 x 2560), Q4_K",
                          "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                         "frac": round(achieved / peak, 4),
-                         "peak_source": "measured (MEASURED_PEAKS.json hbm_gbs)" if peaks
-                         else "fallback 6650",
+                         "frac": round(achieved / peak, 4), "peak_source": source,
                          "us_per_launch": round(glu_us, 3), "bytes_per_launch": glu_b,
                          "frac_of_8tbs_spec": round(achieved / 8000.0, 4),
                          "traffic": args.traffic if args.traffic is not None else
-                         (NCU_GLU_DRAM_BYTES_B1 if batch == 1 and world == 1 else None)},
+                         (NCU_GLU_DRAM_BYTES_B1 if batch == 1 and world == 1 else None),
+                         "others": others},
             "clocks": clocks,
         }
+        if sharded_lines is not None:
+            line["sharded"] = sharded_lines
         if world == 1 and not args.no_cpu:
             _cpu_step(batch, 4)  # warm: builds the host weights
             gbs, per_layer, threads, text = _cpu_step(batch, 24)
@@ -481,6 +532,32 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def _q8_0_roofline(torch, ops, stream, use_graph, repeats):
+    """BASELINE configs[0]: Q8_0 4096 x 4096, batch 1; 16 weight copies (285 MB) walked in
+    order inside one captured graph."""
+    import numpy as np
+
+    from llmp_b200 import synth
+    n = k = 4096
+    rng = np.random.default_rng(0)
+    ws = [torch.from_numpy(synth.q8_0_weights(rng, n, k)).cuda() for _ in range(16)]
+    q8 = ops.quantize_q8(torch.randn((1, k), device="cuda"))
+    out = torch.empty((1, n), device="cuda")
+
+    def body():
+        for w in ws:
+            ops.vecq(w, ops.TYPE_Q8_0, k, n, q8, 1, out=out)
+
+    graph = _graphed(torch, body, stream, use_graph)
+    run = graph.replay if graph is not None else body
+    run()
+    us = 1e3 * _median_ms(run, stream, 5, repeats, torch.cuda.synchronize, torch) / len(ws)
+    nbytes = 17_825_792 + 4_608 + 16_384
+    return {"kernel": "Q8_0 product 4096 x 4096", "bound": "hbm",
+            "achieved": round(nbytes / (us * 1e-6) / 1e9, 1), "unit": "GB/s",
+            "us_per_launch": round(us, 3), "bytes_per_launch": nbytes}
 
 
 # --------------------------------------------------------------------------- other configs
@@ -496,7 +573,7 @@ def run_other(args):
         raise SystemExit("bench.py: no B200 / native library: " + ops._native.last_error())
     gen = torch.Generator(device="cuda")
     gen.manual_seed(0)
-    peaks = {"mxf8f6f4": 4466.5, "i8": 4567.3}  # profiles/tcgen05_microbenchmarks.md
+    peaks = {"mxf8f6f4": 4466.5, "i8": 4567.3}  # measured with the bare tcgen05.mma loop (make probe)
 
     def timed(fns, steps, warmup):
         for i in range(max(warmup, 3)):
@@ -528,8 +605,7 @@ def run_other(args):
                 "roofline": {"bound": "tensor", "achieved": round(rate, 1),
                              "peak": peaks["mxf8f6f4"], "unit": "TFLOP/s",
                              "frac": round(rate / peaks["mxf8f6f4"], 4),
-                             "peak_source": "bare tcgen05.mma loop on this pool "
-                                            "(profiles/tcgen05_microbenchmarks.md)"}}
+                             "peak_source": "bare tcgen05.mma loop measured on this pool"}}
     elif args.workload == "q8_0_gemv":
         # BASELINE configs[0]: Q8_0 4096 x 4096, batch 1 (the reference's CPU-runnable case);
         # 16 weight copies (285 MB) walked in order inside one captured graph.
@@ -576,16 +652,24 @@ def run_other(args):
         yq = ops.mmq_quantize(x)
         sets = [(make_q4k_device(torch, n, k, gen), torch.empty((m, n), device="cuda"))
                 for _ in range(2)]
-        fns = [lambda t=t: ops.mmq(t[0], yq, k, n, out=t[1]) for t in sets]
-        ms = timed(fns, args.steps, args.warmup)
+        slabs = [ops.q4k_relayout(t[0], k, n) for t in sets]     # load time: outside the timing
+        scratch = ops.mmq_scratch(k, n)
+        # the weights relaid at load time (the headline), relaid by every call, unpacked in the kernel
+        ms = timed([lambda t=t, sl=sl: ops.mmq(None, yq, k, n, out=t[1], slab=sl)
+                    for t, sl in zip(sets, slabs)], args.steps, args.warmup)
+        ms_call = timed([lambda t=t: ops.mmq(t[0], yq, k, n, out=t[1], scratch=scratch) for t in sets],
+                        args.steps, args.warmup)
+        ms_raw = timed([lambda t=t: ops.mmq(t[0], yq, k, n, out=t[1]) for t in sets],
+                       args.steps, args.warmup)
         rate = 2.0 * m * n * k / (ms * 1e-3) / 1e12
         line = {"metric": "mmq_q4k_int8_gemm_throughput", "value": round(rate, 1), "unit": "TOP/s",
                 "ms_per_step": round(ms, 5),
-                "config": {"workload": f"Q4_K x Q8_1-MMQ int8 GEMM M {m} K {k} N {n}"},
+                "ms_relayout_every_call": round(ms_call, 5), "ms_raw_blocks": round(ms_raw, 5),
+                "config": {"workload": f"Q4_K x Q8_1-MMQ int8 GEMM M {m} K {k} N {n}",
+                           "weights": "slab relaid at load time (llmp_b200_q4k_relayout)"},
                 "roofline": {"bound": "tensor", "achieved": round(rate, 1), "peak": peaks["i8"],
                              "unit": "TOP/s", "frac": round(rate / peaks["i8"], 4),
-                             "peak_source": "bare tcgen05.mma loop on this pool "
-                                            "(profiles/tcgen05_microbenchmarks.md)"}}
+                             "peak_source": "bare tcgen05.mma loop measured on this pool"}}
     else:  # moe
         import numpy as np
 
@@ -597,7 +681,9 @@ def run_other(args):
         ids, w = synth.topk_route(np.random.default_rng(0), tokens, experts, used)
         ids_d, w_d = torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda()
         x = torch.randn((tokens, hidden), device="cuda", generator=gen)
-        fns = [lambda: ops.moe_ffn(x, ids_d, w_d, gate_up, down, hidden, inter)]
+        slabs = (ops.q4k_relayout(gate_up, hidden, 2 * inter), ops.q4k_relayout(down, inter, hidden)) \
+            if tokens > ops.ops.DECODE_TOKENS else None         # load time: outside the timing
+        fns = [lambda: ops.moe_ffn(x, ids_d, w_d, gate_up, down, hidden, inter, slabs=slabs)]
         if not args.no_graph:
             # The block queues 7 to 40 small launches: replay them as one captured graph so
             # that the host's launch rate is not what is timed.
@@ -635,132 +721,286 @@ def run_other(args):
     print(json.dumps(line), flush=True)
 
 
-def run_mmq_sharded(args, rank: int, world: int, local_rank: int):
-    """The prefill GEMM N-column sharded (BASELINE configs[2]): every rank holds the weight
-    rows [rank * n / world, +n / world) and the whole activation batch, computes its slice
-    D[:, slice] and the slices are all-gathered over NVLink (NCCL) into [world, m, n / world]
-    on every rank.  Strong scaling: the product is the same at every N."""
-    import torch
-    import torch.distributed as dist
+def _max_over_ranks(torch, dist, value: float) -> float:
+    t = torch.tensor([value], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
 
-    torch.cuda.set_device(local_rank)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    import llmp_b200 as ops
+
+def _all_true(torch, dist, flag: bool) -> bool:
+    t = torch.tensor([1.0 if flag else 0.0], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    return bool(t.item() > 0.5)
+
+
+def bench_mmq_sharded(torch, dist, ops, rank, world, tokens=4096, steps=10, warmup=3, chunks=4):
+    """The prefill GEMM N-column sharded (BASELINE configs[2]).  Every rank holds the weight
+    rows [rank * n / world, +n / world) (relaid into its slab at load time) and the whole
+    activation batch, which it quantizes itself; the product runs in `chunks` token chunks,
+    and each chunk's F32 slice is all-gathered over NVLink (NCCL) while the next chunk's
+    product runs.  The gathered layout is [chunk][rank][tokens / chunks][n / world].  Strong
+    scaling: the product is the same at every N.  Parity: rank 0 also holds the whole matrix
+    and computes the unsharded product once, outside the timed region; the gathered result
+    must equal it bit for bit."""
     from llmp_b200 import shard
-    m, n, k = args.tokens or 4096, 14336, 4096
+    m, n, k = tokens, 14336, 4096
     lo, hi = shard.row_shard(n, world, rank, multiple=128)
-    width = shard.row_shard(n, world, 0, multiple=128)
-    width = width[1] - width[0]                      # the widest slice; others pad to it
+    width = hi - lo
+    if n % (world * 128) != 0 or m % chunks != 0:
+        return {"unavailable": "column shards of unequal width are not benchmarked"}
     gen = torch.Generator(device="cuda")
-    gen.manual_seed(7)                               # the same activations on every rank
+    gen.manual_seed(7)                               # the same operands on every rank
     x = torch.randn((m, k), device="cuda", generator=gen).bfloat16()
-    gen.manual_seed(100 + rank)
-    if hi - lo != width:
-        raise SystemExit("bench.py: N-column shards of unequal width are not benchmarked")
-    sets = [(make_q4k_device(torch, width, k, gen), torch.empty((m, width), device="cuda"),
-             torch.empty((world, m, width), device="cuda")) for _ in range(2)]
+    w_full = make_q4k_device(torch, n, k, gen)
+    w_mine = w_full[lo:hi].contiguous()
+    slab = ops.q4k_relayout(w_mine, k, width)
+    mc = m // chunks
+    mine = [torch.empty((mc, width), device="cuda") for _ in range(chunks)]
+    full = torch.empty((chunks, world, mc, width), device="cuda")
+    if rank != 0:
+        w_full = None
 
-    def step(i):
-        w, mine, full = sets[i % 2]
+    def step():
         yq = ops.mmq_quantize(x)
-        ops.mmq(w, yq, k, width, out=mine)
-        dist.all_gather_into_tensor(full, mine)
+        works = []
+        for c in range(chunks):
+            ops.mmq(None, yq[:, c * mc:(c + 1) * mc], k, width, out=mine[c], slab=slab)
+            works.append(dist.all_gather_into_tensor(full[c], mine[c], async_op=True))
+        for w in works:
+            w.wait()
         return full
 
-    for i in range(max(args.warmup, 3)):
-        step(i)
+    def one_gpu():
+        yq = ops.mmq_quantize(x)
+        return ops.mmq(w_mine, yq, k, width, slab=slab)
+
+    for _ in range(warmup):
+        step()
     dist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(args.steps):
-        out = step(i)
+    for _ in range(steps):
+        out = step()
     e1.record()
     dist.barrier()
     torch.cuda.synchronize()
-    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device="cuda", dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ok = torch.tensor([float(torch.isfinite(out).all())], device="cuda")
-    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    ms = _max_over_ranks(torch, dist, e0.elapsed_time(e1) / steps)
+    # the shard's own product alone (no exchange), for the exchange's share of the step
+    one_gpu()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        one_gpu()
+    e1.record()
+    torch.cuda.synchronize()
+    compute_ms = _max_over_ranks(torch, dist, e0.elapsed_time(e1) / steps)
+    parity = True
     if rank == 0:
-        ms = float(t.item())
-        rate = 2.0 * m * n * k / (ms * 1e-3) / 1e12
-        print(json.dumps({
-            "metric": "mmq_q4k_int8_gemm_throughput", "value": round(rate, 1), "unit": "TOP/s",
-            "ms_per_step": round(ms, 5), "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "higher_is_better": True, "scaling": "strong",
-            "data": "synthetic", "vs_baseline": None, "finite": bool(ok.item()),
+        want = ops.mmq(w_full, ops.mmq_quantize(x), k, n, scratch=ops.mmq_scratch(k, n))  # [m, n]
+        got = out.permute(0, 2, 1, 3).reshape(m, n)      # [chunk][rank][mc][width] -> [m][n]
+        parity = bool(torch.equal(got, want))
+    parity = _all_true(torch, dist, parity)
+    rate = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+    return {"metric": "mmq_q4k_int8_gemm_throughput", "value": round(rate, 1), "unit": "TOP/s",
+            "ms_per_step": round(ms, 5), "shard_product_ms": round(compute_ms, 5), "n_gpus": world,
+            "steps": steps, "warmup": warmup, "scaling": "strong", "parity": parity,
             "faults": ops.device_faults(),
             "config": {"workload": f"Q4_K x Q8_1-MMQ int8 GEMM M {m} K {k} N {n}",
                        "parallelism": f"N-column shards x{world} (slices of {width} columns), "
-                                      "activation quantizer on every rank, NCCL all-gather of "
-                                      f"the F32 output ({m * n * 4 / 1e6:.0f} MB)"},
+                                      f"activation quantizer on every rank, NCCL all-gather of the "
+                                      f"F32 output ({m * n * 4 / 1e6:.0f} MB) in {chunks} token chunks "
+                                      "behind the next chunk's product"},
             "roofline": {"bound": "tensor", "achieved": round(rate, 1), "peak": 4567.3 * world,
                          "unit": "TOP/s", "frac": round(rate / (4567.3 * world), 4),
-                         "peak_source": "bare tcgen05.mma loop on this pool "
-                                        "(profiles/tcgen05_microbenchmarks.md) x N"}}), flush=True)
-    dist.destroy_process_group()
+                         "peak_source": "bare tcgen05.mma kind::i8 loop measured on this pool x N"}}
 
 
-def run_moe_ep(args, rank: int, world: int, local_rank: int):
-    """Expert-parallel MoE block: each rank owns 128 / world whole experts and `--tokens` tokens
-    (weak scaling); rows travel to their experts' owners and back with NCCL all-to-all
-    (llmp_b200/shard.py) and are combined on the home rank in slot order."""
+def bench_moe_ep(torch, dist, ops, rank, world, tokens=1024, steps=10, warmup=3):
+    """Expert-parallel MoE block (BASELINE configs[4]): each rank owns 128 / world whole experts
+    (relaid into slabs at load time) and `tokens` tokens (weak scaling); rows travel to their
+    experts' owners and back in NCCL all-to-alls of fixed size (llmp_b200.moe_ep_pack packs
+    lanes of a set capacity, so no split size reaches the host) and are combined on the home
+    rank in slot order by llmp_b200.moe_combine.  Parity: rank 0 also holds every expert and
+    computes its own tokens' block on one GPU; the two results must be equal bit for bit."""
     import numpy as np
+
+    from llmp_b200 import shard, synth
+    experts, used, hidden, inter = 128, 8, 2048, 768
+    if experts % world != 0:
+        return {"unavailable": "experts must divide over the ranks"}
+    per = experts // world
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(100)                              # the same experts on every rank
+    gate_up_all = make_q4k_device(torch, experts * 2 * inter, hidden, gen).view(experts, 2 * inter, -1)
+    down_all = make_q4k_device(torch, experts * hidden, inter, gen).view(experts, hidden, -1)
+    b = rank * per
+    gate_up = gate_up_all[b:b + per].contiguous()
+    down = down_all[b:b + per].contiguous()
+    slabs = (ops.q4k_relayout(gate_up, hidden, 2 * inter), ops.q4k_relayout(down, inter, hidden))
+    if rank != 0:
+        gate_up_all = down_all = None
+        torch.cuda.empty_cache()
+    ids, w = synth.topk_route(np.random.default_rng(rank), tokens, experts, used)
+    ids_d, w_d = torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda()
+    gen.manual_seed(200 + rank)
+    x = torch.randn((tokens, hidden), device="cuda", generator=gen)
+    capacity = shard.ep_capacity(tokens, used, world)
+    dropped = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ones = torch.ones((world * capacity, 1), device="cuda")
+
+    def pack(xt, idt):
+        return ops.moe_ep_pack(xt, idt, experts, world, capacity, dropped)
+
+    def local(rows, local_ids):
+        return ops.moe_ffn(rows, local_ids.view(-1, 1), ones, gate_up, down, hidden, inter,
+                           decode_tokens=0, slabs=slabs)
+
+    def combine(back, home, wt):
+        return ops.moe_combine(back, home, wt, tokens, used)
+
+    def step():
+        return shard.ep_moe_ffn_padded(x, ids_d, w_d, experts, capacity, pack, local, combine)
+
+    def one_gpu():   # the same rows through this rank's experts only: the compute of a step
+        return local(torch.zeros((world * capacity, hidden), device="cuda"),
+                     torch.arange(world * capacity, dtype=torch.int32, device="cuda") % per)
+
+    for _ in range(warmup):
+        out = step()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        out = step()
+    e1.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    ms = _max_over_ranks(torch, dist, e0.elapsed_time(e1) / steps)
+    one_gpu()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        one_gpu()
+    e1.record()
+    torch.cuda.synchronize()
+    compute_ms = _max_over_ranks(torch, dist, e0.elapsed_time(e1) / steps)
+    lost = int(dropped.item())
+    parity = lost == 0
+    if rank == 0:
+        want = ops.moe_ffn(x, ids_d, w_d, gate_up_all, down_all, hidden, inter, decode_tokens=0)
+        parity = parity and bool(torch.equal(out, want))
+    parity = _all_true(torch, dist, parity)
+    ops_count = 3 * 2.0 * hidden * inter * tokens * used * world
+    return {"metric": "moe_grouped_gemm_throughput", "unit": "TOP/s",
+            "value": round(ops_count / (ms * 1e-3) / 1e12, 1), "ms_per_step": round(ms, 4),
+            "local_block_ms": round(compute_ms, 4), "n_gpus": world, "steps": steps,
+            "warmup": warmup, "scaling": "weak", "parity": parity, "rows_dropped": lost,
+            "faults": ops.device_faults(),
+            "config": {"workload": f"MoE block, 128 experts top-8, hidden 2048, intermediate 768, "
+                                   f"Q4_K, {tokens} tokens a rank",
+                       "parallelism": f"expert parallel x{world}: {per} experts a rank, NCCL "
+                                      f"all-to-all dispatch and combine in lanes of {capacity} rows "
+                                      "a destination, tokens data-parallel"}}
+
+
+def bench_ffn_columns(torch, dist, ops, rank, world, batch, steps=5, warmup=2):
+    """The decode step N-column sharded: every rank owns 1 / world of every matrix's output
+    rows; the GLU output and the layer output are all-gathered (NCCL) inside the step.  Strong
+    scaling.  Parity: rank 0 also holds whole matrices for two of the layers and computes
+    them unsharded; the gathered outputs must equal them bit for bit."""
+    if INTER % (world * 16) != 0 or HIDDEN % (world * 16) != 0:
+        return {"unavailable": "rows do not divide over the ranks"}
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(4321)                             # the same matrices on every rank
+    n_glu, n_down = INTER // world, HIDDEN // world
+    check_layers = (0, LAYERS - 1)
+    whole = {}
+    layers = []
+    for l in range(LAYERS):
+        gate = make_q4k_device(torch, INTER, HIDDEN, gen)
+        up = make_q4k_device(torch, INTER, HIDDEN, gen)
+        down = make_q4k_device(torch, HIDDEN, INTER, gen)
+        layers.append((gate[rank * n_glu:(rank + 1) * n_glu].contiguous(),
+                       up[rank * n_glu:(rank + 1) * n_glu].contiguous(),
+                       down[rank * n_down:(rank + 1) * n_down].contiguous()))
+        if rank == 0 and l in check_layers:
+            whole[l] = (gate, up, down)
+        del gate, up, down
+    x = torch.randn((LAYERS, batch, HIDDEN), device="cuda", generator=gen)
+    T = ops.TYPE_Q4_K
+    q8x = torch.empty((batch, ops.q8_1_row_blocks(HIDDEN) * 36), dtype=torch.uint8, device="cuda")
+    q8h = torch.empty((batch, ops.q8_1_row_blocks(INTER) * 36), dtype=torch.uint8, device="cuda")
+    h_shard = torch.empty((batch, n_glu), device="cuda")
+    h_full = torch.empty((world, batch, n_glu), device="cuda")
+    h_rows = torch.empty((batch, INTER), device="cuda")
+    y_shard = torch.empty((batch, n_down), device="cuda")
+    y_full = torch.empty((LAYERS, world, batch, n_down), device="cuda")
+    h_seen = {}
+
+    def step(keep=False):
+        for l, (gate, up, down) in enumerate(layers):
+            ops.quantize_q8(x[l], out=q8x)
+            ops.vecq(up, T, HIDDEN, n_glu, q8x, batch, gate=gate, glu=ops.GLU_GEGLU, out=h_shard)
+            dist.all_gather_into_tensor(h_full, h_shard)
+            h_rows.view(batch, world, n_glu).copy_(h_full.transpose(0, 1))
+            if keep and l in check_layers:
+                h_seen[l] = h_rows.clone()
+            ops.quantize_q8(h_rows, out=q8h)
+            ops.vecq(down, T, INTER, n_down, q8h, batch, out=y_shard)
+            dist.all_gather_into_tensor(y_full[l], y_shard)
+
+    for _ in range(warmup):
+        step()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    ms = _max_over_ranks(torch, dist, e0.elapsed_time(e1) / steps)
+    step(keep=True)
+    torch.cuda.synchronize()
+    parity = True
+    if rank == 0:
+        for l in check_layers:
+            gate, up, down = whole[l]
+            q = ops.quantize_q8(x[l])
+            h = ops.vecq(up, T, HIDDEN, INTER, q, batch, gate=gate, glu=ops.GLU_GEGLU)
+            y = ops.vecq(down, T, INTER, HIDDEN, ops.quantize_q8(h), batch)
+            got_y = y_full[l].transpose(0, 1).reshape(batch, HIDDEN)
+            parity = parity and bool(torch.equal(h_seen[l], h)) and bool(torch.equal(got_y, y))
+    parity = _all_true(torch, dist, parity)
+    sb = step_bytes(batch)
+    return {"metric": METRIC, "value": round(sb / (ms * 1e-3) / 1e9, 2), "unit": UNIT,
+            "ms_per_step": round(ms, 4), "n_gpus": world, "steps": steps, "warmup": warmup,
+            "scaling": "strong", "parity": parity, "faults": ops.device_faults(),
+            "config": {"workload": f"Gemma-3-4B FFN decode products, Q4_K, {LAYERS} layers, batch {batch}",
+                       "parallelism": f"N-column shards x{world}, NCCL all-gather of the GLU output "
+                                      "and of the layer output, plain stream launches"}}
+
+
+def run_sharded_only(args, rank: int, world: int, local_rank: int, which: str):
+    """--workload mmq_q4k | moe under torchrun: that sharded form alone, one JSON line."""
     import torch
     import torch.distributed as dist
 
     torch.cuda.set_device(local_rank)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     import llmp_b200 as ops
-    from llmp_b200 import shard, synth
-    tokens = args.tokens or 4096
-    experts, used, hidden, inter = 128, 8, 2048, 768
-    b, e = shard.expert_range(experts, world, rank)
-    gen = torch.Generator(device="cuda")
-    gen.manual_seed(100 + rank)
-    gate_up = make_q4k_device(torch, (e - b) * 2 * inter, hidden, gen).view(e - b, 2 * inter, -1)
-    down = make_q4k_device(torch, (e - b) * hidden, inter, gen).view(e - b, hidden, -1)
-    ids, w = synth.topk_route(np.random.default_rng(rank), tokens, experts, used)
-    ids_d, w_d = torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda()
-    x = torch.randn((tokens, hidden), device="cuda", generator=gen)
-
-    def local(rows, local_ids):
-        ones = torch.ones((rows.shape[0], 1), device=rows.device)
-        return ops.moe_ffn(rows, local_ids.view(-1, 1).contiguous(), ones, gate_up, down, hidden,
-                           inter)
-
-    def step():
-        return shard.ep_moe_ffn(x, ids_d, w_d, experts, local)
-
-    for _ in range(max(args.warmup, 3)):
-        out = step()
-    dist.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        out = step()
-    e1.record()
-    dist.barrier()
-    torch.cuda.synchronize()
-    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device="cuda", dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ok = torch.tensor([float(torch.isfinite(out).all())], device="cuda")
-    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if which == "mmq_q4k":
+        line = bench_mmq_sharded(torch, dist, ops, rank, world, tokens=args.tokens or 4096,
+                                 steps=args.steps, warmup=max(args.warmup, 3))
+    else:
+        line = bench_moe_ep(torch, dist, ops, rank, world, tokens=args.tokens or 1024,
+                            steps=args.steps, warmup=max(args.warmup, 3))
     if rank == 0:
-        ms = float(t.item())
-        ops_count = 3 * 2.0 * hidden * inter * tokens * used * world
-        print(json.dumps({
-            "metric": "moe_grouped_gemm_throughput", "unit": "TOP/s",
-            "value": round(ops_count / (ms * 1e-3) / 1e12, 1), "ms_per_step": round(ms, 4),
-            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "higher_is_better": True, "scaling": "weak", "data": "synthetic", "vs_baseline": None,
-            "finite": bool(ok.item()), "faults": ops.device_faults(),
-            "config": {"workload": f"MoE block, 128 experts top-8, hidden 2048, intermediate 768, "
-                                   f"Q4_K, {tokens} tokens a rank",
-                       "parallelism": f"expert parallel x{world}, NCCL all-to-all dispatch and "
-                                      "combine, tokens data-parallel"}}), flush=True)
+        line.update({"higher_is_better": True, "data": "synthetic", "vs_baseline": None})
+        print(json.dumps(line), flush=True)
     dist.destroy_process_group()
 
 
@@ -791,10 +1031,14 @@ def main():
                     help="N > 1: replicas (each GPU its own batch, weak scaling) or columns "
                          "(rows of every matrix split, NCCL all-gather, strong scaling)")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--repeats", type=int, default=10,
+                    help="the timed block of --steps steps is repeated this often; the median counts")
+    ap.add_argument("--no-sharded", action="store_true",
+                    help="N > 1: skip the sharded forms (replicas only)")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--traffic", type=float, default=None,
                     help="dram bytes per launch of the dominant kernel from an ncu capture "
-                         "(default: the figure in profiles/vecq_rowlane_glu_b1.md at batch 1)")
+                         "(default: the captured figure at batch 1)")
     args = ap.parse_args()
     LAYERS = args.layers
     rank = int(os.environ.get("RANK", "0"))
@@ -803,11 +1047,8 @@ def main():
     if args.impl == "reference":
         run_reference(args, rank)
         return
-    if args.workload == "moe" and world > 1:
-        run_moe_ep(args, rank, world, local_rank)
-        return
-    if args.workload == "mmq_q4k" and world > 1:
-        run_mmq_sharded(args, rank, world, local_rank)
+    if args.workload in ("moe", "mmq_q4k") and world > 1:
+        run_sharded_only(args, rank, world, local_rank, args.workload)
         return
     if args.workload != "ffn_q4k":
         if rank == 0:

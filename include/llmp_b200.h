@@ -15,7 +15,8 @@
  *     why).  <0: a CUDA call failed after work may have been queued; the
  *     caller must treat its stream's context as faulted;
  *   - results are deterministic: no floating-point atomics, fixed summation
- *     orders; a token's sums do not depend on which other tokens share a call;
+ *     orders; a token's sums do not depend on which other tokens share a call
+ *     when the launch configuration is the same (see llmp_b200_vecq's variants);
  *   - thread-compatible: one stream per calling thread.
  *
  * There is no CPU fallback: on a machine without an sm_100 GPU every launch
@@ -63,6 +64,14 @@ const char* llmp_b200_last_error(void);
  * was loaded.  0 on a healthy device with well-formed operands; synchronizes the device, so it
  * is for tests and post-mortems, never for the launch path.  -1: unreadable. */
 int llmp_b200_device_faults(void);
+/* The same count, which is then set back to zero (synchronizes the device too). */
+int llmp_b200_device_faults_clear(void);
+/* Diagnostics, no reference counterpart: runs the give-up path of the library's bounded
+ * waits once, harmlessly.  One warp waits at most `polls` polls (1..4096; a pending poll
+ * suspends for about a microsecond) on a barrier nothing will ever arrive at, gives up,
+ * raises llmp_b200_device_faults() by one and writes 1 to *status (a device int32).  The
+ * context stays usable: a test follows it with an ordinary launch. */
+int llmp_b200_wait_selftest(int polls, int32_t* status, void* stream);
 
 /* ------------------------------------------------------------------ Q8_1 */
 /* Replaces RunQuantizeQ8 (src/kernels/ggml/vecq.cu:1095-1111), which calls
@@ -101,11 +110,23 @@ typedef struct llmp_b200_vecq_desc {
 
 /* Replaces VecQVariants / VecQVariantName / LaunchVecQ
  * (src/kernels/ggml/vecq.h:44-49) together with the operand checks of
- * CheckVecQ (src/kernels/ggml/llmp_ops.cc:2915-2982).  variant -1 picks the
- * launch configuration for the shape.  Types: Q8_0, Q4_K. */
+ * CheckVecQ (src/kernels/ggml/llmp_ops.cc:2915-2982).  Types: Q8_0, Q4_K.
+ * variant >= 0: that launch configuration (status > 0 if it does not take the product).
+ * variant -1: the configuration that measured fastest on B200 for this very (k, n, GLU,
+ * token count) when the rank table has it, else the rule for the shape; a token's F32 bits
+ * may then differ between token counts (as the reference's MMVQ's do).
+ * variant -2: the rule for the shape alone, whose geometry is the one-token plan's whatever
+ * the token count: a token's bits do not depend on its company (the reference's
+ * row_invariant capability; llmp_b200_mmvq_rows runs on it). */
 int llmp_b200_vecq_variants(void);
 const char* llmp_b200_vecq_variant_name(int variant);
 int llmp_b200_vecq(int type, const llmp_b200_vecq_desc* desc, int variant, void* stream);
+/* The measured rank table (the role of src/kernels/ggml/measured_ranks.h and
+ * src/execution/rank_data.h): row i names the launch configuration that measured fastest on
+ * B200 for the dense Q4_K product (k, n, fused GLU, tokens a pass) and its time.  Returns the
+ * configuration's name ("" past the table). */
+int llmp_b200_vecq_rank_count(void);
+const char* llmp_b200_vecq_rank(int row, int* k, int* n, int* glu, int* tokens, float* microseconds);
 
 /* The product with its activation quantization fused: the reference lowers a
  * shared QuantizeQ8 node in front of its products (src/kernels/ggml/shared_q8.h
@@ -310,6 +331,22 @@ int llmp_b200_grouped_gemm_static(const llmp_b200_grouped_gemm_desc* gemm, int s
  * Q8_1-MMQ blocks [f / 128][rows] of glu(gate, up). */
 int llmp_b200_moe_glu_quantize(const float* gate_up, int64_t row_stride, int f, int64_t rows,
                                int glu, float limit, void* out, void* stream);
+
+/* Expert-parallel dispatch (the reference models expert parallelism as a partition of whole
+ * experts, src/planner/partition.h:57-67, src/components/moe.cc:521-531, with kAllToAll as its
+ * exchange, src/ir/op.h:246-250): packs this rank's (token, slot) rows for an all-to-all of
+ * FIXED size, so no split size ever reaches the host.  Rank r owns experts [r, r + 1) * experts /
+ * world.  `route` is llmp_b200_moe_route's blob over the slots' owner ranks (ids / (experts /
+ * world), world "experts").  Lane i of destination r, send_rows[(r * capacity + i) * hidden ..],
+ * takes the i-th row bound for r in (token, slot) order and send_ids[r * capacity + i] its
+ * expert's index on r (unused lanes: -1).  home[slot] is the lane the slot's result comes back
+ * in after the return all-to-all (the `position` of llmp_b200_moe_combine over the returned
+ * rows), -1 for an id outside the experts.  A row beyond a destination's capacity is dropped,
+ * counted in *dropped (a device int the caller zeroes) and its home is -1. */
+int llmp_b200_moe_ep_pack(const float* x, int64_t x_stride, int hidden, const int32_t* ids,
+                          int ids_stride, int used, int tokens, int experts, int world, int capacity,
+                          const int32_t* route, float* send_rows, int32_t* send_ids, int32_t* home,
+                          int32_t* dropped, void* stream);
 
 /* Replaces llmp.moe.combine_sorted (llmp_moe.cu:393-435) without NVFP4's global
  * scales and the shared expert: dst[t] = sum over the token's slots, in slot

@@ -99,12 +99,18 @@ SIGNATURES = {
     "llmp_b200_available": (C.c_int, []),
     "llmp_b200_sm_count": (C.c_int, []),
     "llmp_b200_last_error": (C.c_char_p, []),
+    "llmp_b200_wait_selftest": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p]),
     "llmp_b200_device_faults": (C.c_int, []),
+    "llmp_b200_device_faults_clear": (C.c_int, []),
     "llmp_b200_q8_1_row_blocks": (C.c_int64, [C.c_int64]),
     "llmp_b200_q8_1_quantize": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
                                           C.c_int64, C.c_void_p, C.c_void_p]),
     "llmp_b200_vecq_variants": (C.c_int, []),
     "llmp_b200_vecq_variant_name": (C.c_char_p, [C.c_int]),
+    "llmp_b200_vecq_rank_count": (C.c_int, []),
+    "llmp_b200_vecq_rank": (C.c_char_p, [C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int),
+                                         C.POINTER(C.c_int), C.POINTER(C.c_int),
+                                         C.POINTER(C.c_float)]),
     "llmp_b200_vecq": (C.c_int, [C.c_int, C.POINTER(VecQDesc), C.c_int, C.c_void_p]),
     "llmp_b200_mmq_q8_1_bytes": (C.c_int64, [C.c_int64, C.c_int64]),
     "llmp_b200_mmq_quantize": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int64,
@@ -124,6 +130,9 @@ SIGNATURES = {
     "llmp_b200_grouped_gemm_static": (C.c_int, [C.POINTER(GroupedGemmDesc), C.c_int, C.c_void_p]),
     "llmp_b200_moe_glu_quantize": (C.c_int, [C.c_void_p, C.c_int64, C.c_int, C.c_int64, C.c_int,
                                              C.c_float, C.c_void_p, C.c_void_p]),
+    "llmp_b200_moe_ep_pack": (C.c_int, [C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_int, C.c_int,
+                                        C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
+                                        C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "llmp_b200_moe_combine": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int,
                                         C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "llmp_b200_mxfp8_padded_rows": (C.c_uint64, [C.c_uint64]),

@@ -23,6 +23,7 @@ int SmCount();
 // Device address of the counter of bounded waits that ran out (per device), or null.
 unsigned int* FaultCounter();
 int ReadFaultCounter();
+int ClearFaultCounter();  // the count before, or -1
 
 // After a launch: 0, or a negative status carrying the CUDA error.
 inline int Launched(const char* what) {

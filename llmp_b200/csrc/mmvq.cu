@@ -12,12 +12,13 @@
 //
 // Row invariance.  The reference needs mmvq_rows because GGML's launch geometry,
 // and with it the order a column's sums are added in, changes with the column
-// count (mmvq_rows.cu:5-18).  This build's dense products fix the geometry from
-// the one-column plan whatever the column count (vecq.cu), so a column's F32
-// result is the same bits alone or in company up to 8 columns; the rows entry
-// extends that to any column count by queueing passes of at most 8 columns, each
-// with the one-column geometry (the weights of a 15 to 30 MB matrix stay in the
-// 126 MB L2 between the passes).
+// count (mmvq_rows.cu:5-18).  Here the ordinary entries take whatever launch
+// configuration measured fastest for the shape and column count (vecq_ranks.h), so
+// their bits may change with the column count too; the rows entry runs the products
+// under the launch rule that fixes the geometry from the one-column plan (llmp.vecq's
+// variant -2), in passes of at most 8 columns: a column's F32 result is then the same
+// bits alone or in any company (the weights of a 15 to 30 MB matrix stay in the 126 MB
+// L2 between the passes).
 #include "common.cuh"
 
 namespace llmp_b200 {
@@ -84,7 +85,7 @@ llmp_b200_vecq_desc ProductOf(const Desc& d, const void* q8, int first, int cols
 }
 
 // Quantize (unless prepared), then the product in passes of at most `pass` columns.
-int Run(const Desc& d, bool prepared, int pass, void* stream) {
+int Run(const Desc& d, bool prepared, int pass, void* stream, int variant = -1) {
   if (d.dst_col_stride > 0x7fffffffLL) return Reject("mmvq: output stride beyond int");
   const void* q8 = d.q8;
   bool queued = false;
@@ -97,7 +98,7 @@ int Run(const Desc& d, bool prepared, int pass, void* stream) {
   }
   for (int first = 0; first < d.cols; first += pass) {
     const llmp_b200_vecq_desc v = ProductOf(d, q8, first, d.cols - first < pass ? d.cols - first : pass);
-    const int status = llmp_b200_vecq(d.type, &v, -1, stream);
+    const int status = llmp_b200_vecq(d.type, &v, variant, stream);
     // Work is already queued: a refusal now is reported as a failure after queueing.
     if (status != 0) return (queued && status > 0) ? -status : status;
     queued = true;
@@ -143,7 +144,9 @@ int llmp_b200_mmvq_rows(const llmp_b200_mmvq_desc* desc, void* stream) {
   if (const int status = DeviceStatus(); status != 0) return status;
   // Columns a pass: what the product's fixed-geometry kernels take at once (vecq.cu: the
   // Q4_K row-lane kernel 8 tokens, the Q8_0 stream kernel 4).
-  return Run(*desc, prepared, desc->type == LLMP_B200_TYPE_Q4_K ? 8 : 4, stream);
+  // ... under the launch rule that keeps the one-column geometry (variant -2), not the
+  // measured-rank table, whose choice may change with the column count.
+  return Run(*desc, prepared, desc->type == LLMP_B200_TYPE_Q4_K ? 8 : 4, stream, -2);
 }
 
 }  // extern "C"

@@ -306,6 +306,54 @@ __global__ void CombineKernel(const float* __restrict__ rows, std::int64_t row_s
   dst[i] = acc;
 }
 
+// Expert-parallel dispatch with lanes of fixed capacity: a warp a (token, slot).
+// `route` is this library's route blob over the slots' OWNER RANKS (the counting sort
+// with the ranks as its experts), so position[slot] - offsets[rank] is the slot's
+// ordinal among the rows this rank sends to that owner, in (token, slot) order.
+__global__ void __launch_bounds__(256)
+EpPackKernel(const float* __restrict__ x, std::int64_t x_stride, int hidden,
+             const std::int32_t* __restrict__ ids, int ids_stride, int used, int tokens,
+             int per_rank, int world, int capacity, const std::int32_t* __restrict__ offsets,
+             const std::int32_t* __restrict__ position, float* __restrict__ send_rows,
+             std::int32_t* __restrict__ send_ids, std::int32_t* __restrict__ home,
+             std::int32_t* __restrict__ dropped) {
+  GridLaunchDependents();
+  GridDependencyWait();
+  const int lane = static_cast<int>(threadIdx.x) & 31;
+  const std::int64_t slot = (static_cast<std::int64_t>(blockIdx.x) * 8) + (threadIdx.x >> 5);
+  if (slot >= static_cast<std::int64_t>(tokens) * used) return;
+  const int t = static_cast<int>(slot / used);
+  const int e = ids[(static_cast<std::int64_t>(t) * ids_stride) + (slot % used)];
+  const int row = position[slot];
+  if (row < 0 || e < 0 || e >= per_rank * world) {  // an id outside the experts
+    if (lane == 0) home[slot] = -1;
+    return;
+  }
+  const int rank = e / per_rank;
+  const int i = row - offsets[rank];
+  if (i >= capacity) {  // more rows for one owner than a lane block holds
+    if (lane == 0) {
+      home[slot] = -1;
+      atomicAdd(dropped, 1);
+    }
+    return;
+  }
+  const std::int64_t at = (static_cast<std::int64_t>(rank) * capacity) + i;
+  const float4* src = reinterpret_cast<const float4*>(x + (static_cast<std::int64_t>(t) * x_stride));
+  float4* dst = reinterpret_cast<float4*>(send_rows + (at * hidden));
+  for (int c = lane; c < hidden / 4; c += 32) dst[c] = src[c];
+  if (lane == 0) {
+    send_ids[at] = e - (rank * per_rank);
+    home[slot] = static_cast<std::int32_t>(at);
+  }
+}
+
+// Lanes nothing was packed into carry the id -1.
+__global__ void FillKernel(std::int32_t* __restrict__ p, std::int64_t n, std::int32_t v) {
+  const std::int64_t i = (static_cast<std::int64_t>(blockIdx.x) * blockDim.x) + threadIdx.x;
+  if (i < n) p[i] = v;
+}
+
 int CheckGrouped(const llmp_b200_grouped_gemm_desc& g) {
   if (g.groups < 1 || g.groups > kMaxExperts || g.n < 1 || g.k < 256 || g.k % 256 != 0 ||
       g.rows < 1) {
@@ -490,6 +538,39 @@ int llmp_b200_moe_glu_quantize(const float* gate_up, int64_t row_stride, int f, 
                                   static_cast<cudaStream_t>(stream), gate_up, row_stride, f, rows,
                                   glu, limit, static_cast<std::uint8_t*>(out), lanes);
   if (e != cudaSuccess) return Failed(e, "moe.glu_quantize launch");
+  return 0;
+}
+
+int llmp_b200_moe_ep_pack(const float* x, int64_t x_stride, int hidden, const int32_t* ids,
+                          int ids_stride, int used, int tokens, int experts, int world, int capacity,
+                          const int32_t* route, float* send_rows, int32_t* send_ids, int32_t* home,
+                          int32_t* dropped, void* stream) {
+  using namespace llmp_b200;
+  if (x == nullptr || ids == nullptr || route == nullptr || send_rows == nullptr ||
+      send_ids == nullptr || home == nullptr || dropped == nullptr) {
+    return Reject("moe.ep_pack: rows, ids, the owners' route and the four outputs");
+  }
+  if (hidden < 4 || hidden % 4 != 0 || x_stride < hidden || x_stride % 4 != 0 || used < 1 ||
+      tokens < 1 || ids_stride < used || world < 1 || world > kMaxExperts || experts < world ||
+      experts % world != 0 || capacity < 1) {
+    return Reject("moe.ep_pack: hidden a positive multiple of 4, experts a multiple of the ranks, "
+                  "a positive capacity");
+  }
+  if (!Aligned(x, 16) || !Aligned(send_rows, 16)) return Reject("moe.ep_pack: 16-byte aligned rows");
+  if (const int status = DeviceStatus(); status != 0) return status;
+  auto* s = static_cast<cudaStream_t>(stream);
+  const std::int64_t lanes = static_cast<std::int64_t>(world) * capacity;
+  FillKernel<<<static_cast<unsigned>((lanes + 255) / 256), 256, 0, s>>>(send_ids, lanes, -1);
+  if (const int status = Launched("moe.ep_pack fill"); status != 0) return status;
+  const Route r = RouteOf(const_cast<std::int32_t*>(route), world, used, tokens);
+  const std::int64_t slots = static_cast<std::int64_t>(tokens) * used;
+  const cudaError_t e = LaunchPdl(EpPackKernel, dim3(static_cast<unsigned>((slots + 7) / 8)), dim3(256),
+                                  0, s, x, x_stride, hidden, ids, ids_stride, used, tokens,
+                                  experts / world, world, capacity,
+                                  static_cast<const std::int32_t*>(r.offsets),
+                                  static_cast<const std::int32_t*>(r.position), send_rows, send_ids,
+                                  home, dropped);
+  if (e != cudaSuccess) return Failed(e, "moe.ep_pack launch");
   return 0;
 }
 

@@ -73,6 +73,8 @@ int SmCount() { return DeviceStatus() == 0 ? Facts().sms : 0; }
 // Raised by a kernel whose bounded wait ran out; never by a healthy run.
 __device__ unsigned int g_wait_timeouts = 0;
 
+int ReadFaultCounter();
+
 unsigned int* FaultCounter() {
   static thread_local int cached_device = -1;
   static thread_local unsigned int* cached = nullptr;
@@ -88,6 +90,16 @@ unsigned int* FaultCounter() {
     cached_device = device;
   }
   return cached;
+}
+
+int ClearFaultCounter() {
+  const int before = ReadFaultCounter();
+  const unsigned int zero = 0;
+  if (before < 0 || cudaMemcpyToSymbol(g_wait_timeouts, &zero, sizeof(zero)) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  return before;
 }
 
 int ReadFaultCounter() {
@@ -107,5 +119,8 @@ int llmp_b200_sm_count(void) { return llmp_b200::SmCount(); }
 const char* llmp_b200_last_error(void) { return llmp_b200::ErrorBuffer(); }
 int llmp_b200_device_faults(void) {
   return llmp_b200::DeviceStatus() != 0 ? 0 : llmp_b200::ReadFaultCounter();
+}
+int llmp_b200_device_faults_clear(void) {
+  return llmp_b200::DeviceStatus() != 0 ? 0 : llmp_b200::ClearFaultCounter();
 }
 }

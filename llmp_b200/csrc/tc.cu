@@ -34,4 +34,39 @@ bool MakeMapBytes2D(CUtensorMap* map, const void* base, std::uint64_t rows, std:
 }
 
 }  // namespace tc
+
+namespace {
+// One warp waits, with a host-chosen limit, on a barrier nothing arrives at: the
+// give-up path every kernel of this library takes when a copy never lands.
+__global__ void WaitSelfTestKernel(std::uint32_t polls, std::int32_t* status, unsigned int* faults) {
+  __shared__ __align__(8) std::uint64_t never;
+  if (threadIdx.x == 0) {
+    tc::MbarInit(&never, 1);
+    tc::MbarInitFence();
+  }
+  __syncwarp();
+  bool ok = true;
+  if (threadIdx.x == 0) ok = tc::MbarWait(&never, 0, polls);
+  ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+  if (!ok && threadIdx.x == 0) {
+    atomicAdd(faults, 1u);
+    *status = 1;  // gave up, as designed
+  } else if (threadIdx.x == 0) {
+    *status = 2;  // a barrier without an arrival completed: never expected
+  }
+}
+}  // namespace
 }  // namespace llmp_b200
+
+extern "C" int llmp_b200_wait_selftest(int polls, int32_t* status, void* stream) {
+  using namespace llmp_b200;
+  if (status == nullptr || polls < 1 || polls > 4096) {
+    return Reject("wait_selftest: a device status word and 1 to 4096 polls");
+  }
+  if (const int code = DeviceStatus(); code != 0) return code;
+  unsigned int* faults = FaultCounter();
+  if (faults == nullptr) return Reject("wait_selftest: no fault counter on this device");
+  WaitSelfTestKernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<std::uint32_t>(polls), status, faults);
+  return Launched("wait_selftest launch");
+}

@@ -58,10 +58,12 @@ __device__ __forceinline__ void MbarExpectTx(std::uint64_t* bar, std::uint32_t b
 __device__ __forceinline__ void MbarArrive(std::uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(Smem(bar)) : "memory");
 }
-// Bounded wait for the phase of parity `parity`; false when it ran out.
-__device__ __forceinline__ bool MbarWait(std::uint64_t* bar, std::uint32_t parity) {
+// Bounded wait for the phase of parity `parity`; false when it ran out (`polls`
+// polls: a pending try_wait suspends the thread for up to about a microsecond).
+__device__ __forceinline__ bool MbarWait(std::uint64_t* bar, std::uint32_t parity,
+                                         std::uint32_t polls = kSpinLimit) {
   const std::uint32_t addr = Smem(bar);
-  for (std::uint32_t i = 0; i < kSpinLimit; ++i) {
+  for (std::uint32_t i = 0; i < polls; ++i) {
     std::uint32_t done;
     asm volatile(
         "{\n"

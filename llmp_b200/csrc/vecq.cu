@@ -1,7 +1,11 @@
 // llmp.vecq entry points: operand checks, launch choice, and the per-block
 // int32 sums used to verify the product kernels.  The kernels themselves are
 // in vecq_impl.cuh, instantiated per weight type in vecq_q4k.cu / vecq_q8_0.cu.
+#include <cstring>
+
+#include "vecq_ranks.h"
 #include "vecq_rowlane.cuh"
+#include "vecq_rowmma.cuh"
 
 namespace llmp_b200 {
 namespace vecq {
@@ -162,6 +166,19 @@ const char* llmp_b200_vecq_variant_name(int variant) {
   return llmp_b200::kVariants[variant].name;
 }
 
+int llmp_b200_vecq_rank_count(void) { return llmp_b200::vecq::kMeasuredRankCount; }
+
+const char* llmp_b200_vecq_rank(int row, int* k, int* n, int* glu, int* tokens, float* microseconds) {
+  if (row < 0 || row >= llmp_b200::vecq::kMeasuredRankCount) return "";
+  const llmp_b200::vecq::MeasuredRank& r = llmp_b200::vecq::kMeasuredRanks[row];
+  if (k != nullptr) *k = r.k;
+  if (n != nullptr) *n = r.n;
+  if (glu != nullptr) *glu = r.glu;
+  if (tokens != nullptr) *tokens = r.tokens;
+  if (microseconds != nullptr) *microseconds = r.microseconds;
+  return r.variant;
+}
+
 namespace llmp_b200 {
 namespace {
 int LaunchVecQ(int type, const llmp_b200_vecq_desc* desc, int variant, bool f32_input, void* q8_out,
@@ -216,7 +233,7 @@ int LaunchVecQ(int type, const llmp_b200_vecq_desc* desc, int variant, bool f32_
   if (desc == nullptr) return Reject("vecq: null descriptor");
   bool q8_fast = false;
   if (const int status = Check(type, *desc, &q8_fast); status != 0) return status;
-  if (variant < -1 || variant >= kVariantCount) return Reject("vecq: no variant %d", variant);
+  if (variant < -2 || variant >= kVariantCount) return Reject("vecq: no variant %d", variant);
   if (const int status = DeviceStatus(); status != 0) return status;
   const Desc& d = *desc;
   const bool glu = d.glu != LLMP_B200_GLU_NONE;
@@ -226,6 +243,27 @@ int LaunchVecQ(int type, const llmp_b200_vecq_desc* desc, int variant, bool f32_
   const int most = d.ids != nullptr ? std::min(d.tokens, 8) : d.tokens;
   while (p < most && p < 8) p *= 2;
   while (p > 1 && StageBytes(d.ncols_x, p) > 200 * 1024) p /= 2;
+  // variant -1: the fastest measured configuration of this very product, when the table
+  // has it (the bits of a token may then differ between token counts, as the reference's
+  // MMVQ's do); a configuration that turns the product down falls through to the rule
+  // below.  variant -2: the rule below alone, whose row-lane geometry is the one-token
+  // plan's whatever the token count (what llmp_b200_mmvq_rows runs on).
+  if (variant == -1 && type == LLMP_B200_TYPE_Q4_K && d.ids == nullptr && d.used == 1 &&
+      d.tokens <= 8 && !f32_input && q8_dst == nullptr && d.stride_row == d.ncols_x / 256) {
+    for (int i = 0; i < kMeasuredRankCount; ++i) {
+      const MeasuredRank& r = kMeasuredRanks[i];
+      if (r.k != d.ncols_x || r.n != d.nrows || (r.glu != 0) != glu || r.tokens != p) continue;
+      for (int v = 0; v < kVariantCount; ++v) {
+        if (std::strcmp(kVariants[v].name, r.variant) != 0) continue;
+        if (v == kRowLaneVariant) break;  // the rule below is that kernel
+        const int status = LaunchVecQ(type, desc, v, false, nullptr, nullptr, nullptr, stream);
+        if (status <= 0) return status;   // queued, or failed after queueing
+        break;                            // refused cleanly: the rule below
+      }
+      break;
+    }
+  }
+  if (variant == -2) variant = -1;
   const int slots = d.ids != nullptr ? d.used * d.tokens : d.used;
   auto* s = static_cast<cudaStream_t>(stream);
   cudaError_t e;
@@ -240,13 +278,28 @@ int LaunchVecQ(int type, const llmp_b200_vecq_desc* desc, int variant, bool f32_
       PlanStream(d, q4 ? (p == 1 ? 256 : 64) : 128, q4 ? 144 : 34, q4 ? 256 : 32, p, SmCount(),
                  &plan);
   RowLanePlan lanes;
+  const bool aligned16 = Aligned(d.w, 16) && (d.g == nullptr || Aligned(d.g, 16));
+  if (variant >= kRowMmaVariant && variant < kRowLaneSplitVariant) {
+    RowMmaPlan tiles;
+    const int ctas = variant == kRowMmaVariant ? 1 : kVariants[variant].u;
+    if (!(dense && q4 && aligned16 && f32_input == false && q8_dst == nullptr &&
+          PlanRowMma(d, p, SmCount(), &tiles, ctas))) {
+      return Reject("vecq: the rowmma variant takes dense Q4_K products of up to 8 tokens");
+    }
+    e = LaunchRowMma(d, p, tiles, s);
+    if (e != cudaSuccess) return Failed(e, "vecq rowmma launch");
+    return 0;
+  }
   const bool wants_rowlane = variant >= kRowLaneVariant;
   bool rowlane_ok = false;
   if (dense && q4 && Aligned(d.w, 16) && (d.g == nullptr || Aligned(d.g, 16))) {
     if (wants_rowlane) {
       const Variant& forced = kVariants[variant];
-      rowlane_ok = PlanRowLane(d, p, SmCount(), forced.r, forced.u == 1, &lanes, 0, forced.u == 2,
-                               forced.warps > 0 ? forced.warps : kRowLaneWarps);
+      const bool split = variant >= kRowLaneSplitVariant;
+      const int share = split ? std::max(2, forced.warps) : 2;
+      rowlane_ok = PlanRowLane(d, p, split ? share * SmCount() : SmCount(), forced.r,
+                               forced.u == 1 || split, &lanes, 0, forced.u == 2 || forced.u == 4,
+                               (!split && forced.warps > 0) ? forced.warps : kRowLaneWarps, share);
     } else {
       // A row's sum adds its super-blocks up in an order the geometry (rows and phases
       // a warp) fixes.  So that a token gives the same bits alone or in company, more

@@ -33,13 +33,16 @@
 namespace llmp_b200 {
 namespace vecq {
 
-constexpr int kRowLaneMaxWarps = 24;      // a CTA that owns its SM: 24 warps of 85 registers for one
-                                          // token a pass, 16 of 128 up to four, 12 of 168 for eight
+constexpr int kRowLaneMaxWarps = 12;      // a CTA that owns its SM: 12 warps leave a thread up to
+                                          // 168 registers, which the unrolled loads want (24 warps
+                                          // of 85 registers measured slower: 9.2 against 7.9 us)
 constexpr int kRowLaneWarps = 12;         // ... by default
-constexpr int kRowLaneHalfWarps = 9;      // a CTA that shares its SM with the next kernel's
+constexpr int kRowLaneHalfWarps = 9;      // a CTA that shares its SM with the next kernel's (12 for
+                                          // one token a pass: 85 registers a thread)
 constexpr int kRowLaneMaxStages = 8;
 
-__host__ __device__ constexpr int RowLaneWarpLimit(int p) { return p == 1 ? 24 : p <= 4 ? 16 : 12; }
+__host__ __device__ constexpr int RowLaneWarpLimit(int p) { return p >= 1 ? 12 : 12; }
+__host__ __device__ constexpr int RowLaneHalfWarpLimit(int p) { return p == 1 ? 12 : 9; }
 
 struct RowLanePlan {
   int warps;         // W
@@ -71,7 +74,7 @@ struct RowLanePlan {
 // after this one (launched as a programmatic dependent) becomes resident and
 // requests its weights while this one still computes.
 template <int P, bool kGlu, bool kHalf>
-__global__ void __launch_bounds__(kHalf ? kRowLaneHalfWarps * 32 : RowLaneWarpLimit(P) * 32,
+__global__ void __launch_bounds__(kHalf ? RowLaneHalfWarpLimit(P) * 32 : RowLaneWarpLimit(P) * 32,
                                   kHalf ? 2 : 1)
 VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
   constexpr int kMats = kGlu ? 2 : 1;
@@ -413,15 +416,18 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
 // Host: the geometry for a dense Q4_K product, or false if it does not fit.
 inline bool PlanRowLane(const Desc& d, int p, int sms, int force_rows, bool half,
                         RowLanePlan* plan, int force_phases = 0, bool packed = false,
-                        int warps_limit = kRowLaneWarps) {
+                        int warps_limit = kRowLaneWarps, int share = 2) {
   const int mats = d.glu != LLMP_B200_GLU_NONE ? 2 : 1;
   const int ur = d.ncols_x / 256;
   if (ur < 1) return false;
   const int grid = std::max(1, std::min(sms, d.nrows));
   const int cta_rows = (d.nrows + grid - 1) / grid;
   const int acts_bytes = (ur * 256) + (ur * 64);
-  const int budget = (half ? 110 : 220) * 1024 - (p * acts_bytes) - 1024;
-  const int max_warps = half ? kRowLaneHalfWarps : std::min(warps_limit, RowLaneWarpLimit(p));
+  // half: the CTA takes 1 / share of an SM's shared memory and warps (share = 2: the next
+  // kernel's CTA fits beside it; more: several small CTAs an SM, `sms` then counts them all)
+  const int budget = (half ? 220 / share : 220) * 1024 - (p * acts_bytes) - 1024;
+  const int max_warps = half ? std::max(1, std::min(RowLaneHalfWarpLimit(p), 24 / share))
+                             : std::min(warps_limit, RowLaneWarpLimit(p));
   if (budget <= 0) return false;
   if (packed && d.stride_row != ur) return false;  // rows must follow one another in memory
   double best_score = -1.0;
@@ -466,7 +472,9 @@ inline bool PlanRowLane(const Desc& d, int p, int sms, int force_rows, bool half
     }
     if (stages < 1) continue;
     // (a forced geometry may run on a one-stage ring: slower, but the sums keep their order)
-    if (!packed && stages < steps && stages < 2 && force_phases == 0) continue;
+    // (a CTA that owns its SM wants two stages a warp when the ring is recycled; one that
+    // shares it runs on one: the neighbour CTA's copies fill the gaps)
+    if (!packed && !half && stages < steps && stages < 2 && force_phases == 0) continue;
     // Lane utilization, with a preference for more warps and for a ring that
     // holds the whole range.
     // (all 32 lanes of every warp count: lanes past R * PH idle)

@@ -16,11 +16,11 @@ from ._native import (GLU_GEGLU, GLU_NONE, GLU_SWIGLU, GLU_SWIGLU_CLAMP, TYPE_Q4
                       LaunchFailed, Rejected)
 
 __all__ = ["available", "sm_count", "device_faults", "block_bytes", "block_elems", "q8_1_row_blocks",
-           "quantize_q8", "vecq", "mmvq", "vecq_f32", "vecq_q8", "vecq_q8_scratch", "vecq_variants", "vecq_block_sums", "mxfp8_padded_rows",
+           "quantize_q8", "vecq", "vecq_ranks", "mmvq", "vecq_f32", "vecq_q8", "vecq_q8_scratch", "vecq_variants", "vecq_block_sums", "mxfp8_padded_rows",
            "mxfp8_quantize", "mxfp8_swizzle", "mxfp8_gemm", "mxfp8_mul_mat_vec", "decode_vector", "decode_rows", "decode_matrix", "decode_grouped", "DECODER_Q8_0", "DECODER_MXFP8_SPLIT",
            "DECODER_MXFP8_ATOMS", "DECODER_BF16", "DECODER_F16", "DECODER_NVFP4_SPLIT", "DECODER_NVFP4_ATOMS",
            "DECODER_MXFP4_SPLIT", "DECODER_MXFP4_ATOMS", "mmq_quantize", "mmq", "mmq_scratch", "mmq_block_sums", "q4k_relayout", "moe_route", "grouped_gemm",
-           "moe_glu_quantize", "moe_combine", "moe_ffn", "TYPE_Q8_0", "TYPE_Q4_K",
+           "moe_glu_quantize", "moe_combine", "moe_ep_pack", "moe_ffn", "TYPE_Q8_0", "TYPE_Q4_K",
            "GLU_NONE", "GLU_SWIGLU", "GLU_SWIGLU_CLAMP", "GLU_GEGLU", "Rejected", "LaunchFailed"]
 
 _BLOCK = {TYPE_Q8_0: (32, 34), TYPE_Q4_K: (256, 144), N.TYPE_Q8_1: (32, 36)}
@@ -88,6 +88,19 @@ def vecq_variants() -> list[str]:
     return [L.llmp_b200_vecq_variant_name(i).decode() for i in range(L.llmp_b200_vecq_variants())]
 
 
+def vecq_ranks() -> list[dict]:
+    """The measured rank table: the fastest launch configuration per dense Q4_K product."""
+    L = N.lib()
+    rows = []
+    for i in range(L.llmp_b200_vecq_rank_count()):
+        k, n, glu, tokens, us = C.c_int(), C.c_int(), C.c_int(), C.c_int(), C.c_float()
+        name = L.llmp_b200_vecq_rank(i, C.byref(k), C.byref(n), C.byref(glu), C.byref(tokens),
+                                     C.byref(us))
+        rows.append({"k": k.value, "n": n.value, "glu": glu.value, "tokens": tokens.value,
+                     "variant": name.decode(), "microseconds": us.value})
+    return rows
+
+
 def vecq(weights: torch.Tensor, wtype: int, k: int, n: int, q8: torch.Tensor, tokens: int, *,
          ids: torch.Tensor | None = None, per_slot: bool = False, gate: torch.Tensor | None = None,
          glu: int = GLU_NONE, limit: float = 0.0, groups: int = 1, stride_row: int | None = None,
@@ -148,6 +161,8 @@ def mmvq(weights: torch.Tensor, wtype: int, k: int, n: int, x: torch.Tensor | No
     rows=True: MulMatVecQRows, every column's bits the one-column product's, any column
     count."""
     _need(weights, torch.uint8, "mmvq weights")
+    if wtype not in (TYPE_Q8_0, TYPE_Q4_K):
+        raise Rejected(f"mmvq: weight type {wtype}")
     d = N.MmvqDesc()
     d.type, d.w, d.k, d.n = wtype, weights.data_ptr(), k, n
     d.gate = gate.data_ptr() if gate is not None else None
@@ -472,6 +487,30 @@ def moe_glu_quantize(gate_up: torch.Tensor, f: int, glu: int = GLU_SWIGLU,
                                                limit, out.data_ptr(), _stream()),
             "llmp_b200_moe_glu_quantize")
     return out
+
+
+def moe_ep_pack(x: torch.Tensor, ids: torch.Tensor, experts: int, world: int, capacity: int,
+                dropped: torch.Tensor):
+    """The expert-parallel dispatch's packing (llmp_b200_moe_ep_pack): x F32 [tokens, hidden],
+    ids I32 [tokens, used] -> (send rows [world * capacity, hidden], send ids I32 [world *
+    capacity], home I32 [tokens * used]); dropped: an I32 device counter of rows past capacity."""
+    _need(x, torch.float32, "moe_ep_pack rows")
+    _need(ids, torch.int32, "moe_ep_pack ids")
+    _need(dropped, torch.int32, "moe_ep_pack dropped counter")
+    tokens, used = ids.shape
+    hidden = x.shape[1]
+    per = experts // world
+    owner = torch.where((ids >= 0) & (ids < experts), ids // per, torch.full_like(ids, -1))
+    route = moe_route(owner.contiguous(), world)
+    send = torch.empty((world * capacity, hidden), dtype=torch.float32, device=x.device)
+    send_ids = torch.empty((world * capacity,), dtype=torch.int32, device=x.device)
+    home = torch.empty((tokens * used,), dtype=torch.int32, device=x.device)
+    N.check(N.lib().llmp_b200_moe_ep_pack(x.data_ptr(), x.stride(0), hidden, ids.data_ptr(),
+                                          ids.stride(0), used, tokens, experts, world, capacity,
+                                          route["blob"].data_ptr(), send.data_ptr(),
+                                          send_ids.data_ptr(), home.data_ptr(), dropped.data_ptr(),
+                                          _stream()), "llmp_b200_moe_ep_pack")
+    return send, send_ids, home
 
 
 def moe_combine(rows: torch.Tensor, position: torch.Tensor, weights: torch.Tensor, tokens: int,

@@ -124,3 +124,68 @@ def ep_moe_ffn(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, expert
         out = out + y[:, j] * weights[:, j:j + 1]
     del rank, begin
     return out
+
+
+# ------------------------------------------------------------------ fixed-capacity form
+def ep_capacity(tokens: int, used: int, world: int, factor: float = 1.25, multiple: int = 128) -> int:
+    """Rows a rank may send to one destination in a step: the mean load tokens * used / world
+    times `factor`, rounded up to `multiple`.  Sizes are then known before the step, so nothing
+    of the exchange waits on the host."""
+    mean = -(-tokens * used // world)
+    return max(multiple, -(-int(mean * factor) // multiple) * multiple)
+
+
+def pack_reference(x, ids, experts: int, world: int, capacity: int):
+    """What llmp_b200.moe_ep_pack computes, in plain torch (the CPU tests' stand-in): each
+    (token, slot) row goes to lane i of its expert's owner, i counting that owner's rows in
+    (token, slot) order.  Returns send rows [world * capacity, hidden], send ids I32 [world *
+    capacity] (the local expert id, -1 for an unused lane), home I32 [tokens * used] (the
+    row's index world * capacity-wide, -1 for an id outside the experts or a row past the
+    capacity) and the number of rows dropped for capacity."""
+    tokens, used = ids.shape
+    per = experts // world
+    flat = ids.reshape(-1).to(torch.int64)
+    valid = (flat >= 0) & (flat < experts)
+    owner = torch.where(valid, flat // per, torch.zeros_like(flat))
+    send = torch.zeros((world * capacity, x.shape[1]), dtype=x.dtype, device=x.device)
+    send_ids = torch.full((world * capacity,), -1, dtype=torch.int32, device=x.device)
+    home = torch.full((tokens * used,), -1, dtype=torch.int32, device=x.device)
+    count = [0] * world
+    dropped = 0
+    for s in range(tokens * used):
+        if not bool(valid[s]):
+            continue
+        r = int(owner[s])
+        i = count[r]
+        count[r] += 1
+        if i >= capacity:
+            dropped += 1
+            continue
+        send[r * capacity + i] = x[s // used]
+        send_ids[r * capacity + i] = int(flat[s]) - r * per
+        home[s] = r * capacity + i
+    return send, send_ids, home, dropped
+
+
+def ep_moe_ffn_padded(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, experts: int,
+                      capacity: int, pack: Callable, local_compute: Callable, combine: Callable,
+                      group=None) -> torch.Tensor:
+    """Expert-parallel routed block with exchanges of fixed size (no value reaches the host):
+    pack(x, ids) -> (send rows [world * capacity, hidden], send ids I32 [world * capacity],
+    home I32 [tokens * used]); an all-to-all of equal splits carries lane block r to rank r;
+    local_compute(rows, local ids with -1 for unused lanes) -> [world * capacity, hidden_out]
+    runs this rank's experts; the all-to-all back returns every lane to its sender and
+    combine(returned rows, home, weights) sums a token's slots in slot order.  experts must be
+    a multiple of the world size."""
+    world = dist.get_world_size(group)
+    if experts % world != 0:
+        raise ValueError("the fixed-capacity exchange takes experts a multiple of the ranks")
+    send, send_ids, home = pack(x, ids)
+    rows = torch.empty_like(send)
+    local_ids = torch.empty_like(send_ids)
+    dist.all_to_all_single(rows, send, group=group)
+    dist.all_to_all_single(local_ids, send_ids, group=group)
+    y = local_compute(rows, local_ids)
+    back = torch.empty_like(y)
+    dist.all_to_all_single(back, y.contiguous(), group=group)
+    return combine(back, home, weights)

@@ -133,3 +133,56 @@ def test_expert_parallel_all_to_all_equals_one_rank(tmp_path, orc):
         assert np.array_equal(np.isnan(got[rank]), np.isnan(want))
         ok = ~np.isnan(want)
         assert np.array_equal(got[rank][ok], want[ok])
+
+
+def _expert_parallel_padded(rank, world):
+    from llmp_b200 import shard
+    from oracle import binding as orc
+    experts, hidden, inter, gate_up, down = _expert_weights()
+    b, e = shard.expert_range(experts, world, rank)
+    x, ids, w = _tokens(rank)
+    tokens, used = ids.shape
+    capacity = 8                               # small: rank 1's seven-token batch overflows no lane
+
+    def pack(xt, idt):
+        send, send_ids, home, dropped = shard.pack_reference(xt, idt, experts, world, capacity)
+        assert dropped == 0
+        return send, send_ids, home
+
+    def local(rows, local_ids):
+        lid = local_ids.numpy()
+        out = np.full((rows.shape[0], hidden), np.nan, np.float32)     # unused lanes: never read back
+        live = lid >= 0
+        out[live] = _expert_rows(orc, gate_up[b:e], down[b:e], hidden, inter, rows.numpy()[live],
+                                 lid[live])
+        return torch.from_numpy(out)
+
+    def combine(back, home, wt):
+        return torch.from_numpy(orc.moe_combine(back.numpy(), home.numpy(), wt.numpy(), tokens, used))
+
+    return shard.ep_moe_ffn_padded(torch.from_numpy(x), torch.from_numpy(ids), torch.from_numpy(w),
+                                   experts, capacity, pack, local, combine).numpy()
+
+
+def test_fixed_capacity_expert_parallel_equals_one_rank(tmp_path, orc):
+    """The exchange of fixed-size lanes (the form the GPUs run: no split size ever reaches the
+    host) gives the single-rank block bit for bit, ids outside the experts included."""
+    from llmp_b200 import shard
+    got = _run(_expert_parallel_padded, tmp_path)
+    experts, hidden, inter, gate_up, down = _expert_weights()
+    for rank in range(2):
+        x, ids, w = _tokens(rank)
+        tokens, used = ids.shape
+        flat = ids.reshape(-1)
+        rows = _expert_rows(orc, gate_up, down, hidden, inter, x[np.arange(tokens * used) // used],
+                            flat.clip(0, experts - 1))
+        position = np.where((flat >= 0) & (flat < experts), np.arange(tokens * used), -1)
+        want = orc.moe_combine(rows, position.astype(np.int32), w, tokens, used)
+        assert np.array_equal(np.isnan(got[rank]), np.isnan(want))
+        ok = ~np.isnan(want)
+        assert np.array_equal(got[rank][ok], want[ok])
+    assert shard.ep_capacity(1024, 8, 8) == 1280 and shard.ep_capacity(1, 8, 8) == 128
+    # a lane that overflows drops rows and says so
+    x, ids, _ = _tokens(1)
+    _, _, home, dropped = shard.pack_reference(torch.from_numpy(x), torch.from_numpy(ids), 6, 2, 2)
+    assert dropped > 0 and int((home < 0).sum()) == dropped

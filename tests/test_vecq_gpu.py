@@ -104,7 +104,7 @@ def test_every_launch_variant_matches(cuda, orc, wtype, n, k):
             except ops.Rejected:
                 # the specialised kernels refuse what they do not take (as the
                 # reference's LaunchVecQ returns false); the generic ones never do
-                assert name.startswith(("stream", "rowlane")), name
+                assert name.startswith(("stream", "rowlane", "rowmma")), name
                 continue
             taken += 1
             assert_close_to_f64(got, f32, s64, a64, f"{wtype} variant {name} b{tokens}")
@@ -140,10 +140,13 @@ def test_a_token_alone_gives_the_same_bits(cuda, orc, n, k, tokens, glu):
     q8 = ops.quantize_q8(x)
     buf = torch.full((tokens * n + 32,), float("nan"), device="cuda")
     together = buf[: tokens * n].view(tokens, n)
-    ops.vecq(w, orc.Q4_K, k, n, q8, tokens, gate=g, glu=glu, out=together)
+    # variant -2: the launch rule that keeps the one-token geometry (the default, -1, takes
+    # whatever measured fastest for the token count)
+    ops.vecq(w, orc.Q4_K, k, n, q8, tokens, gate=g, glu=glu, out=together, variant=-2)
     assert torch.isnan(buf[tokens * n:]).all() and torch.isfinite(together).all()
     for j in sorted({0, tokens // 2, tokens - 1}):
-        alone = ops.vecq(w, orc.Q4_K, k, n, ops.quantize_q8(x[j:j + 1]), 1, gate=g, glu=glu)
+        alone = ops.vecq(w, orc.Q4_K, k, n, ops.quantize_q8(x[j:j + 1]), 1, gate=g, glu=glu,
+                         variant=-2)
         assert torch.equal(alone[0], together[j]), (j, (alone[0] != together[j]).sum().item())
     assert ops.device_faults() == 0
 
@@ -316,3 +319,105 @@ def test_no_bounded_wait_ran_out(cuda):
     """Collected after the product tests of this file: the TMA-fed kernels'
     bounded mbarrier waits never expired."""
     assert _ops().device_faults() == 0
+
+
+def _exact_q4k_case(rng, n, k, tokens):
+    """Operands whose every product and sum is exact in F32 whatever the order: power-of-two
+    d, dmin and activation scales, small integer scales, minima and activations.  Returns the
+    weights, the F32 activations and the exact result."""
+    nb = k // 256
+    w = rng.integers(0, 256, size=(n, nb, 144), dtype=np.uint8)
+    sc = rng.integers(0, 4, size=(n * nb, 8), dtype=np.uint8)
+    mn = rng.integers(0, 4, size=(n * nb, 8), dtype=np.uint8)
+    w[:, :, 4:16] = synth.pack_q4_k_scales(sc, mn).reshape(n, nb, 12)
+    w[:, :, 0:2] = np.array([2.0 ** -6], np.float16).view(np.uint8)
+    w[:, :, 2:4] = np.array([2.0 ** -5], np.float16).view(np.uint8)
+    w = w.reshape(n, nb * 144)
+    q = rng.integers(-7, 8, size=(tokens, k)).astype(np.float32)
+    q[:, ::32] = 127.0                                   # every block's amax: d8 = 1/8 exactly
+    x = q / 8.0
+    codes = np.empty((n, k), np.int64)
+    raw = w.reshape(n, nb, 144)[:, :, 16:].reshape(n, nb, 4, 32)
+    for c in range(4):
+        codes.reshape(n, nb, 8, 32)[:, :, 2 * c] = raw[:, :, c] & 15
+        codes.reshape(n, nb, 8, 32)[:, :, 2 * c + 1] = raw[:, :, c] >> 4
+    scale = np.repeat(sc.reshape(n, nb * 8).astype(np.int64), 32, axis=1)
+    minimum = np.repeat(mn.reshape(n, nb * 8).astype(np.int64), 32, axis=1)
+    qi = q.astype(np.int64)
+    exact = ((codes * scale) @ qi.T).T * (2.0 ** -6 / 8.0) - (minimum @ qi.T).T * (2.0 ** -5 / 8.0)
+    return w, x, exact.astype(np.float64)
+
+
+@pytest.mark.parametrize("variant", ["rowlane", "rowlane.packed", "rowmma", "stream", "l8r1u2w4"])
+@pytest.mark.parametrize("n,k,tokens", [(300, 2560, 1), (77, 1024, 4), (2560, 10240, 1)])
+def test_product_kernels_integer_sums_are_exact(cuda, orc, variant, n, k, tokens):
+    """Each shipped kernel's own int32 accumulation (nibble masks, the x16 trick, dp4a or mma
+    chains): with operands whose arithmetic is exact in F32 whatever the order, the output must
+    equal the exact value bit for bit; any slip in an integer sum shows."""
+    torch = cuda
+    ops = _ops()
+    rng = np.random.default_rng(n + k)
+    w, x, exact = _exact_q4k_case(rng, n, k, tokens)
+    q8 = ops.quantize_q8(to_dev(torch, x))
+    names = ops.vecq_variants()
+    try:
+        got = ops.vecq(to_dev(torch, w), orc.Q4_K, k, n, q8, tokens, variant=names.index(variant))
+    except ops.Rejected:
+        pytest.skip(f"{variant} does not take this shape")
+    assert np.array_equal(got.cpu().numpy().astype(np.float64), exact)
+    assert ops.device_faults() == 0
+
+
+@pytest.mark.parametrize("n,k,tokens,glu", [(10240, 2560, 1, 3), (2560, 10240, 1, 0), (10240, 2560, 8, 3),
+                                            (333, 2560, 3, 1), (2560, 10240, 8, 0), (41, 512, 2, 0),
+                                            (1000, 4096, 1, 0), (5000, 7168, 2, 1)])
+def test_rowmma_matches_the_oracle_and_keeps_a_token_alone(cuda, orc, n, k, tokens, glu):
+    torch = cuda
+    ops = _ops()
+    rng = np.random.default_rng(n + k + tokens)
+    v = ops.vecq_variants().index("rowmma")
+    w = synth.q4_k_weights(rng, n, k)
+    g = synth.q4_k_weights(rng, n, k) if glu else None
+    x = rng.normal(0, 1, size=(tokens, k)).astype(np.float32)
+    q8 = ops.quantize_q8(to_dev(torch, x))
+    wd, gd = to_dev(torch, w), (to_dev(torch, g) if glu else None)
+    buf = torch.full((tokens * n + 32,), float("nan"), device="cuda")
+    out = buf[: tokens * n].view(tokens, n)
+    ops.vecq(wd, orc.Q4_K, k, n, q8, tokens, gate=gd, glu=glu, out=out, variant=v)
+    torch.cuda.synchronize()
+    assert ops.device_faults() == 0
+    assert torch.isnan(buf[tokens * n:]).all() and torch.isfinite(out).all()
+    if glu:
+        want = orc.vecq(orc.Q4_K, w, q8.cpu().numpy(), k, n, tokens, g=g, glu=glu)[:, 0, :]
+        assert np.abs(out.cpu().numpy() - want).max() <= 4e-5 * np.abs(want).max()
+    else:
+        f32, s64, a64 = orc.vecq(orc.Q4_K, w, q8.cpu().numpy(), k, n, tokens, want64=True)
+        assert_close_to_f64(out.cpu().numpy(), f32[:, 0, :], s64[:, 0, :], a64[:, 0, :], "rowmma")
+    if tokens > 1:
+        j = tokens - 1
+        alone = ops.vecq(wd, orc.Q4_K, k, n, ops.quantize_q8(to_dev(torch, x[j:j + 1])), 1, gate=gd,
+                         glu=glu, variant=v)
+        assert torch.equal(alone[0], out[j])
+
+
+def test_rank_table_names_configurations_the_library_has(cuda, orc):
+    """Every row of the measured rank table names a launch configuration that exists, and
+    the default launch of a listed product gives the oracle's result."""
+    torch = cuda
+    ops = _ops()
+    names = set(ops.vecq_variants())
+    rows = ops.vecq_ranks()
+    assert len(rows) >= 8
+    for r in rows:
+        assert r["variant"] in names, r
+        assert r["tokens"] in (1, 2, 4, 8) and r["k"] % 256 == 0 and r["microseconds"] > 0
+    rng = np.random.default_rng(3)
+    for r in [x for x in rows if x["n"] * x["k"] <= 2560 * 10240 and not x["glu"]][:12]:
+        n, k, tokens = r["n"], r["k"], r["tokens"]
+        w = synth.q4_k_weights(rng, n, k)
+        x = rng.normal(0, 1, size=(tokens, k)).astype(np.float32)
+        q8 = ops.quantize_q8(to_dev(torch, x))
+        got = ops.vecq(to_dev(torch, w), orc.Q4_K, k, n, q8, tokens).cpu().numpy()
+        f32, s64, a64 = orc.vecq(orc.Q4_K, w, q8.cpu().numpy(), k, n, tokens, want64=True)
+        assert_close_to_f64(got, f32[:, 0, :], s64[:, 0, :], a64[:, 0, :], str(r))
+    assert ops.device_faults() == 0

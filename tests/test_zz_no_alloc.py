@@ -67,3 +67,22 @@ def test_static_tile_list_refuses_what_exceeds_it(cuda):
     assert status == N.REJECTED
     assert "256 groups" in N.last_error()
     torch.cuda.synchronize()
+
+
+def test_static_tile_list_at_its_group_limit(cuda):
+    """Exactly 256 groups (the built-in list's limit), most of them with a row or none."""
+    torch = cuda
+    import llmp_b200 as ops
+    from llmp_b200 import _native as N
+    rng = np.random.default_rng(256)
+    experts, n, k, rows = 256, 8, 256, 300
+    w = to_dev(torch, synth.q4_k_weights(rng, experts * n, k).reshape(experts, n, -1))
+    counts = np.bincount(rng.integers(0, experts, size=rows), minlength=experts)
+    offsets = to_dev(torch, np.concatenate([[0], np.cumsum(counts)]).astype(np.int32))
+    x = to_dev(torch, rng.normal(0, 1, size=(rows, k)).astype(np.float32))
+    aq = ops.mmq_quantize(x)
+    want = ops.grouped_gemm(w, aq, offsets, k, n)
+    got = torch.full_like(want, float("nan"))
+    assert _call_static(N, w, aq, offsets, k, n, got) == 0, N.last_error()
+    torch.cuda.synchronize()
+    assert torch.equal(got, want) and torch.isfinite(got).all()
