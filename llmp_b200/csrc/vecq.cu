@@ -279,7 +279,7 @@ int LaunchVecQ(int type, const llmp_b200_vecq_desc* desc, int variant, bool f32_
                  &plan);
   RowLanePlan lanes;
   const bool aligned16 = Aligned(d.w, 16) && (d.g == nullptr || Aligned(d.g, 16));
-  if (variant >= kRowMmaVariant && variant < kRowLaneSplitVariant) {
+  if (variant >= kRowMmaVariant) {
     RowMmaPlan tiles;
     const int ctas = variant == kRowMmaVariant ? 1 : kVariants[variant].u;
     if (!(dense && q4 && aligned16 && f32_input == false && q8_dst == nullptr &&
@@ -294,12 +294,8 @@ int LaunchVecQ(int type, const llmp_b200_vecq_desc* desc, int variant, bool f32_
   bool rowlane_ok = false;
   if (dense && q4 && Aligned(d.w, 16) && (d.g == nullptr || Aligned(d.g, 16))) {
     if (wants_rowlane) {
-      const Variant& forced = kVariants[variant];
-      const bool split = variant >= kRowLaneSplitVariant;
-      const int share = split ? std::max(2, forced.warps) : 2;
-      rowlane_ok = PlanRowLane(d, p, split ? share * SmCount() : SmCount(), forced.r,
-                               forced.u == 1 || split, &lanes, 0, forced.u == 2 || forced.u == 4,
-                               (!split && forced.warps > 0) ? forced.warps : kRowLaneWarps, share);
+      rowlane_ok = PlanRowLane(d, p, SmCount(), kVariants[variant].r, kVariants[variant].u == 1,
+                               &lanes);
     } else {
       // A row's sum adds its super-blocks up in an order the geometry (rows and phases
       // a warp) fixes.  So that a token gives the same bits alone or in company, more

@@ -509,8 +509,6 @@ constexpr Variant kVariants[] = {
     {"rowlane.r32", 0, 32, 0, 0},
     // Half an SM a CTA (u field = 1), so consecutive kernels overlap.
     {"rowlane.half", 0, 0, 1, 0},
-    // Whole rows in one bulk copy a warp and matrix (u field = 2).
-    {"rowlane.packed", 0, 0, 2, 0},
     // The int8 products on mma.sync tiles of 16 rows (vecq_rowmma.cuh); dense Q4_K
     // products of up to 8 tokens.
     {"rowmma", 0, 0, 0, 0},
@@ -518,24 +516,11 @@ constexpr Variant kVariants[] = {
     {"rowmma.c2", 0, 0, 2, 0},
     {"rowmma.c3", 0, 0, 3, 0},
     {"rowmma.c4", 0, 0, 4, 0},
-    // The row-lane kernel as two half-SM CTAs an SM (u field = 3).
-    {"rowlane.c2", 0, 0, 3, 0},
-    // ... with whole rows in one bulk copy a warp and matrix (u field = 4).
-    {"rowlane.packed.c2", 0, 0, 4, 0},
-    // Several small CTAs an SM (warps field: how many), each with its whole share resident;
-    // u = 4: whole rows in one bulk copy a warp and matrix.
-    {"rowlane.c3", 0, 0, 3, 3},
-    {"rowlane.c4", 0, 0, 3, 4},
-    {"rowlane.c6", 0, 0, 3, 6},
-    {"rowlane.c8", 0, 0, 3, 8},
-    {"rowlane.packed.c4", 0, 0, 4, 4},
-    {"rowlane.packed.c8", 0, 0, 4, 8},
 };
 constexpr int kVariantCount = static_cast<int>(sizeof(kVariants) / sizeof(kVariants[0]));
-constexpr int kStreamVariant = kVariantCount - 22;
-constexpr int kRowLaneVariant = kVariantCount - 21;  // and its eight forced forms after it
-constexpr int kRowMmaVariant = kVariantCount - 12;   // and its three split forms after it
-constexpr int kRowLaneSplitVariant = kVariantCount - 8;  // and the other split forms after it
+constexpr int kStreamVariant = kVariantCount - 13;
+constexpr int kRowLaneVariant = kVariantCount - 12;  // and its seven forced forms after it
+constexpr int kRowMmaVariant = kVariantCount - 4;    // and its three split forms after it
 
 template <typename Unit, int P, int LPR, int R, int U, bool kGlu>
 cudaError_t LaunchOne(const Desc& d, int warps, cudaStream_t stream) {

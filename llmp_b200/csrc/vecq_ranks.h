@@ -23,8 +23,8 @@ struct MeasuredRank {
 constexpr MeasuredRank kMeasuredRanks[] = {
     // k, n, fused GLU, tokens, variant, microseconds a launch, GB/s of weight bytes
     {2560, 10240, 1, 1, "rowlane", 8.784f, 3357},
-    {2560, 10240, 1, 2, "rowlane.packed", 9.824f, 3002},
-    {2560, 10240, 1, 4, "rowlane.packed", 13.278f, 2221},
+    {2560, 10240, 1, 2, "rowlane", 10.567f, 2791},
+    {2560, 10240, 1, 4, "rowlane", 14.096f, 2092},
     {2560, 10240, 1, 8, "rowlane", 31.543f, 935},
     {10240, 2560, 0, 1, "rowmma.c2", 5.202f, 2835},
     {10240, 2560, 0, 2, "rowmma", 8.281f, 1781},
@@ -38,7 +38,7 @@ constexpr MeasuredRank kMeasuredRanks[] = {
     {4096, 14336, 1, 2, "rowlane", 25.883f, 2552},
     {4096, 14336, 1, 4, "rowmma", 32.251f, 2048},
     {4096, 14336, 1, 8, "rowlane", 63.216f, 1045},
-    {14336, 4096, 0, 1, "rowlane.c2", 11.029f, 2995},
+    {14336, 4096, 0, 1, "rowmma", 11.069f, 2984},
     {14336, 4096, 0, 2, "rowmma", 13.099f, 2522},
     {14336, 4096, 0, 4, "rowmma", 17.533f, 1884},
     {14336, 4096, 0, 8, "rowlane", 29.213f, 1131},
@@ -46,20 +46,20 @@ constexpr MeasuredRank kMeasuredRanks[] = {
     {2048, 2048, 0, 2, "rowlane", 3.021f, 781},
     {2048, 2048, 0, 4, "rowmma", 4.269f, 553},
     {2048, 2048, 0, 8, "rowmma", 6.031f, 391},
-    {8192, 8192, 0, 1, "rowlane.c2", 10.950f, 3447},
-    {8192, 8192, 0, 2, "rowlane.c2", 13.065f, 2889},
+    {8192, 8192, 0, 1, "rowmma.c2", 11.040f, 3419},
+    {8192, 8192, 0, 2, "rowmma.c2", 13.344f, 2829},
     {8192, 8192, 0, 4, "rowmma", 18.263f, 2067},
     {8192, 8192, 0, 8, "rowlane", 31.200f, 1210},
     {2048, 1536, 0, 1, "rowlane", 2.232f, 793},
-    {2048, 1536, 0, 2, "rowlane.packed", 2.888f, 613},
+    {2048, 1536, 0, 2, "rowlane", 2.979f, 594},
     {2048, 1536, 0, 4, "rowmma", 4.114f, 430},
     {2048, 1536, 0, 8, "rowmma", 5.839f, 303},
-    {2048, 6144, 1, 1, "rowlane.c2", 4.929f, 2872},
+    {2048, 6144, 1, 1, "rowlane", 5.259f, 2692},
     {2048, 6144, 1, 2, "rowlane", 6.814f, 2077},
     {2048, 6144, 1, 4, "rowlane", 9.784f, 1447},
     {2048, 6144, 1, 8, "rowlane", 17.121f, 827},
-    {6144, 2048, 0, 1, "rowlane.packed", 3.440f, 2058},
-    {6144, 2048, 0, 2, "rowlane.packed", 4.872f, 1453},
+    {6144, 2048, 0, 1, "rowlane", 3.742f, 1891},
+    {6144, 2048, 0, 2, "rowmma", 4.934f, 1435},
     {6144, 2048, 0, 4, "rowmma", 5.655f, 1252},
     {6144, 2048, 0, 8, "rowmma", 8.567f, 826},
     {4096, 11008, 1, 1, "rowlane", 13.408f, 3783},
@@ -70,7 +70,7 @@ constexpr MeasuredRank kMeasuredRanks[] = {
     {11008, 4096, 0, 2, "rowmma", 9.710f, 2612},
     {11008, 4096, 0, 4, "rowmma", 14.074f, 1802},
     {11008, 4096, 0, 8, "rowmma", 20.650f, 1228},
-    {5120, 5120, 0, 1, "rowlane.packed", 5.773f, 2554},
+    {5120, 5120, 0, 1, "rowlane", 6.037f, 2443},
     {5120, 5120, 0, 2, "rowmma", 7.333f, 2011},
     {5120, 5120, 0, 4, "rowmma", 10.033f, 1470},
     {5120, 5120, 0, 8, "rowmma", 15.009f, 982},

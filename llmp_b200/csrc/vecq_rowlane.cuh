@@ -33,16 +33,9 @@
 namespace llmp_b200 {
 namespace vecq {
 
-constexpr int kRowLaneMaxWarps = 12;      // a CTA that owns its SM: 12 warps leave a thread up to
-                                          // 168 registers, which the unrolled loads want (24 warps
-                                          // of 85 registers measured slower: 9.2 against 7.9 us)
-constexpr int kRowLaneWarps = 12;         // ... by default
-constexpr int kRowLaneHalfWarps = 9;      // a CTA that shares its SM with the next kernel's (12 for
-                                          // one token a pass: 85 registers a thread)
+constexpr int kRowLaneMaxWarps = 12;      // a CTA that owns its SM
+constexpr int kRowLaneHalfWarps = 9;      // a CTA that shares its SM with the next kernel's
 constexpr int kRowLaneMaxStages = 8;
-
-__host__ __device__ constexpr int RowLaneWarpLimit(int p) { return p >= 1 ? 12 : 12; }
-__host__ __device__ constexpr int RowLaneHalfWarpLimit(int p) { return p == 1 ? 12 : 9; }
 
 struct RowLanePlan {
   int warps;         // W
@@ -57,8 +50,6 @@ struct RowLanePlan {
   int smem_bytes;
   int grid;
   int half;          // the kHalf instantiation
-  int packed;        // whole rows, all steps, in ONE bulk copy a warp and matrix (rows contiguous
-                     // in memory, ring depth = steps): pitch = a row's bytes
   double score;      // the planner's figure of merit (lane use x warps x ring depth)
   int f32_input;     // activations are F32: quantize to Q8_1 while staging
   int q8_row_blocks; // Q8_1 blocks between tokens' rows in q8_out
@@ -74,7 +65,7 @@ struct RowLanePlan {
 // after this one (launched as a programmatic dependent) becomes resident and
 // requests its weights while this one still computes.
 template <int P, bool kGlu, bool kHalf>
-__global__ void __launch_bounds__(kHalf ? RowLaneHalfWarpLimit(P) * 32 : RowLaneWarpLimit(P) * 32,
+__global__ void __launch_bounds__(kHalf ? kRowLaneHalfWarps * 32 : kRowLaneMaxWarps * 32,
                                   kHalf ? 2 : 1)
 VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
   constexpr int kMats = kGlu ? 2 : 1;
@@ -138,19 +129,7 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
 
   GridLaunchDependents();
   if (my_rows > 0) {
-    if (plan.packed) {
-      // The warp's rows are one contiguous run of the matrix: a single copy a matrix.
-      const std::uint32_t bytes = static_cast<std::uint32_t>(my_rows) * static_cast<std::uint32_t>(UR) * 144u;
-      if (lane == 0) MbarExpectTx(&full[warp][0], bytes * kMats);
-      __syncwarp();
-      if (lane < kMats) {
-        BulkLoad(ring + (static_cast<std::size_t>(lane) * R * plan.pitch),
-                 mats[lane] + (static_cast<std::size_t>(row_begin) * a.stride_row * 144), bytes,
-                 &full[warp][0]);
-      }
-    } else {
-      for (int j = 0; j < min(S, J); ++j) request(j);
-    }
+    for (int j = 0; j < min(S, J); ++j) request(j);
   }
   GridDependencyWait();
 
@@ -247,14 +226,13 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
 
   bool healthy = true;
   for (int j = 0; j < J; ++j) {
-    const int s = plan.packed ? 0 : j % S;
-    if (healthy && lane == 0 && (j == 0 || !plan.packed) &&
-        !MbarWait(&full[warp][s], plan.packed ? 0u : static_cast<std::uint32_t>((j / S) & 1))) {
+    const int s = j % S;
+    if (healthy && lane == 0 &&
+        !MbarWait(&full[warp][s], static_cast<std::uint32_t>((j / S) & 1))) {
       healthy = false;
       atomicAdd(plan.faults, 1u);
     }
-    healthy = __shfl_sync(0xffffffffu, healthy ? 1 : 0, 0) != 0;
-    if (!healthy) return;  // nothing of an incomplete stage is summed or stored
+    __syncwarp();
     const int c = (j * PH) + ph;
     if (ph < PH && c < UR && r < my_rows) {
       const unsigned char* base = ring + (static_cast<std::size_t>(s) * plan.stage_bytes);
@@ -266,8 +244,7 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
 #pragma unroll
       for (int m = 0; m < kMats; ++m) {
         Q4KBlockUnit raw;
-        raw.LoadShared(base + ((static_cast<std::size_t>(m) * R + r) * plan.pitch),
-                       plan.packed ? c : ph);
+        raw.LoadShared(base + ((static_cast<std::size_t>(m) * R + r) * plan.pitch), ph);
         int sc[8], mn[8];
         Q4KBlockScales(raw, sc, mn);
         float fmn[8];
@@ -337,11 +314,14 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
       }
     }
     __syncwarp();
-    if (!plan.packed && j + S < J) {
+    if (j + S < J) {
       FenceProxyAsync();
       request(j + S);
     }
   }
+
+  // A stage that never arrived: nothing of this warp's rows is stored.
+  if (__shfl_sync(0xffffffffu, healthy ? 1 : 0, 0) == 0) return;
 
   // The phases of a row meet in phase order: lane r adds lanes r + R, r + 2R, ...
 #pragma unroll
@@ -415,21 +395,16 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
 
 // Host: the geometry for a dense Q4_K product, or false if it does not fit.
 inline bool PlanRowLane(const Desc& d, int p, int sms, int force_rows, bool half,
-                        RowLanePlan* plan, int force_phases = 0, bool packed = false,
-                        int warps_limit = kRowLaneWarps, int share = 2) {
+                        RowLanePlan* plan, int force_phases = 0) {
   const int mats = d.glu != LLMP_B200_GLU_NONE ? 2 : 1;
   const int ur = d.ncols_x / 256;
   if (ur < 1) return false;
   const int grid = std::max(1, std::min(sms, d.nrows));
   const int cta_rows = (d.nrows + grid - 1) / grid;
   const int acts_bytes = (ur * 256) + (ur * 64);
-  // half: the CTA takes 1 / share of an SM's shared memory and warps (share = 2: the next
-  // kernel's CTA fits beside it; more: several small CTAs an SM, `sms` then counts them all)
-  const int budget = (half ? 220 / share : 220) * 1024 - (p * acts_bytes) - 1024;
-  const int max_warps = half ? std::max(1, std::min(RowLaneHalfWarpLimit(p), 24 / share))
-                             : std::min(warps_limit, RowLaneWarpLimit(p));
+  const int budget = (half ? 110 : 220) * 1024 - (p * acts_bytes) - 1024;
+  const int max_warps = half ? kRowLaneHalfWarps : kRowLaneMaxWarps;
   if (budget <= 0) return false;
-  if (packed && d.stride_row != ur) return false;  // rows must follow one another in memory
   double best_score = -1.0;
   RowLanePlan best{};
   for (int rows = 1; rows <= 32; ++rows) {
@@ -462,26 +437,19 @@ inline bool PlanRowLane(const Desc& d, int p, int sms, int force_rows, bool half
       }
       pitch16 += best_pad;
     }
-    const int pitch = packed ? ur * 144 : pitch16 * 16;
+    const int pitch = pitch16 * 16;
     const int stage_bytes = rows * pitch * mats;
     int stages = std::min({steps, kRowLaneMaxStages, budget / (warps * stage_bytes)});
-    if (packed) {
-      // one stage holds every step: the whole of the warp's rows
-      if (warps * stage_bytes > budget) continue;
-      stages = 1;
-    }
     if (stages < 1) continue;
     // (a forced geometry may run on a one-stage ring: slower, but the sums keep their order)
-    // (a CTA that owns its SM wants two stages a warp when the ring is recycled; one that
-    // shares it runs on one: the neighbour CTA's copies fill the gaps)
-    if (!packed && !half && stages < steps && stages < 2 && force_phases == 0) continue;
+    if (stages < steps && stages < 2 && force_phases == 0) continue;
     // Lane utilization, with a preference for more warps and for a ring that
     // holds the whole range.
     // (all 32 lanes of every warp count: lanes past R * PH idle)
     const double lanes = static_cast<double>(cta_rows) * ur /
                          (static_cast<double>(warps) * 32 * steps);
     const double score = lanes * (0.6 + 0.4 * std::min(1.0, warps / 8.0)) *
-                         (0.7 + 0.3 * (packed ? 1.0 : static_cast<double>(stages) / steps));
+                         (0.7 + 0.3 * static_cast<double>(stages) / steps);
     if (score > best_score) {
       best_score = score;
       best.warps = warps;
@@ -496,7 +464,6 @@ inline bool PlanRowLane(const Desc& d, int p, int sms, int force_rows, bool half
       best.smem_bytes = (p * acts_bytes) + (warps * stages * stage_bytes);
       best.grid = grid;
       best.half = half ? 1 : 0;
-      best.packed = packed ? 1 : 0;
       best.score = score;
       best.f32_input = 0;
       best.q8_row_blocks = 0;

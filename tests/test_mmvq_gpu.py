@@ -62,7 +62,7 @@ def test_mmvq_rows_columns_are_the_one_column_bits(cuda, orc, wtype, n, k, cols)
     ops.mmvq(w, t, k, n, x, rows=True, out=out)
     assert torch.isnan(buf[cols * n:]).all() and torch.isfinite(out).all()
     for c in sorted({0, 3, 8, cols - 1}):
-        alone = ops.mmvq(w, t, k, n, x[c:c + 1].contiguous())
+        alone = ops.mmvq(w, t, k, n, x[c:c + 1].contiguous(), rows=True)
         assert torch.equal(alone[0], out[c]), (c, int((alone[0] != out[c]).sum()))
     want = orc.vecq(t, w.cpu().numpy(), orc.quantize_q8_1(x.cpu().numpy()), k, n, cols)[:, 0, :]
     assert np.abs(out.cpu().numpy() - want).max() <= 1e-5 * np.abs(want).max()

@@ -273,7 +273,7 @@ def test_fused_quantization_gives_the_two_call_bits(cuda, orc, n, k, tokens, glu
     x[0, 32:64] = 0.0
     xd = to_dev(torch, x)
     q8 = ops.quantize_q8(xd)
-    want = ops.vecq(w, orc.Q4_K, k, n, q8, tokens, gate=g, glu=glu)
+    want = ops.vecq(w, orc.Q4_K, k, n, q8, tokens, gate=g, glu=glu, variant=-2)  # the same kernel
     q8_out = torch.zeros_like(q8)
     got = ops.vecq_f32(w, orc.Q4_K, k, n, xd, gate=g, glu=glu, q8_out=q8_out)
     assert torch.equal(got, want)
@@ -299,7 +299,7 @@ def test_fused_output_quantization_gives_the_two_call_bits(cuda, orc, n, k, toke
     g = to_dev(torch, synth.q4_k_weights(rng, n, k)) if glu else None
     x = rng.normal(0, 1, size=(tokens, k)).astype(np.float32)
     q8 = ops.quantize_q8(to_dev(torch, x))
-    want = ops.vecq(w, orc.Q4_K, k, n, q8, tokens, gate=g, glu=glu)
+    want = ops.vecq(w, orc.Q4_K, k, n, q8, tokens, gate=g, glu=glu, variant=-2)  # the same kernel
     want_q8 = ops.quantize_q8(want)
     rows_done = ops.vecq_q8_scratch(n, tokens, "cuda")
     for _ in range(2):
@@ -348,7 +348,7 @@ def _exact_q4k_case(rng, n, k, tokens):
     return w, x, exact.astype(np.float64)
 
 
-@pytest.mark.parametrize("variant", ["rowlane", "rowlane.packed", "rowmma", "stream", "l8r1u2w4"])
+@pytest.mark.parametrize("variant", ["rowlane", "rowlane.half", "rowmma", "rowmma.c2", "stream", "l8r1u2w4"])
 @pytest.mark.parametrize("n,k,tokens", [(300, 2560, 1), (77, 1024, 4), (2560, 10240, 1)])
 def test_product_kernels_integer_sums_are_exact(cuda, orc, variant, n, k, tokens):
     """Each shipped kernel's own int32 accumulation (nibble masks, the x16 trick, dp4a or mma
