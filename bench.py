@@ -496,7 +496,7 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
                 "launch": "cuda graph replay" if use_graph else "stream launches",
                 "timing": f"median of {repeats} blocks of {args.steps} steps, CUDA events on the "
                           "launching stream, max over ranks",
-                "launches_per_layer": FfnStep.launches_per_layer_of(world, args.fused, args.q8_out),
+                "launches_per_layer": FfnStep.launches_per_layer_of(parts, args.fused, args.q8_out),
                 "parallelism": "single GPU" if world == 1 else
                                (f"N-column shards x{world}, NCCL all-gather of the GLU output and of "
                                 "the layer output" if sharded else
@@ -761,10 +761,10 @@ def bench_mmq_sharded(torch, dist, ops, rank, world, tokens=4096, steps=10, warm
         w_full = None
 
     def step():
-        yq = ops.mmq_quantize(x)
         works = []
         for c in range(chunks):
-            ops.mmq(None, yq[:, c * mc:(c + 1) * mc], k, width, out=mine[c], slab=slab)
+            yq = ops.mmq_quantize(x[c * mc:(c + 1) * mc])
+            ops.mmq(None, yq, k, width, out=mine[c], slab=slab)
             works.append(dist.all_gather_into_tensor(full[c], mine[c], async_op=True))
         for w in works:
             w.wait()
@@ -965,20 +965,29 @@ def bench_ffn_columns(torch, dist, ops, rank, world, batch, steps=5, warmup=2):
     ms = _max_over_ranks(torch, dist, e0.elapsed_time(e1) / steps)
     step(keep=True)
     torch.cuda.synchronize()
-    parity = True
+    # The F32 sums of a decode product are added in an order the launch geometry fixes, and
+    # the geometry follows the rows a CTA owns, so a shard's sums agree with the whole
+    # matrix's to rounding, not bit for bit: the bar is the path's 1e-5 of the output scale
+    # (the down product is checked on the gathered GLU output itself).
+    parity, bits, worst = True, True, 0.0
     if rank == 0:
         for l in check_layers:
             gate, up, down = whole[l]
             q = ops.quantize_q8(x[l])
             h = ops.vecq(up, T, HIDDEN, INTER, q, batch, gate=gate, glu=ops.GLU_GEGLU)
-            y = ops.vecq(down, T, INTER, HIDDEN, ops.quantize_q8(h), batch)
+            y = ops.vecq(down, T, INTER, HIDDEN, ops.quantize_q8(h_seen[l]), batch)
             got_y = y_full[l].transpose(0, 1).reshape(batch, HIDDEN)
-            parity = parity and bool(torch.equal(h_seen[l], h)) and bool(torch.equal(got_y, y))
+            for got, want in ((h_seen[l], h), (got_y, y)):
+                err = float((got - want).abs().max() / want.abs().max())
+                worst = max(worst, err)
+                parity = parity and err <= 1e-5
+                bits = bits and bool(torch.equal(got, want))
     parity = _all_true(torch, dist, parity)
     sb = step_bytes(batch)
     return {"metric": METRIC, "value": round(sb / (ms * 1e-3) / 1e9, 2), "unit": UNIT,
             "ms_per_step": round(ms, 4), "n_gpus": world, "steps": steps, "warmup": warmup,
-            "scaling": "strong", "parity": parity, "faults": ops.device_faults(),
+            "scaling": "strong", "parity": parity, "parity_bar": "1e-5 of the output scale",
+            "max_rel_err": worst, "bit_equal": bits, "faults": ops.device_faults(),
             "config": {"workload": f"Gemma-3-4B FFN decode products, Q4_K, {LAYERS} layers, batch {batch}",
                        "parallelism": f"N-column shards x{world}, NCCL all-gather of the GLU output "
                                       "and of the layer output, plain stream launches"}}

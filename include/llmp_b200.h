@@ -350,7 +350,8 @@ int llmp_b200_moe_ep_pack(const float* x, int64_t x_stride, int hidden, const in
 
 /* Replaces llmp.moe.combine_sorted (llmp_moe.cu:393-435) without NVFP4's global
  * scales and the shared expert: dst[t] = sum over the token's slots, in slot
- * order, of rows[position[t * used + j]] * weights[t * used + j]. */
+ * order, of rows[position[t * used + j]] * weights[t * used + j].  position NULL: the rows
+ * are already in slot order (row t * used + j), as the routed decode products leave them. */
 int llmp_b200_moe_combine(const float* rows, int64_t row_stride, const int32_t* position,
                           const float* weights, int used, int tokens, int width, float* dst,
                           void* stream);

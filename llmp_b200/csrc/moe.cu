@@ -295,7 +295,7 @@ __global__ void CombineKernel(const float* __restrict__ rows, std::int64_t row_s
   const float nan = __uint_as_float(0x7fc00000u);
   float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
   for (int j = 0; j < used; ++j) {
-    const int p = position[(t * used) + j];
+    const int p = position != nullptr ? position[(t * used) + j] : static_cast<int>((t * used) + j);
     const float w = weights[(t * used) + j];
     float4 v = make_float4(nan, nan, nan, nan);
     if (p >= 0) v = *reinterpret_cast<const float4*>(rows + (static_cast<std::int64_t>(p) * row_stride) + (c4 * 4));
@@ -578,7 +578,7 @@ int llmp_b200_moe_combine(const float* rows, int64_t row_stride, const int32_t* 
                           const float* weights, int used, int tokens, int width, float* dst,
                           void* stream) {
   using namespace llmp_b200;
-  if (rows == nullptr || position == nullptr || weights == nullptr || dst == nullptr || used < 1 ||
+  if (rows == nullptr || weights == nullptr || dst == nullptr || used < 1 ||
       tokens < 1 || width < 4 || width % 4 != 0 || row_stride < width || row_stride % 4 != 0) {
     return Reject("moe.combine: sorted rows F32 [width, slots], width a positive multiple of 4");
   }

@@ -371,6 +371,8 @@ def q4k_relayout(weights: torch.Tensor, k: int, n: int) -> torch.Tensor:
 def _mmq_desc(weights, yq, k, n, wtype, ids_dst, expert_bounds, out_cols, max_cols_per_expert,
               stride_row, stride_expert, out, slab, scratch):
     _need(yq, torch.uint8, "mmq activations")
+    if yq.dim() != 3 or yq.shape[2] != 144 or not yq.is_contiguous():
+        raise Rejected("mmq: packed Q8_1-MMQ blocks [k / 128, cols, 144]")
     ncols = yq.shape[1]
     out_cols = ncols if out_cols is None else out_cols
     if out is None:
@@ -513,15 +515,19 @@ def moe_ep_pack(x: torch.Tensor, ids: torch.Tensor, experts: int, world: int, ca
     return send, send_ids, home
 
 
-def moe_combine(rows: torch.Tensor, position: torch.Tensor, weights: torch.Tensor, tokens: int,
-                used: int) -> torch.Tensor:
-    """MoeCombineSorted: rows F32 [slots, width] -> F32 [tokens, width]."""
+def moe_combine(rows: torch.Tensor, position: torch.Tensor | None, weights: torch.Tensor, tokens: int,
+                used: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """MoeCombineSorted: rows F32 [slots, width] -> F32 [tokens, width]; position None: the
+    rows are in slot order."""
     _need(rows, torch.float32, "moe_combine rows")
-    _need(position, torch.int32, "moe_combine position")
+    if position is not None:
+        _need(position, torch.int32, "moe_combine position")
     _need(weights, torch.float32, "moe_combine weights")
     width = rows.shape[1]
-    out = torch.empty((tokens, width), dtype=torch.float32, device=rows.device)
-    N.check(N.lib().llmp_b200_moe_combine(rows.data_ptr(), rows.stride(0), position.data_ptr(),
+    if out is None:
+        out = torch.empty((tokens, width), dtype=torch.float32, device=rows.device)
+    N.check(N.lib().llmp_b200_moe_combine(rows.data_ptr(), rows.stride(0),
+                                          position.data_ptr() if position is not None else None,
                                           weights.data_ptr(), used, tokens, width, out.data_ptr(),
                                           _stream()), "llmp_b200_moe_combine")
     return out
@@ -548,21 +554,22 @@ def moe_ffn(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, gate_up: 
         gate_w = gate_up[:, :inter]
         up_w = gate_up[:, inter:]
         bpr = hidden // 256
-        xf = x.float()
-        weights = weights.contiguous()
+        xf = x if x.dtype == torch.float32 else x.float()
+        weights = weights if weights.is_contiguous() else weights.contiguous()
         out = torch.empty((tokens, hidden), dtype=torch.float32, device=x.device)
+        # Five launches a call of up to `chunk` tokens, nothing else queued: quantize, the routed
+        # gate|up GLU product, quantize, the routed down product, the ordered combine (its rows
+        # are already in slot order).
         for t0 in range(0, tokens, chunk):
             t1 = min(tokens, t0 + chunk)
             n = t1 - t0
-            part_ids = ids[t0:t1].contiguous()
+            part_ids = ids[t0:t1]
             q8 = quantize_q8(xf[t0:t1])
             h = vecq(up_w, TYPE_Q4_K, hidden, inter, q8, n, ids=part_ids, gate=gate_w, glu=glu,
                      stride_row=bpr, stride_expert=2 * inter * bpr)
             q8h = quantize_q8(h.view(n * used, inter))
             y = vecq(down, TYPE_Q4_K, inter, hidden, q8h, n, ids=part_ids, per_slot=True)
-            position = torch.arange(n * used, dtype=torch.int32, device=x.device)
-            out[t0:t1] = moe_combine(y.view(n * used, hidden), position, weights[t0:t1].contiguous(),
-                                     n, used)
+            moe_combine(y.view(n * used, hidden), None, weights[t0:t1], n, used, out=out[t0:t1])
         return out
     route = moe_route(ids, experts)
     slots = tokens * used
