@@ -493,6 +493,14 @@ typedef struct llmp_b200_mxfp8_gemm_desc {
 int llmp_b200_mxfp8_gemm_available(void);
 size_t llmp_b200_mxfp8_gemm_scratch(const llmp_b200_mxfp8_gemm_desc* gemm, int sms);
 int llmp_b200_mxfp8_gemm(const llmp_b200_mxfp8_gemm_desc* gemm, int sms, void* stream);
+/* The same product by a named kernel: 0 the rule llmp_b200_mxfp8_gemm follows (CTA pairs once
+ * m exceeds one 128-row tile), 1 one CTA a 128 x 192 tile, 2 a pair of CTAs (cta_group::2) a
+ * 256 x 192 tile.  The kernels accumulate a tile's k-steps in the same order, so their
+ * results are the same bits; the entry exists for measurement and tests. */
+int llmp_b200_mxfp8_gemm_variant(const llmp_b200_mxfp8_gemm_desc* gemm, int sms, int variant,
+                                 void* stream);
+/* How many CTA pairs of the pair kernel the current device holds at once (0: none). */
+int llmp_b200_mxfp8_gemm_resident_pairs(void);
 
 #ifdef __cplusplus
 }

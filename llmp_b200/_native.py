@@ -146,6 +146,8 @@ SIGNATURES = {
     "llmp_b200_mxfp8_gemm_available": (C.c_int, []),
     "llmp_b200_mxfp8_gemm_scratch": (C.c_size_t, [C.POINTER(Mxfp8GemmDesc), C.c_int]),
     "llmp_b200_mxfp8_gemm": (C.c_int, [C.POINTER(Mxfp8GemmDesc), C.c_int, C.c_void_p]),
+    "llmp_b200_mxfp8_gemm_resident_pairs": (C.c_int, []),
+    "llmp_b200_mxfp8_gemm_variant": (C.c_int, [C.POINTER(Mxfp8GemmDesc), C.c_int, C.c_int, C.c_void_p]),
     "llmp_b200_decode_vector": (C.c_int, [C.POINTER(DecodeProduct), C.c_void_p]),
     "llmp_b200_decode_vector_glu": (C.c_int, [C.POINTER(DecodeGluProduct), C.c_void_p]),
     "llmp_b200_decode_rows": (C.c_int, [C.POINTER(DecodeOperand), C.c_void_p, C.c_uint64,

@@ -141,6 +141,65 @@ struct GemmShared {
   std::uint32_t abort;
 };
 
+// 32 consecutive columns of one output row, from the accumulator's registers.
+__device__ __forceinline__ void StoreChunk(void* __restrict__ d, bool bf16, int row, int col, int m,
+                                           int n, const std::uint32_t (&r)[32]) {
+  if (row >= m || col >= n) return;
+  if (bf16) {
+    auto* out = static_cast<__nv_bfloat16*>(d) + (static_cast<std::size_t>(row) * n) + col;
+    if (col + 32 <= n && (n % 8) == 0) {
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        std::uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(r[(8 * v) + (2 * j)]),
+                                                         __uint_as_float(r[(8 * v) + (2 * j) + 1]));
+          w[j] = *reinterpret_cast<const std::uint32_t*>(&p);
+        }
+        reinterpret_cast<uint4*>(out)[v] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    } else {
+      // unrolled, so that r[] is only ever indexed by constants and stays in registers
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (col + j < n) out[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+      }
+    }
+  } else {
+    auto* out = static_cast<float*>(d) + (static_cast<std::size_t>(row) * n) + col;
+    if (col + 32 <= n && (n % 4) == 0) {
+#pragma unroll
+      for (int v = 0; v < 8; ++v) {
+        reinterpret_cast<uint4*>(out)[v] =
+            make_uint4(r[4 * v], r[(4 * v) + 1], r[(4 * v) + 2], r[(4 * v) + 3]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (col + j < n) out[j] = __uint_as_float(r[j]);
+      }
+    }
+  }
+}
+
+// This warp's 32 accumulator rows x kBN columns out of tensor memory and into D: the next
+// 32 columns are already on their way while the last 32 are converted and stored.
+__device__ __forceinline__ void DrainAccumulator(std::uint32_t taddr, void* __restrict__ d, bool bf16,
+                                                 int row, int col0, int m, int n) {
+  std::uint32_t r0[32], r1[32];
+  tc::TmemLoad32(taddr, r0);
+#pragma unroll
+  for (int c = 0; c < kBN / 32; c += 2) {
+    tc::TmemLoadWait32(r0);
+    tc::TmemLoad32(taddr + ((c + 1) * 32), r1);
+    StoreChunk(d, bf16, row, col0 + (c * 32), m, n, r0);
+    tc::TmemLoadWait32(r1);
+    if (c + 2 < kBN / 32) tc::TmemLoad32(taddr + ((c + 2) * 32), r0);
+    StoreChunk(d, bf16, row, col0 + ((c + 1) * 32), m, n, r1);
+  }
+}
+
 __global__ void __launch_bounds__(kGemmThreads, 1)
 Mxfp8GemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const std::uint8_t* __restrict__ sfa, const std::uint8_t* __restrict__ sfb,
@@ -187,73 +246,90 @@ Mxfp8GemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
   if (warp == 0) {
     // ---------------------------------------------------------- TMA producer
-    if (lane == 0) {
+    // The whole warp walks the loop and one elected lane issues: loop state that is the same in
+    // every lane stays where copy and tcgen05 instructions take their operands from (issued
+    // from inside a one-lane branch each such instruction held the thread 60 to 190 cycles,
+    // which bounded the kernel).  The next stage's barrier is looked at without blocking
+    // before this stage's copies go out: a blocking wait costs about 180 cycles even on a
+    // phase that completed long ago.
+    const bool elected = tc::ElectOne();
+    if (elected) {
       tc::PrefetchMap(&map_a);
       tc::PrefetchMap(&map_b);
-      std::uint32_t it = 0;
-      for (int t = static_cast<int>(blockIdx.x); t < tiles && !*abort_flag; t += gridDim.x) {
-        const int mb = t % tiles_m, nb = t / tiles_m;
-        for (int ks = 0; ks < ksteps; ++ks, ++it) {
-          const int s = static_cast<int>(it % kStages);
-          if (!tc::MbarWait(&sh->empty[s], ((it / kStages) & 1u) ^ 1u)) {
-            *abort_flag = 1;
-            atomicAdd(faults, 1u);
-            break;
-          }
-          // The tile's B rows [nb * 192, +192) touch two scale atoms (128 rows each).
-          const int atom0 = (nb * kBN) / 128;
-          const bool second = (atom0 + 1) * 128 < sfb_rows_padded;
+    }
+    std::uint32_t it = 0;
+    bool ready = false, ok = true;
+    for (int t = static_cast<int>(blockIdx.x); t < tiles && !*abort_flag; t += gridDim.x) {
+      const int mb = t % tiles_m, nb = t / tiles_m;
+      // The tile's B rows [nb * 192, +192) touch two scale atoms (128 rows each).
+      const int atom0 = (nb * kBN) / 128;
+      const bool second = (atom0 + 1) * 128 < sfb_rows_padded;
+      const std::uint8_t* sfa_at = sfa + (static_cast<std::size_t>(mb) * (kb / 4) * 512);
+      const std::uint8_t* sfb_at = sfb + (static_cast<std::size_t>(atom0) * (kb / 4) * 512);
+      const std::size_t sfb_next = static_cast<std::size_t>(kb / 4) * 512;
+      for (int ks = 0; ks < ksteps; ++ks, ++it) {
+        const int s = static_cast<int>(it % kStages);
+        if (!ready) ok = tc::MbarWait(&sh->empty[s], ((it / kStages) & 1u) ^ 1u);
+        if (!ok) break;
+        const std::uint32_t next = it + 1;
+        ready = tc::MbarTest(&sh->empty[next % kStages], ((next / kStages) & 1u) ^ 1u);
+        if (elected) {
           tc::MbarExpectTx(&sh->full[s], kABytes + kBBytes + kSfaBytes + (second ? 1024u : 512u));
           tc::TmaLoad2D(a_tiles + (s * kABytes), &map_a, ks * kBK, mb * kBM, &sh->full[s]);
           tc::TmaLoad2D(b_tiles + (s * kBBytes), &map_b, ks * kBK, nb * kBN, &sh->full[s]);
-          tc::BulkLoad(sfa_tiles + (s * kSfaBytes),
-                       sfa + ((static_cast<std::size_t>(mb) * (kb / 4) + ks) * 512), 512,
-                       &sh->full[s]);
-          tc::BulkLoad(sfb_tiles + (s * kSfbBytes),
-                       sfb + ((static_cast<std::size_t>(atom0) * (kb / 4) + ks) * 512), 512,
-                       &sh->full[s]);
+          tc::BulkLoad(sfa_tiles + (s * kSfaBytes), sfa_at + (ks * 512), 512, &sh->full[s]);
+          tc::BulkLoad(sfb_tiles + (s * kSfbBytes), sfb_at + (ks * 512), 512, &sh->full[s]);
           if (second) {
-            tc::BulkLoad(sfb_tiles + (s * kSfbBytes) + 512,
-                         sfb + ((static_cast<std::size_t>(atom0 + 1) * (kb / 4) + ks) * 512), 512,
+            tc::BulkLoad(sfb_tiles + (s * kSfbBytes) + 512, sfb_at + sfb_next + (ks * 512), 512,
                          &sh->full[s]);
           }
         }
+        ready = __all_sync(0xffffffffu, ready);
+      }
+      if (!__all_sync(0xffffffffu, ok)) {
+        if (elected) {
+          *abort_flag = 1;
+          atomicAdd(faults, 1u);
+        }
+        break;
       }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer
-    if (lane == 0) {
-      std::uint32_t it = 0, tile_it = 0;
-      for (int t = static_cast<int>(blockIdx.x); t < tiles && !*abort_flag; t += gridDim.x, ++tile_it) {
-        const int nb = t / tiles_m;
-        const int acc = static_cast<int>(tile_it & 1u);
-        if (!tc::MbarWait(&sh->tmem_empty[acc], ((tile_it >> 1) & 1u) ^ 1u)) {
+    const bool elected = tc::ElectOne();
+    std::uint32_t it = 0, tile_it = 0;
+    bool ready = false;
+    for (int t = static_cast<int>(blockIdx.x); t < tiles && !*abort_flag; t += gridDim.x, ++tile_it) {
+      const int nb = t / tiles_m;
+      const int acc = static_cast<int>(tile_it & 1u);
+      bool ok = tc::MbarWait(&sh->tmem_empty[acc], ((tile_it >> 1) & 1u) ^ 1u);
+      if (!__all_sync(0xffffffffu, ok)) {
+        if (elected) {
           *abort_flag = 1;
           atomicAdd(faults, 1u);
-          break;
         }
+        break;
+      }
+      const std::uint32_t tacc = tmem + (acc * kAccColumns);
+      // The two atoms always land on 4-column boundaries (tcgen05.cp's unit); an
+      // odd tile starts in the middle of its first atom, whose last two columns
+      // (rows 64..127) are the tile's first two: the MMA reads from +2.
+      const int shift = (nb & 1) ? 2 : 0;
+      for (int ks = 0; ks < ksteps; ++ks, ++it) {
+        const int s = static_cast<int>(it % kStages);
+        if (!ready) ok = tc::MbarWait(&sh->full[s], (it / kStages) & 1u);
+        if (!ok) break;
         tc::TcFenceAfter();
-        const std::uint32_t tacc = tmem + (acc * kAccColumns);
-        // The two atoms always land on 4-column boundaries (tcgen05.cp's unit); an
-        // odd tile starts in the middle of its first atom, whose last two columns
-        // (rows 64..127) are the tile's first two: the MMA reads from +2.
-        const int shift = (nb & 1) ? 2 : 0;
-        for (int ks = 0; ks < ksteps; ++ks, ++it) {
-          const int s = static_cast<int>(it % kStages);
-          if (!tc::MbarWait(&sh->full[s], (it / kStages) & 1u)) {
-            *abort_flag = 1;
-            atomicAdd(faults, 1u);
-            break;
-          }
-          tc::TcFenceAfter();
-          const std::uint32_t tsfa = tmem + kSfColumn + (s * kSfStride);
-          const std::uint32_t tsfb = tsfa + 4 + shift;
+        const std::uint32_t next = it + 1;
+        ready = tc::MbarTest(&sh->full[next % kStages], (next / kStages) & 1u);
+        const std::uint32_t tsfa = tmem + kSfColumn + (s * kSfStride);
+        const std::uint32_t tsfb = tsfa + 4 + shift;
+        const std::uint64_t adesc = tc::SmemDesc(a_tiles + (s * kABytes), true, 1024);
+        const std::uint64_t bdesc = tc::SmemDesc(b_tiles + (s * kBBytes), true, 1024);
+        if (elected) {
           tc::TmemCopyScales(tsfa, tc::SmemDesc(sfa_tiles + (s * kSfaBytes), false, 128));
           tc::TmemCopyScales(tsfa + 4, tc::SmemDesc(sfb_tiles + (s * kSfbBytes), false, 128));
-          tc::TmemCopyScales(tsfa + 8,
-                             tc::SmemDesc(sfb_tiles + (s * kSfbBytes) + 512, false, 128));
-          const std::uint64_t adesc = tc::SmemDesc(a_tiles + (s * kABytes), true, 1024);
-          const std::uint64_t bdesc = tc::SmemDesc(b_tiles + (s * kBBytes), true, 1024);
+          tc::TmemCopyScales(tsfa + 8, tc::SmemDesc(sfb_tiles + (s * kSfbBytes) + 512, false, 128));
 #pragma unroll
           for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
             // 32 bytes along K inside the 128-byte swizzle row: +2 in 16-byte units
@@ -262,8 +338,16 @@ Mxfp8GemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           }
           tc::TcCommit(&sh->empty[s]);  // the stage's bytes are free once these MMAs retire
         }
-        tc::TcCommit(&sh->tmem_full[acc]);
+        ready = __all_sync(0xffffffffu, ready);
       }
+      if (!__all_sync(0xffffffffu, ok)) {
+        if (elected) {
+          *abort_flag = 1;
+          atomicAdd(faults, 1u);
+        }
+        break;
+      }
+      if (elected) tc::TcCommit(&sh->tmem_full[acc]);
     }
   } else {
     // ---------------------------------------------------------- epilogue
@@ -284,49 +368,8 @@ Mxfp8GemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       }
       tc::TcFenceAfter();
       const int row = (mb * kBM) + (quadrant * 32) + lane;
-#pragma unroll 1
-      for (int c = 0; c < kBN / 32; ++c) {
-        std::uint32_t r[32];
-        tc::TmemLoad32(tmem + (static_cast<std::uint32_t>(quadrant * 32) << 16) +
-                           (acc * kAccColumns) + (c * 32), r);
-        tc::TmemLoadWait();
-        const int col = (nb * kBN) + (c * 32);
-        if (row < m && col < n) {
-          if (bf16) {
-            auto* out = static_cast<__nv_bfloat16*>(d) + (static_cast<std::size_t>(row) * n) + col;
-            if (col + 32 <= n && (n % 8) == 0) {
-#pragma unroll
-              for (int v = 0; v < 4; ++v) {
-                uint4 q;
-                std::uint32_t w[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(r[(8 * v) + (2 * j)]),
-                                                                 __uint_as_float(r[(8 * v) + (2 * j) + 1]));
-                  w[j] = *reinterpret_cast<const std::uint32_t*>(&p);
-                }
-                q = make_uint4(w[0], w[1], w[2], w[3]);
-                reinterpret_cast<uint4*>(out)[v] = q;
-              }
-            } else {
-              for (int j = 0; j < 32 && col + j < n; ++j) {
-                out[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
-              }
-            }
-          } else {
-            auto* out = static_cast<float*>(d) + (static_cast<std::size_t>(row) * n) + col;
-            if (col + 32 <= n && (n % 4) == 0) {
-#pragma unroll
-              for (int v = 0; v < 8; ++v) {
-                reinterpret_cast<uint4*>(out)[v] =
-                    make_uint4(r[4 * v], r[(4 * v) + 1], r[(4 * v) + 2], r[(4 * v) + 3]);
-              }
-            } else {
-              for (int j = 0; j < 32 && col + j < n; ++j) out[j] = __uint_as_float(r[j]);
-            }
-          }
-        }
-      }
+      DrainAccumulator(tmem + (static_cast<std::uint32_t>(quadrant * 32) << 16) + (acc * kAccColumns),
+                       d, bf16 != 0, row, nb * kBN, m, n);
       tc::TcFenceBefore();
       __syncwarp();
       if (lane == 0) tc::MbarArrive(&sh->tmem_empty[acc]);
@@ -339,6 +382,248 @@ Mxfp8GemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   if (warp == 1) {
     tc::TcFenceAfter();
     tc::TmemDealloc(tmem, kTmemColumns);
+  }
+}
+
+// ------------------------------------------------------------------ GEMM on CTA pairs
+// The same roles over a cluster of two CTAs (cta_group::2): one 256 x 192 tile a pair.  Each
+// CTA fetches its own 128 rows of A and 96 of the tile's 192 rows of B - 28 KB a k-step into
+// an SM instead of 40 KB, which is what bounds the single-CTA kernel - plus its rows' scale
+// atom and the tile's B scale atoms (both CTAs need all 192 columns' scales).  The even CTA's
+// MMA thread issues M 256 MMAs that read both halves and accumulate 128 lanes x 192 columns in
+// each CTA's tensor memory; tcgen05.commit reaches the barriers of both CTAs.  The odd CTA's
+// MMA warp only relays "my stage has landed" to the even CTA, and its epilogue warps release
+// an accumulator by arriving on the even CTA's barrier.  Loads carry no multicast.  Waits on
+// barriers the other CTA arrives at are the ordinary ones: a cluster-scope acquire on every
+// wait measured 2.2 times the whole kernel's time, and what crosses the pair is read by the
+// tensor core's own path (operands) or ordered by tcgen05 fences (accumulators), not by this
+// thread's loads.
+constexpr int kPairBM = 256, kPairHalfN = kBN / 2, kPairStages = 7;
+constexpr int kPairBBytes = kPairHalfN * kBK;
+constexpr int kPairStageBytes = kABytes + kPairBBytes + kSfaBytes + kSfbBytes;
+constexpr int kPairSmem = (kPairStages * kPairStageBytes) + 1024 + 512;
+static_assert(kSfColumn + (kPairStages * kSfStride) <= kTmemColumns, "scale columns fit");
+
+
+struct PairShared {
+  std::uint64_t full[kPairStages];
+  std::uint64_t empty[kPairStages];
+  std::uint64_t tmem_full[2];
+  std::uint64_t tmem_empty[2];  // even CTA: the epilogue warps of both CTAs
+  std::uint32_t tmem_base;
+  std::uint32_t abort;
+};
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+Mxfp8GemmPairKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const std::uint8_t* __restrict__ sfa, const std::uint8_t* __restrict__ sfb,
+                    void* __restrict__ d, int m, int n, int k, int bf16, int sfa_rows_padded,
+                    int sfb_rows_padded, unsigned int* faults) {
+  extern __shared__ unsigned char raw_smem[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<std::uintptr_t>(raw_smem) + 1023) & ~static_cast<std::uintptr_t>(1023));
+  unsigned char* a_tiles = smem;
+  unsigned char* b_tiles = a_tiles + (kPairStages * kABytes);
+  unsigned char* sfa_tiles = b_tiles + (kPairStages * kPairBBytes);
+  unsigned char* sfb_tiles = sfa_tiles + (kPairStages * kSfaBytes);
+  PairShared* sh = reinterpret_cast<PairShared*>(sfb_tiles + (kPairStages * kSfbBytes));
+
+  const int warp = static_cast<int>(threadIdx.x) >> 5;
+  const int lane = static_cast<int>(threadIdx.x) & 31;
+  const int rank = static_cast<int>(tc::ClusterCtaRank());  // 0: issues the MMAs
+  const int pair = static_cast<int>(blockIdx.x) >> 1;
+  const int pairs = static_cast<int>(gridDim.x) >> 1;
+  const int tiles_m = (m + kPairBM - 1) / kPairBM;
+  const int tiles_n = (n + kBN - 1) / kBN;
+  const int tiles = tiles_m * tiles_n;
+  const int ksteps = k / kBK;
+  const int kb = k / 32;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      // the even CTA's "full" also counts the odd CTA's relay: one wait covers both halves
+      tc::MbarInit(&sh->full[s], rank == 0 ? 2 : 1);
+      tc::MbarInit(&sh->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      tc::MbarInit(&sh->tmem_full[b], 1);
+      tc::MbarInit(&sh->tmem_empty[b], 8);
+    }
+    sh->abort = 0;
+    tc::MbarInitFence();
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc::TmemAllocPair(&sh->tmem_base, kTmemColumns);
+    tc::TmemRelinquishPair();
+  }
+  tc::TcFenceBefore();
+  __syncthreads();
+  tc::ClusterBarrier();  // both CTAs' barriers are initialised before either reaches across
+  tc::TcFenceAfter();
+  const std::uint32_t tmem = sh->tmem_base;
+  volatile std::uint32_t* abort_flag = &sh->abort;
+  const std::uint32_t peer_abort = tc::PeerSmem(&sh->abort, static_cast<std::uint32_t>(rank ^ 1));
+  auto give_up = [&]() {
+    *abort_flag = 1;
+    tc::StorePeerU32(peer_abort, 1u);
+    atomicAdd(faults, 1u);
+  };
+
+  if (warp == 0) {
+    // ---------------------------------------------------------- TMA producer (both CTAs)
+    // The whole warp walks the loop and one elected lane issues the copies (see the MMA warp).
+    const bool elected = tc::ElectOne();
+    if (elected) {
+      tc::PrefetchMap(&map_a);
+      tc::PrefetchMap(&map_b);
+    }
+    std::uint32_t it = 0;
+    bool ready = false, ok = true;
+    for (int t = pair; t < tiles && !*abort_flag; t += pairs) {
+      const int mb = t % tiles_m, nb = t / tiles_m;
+      // This CTA's rows of A; a half tile wholly below the matrix reads zeros and borrows
+      // the last atom's scales (its rows are never stored).
+      int a_atom = (mb * 2) + rank;
+      if (a_atom * 128 >= sfa_rows_padded) a_atom = (sfa_rows_padded / 128) - 1;
+      const int atom0 = (nb * kBN) / 128;
+      const bool second = (atom0 + 1) * 128 < sfb_rows_padded;
+      const std::uint8_t* sfa_at = sfa + (static_cast<std::size_t>(a_atom) * (kb / 4) * 512);
+      const std::uint8_t* sfb_at = sfb + (static_cast<std::size_t>(atom0) * (kb / 4) * 512);
+      const std::size_t sfb_next = static_cast<std::size_t>(kb / 4) * 512;
+      const int a_row = (mb * kPairBM) + (rank * kBM);
+      const int b_row = (nb * kBN) + (rank * kPairHalfN);
+      for (int ks = 0; ks < ksteps; ++ks, ++it) {
+        const int s = static_cast<int>(it % kPairStages);
+        if (!ready) ok = tc::MbarWait(&sh->empty[s], ((it / kPairStages) & 1u) ^ 1u);
+        if (!ok) break;
+        const std::uint32_t next = it + 1;
+        ready = tc::MbarTest(&sh->empty[next % kPairStages], ((next / kPairStages) & 1u) ^ 1u);
+        if (elected) {
+          tc::MbarExpectTx(&sh->full[s],
+                           kABytes + kPairBBytes + kSfaBytes + (second ? 1024u : 512u));
+          tc::TmaLoad2D(a_tiles + (s * kABytes), &map_a, ks * kBK, a_row, &sh->full[s]);
+          tc::TmaLoad2D(b_tiles + (s * kPairBBytes), &map_b, ks * kBK, b_row, &sh->full[s]);
+          tc::BulkLoad(sfa_tiles + (s * kSfaBytes), sfa_at + (ks * 512), 512, &sh->full[s]);
+          tc::BulkLoad(sfb_tiles + (s * kSfbBytes), sfb_at + (ks * 512), 512, &sh->full[s]);
+          if (second) {
+            tc::BulkLoad(sfb_tiles + (s * kSfbBytes) + 512, sfb_at + sfb_next + (ks * 512), 512,
+                         &sh->full[s]);
+          }
+        }
+        ready = __all_sync(0xffffffffu, ready);
+      }
+      if (!__all_sync(0xffffffffu, ok)) {
+        if (elected) give_up();
+        break;
+      }
+    }
+  } else if (warp == 1) {
+    if (rank == 1) {
+      // ---------------------------------------------------------- relay (odd CTA)
+      if (lane == 0) {
+        std::uint32_t it = 0;
+        for (int t = pair; t < tiles && !*abort_flag; t += pairs) {
+          for (int ks = 0; ks < ksteps; ++ks, ++it) {
+            const int s = static_cast<int>(it % kPairStages);
+            if (!tc::MbarWait(&sh->full[s], (it / kPairStages) & 1u)) {
+              give_up();
+              break;
+            }
+            tc::MbarArrivePeer(tc::PeerSmem(&sh->full[s], 0u));
+          }
+        }
+      }
+    } else {
+      // ---------------------------------------------------------- MMA issuer (even CTA)
+      // The whole warp walks the loop and one elected lane issues: the loop's state (stage,
+      // descriptors, tensor-memory addresses) is then the same in every lane, which lets the
+      // compiler keep it where tcgen05 instructions take their operands from.  The
+      // instruction stream of this warp is what bounds the kernel, so the next stage's
+      // barrier is looked at, without blocking, before this stage's MMAs are issued.
+      const bool elected = tc::ElectOne();
+      std::uint32_t it = 0, tile_it = 0;
+      bool ready = false;
+      for (int t = pair; t < tiles && !*abort_flag; t += pairs, ++tile_it) {
+        const int nb = t / tiles_m;
+        const int acc = static_cast<int>(tile_it & 1u);
+        bool ok = tc::MbarWait(&sh->tmem_empty[acc], ((tile_it >> 1) & 1u) ^ 1u);
+        if (!__all_sync(0xffffffffu, ok)) {
+          if (elected) give_up();
+          break;
+        }
+        const std::uint32_t tacc = tmem + (acc * kAccColumns);
+        const int shift = (nb & 1) ? 2 : 0;
+        for (int ks = 0; ks < ksteps; ++ks, ++it) {
+          const int s = static_cast<int>(it % kPairStages);
+          if (!ready) ok = tc::MbarWait(&sh->full[s], (it / kPairStages) & 1u);
+          if (!ok) break;
+          tc::TcFenceAfter();
+          const std::uint32_t next = it + 1;
+          ready = tc::MbarTest(&sh->full[next % kPairStages], (next / kPairStages) & 1u);
+          const std::uint32_t tsfa = tmem + kSfColumn + (s * kSfStride);
+          const std::uint32_t tsfb = tsfa + 4 + shift;
+          const std::uint64_t adesc = tc::SmemDesc(a_tiles + (s * kABytes), true, 1024);
+          const std::uint64_t bdesc = tc::SmemDesc(b_tiles + (s * kPairBBytes), true, 1024);
+          if (elected) {
+            tc::TmemCopyScalesPair(tsfa, tc::SmemDesc(sfa_tiles + (s * kSfaBytes), false, 128));
+            tc::TmemCopyScalesPair(tsfa + 4, tc::SmemDesc(sfb_tiles + (s * kSfbBytes), false, 128));
+            tc::TmemCopyScalesPair(tsfa + 8,
+                                   tc::SmemDesc(sfb_tiles + (s * kSfbBytes) + 512, false, 128));
+#pragma unroll
+            for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
+              tc::MmaMxf8Pair(tacc, adesc + (kk * 2), bdesc + (kk * 2),
+                              tc::IdescMxf8(kPairBM, kBN, kk, kk), ks > 0 || kk > 0, tsfa, tsfb);
+            }
+            tc::TcCommitPair(&sh->empty[s], 3);  // both CTAs' stage is free once these retire
+          }
+          ready = __all_sync(0xffffffffu, ready);
+        }
+        if (!__all_sync(0xffffffffu, ok)) {
+          if (elected) give_up();
+          break;
+        }
+        if (elected) tc::TcCommitPair(&sh->tmem_full[acc], 3);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------- epilogue (both CTAs)
+    const int quadrant = warp & 3;
+    std::uint32_t tile_it = 0;
+    for (int t = pair; t < tiles; t += pairs, ++tile_it) {
+      const int mb = t % tiles_m, nb = t / tiles_m;
+      const int acc = static_cast<int>(tile_it & 1u);
+      bool ok = true;
+      if (lane == 0) ok = tc::MbarWait(&sh->tmem_full[acc], (tile_it >> 1) & 1u);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok || *abort_flag) {
+        if (lane == 0 && !ok) give_up();
+        break;
+      }
+      tc::TcFenceAfter();
+      const int row = (mb * kPairBM) + (rank * kBM) + (quadrant * 32) + lane;
+      DrainAccumulator(tmem + (static_cast<std::uint32_t>(quadrant * 32) << 16) + (acc * kAccColumns),
+                       d, bf16 != 0, row, nb * kBN, m, n);
+      tc::TcFenceBefore();
+      __syncwarp();
+      if (lane == 0) {
+        if (rank == 0) {
+          tc::MbarArrive(&sh->tmem_empty[acc]);
+        } else {
+          tc::MbarArrivePeer(tc::PeerSmem(&sh->tmem_empty[acc], 0u));
+        }
+      }
+    }
+  }
+
+  // Teardown: both CTAs meet (no thread may still reach into the other's memory), then the
+  // allocating warps free the pair's tensor memory.
+  tc::TcFenceBefore();
+  __syncthreads();
+  tc::ClusterBarrier();
+  if (warp == 1) {
+    tc::TcFenceAfter();
+    tc::TmemDeallocPair(tmem, kTmemColumns);
   }
 }
 
@@ -404,7 +689,8 @@ size_t llmp_b200_mxfp8_gemm_scratch(const llmp_b200_mxfp8_gemm_desc* gemm, int s
   return 0;  // accumulators live in tensor memory; no workspace
 }
 
-int llmp_b200_mxfp8_gemm(const llmp_b200_mxfp8_gemm_desc* gemm, int sms, void* stream) {
+int llmp_b200_mxfp8_gemm_variant(const llmp_b200_mxfp8_gemm_desc* gemm, int sms, int variant,
+                                 void* stream) {
   using namespace llmp_b200;
   if (gemm == nullptr) return Reject("mxfp8.gemm: null descriptor");
   const Gemm& g = *gemm;
@@ -419,35 +705,106 @@ int llmp_b200_mxfp8_gemm(const llmp_b200_mxfp8_gemm_desc* gemm, int sms, void* s
       !Aligned(g.b_scales, 16) || !Aligned(g.d, 16)) {
     return Reject("mxfp8.gemm: operands 16-byte aligned");
   }
+  if (variant < 0 || variant > 2) return Reject("mxfp8.gemm: variant 0 (rule), 1 (one CTA a tile) or 2 (CTA pairs)");
   if (const int status = DeviceStatus(); status != 0) return status;
   if (sms <= 0) sms = SmCount();
+  unsigned int* faults = FaultCounter();
+  if (faults == nullptr) return Reject("mxfp8.gemm: no fault counter on this device");
+  // Once a device: shared-memory limits, and how many CTA pairs it holds at once.
+  static thread_local int configured_device = -1;
+  static thread_local int resident_pairs = 0;
+  int device = -1;
+  cudaGetDevice(&device);
+  if (configured_device != device) {
+    cudaError_t e = cudaFuncSetAttribute(Mxfp8GemmKernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kGemmSmem);
+    if (e == cudaSuccess) {
+      e = cudaFuncSetAttribute(Mxfp8GemmPairKernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               kPairSmem);
+    }
+    if (e != cudaSuccess) return Failed(e, "mxfp8.gemm attribute");
+    const int clusters = llmp_b200_mxfp8_gemm_resident_pairs();
+    resident_pairs = clusters;
+    configured_device = device;
+  }
+  // Pairs once the matrix has more than one 128-row tile of rows (a pair's second CTA would
+  // otherwise multiply zeros), and only if the device holds pairs of this size at all.
+  const bool pairs = variant == 2 || (variant == 0 && g.m > kBM && resident_pairs > 0);
+  if (pairs && resident_pairs < 1) return Reject("mxfp8.gemm: this device holds no CTA pair of the kernel's size");
   CUtensorMap map_a, map_b;
   if (!tc::MakeMapBytes2D(&map_a, g.a, static_cast<std::uint64_t>(g.m), static_cast<std::uint64_t>(g.k),
                           static_cast<std::uint64_t>(g.k), kBM, kBK) ||
       !tc::MakeMapBytes2D(&map_b, g.b, static_cast<std::uint64_t>(g.n), static_cast<std::uint64_t>(g.k),
-                          static_cast<std::uint64_t>(g.k), kBN, kBK)) {
+                          static_cast<std::uint64_t>(g.k), pairs ? kPairHalfN : kBN, kBK)) {
     return Reject("mxfp8.gemm: the driver refused a tensor map for these operands");
   }
-  unsigned int* faults = FaultCounter();
-  if (faults == nullptr) return Reject("mxfp8.gemm: no fault counter on this device");
-  static thread_local int configured_device = -1;
-  int device = -1;
-  cudaGetDevice(&device);
-  if (configured_device != device) {
-    const cudaError_t e = cudaFuncSetAttribute(
-        Mxfp8GemmKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem);
-    if (e != cudaSuccess) return Failed(e, "mxfp8.gemm attribute");
-    configured_device = device;
+  const auto* a_scales = static_cast<const std::uint8_t*>(g.a_scales);
+  const auto* b_scales = static_cast<const std::uint8_t*>(g.b_scales);
+  const int n_padded = static_cast<int>(llmp_b200_mxfp8_padded_rows(static_cast<uint64_t>(g.n)));
+  if (pairs) {
+    const int tiles = ((g.m + kPairBM - 1) / kPairBM) * ((g.n + kBN - 1) / kBN);
+    int count = tiles < sms / 2 ? tiles : sms / 2;
+    if (count > resident_pairs) count = resident_pairs;
+    if (count < 1) count = 1;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(2u * static_cast<unsigned>(count));
+    config.blockDim = dim3(kGemmThreads);
+    config.dynamicSmemBytes = kPairSmem;
+    config.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute cluster[1];
+    cluster[0].id = cudaLaunchAttributeClusterDimension;
+    cluster[0].val.clusterDim.x = 2;
+    cluster[0].val.clusterDim.y = 1;
+    cluster[0].val.clusterDim.z = 1;
+    config.attrs = cluster;
+    config.numAttrs = 1;
+    const int m_padded = static_cast<int>(llmp_b200_mxfp8_padded_rows(static_cast<uint64_t>(g.m)));
+    const cudaError_t e = cudaLaunchKernelEx(&config, Mxfp8GemmPairKernel, map_a, map_b, a_scales,
+                                             b_scales, g.d, g.m, g.n, g.k, g.bf16 ? 1 : 0, m_padded,
+                                             n_padded, faults);
+    if (e != cudaSuccess) return Failed(e, "mxfp8.gemm pair launch");
+    return 0;
   }
   const int tiles = ((g.m + kBM - 1) / kBM) * ((g.n + kBN - 1) / kBN);
   const int grid = tiles < sms ? tiles : sms;
   Mxfp8GemmKernel<<<grid, kGemmThreads, kGemmSmem, static_cast<cudaStream_t>(stream)>>>(
-      map_a, map_b, static_cast<const std::uint8_t*>(g.a_scales),
-      static_cast<const std::uint8_t*>(g.b_scales), g.d, g.m, g.n, g.k, g.bf16 ? 1 : 0,
-      static_cast<int>(llmp_b200_mxfp8_padded_rows(static_cast<uint64_t>(g.n))), faults);
+      map_a, map_b, a_scales, b_scales, g.d, g.m, g.n, g.k, g.bf16 ? 1 : 0, n_padded, faults);
   const cudaError_t e = cudaPeekAtLastError();
   if (e != cudaSuccess) return Failed(cudaGetLastError(), "mxfp8.gemm launch");
   return 0;
+}
+
+int llmp_b200_mxfp8_gemm(const llmp_b200_mxfp8_gemm_desc* gemm, int sms, void* stream) {
+  return llmp_b200_mxfp8_gemm_variant(gemm, sms, 0, stream);
+}
+
+
+
+int llmp_b200_mxfp8_gemm_resident_pairs(void) {
+  using namespace llmp_b200;
+  if (DeviceStatus() != 0) return 0;
+  if (cudaFuncSetAttribute(Mxfp8GemmPairKernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           kPairSmem) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  cudaLaunchConfig_t probe = {};
+  probe.gridDim = dim3(2u * static_cast<unsigned>(SmCount()));
+  probe.blockDim = dim3(kGemmThreads);
+  probe.dynamicSmemBytes = kPairSmem;
+  cudaLaunchAttribute cluster[1];
+  cluster[0].id = cudaLaunchAttributeClusterDimension;
+  cluster[0].val.clusterDim.x = 2;
+  cluster[0].val.clusterDim.y = 1;
+  cluster[0].val.clusterDim.z = 1;
+  probe.attrs = cluster;
+  probe.numAttrs = 1;
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, Mxfp8GemmPairKernel, &probe) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return clusters;
 }
 
 }  // extern "C"

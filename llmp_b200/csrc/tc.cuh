@@ -78,6 +78,21 @@ __device__ __forceinline__ bool MbarWait(std::uint64_t* bar, std::uint32_t parit
   }
   return false;
 }
+// One non-blocking look at the phase (no suspension): for a look ahead whose answer is
+// only needed after other work has been issued.
+__device__ __forceinline__ bool MbarTest(std::uint64_t* bar, std::uint32_t parity) {
+  std::uint32_t done;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(done)
+      : "r"(Smem(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
 // The same with a sleep between polls: for a role that runs far ahead and whose
 // polling would take issue slots from the warps doing the work.
 __device__ __forceinline__ bool MbarWaitSleep(std::uint64_t* bar, std::uint32_t parity,
@@ -223,6 +238,73 @@ __device__ __forceinline__ void TmemCopyScales(std::uint32_t taddr, std::uint64_
                : "memory");
 }
 
+// ---- CTA pairs (cta_group::2): two CTAs of a cluster, ranks 2i and 2i+1, run one MMA over
+// both SMs' shared and tensor memory.  The even CTA's thread issues; barriers of the other
+// CTA are reached through its shared::cluster address.
+__device__ __forceinline__ std::uint32_t ClusterCtaRank() {
+  std::uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void ClusterBarrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n"
+               "barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The shared::cluster address of `p` (an object of this CTA's shared memory) in CTA `rank`.
+__device__ __forceinline__ std::uint32_t PeerSmem(const void* p, std::uint32_t rank) {
+  std::uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(Smem(p)), "r"(rank));
+  return out;
+}
+__device__ __forceinline__ void MbarArrivePeer(std::uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+__device__ __forceinline__ void StorePeerU32(std::uint32_t cluster_addr, std::uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+// Tensor memory of both CTAs: the same warp of each CTA calls these, with the same arguments.
+__device__ __forceinline__ void TmemAllocPair(std::uint32_t* smem_result, std::uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+               ::"r"(Smem(smem_result)), "r"(columns)
+               : "memory");
+}
+__device__ __forceinline__ void TmemRelinquishPair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void TmemDeallocPair(std::uint32_t taddr, std::uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(columns)
+               : "memory");
+}
+// The pair's MMAs and copies issued so far arrive, when done, on the barrier at this
+// offset in every CTA of `cta_mask` (bit i = cluster rank i).
+__device__ __forceinline__ void TcCommitPair(std::uint64_t* bar, std::uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+      "[%0], %1;"
+      ::"r"(Smem(bar)), "h"(cta_mask)
+      : "memory");
+}
+// M 256 (128 rows from each CTA's A tile), N columns (half of B's rows in each CTA).
+__device__ __forceinline__ void MmaMxf8Pair(std::uint32_t tmem_d, std::uint64_t a, std::uint64_t b,
+                                            std::uint32_t idesc, bool accumulate,
+                                            std::uint32_t tmem_sfa, std::uint32_t tmem_sfb) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n"
+      "}\n"
+      ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate ? 1u : 0u), "r"(tmem_sfa),
+        "r"(tmem_sfb)
+      : "memory");
+}
+// A scale atom of each CTA's shared memory (same offset) into each CTA's tensor memory.
+__device__ __forceinline__ void TmemCopyScalesPair(std::uint32_t taddr, std::uint64_t smem_desc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc)
+               : "memory");
+}
+
 // This warp's 32 TMEM lanes x 32 consecutive 32-bit columns into registers.
 __device__ __forceinline__ void TmemLoad32(std::uint32_t taddr, std::uint32_t (&r)[32]) {
   asm volatile(
@@ -253,6 +335,17 @@ __device__ __forceinline__ void TmemLoadWait16(std::uint32_t (&r)[16]) {
                : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]),
                  "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]),
                  "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+               :
+               : "memory");
+}
+__device__ __forceinline__ void TmemLoadWait32(std::uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]),
+                 "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]),
+                 "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]),
+                 "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
+                 "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]),
+                 "+r"(r[31])
                :
                : "memory");
 }

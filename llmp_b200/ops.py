@@ -308,8 +308,10 @@ def mxfp8_swizzle(scales: torch.Tensor) -> torch.Tensor:
 
 
 def mxfp8_gemm(a: torch.Tensor, a_scales: torch.Tensor, b: torch.Tensor, b_scales: torch.Tensor,
-               *, bf16: bool = True, out: torch.Tensor | None = None, sms: int = 0) -> torch.Tensor:
-    """Mxfp8Gemm: D[m, n] = A[m, k] . B[n, k]^T; codes uint8, scales in atoms."""
+               *, bf16: bool = True, out: torch.Tensor | None = None, sms: int = 0,
+               variant: int = 0) -> torch.Tensor:
+    """Mxfp8Gemm: D[m, n] = A[m, k] . B[n, k]^T; codes uint8, scales in atoms.  variant 0: the
+    library's rule; 1: one CTA a tile; 2: CTA pairs (llmp_b200_mxfp8_gemm_variant)."""
     for t, what in ((a, "a"), (b, "b"), (a_scales, "a_scales"), (b_scales, "b_scales")):
         _need(t, torch.uint8, f"mxfp8_gemm {what}")
     m, k = a.shape
@@ -329,7 +331,11 @@ def mxfp8_gemm(a: torch.Tensor, a_scales: torch.Tensor, b: torch.Tensor, b_scale
     g.a, g.a_scales, g.b, g.b_scales = a.data_ptr(), a_scales.data_ptr(), b.data_ptr(), \
         b_scales.data_ptr()
     g.d, g.bf16, g.scratch = out.data_ptr(), int(bf16), None
-    N.check(N.lib().llmp_b200_mxfp8_gemm(C.byref(g), sms, _stream()), "llmp_b200_mxfp8_gemm")
+    if variant == 0:
+        N.check(N.lib().llmp_b200_mxfp8_gemm(C.byref(g), sms, _stream()), "llmp_b200_mxfp8_gemm")
+    else:
+        N.check(N.lib().llmp_b200_mxfp8_gemm_variant(C.byref(g), sms, variant, _stream()),
+                "llmp_b200_mxfp8_gemm_variant")
     return out
 
 

@@ -70,9 +70,10 @@ def _operands(torch, orc, rng, m, n, k):
     # a caller that grants few SMs: every CTA walks many tiles, so both TMEM
     # accumulators and every smem stage are reused many times over
     (256, 512, 1024, False, 1), (384, 1280, 2048, True, 2), (129, 600, 384, False, 1),
-    (700, 400, 256, True, 3),
+    (700, 400, 256, True, 3), (2176, 192, 256, False, 0), (513, 1000, 896, False, 4),
 ])
-def test_gemm_equals_the_product_of_its_quantized_operands(cuda, orc, m, n, k, bf16, sms):
+@pytest.mark.parametrize("variant", [1, 2], ids=["one-cta", "cta-pair"])
+def test_gemm_equals_the_product_of_its_quantized_operands(cuda, orc, m, n, k, bf16, sms, variant):
     torch = cuda
     ops = _ops()
     rng = np.random.default_rng(m + n + k)
@@ -81,10 +82,13 @@ def test_gemm_equals_the_product_of_its_quantized_operands(cuda, orc, m, n, k, b
     esz = torch.bfloat16 if bf16 else torch.float32
     buf = torch.full((m * n + 64,), float("nan"), dtype=esz, device="cuda")
     out = buf[: m * n].view(m, n)
-    ops.mxfp8_gemm(a, a_s, b, bs, bf16=bf16, out=out, sms=sms)
+    ops.mxfp8_gemm(a, a_s, b, bs, bf16=bf16, out=out, sms=sms, variant=variant)
     torch.cuda.synchronize()
     assert ops.device_faults() == 0
     assert torch.isnan(buf[m * n:]).all()
+    # the entry point's own rule picks one of the two kernels: the same bits
+    assert torch.equal(ops.mxfp8_gemm(a, a_s, b, bs, bf16=bf16, sms=sms), out) or variant != (
+        2 if m > 128 else 1)
     got = out.float().cpu().numpy().astype(np.float64)
     _, want = orc.mxfp8_gemm(a.cpu().numpy(), a_s.cpu().numpy(), b.cpu().numpy(),
                              bs.cpu().numpy(), bf16=False, want64=True)
@@ -110,6 +114,9 @@ def test_gemm_at_the_benchmark_shape_by_linearity(cuda, orc):
     assert torch.isfinite(d).all()
     d2 = ops.mxfp8_gemm(a, a_s + 1, b, bs, bf16=False)
     assert torch.equal(d2, d * 2)
+    # one CTA a tile and CTA pairs add a tile's k-steps in the same order
+    assert torch.equal(ops.mxfp8_gemm(a, a_s, b, bs, bf16=False, variant=1),
+                       ops.mxfp8_gemm(a, a_s, b, bs, bf16=False, variant=2))
     # a slab against the oracle
     rows = slice(1000, 1064)
     cols = slice(6000, 6096)
