@@ -989,13 +989,108 @@ def bench_ffn_columns(torch, dist, ops, rank, world, batch, steps=5, warmup=2):
                 bits = bits and bool(torch.equal(got, want))
     parity = _all_true(torch, dist, parity)
     sb = step_bytes(batch)
-    return {"metric": METRIC, "value": round(sb / (ms * 1e-3) / 1e9, 2), "unit": UNIT,
+    line = {"metric": METRIC, "value": round(sb / (ms * 1e-3) / 1e9, 2), "unit": UNIT,
             "ms_per_step": round(ms, 4), "n_gpus": world, "steps": steps, "warmup": warmup,
             "scaling": "strong", "parity": parity, "parity_bar": "1e-5 of the output scale",
             "max_rel_err": worst, "bit_equal": bits, "faults": ops.device_faults(),
             "config": {"workload": f"Gemma-3-4B FFN decode products, Q4_K, {LAYERS} layers, batch {batch}",
                        "parallelism": f"N-column shards x{world}, NCCL all-gather of the GLU output "
                                       "and of the layer output, plain stream launches"}}
+    if batch == 1:
+        try:
+            line["peer_stores"] = _ffn_columns_peer(torch, dist, ops, rank, world, layers, whole,
+                                                    check_layers, x, n_glu, n_down, steps=20, warmup=3)
+        except Exception as e:                       # the NCCL form above stands by itself
+            line["peer_stores"] = {"unavailable": repr(e)[:200]}
+    return line
+
+
+def _ffn_columns_peer(torch, dist, ops, rank, world, layers, whole, check_layers, x, n_glu, n_down,
+                      steps, warmup):
+    """The same sharded step with no collective library in it: each shard product's slice is
+    stored into every rank's copy of the vector by llmp_b200_peer_publish (plain peer stores
+    into CUDA-IPC mapped memory) and the next quantizer starts by waiting, with a bound, for
+    every rank's flag.  No NCCL call inside the step, so the step is one replayed CUDA graph.
+    The layers' inputs are independent, as in the one-GPU step, but every layer waits for the
+    layer before's output exchange: that is what lets one gathered buffer be reused."""
+    from llmp_b200 import peer
+    T = ops.TYPE_Q4_K
+    ex = peer.PeerExchange(world, rank, {"h": INTER, "y": LAYERS * HIDDEN}, sites=2 * LAYERS)
+    everyone = [None] * world
+    dist.all_gather_object(everyone, ex.handles())
+    ex.connect(everyone)
+    polls = 1 << 24                                  # about 1.7 s: ranks start a step together
+    q8x = torch.empty((1, ops.q8_1_row_blocks(HIDDEN) * 36), dtype=torch.uint8, device="cuda")
+    q8h = torch.empty((1, ops.q8_1_row_blocks(INTER) * 36), dtype=torch.uint8, device="cuda")
+    h_shard = torch.empty((1, n_glu), device="cuda")
+    y_shard = torch.empty((1, n_down), device="cuda")
+    h_seen = {}
+
+    def step(keep=False):
+        ex.begin_step()
+        for l, (gate, up, down) in enumerate(layers):
+            if l == 0:
+                ops.quantize_q8(x[0], out=q8x)
+            else:                                    # back-pressure: layer l - 1 is out everywhere
+                ex.quantize_q8("y", 2 * l - 1, q8x, polls, x=x[l])
+            ops.vecq(up, T, HIDDEN, n_glu, q8x, 1, gate=gate, glu=ops.GLU_GEGLU, out=h_shard)
+            ex.publish("h", 2 * l, h_shard.view(-1), rank * n_glu)
+            ex.quantize_q8("h", 2 * l, q8h, polls)
+            if keep and l in check_layers:
+                h_seen[l] = ex.vectors["h"].clone()
+            ops.vecq(down, T, INTER, n_down, q8h, 1, out=y_shard)
+            ex.publish("y", 2 * l + 1, y_shard.view(-1), (l * HIDDEN) + (rank * n_down))
+        ex.wait("y", (2 * LAYERS) - 1, polls)
+
+    dist.barrier()
+    torch.cuda.synchronize()
+    step()                                           # plain launches once
+    torch.cuda.synchronize()
+    dist.barrier()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    for _ in range(warmup):
+        graph.replay()
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = _max_over_ranks(torch, dist, e0.elapsed_time(e1) / steps)
+    timed_out = ex.timed_out()
+    dist.barrier()
+    step(keep=True)
+    torch.cuda.synchronize()
+    timed_out = timed_out or ex.timed_out()
+    parity, worst = True, 0.0
+    if rank == 0:
+        for l in check_layers:
+            gate, up, down = whole[l]
+            h = ops.vecq(up, T, HIDDEN, INTER, ops.quantize_q8(x[l]), 1, gate=gate, glu=ops.GLU_GEGLU)
+            y = ops.vecq(down, T, INTER, HIDDEN, ops.quantize_q8(h_seen[l].view(1, -1)), 1)
+            got_y = ex.vectors["y"][l * HIDDEN:(l + 1) * HIDDEN].view(1, -1)
+            for got, want in ((h_seen[l].view(1, -1), h), (got_y, y)):
+                err = float((got - want).abs().max() / want.abs().max())
+                worst = max(worst, err)
+                parity = parity and err <= 1e-5
+    parity = _all_true(torch, dist, parity and not timed_out)
+    dist.barrier()
+    ex.close()
+    return {"value": round(step_bytes(1) / (ms * 1e-3) / 1e9, 2), "unit": UNIT,
+            "ms_per_step": round(ms, 4), "steps": steps, "warmup": warmup, "parity": parity,
+            "parity_bar": "1e-5 of the output scale", "max_rel_err": worst,
+            "waits_timed_out": bool(timed_out), "faults": ops.device_faults(),
+            "launch": "cuda graph replay, no collective library in the step",
+            "parallelism": f"N-column shards x{world}; each slice stored into every rank's vector "
+                           "(CUDA IPC, plain peer stores) and flagged; consumers wait with a bound"}
 
 
 def run_sharded_only(args, rank: int, world: int, local_rank: int, which: str):

@@ -192,6 +192,47 @@ int llmp_b200_mmvq_prepared(const llmp_b200_mmvq_desc* desc, void* stream);
  * x or prepared q8.  No fused GLU. */
 int llmp_b200_mmvq_rows(const llmp_b200_mmvq_desc* desc, void* stream);
 
+/* ------------------------------------------------------------------ peer exchange */
+/* The all-gather after an N-column sharded projection (the reference's kAllGather node,
+ * src/ir/op.h:246-250, src/planner/partition.h:39-56, src/components/ffn.cc:67-81) without a
+ * collective library: llmp_b200_peer_publish stores this rank's slice into every rank's copy of
+ * the gathered vector (plain stores into memory of the other GPUs, mapped through CUDA IPC)
+ * and raises a flag word on each; the consumer begins by waiting, with a bound, for every
+ * rank's flag (llmp_b200_q8_1_quantize_gathered, or llmp_b200_peer_wait alone).  One process a
+ * GPU.  Memory that other processes map comes from llmp_b200_peer_alloc (zeroed; the one place
+ * this library allocates, because an exportable allocation must be a whole one). */
+#define LLMP_B200_PEER_HANDLE_BYTES 64
+int llmp_b200_peer_alloc(size_t bytes, void** ptr);
+int llmp_b200_peer_free(void* ptr);
+int llmp_b200_peer_export(const void* ptr, void* handle /* 64 bytes out */);
+int llmp_b200_peer_import(const void* handle, void** ptr);  /* another process's allocation */
+int llmp_b200_peer_close(void* ptr);
+typedef struct llmp_b200_peer_site {
+  int world, rank;
+  void* const* buffers;    /* device array [world]: every rank's copy of the gathered vector ([rank]: local) */
+  int32_t* const* flags;   /* device array [world]: every rank's flag words, I32 [sites][world], zeroed */
+  const int32_t* step;     /* device word, this rank's: the step number flags are compared with */
+  int site;                /* which exchange of the step: its own row of flags */
+} llmp_b200_peer_site;
+/* Raises the step word by one: once at the start of a step (a captured graph replays it). */
+int llmp_b200_peer_begin_step(int32_t* step, void* stream);
+/* slice (bytes, 16-byte aligned, the kernel before's output) -> offset in every rank's buffer,
+ * then flags[to][site][rank] = step on every rank `to`. */
+int llmp_b200_peer_publish(const llmp_b200_peer_site* site, const void* slice, size_t offset,
+                           size_t bytes, void* stream);
+/* Waits until local_flags[site][r] has reached the step number for every r, polling each at
+ * most `polls` times about 0.1 us apart.  A wait that runs out writes 1 to *status (a device
+ * int32, may be NULL), raises llmp_b200_device_faults() by one and RETURNS: the stream always
+ * finishes. */
+int llmp_b200_peer_wait(const llmp_b200_peer_site* site, const int32_t* local_flags, int polls,
+                        int32_t* status, void* stream);
+/* llmp_b200_q8_1_quantize of one plane whose input is a gathered vector: every CTA first waits
+ * as llmp_b200_peer_wait does. */
+int llmp_b200_q8_1_quantize_gathered(const float* x, int64_t k, int64_t rows, int64_t stride_row,
+                                     void* out, const llmp_b200_peer_site* site,
+                                     const int32_t* local_flags, int polls, int32_t* status,
+                                     void* stream);
+
 /* Verification entry with no reference counterpart as a separate call: the
  * int32 per-block sums the product kernels form (the quantity the reference
  * checks bit for bit, tests/unit/dsv4_fast_test.cc:511-540), for nrows weight

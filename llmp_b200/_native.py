@@ -34,6 +34,12 @@ class VecQDesc(C.Structure):
                         ("limit", C.c_float)]
 
 
+class PeerSite(C.Structure):
+    """llmp_b200_peer_site (include/llmp_b200.h)."""
+    _fields_ = [("world", C.c_int), ("rank", C.c_int), ("buffers", C.c_void_p),
+                ("flags", C.c_void_p), ("step", C.c_void_p), ("site", C.c_int)]
+
+
 class MmvqDesc(C.Structure):
     """llmp_b200_mmvq_desc (include/llmp_b200.h)."""
     _fields_ = [("type", C.c_int), ("w", C.c_void_p), ("gate", C.c_void_p), ("glu", C.c_int),
@@ -105,6 +111,19 @@ SIGNATURES = {
     "llmp_b200_q8_1_row_blocks": (C.c_int64, [C.c_int64]),
     "llmp_b200_q8_1_quantize": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
                                           C.c_int64, C.c_void_p, C.c_void_p]),
+    "llmp_b200_q8_1_quantize_gathered": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
+                                                   C.c_void_p, C.POINTER(PeerSite), C.c_void_p,
+                                                   C.c_int, C.c_void_p, C.c_void_p]),
+    "llmp_b200_peer_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)]),
+    "llmp_b200_peer_free": (C.c_int, [C.c_void_p]),
+    "llmp_b200_peer_export": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "llmp_b200_peer_import": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    "llmp_b200_peer_close": (C.c_int, [C.c_void_p]),
+    "llmp_b200_peer_begin_step": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "llmp_b200_peer_publish": (C.c_int, [C.POINTER(PeerSite), C.c_void_p, C.c_size_t, C.c_size_t,
+                                         C.c_void_p]),
+    "llmp_b200_peer_wait": (C.c_int, [C.POINTER(PeerSite), C.c_void_p, C.c_int, C.c_void_p,
+                                      C.c_void_p]),
     "llmp_b200_vecq_variants": (C.c_int, []),
     "llmp_b200_vecq_variant_name": (C.c_char_p, [C.c_int]),
     "llmp_b200_vecq_rank_count": (C.c_int, []),

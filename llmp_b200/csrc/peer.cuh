@@ -1,0 +1,64 @@
+// Flag waits of the peer-store exchange (peer.cu), shared with the kernels that begin by
+// waiting for a gathered buffer (the Q8_1 quantizer).
+#ifndef LLMP_B200_CSRC_PEER_CUH_
+#define LLMP_B200_CSRC_PEER_CUH_
+
+#include "common.cuh"
+
+namespace llmp_b200 {
+
+// What a consumer kernel needs to wait for one exchange: this rank's flag row of the site
+// (one word a source rank), the step word, and where to report a wait that ran out.
+struct PeerWait {
+  const std::int32_t* flags;  // null: no wait
+  const std::int32_t* step;
+  int world;
+  int polls;
+  std::int32_t* status;
+  unsigned int* faults;
+};
+
+#ifdef __CUDACC__
+__device__ __forceinline__ std::int32_t LoadAcquireSys(const std::int32_t* p) {
+  std::int32_t v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void StoreReleaseSys(std::int32_t* p, std::int32_t v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Every thread of the CTA calls this.  Thread r < world polls source rank r's flag until it
+// reaches the step's number, at most `polls` times (about 0.1 us apart); the CTA then meets.
+// True when every flag arrived.  A wait that runs out is reported once (thread 0 of CTA 0
+// writes 1 to *status and raises the fault counter) and the caller carries on, so that the
+// stream, a captured graph included, always finishes.
+__device__ __forceinline__ bool PeerWaitAll(const PeerWait& w) {
+  if (w.flags == nullptr) return true;
+  bool arrived = true;
+  if (static_cast<int>(threadIdx.x) < w.world) {
+    const std::int32_t want = *w.step;
+    // After one wait of the step has run out, the later ones look once: a rank that is gone
+    // costs a step one time limit, not one per exchange.
+    const int polls = (w.status != nullptr && *w.status != 0) ? 1 : w.polls;
+    arrived = false;
+    for (int i = 0; i < polls; ++i) {
+      if (LoadAcquireSys(w.flags + threadIdx.x) - want >= 0) {
+        arrived = true;
+        break;
+      }
+      __nanosleep(100);
+    }
+  }
+  const bool all = __syncthreads_and(arrived ? 1 : 0) != 0;
+  if (!all && threadIdx.x == 0 && blockIdx.x == 0) {
+    if (w.status != nullptr) *w.status = 1;
+    if (w.faults != nullptr) atomicAdd(w.faults, 1u);
+  }
+  return all;
+}
+#endif  // __CUDACC__
+
+}  // namespace llmp_b200
+
+#endif  // LLMP_B200_CSRC_PEER_CUH_

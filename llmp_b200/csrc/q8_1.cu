@@ -7,7 +7,7 @@
 // Eight lanes share a block, four consecutive values a lane (one 16-byte
 // load).  The 32-value sum is formed as a butterfly over value indices 16, 8,
 // 4, 2, 1 apart, so the FP16 it rounds to does not depend on the lane layout.
-#include "common.cuh"
+#include "peer.cuh"
 
 namespace llmp_b200 {
 namespace {
@@ -18,11 +18,14 @@ template <bool kVec>
 __global__ void __launch_bounds__(kThreads)
 QuantizeQ8_1Kernel(const float* __restrict__ x, std::int64_t k, std::int64_t rows,
                    std::int64_t stride_row, std::int64_t stride_plane, std::int64_t row_blocks,
-                   std::int64_t total_lanes, std::uint8_t* __restrict__ out) {
+                   std::int64_t total_lanes, std::uint8_t* __restrict__ out, const PeerWait gathered) {
   // The input is the kernel before's output; the products after this one may
   // start fetching their weights now.
   GridLaunchDependents();
   GridDependencyWait();
+  // ... or, in the column-sharded step, a vector every rank stores a slice of (peer.cu):
+  // wait, with a bound, for all the slices.
+  PeerWaitAll(gathered);
   const std::int64_t i = (static_cast<std::int64_t>(blockIdx.x) * kThreads) + threadIdx.x;
   const bool live = i < total_lanes;  // whole groups of 8 lanes are live or not
   const std::int64_t block = (live ? i : 0) / 8;
@@ -77,13 +80,14 @@ QuantizeQ8_1Kernel(const float* __restrict__ x, std::int64_t k, std::int64_t row
 }  // namespace
 }  // namespace llmp_b200
 
-extern "C" {
+extern "C" int64_t llmp_b200_q8_1_row_blocks(int64_t k) { return (k + 511) / 512 * 512 / 32; }
 
-int64_t llmp_b200_q8_1_row_blocks(int64_t k) { return (k + 511) / 512 * 512 / 32; }
-
-int llmp_b200_q8_1_quantize(const float* x, int64_t k, int64_t rows, int64_t planes,
-                            int64_t stride_row, int64_t stride_plane, void* out, void* stream) {
-  using namespace llmp_b200;
+namespace llmp_b200 {
+PeerWait PeerWaitOf(const llmp_b200_peer_site& site, const std::int32_t* local_flags, int polls,
+                    std::int32_t* status);
+namespace {
+int Quantize(const float* x, int64_t k, int64_t rows, int64_t planes, int64_t stride_row,
+             int64_t stride_plane, void* out, const PeerWait& gathered, void* stream) {
   if (x == nullptr || out == nullptr || k < 1 || rows < 1 || planes < 1) {
     return Reject("q8_1: F32 input [k, rows, planes] and an output, all non-empty");
   }
@@ -100,12 +104,35 @@ int llmp_b200_q8_1_quantize(const float* x, int64_t k, int64_t rows, int64_t pla
   const cudaError_t e =
       vec ? LaunchPdl(QuantizeQ8_1Kernel<true>, grid, dim3(kThreads), 0,
                       static_cast<cudaStream_t>(stream), x, k, rows, stride_row, stride_plane,
-                      row_blocks, total, o)
+                      row_blocks, total, o, gathered)
           : LaunchPdl(QuantizeQ8_1Kernel<false>, grid, dim3(kThreads), 0,
                       static_cast<cudaStream_t>(stream), x, k, rows, stride_row, stride_plane,
-                      row_blocks, total, o);
+                      row_blocks, total, o, gathered);
   if (e != cudaSuccess) return Failed(e, "q8_1 launch");
   return 0;
+}
+}  // namespace
+}  // namespace llmp_b200
+
+extern "C" {
+
+int llmp_b200_q8_1_quantize(const float* x, int64_t k, int64_t rows, int64_t planes,
+                            int64_t stride_row, int64_t stride_plane, void* out, void* stream) {
+  return llmp_b200::Quantize(x, k, rows, planes, stride_row, stride_plane, out, llmp_b200::PeerWait{},
+                             stream);
+}
+
+int llmp_b200_q8_1_quantize_gathered(const float* x, int64_t k, int64_t rows, int64_t stride_row,
+                                     void* out, const llmp_b200_peer_site* site,
+                                     const int32_t* local_flags, int polls, int32_t* status,
+                                     void* stream) {
+  using namespace llmp_b200;
+  if (site == nullptr || local_flags == nullptr || polls < 1 || site->world < 1 || site->world > 32 ||
+      site->step == nullptr || site->site < 0) {
+    return Reject("q8_1 gathered: a site, this rank's flag words and a poll limit");
+  }
+  return Quantize(x, k, rows, 1, stride_row, 0, out, PeerWaitOf(*site, local_flags, polls, status),
+                  stream);
 }
 
 }  // extern "C"

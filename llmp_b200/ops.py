@@ -15,7 +15,7 @@ from . import _native as N
 from ._native import (GLU_GEGLU, GLU_NONE, GLU_SWIGLU, GLU_SWIGLU_CLAMP, TYPE_Q4_K, TYPE_Q8_0,
                       LaunchFailed, Rejected)
 
-__all__ = ["available", "sm_count", "device_faults", "block_bytes", "block_elems", "q8_1_row_blocks",
+__all__ = ["available", "sm_count", "device_faults", "device_faults_clear", "block_bytes", "block_elems", "q8_1_row_blocks",
            "quantize_q8", "vecq", "vecq_ranks", "mmvq", "vecq_f32", "vecq_q8", "vecq_q8_scratch", "vecq_variants", "vecq_block_sums", "mxfp8_padded_rows",
            "mxfp8_quantize", "mxfp8_swizzle", "mxfp8_gemm", "mxfp8_mul_mat_vec", "decode_vector", "decode_rows", "decode_matrix", "decode_grouped", "DECODER_Q8_0", "DECODER_MXFP8_SPLIT",
            "DECODER_MXFP8_ATOMS", "DECODER_BF16", "DECODER_F16", "DECODER_NVFP4_SPLIT", "DECODER_NVFP4_ATOMS",
@@ -36,6 +36,11 @@ def available() -> bool:
 def device_faults() -> int:
     """Bounded device-side waits that ran out since load (0 when healthy)."""
     return int(N.lib().llmp_b200_device_faults())
+
+
+def device_faults_clear() -> int:
+    """Zeroes that counter; returns what it held."""
+    return int(N.lib().llmp_b200_device_faults_clear())
 
 
 def sm_count() -> int:

@@ -1,0 +1,84 @@
+"""The peer-store exchange (llmp_b200_peer_*): on one GPU, with the ranks emulated in one
+process and every kernel run to completion before the next is queued, so that no kernel here
+ever waits for another kernel of the same GPU; the wait's give-up path by a flag nobody sets."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _pair(world, vectors, sites):
+    from llmp_b200 import peer
+    ranks = [peer.PeerExchange(world, r, vectors, sites) for r in range(world)]
+    everyone = [x.pointers() for x in ranks]
+    for x in ranks:
+        x.connect(everyone)
+    return ranks
+
+
+def test_slices_published_by_every_rank_are_what_the_gathered_quantizer_reads(cuda):
+    torch = cuda
+    import llmp_b200 as ops
+    world, n = 2, 1536
+    ranks = _pair(world, {"h": n}, sites=3)
+    rng = np.random.default_rng(5)
+    for step in range(3):                      # flags carry the step number: replays must work
+        whole = torch.from_numpy(rng.normal(0, 1, size=n).astype(np.float32)).cuda()
+        want = ops.quantize_q8(whole.view(1, n))
+        for x in ranks:
+            x.begin_step()
+        torch.cuda.synchronize()
+        per = n // world
+        for r, x in enumerate(ranks):
+            x.publish("h", 1, whole[r * per:(r + 1) * per].contiguous(), r * per)
+        torch.cuda.synchronize()               # every flag is set before any wait is queued
+        for x in ranks:
+            got = torch.empty_like(want)
+            x.quantize_q8("h", 1, got)
+            torch.cuda.synchronize()
+            assert torch.equal(got, want), step
+            assert torch.equal(x.vectors["h"], whole)
+            assert not x.timed_out()
+            assert int(x.step.item()) == step + 1
+    assert ops.device_faults() == 0
+    for x in ranks:
+        x.close()
+
+
+def test_a_wait_for_a_flag_nobody_sets_gives_up_and_says_so(cuda):
+    torch = cuda
+    import llmp_b200 as ops
+    ranks = _pair(2, {"y": 256}, sites=2)
+    before = ops.device_faults()
+    a = ranks[0]
+    a.begin_step()
+    a.publish("y", 0, torch.ones(128, device="cuda"), 0)     # rank 1 never publishes
+    torch.cuda.synchronize()
+    a.wait("y", 0, polls=50)
+    torch.cuda.synchronize()
+    assert a.timed_out()
+    assert ops.device_faults() == before + 1
+    out = torch.empty((1, ops.q8_1_row_blocks(256) * 36), dtype=torch.uint8, device="cuda")
+    a.quantize_q8("y", 1, out, polls=20)                     # the fused form: same give-up path
+    torch.cuda.synchronize()
+    assert a.timed_out()
+    assert ops.device_faults() == before + 2
+    ops.device_faults_clear()
+    # the context is intact: an ordinary launch afterwards is correct
+    x = torch.randn((1, 512), device="cuda")
+    assert ops.quantize_q8(x).shape[1] == ops.q8_1_row_blocks(512) * 36
+    torch.cuda.synchronize()
+    for r in ranks:
+        r.close()
+
+
+def test_publish_refuses_what_it_cannot_copy(cuda):
+    torch = cuda
+    import llmp_b200 as ops
+    (x,) = _pair(1, {"h": 64}, sites=1)
+    with pytest.raises(ops.Rejected):
+        x.publish("h", 0, torch.ones(16, device="cuda"), 3)          # offset not 16-byte aligned
+    with pytest.raises(ops.Rejected):
+        x.publish("h", 1, torch.ones(16, device="cuda"), 0)          # no such site
+    torch.cuda.synchronize()
+    x.close()
