@@ -1027,20 +1027,23 @@ def _ffn_columns_peer(torch, dist, ops, rank, world, layers, whole, check_layers
     h_seen = {}
 
     def step(keep=False):
+        # Four launches a layer, as on one GPU: each quantizer first stores the product
+        # before's slice into every rank's vector, then waits for all of them.
         ex.begin_step()
         for l, (gate, up, down) in enumerate(layers):
             if l == 0:
                 ops.quantize_q8(x[0], out=q8x)
-            else:                                    # back-pressure: layer l - 1 is out everywhere
-                ex.quantize_q8("y", 2 * l - 1, q8x, polls, x=x[l])
+            else:       # layer l - 1's output goes out; back-pressure: it is out everywhere
+                ex.exchange_quantize_q8("y", 2 * l - 1, y_shard.view(-1),
+                                        ((l - 1) * HIDDEN) + (rank * n_down), q8x, polls, x=x[l])
             ops.vecq(up, T, HIDDEN, n_glu, q8x, 1, gate=gate, glu=ops.GLU_GEGLU, out=h_shard)
-            ex.publish("h", 2 * l, h_shard.view(-1), rank * n_glu)
-            ex.quantize_q8("h", 2 * l, q8h, polls)
+            ex.exchange_quantize_q8("h", 2 * l, h_shard.view(-1), rank * n_glu, q8h, polls)
             if keep and l in check_layers:
                 h_seen[l] = ex.vectors["h"].clone()
             ops.vecq(down, T, INTER, n_down, q8h, 1, out=y_shard)
-            ex.publish("y", 2 * l + 1, y_shard.view(-1), (l * HIDDEN) + (rank * n_down))
-        ex.wait("y", (2 * LAYERS) - 1, polls)
+        last = LAYERS - 1
+        ex.publish("y", (2 * last) + 1, y_shard.view(-1), (last * HIDDEN) + (rank * n_down))
+        ex.wait("y", (2 * last) + 1, polls)
 
     dist.barrier()
     torch.cuda.synchronize()

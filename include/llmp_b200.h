@@ -232,6 +232,14 @@ int llmp_b200_q8_1_quantize_gathered(const float* x, int64_t k, int64_t rows, in
                                      void* out, const llmp_b200_peer_site* site,
                                      const int32_t* local_flags, int polls, int32_t* status,
                                      void* stream);
+/* Publish, wait and quantize in ONE launch: stores `slice` (the kernel before's output) into
+ * every rank's buffer of the site and flags it, waits for every rank's flag, then quantizes the
+ * F32 vector x of k values (the gathered vector itself, or another input when the exchange is
+ * waited for as back-pressure only). */
+int llmp_b200_q8_1_quantize_exchange(const float* x, int64_t k, void* out,
+                                     const llmp_b200_peer_site* site, const int32_t* local_flags,
+                                     const void* slice, size_t offset, size_t bytes, int polls,
+                                     int32_t* status, void* stream);
 
 /* Verification entry with no reference counterpart as a separate call: the
  * int32 per-block sums the product kernels form (the quantity the reference

@@ -114,6 +114,10 @@ SIGNATURES = {
     "llmp_b200_q8_1_quantize_gathered": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
                                                    C.c_void_p, C.POINTER(PeerSite), C.c_void_p,
                                                    C.c_int, C.c_void_p, C.c_void_p]),
+    "llmp_b200_q8_1_quantize_exchange": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p,
+                                                   C.POINTER(PeerSite), C.c_void_p, C.c_void_p,
+                                                   C.c_size_t, C.c_size_t, C.c_int, C.c_void_p,
+                                                   C.c_void_p]),
     "llmp_b200_peer_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)]),
     "llmp_b200_peer_free": (C.c_int, [C.c_void_p]),
     "llmp_b200_peer_export": (C.c_int, [C.c_void_p, C.c_void_p]),

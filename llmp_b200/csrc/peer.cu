@@ -23,25 +23,10 @@ __global__ void BeginStepKernel(std::int32_t* step) {
   if (threadIdx.x == 0 && blockIdx.x == 0) *step = *step + 1;
 }
 
-// CTA p serves destination rank p: copies the slice, makes it visible system-wide, flags.
-__global__ void __launch_bounds__(256)
-PublishKernel(const llmp_b200_peer_site site, const unsigned char* __restrict__ slice,
-              std::size_t offset, std::size_t bytes) {
+__global__ void __launch_bounds__(256) PublishKernel(const PeerPublish publish) {
   GridLaunchDependents();
   GridDependencyWait();  // the slice is the kernel before's output
-  const int to = static_cast<int>(blockIdx.x);
-  unsigned char* dst = static_cast<unsigned char*>(site.buffers[to]) + offset;
-  const std::size_t vectors = bytes / 16;
-  const uint4* src4 = reinterpret_cast<const uint4*>(slice);
-  uint4* dst4 = reinterpret_cast<uint4*>(dst);
-  for (std::size_t i = threadIdx.x; i < vectors; i += blockDim.x) dst4[i] = src4[i];
-  for (std::size_t i = (vectors * 16) + threadIdx.x; i < bytes; i += blockDim.x) dst[i] = slice[i];
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    StoreReleaseSys(site.flags[to] + (static_cast<std::size_t>(site.site) * site.world) + site.rank,
-                    *site.step);
-  }
+  PeerPublishSlice(publish);
 }
 
 __global__ void WaitKernel(const PeerWait wait) {
@@ -61,6 +46,21 @@ int CheckSite(const llmp_b200_peer_site* site, const char* who) {
 }
 
 }  // namespace
+
+PeerPublish PeerPublishOf(const llmp_b200_peer_site& site, const void* slice, std::size_t offset,
+                          std::size_t bytes) {
+  PeerPublish p{};
+  p.slice = static_cast<const unsigned char*>(slice);
+  p.offset = offset;
+  p.bytes = bytes;
+  p.buffers = site.buffers;
+  p.flags = site.flags;
+  p.step = site.step;
+  p.world = site.world;
+  p.rank = site.rank;
+  p.site = site.site;
+  return p;
+}
 
 PeerWait PeerWaitOf(const llmp_b200_peer_site& site, const std::int32_t* local_flags, int polls,
                     std::int32_t* status) {
@@ -151,8 +151,7 @@ int llmp_b200_peer_publish(const llmp_b200_peer_site* site, const void* slice, s
   if (const int status = DeviceStatus(); status != 0) return status;
   const cudaError_t e =
       LaunchPdl(PublishKernel, dim3(static_cast<unsigned>(site->world)), dim3(256), 0,
-                static_cast<cudaStream_t>(stream), *site, static_cast<const unsigned char*>(slice),
-                offset, bytes);
+                static_cast<cudaStream_t>(stream), PeerPublishOf(*site, slice, offset, bytes));
   return e == cudaSuccess ? 0 : Failed(e, "peer_publish launch");
 }
 

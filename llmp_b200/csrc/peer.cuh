@@ -18,6 +18,16 @@ struct PeerWait {
   unsigned int* faults;
 };
 
+// What a kernel that also publishes needs: the slice it owes every rank.
+struct PeerPublish {
+  const unsigned char* slice;  // null: nothing to publish
+  std::size_t offset, bytes;
+  void* const* buffers;        // device array [world]
+  std::int32_t* const* flags;  // device array [world]
+  const std::int32_t* step;
+  int world, rank, site;
+};
+
 #ifdef __CUDACC__
 __device__ __forceinline__ std::int32_t LoadAcquireSys(const std::int32_t* p) {
   std::int32_t v;
@@ -26,6 +36,25 @@ __device__ __forceinline__ std::int32_t LoadAcquireSys(const std::int32_t* p) {
 }
 __device__ __forceinline__ void StoreReleaseSys(std::int32_t* p, std::int32_t v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Every thread of the CTA calls this.  CTA b stores the slice into ranks b, b + gridDim.x, ...
+// and flags each, so any grid publishes to any world.
+__device__ __forceinline__ void PeerPublishSlice(const PeerPublish& p) {
+  if (p.slice == nullptr) return;
+  for (int to = static_cast<int>(blockIdx.x); to < p.world; to += static_cast<int>(gridDim.x)) {
+    unsigned char* dst = static_cast<unsigned char*>(p.buffers[to]) + p.offset;
+    const std::size_t vectors = p.bytes / 16;
+    const uint4* src4 = reinterpret_cast<const uint4*>(p.slice);
+    uint4* dst4 = reinterpret_cast<uint4*>(dst);
+    for (std::size_t i = threadIdx.x; i < vectors; i += blockDim.x) dst4[i] = src4[i];
+    for (std::size_t i = (vectors * 16) + threadIdx.x; i < p.bytes; i += blockDim.x) dst[i] = p.slice[i];
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      StoreReleaseSys(p.flags[to] + (static_cast<std::size_t>(p.site) * p.world) + p.rank, *p.step);
+    }
+  }
 }
 
 // Every thread of the CTA calls this.  Thread r < world polls source rank r's flag until it

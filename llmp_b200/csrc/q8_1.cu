@@ -18,13 +18,17 @@ template <bool kVec>
 __global__ void __launch_bounds__(kThreads)
 QuantizeQ8_1Kernel(const float* __restrict__ x, std::int64_t k, std::int64_t rows,
                    std::int64_t stride_row, std::int64_t stride_plane, std::int64_t row_blocks,
-                   std::int64_t total_lanes, std::uint8_t* __restrict__ out, const PeerWait gathered) {
+                   std::int64_t total_lanes, std::uint8_t* __restrict__ out, const PeerWait gathered,
+                   const PeerPublish publish) {
   // The input is the kernel before's output; the products after this one may
   // start fetching their weights now.
   GridLaunchDependents();
   GridDependencyWait();
   // ... or, in the column-sharded step, a vector every rank stores a slice of (peer.cu):
-  // wait, with a bound, for all the slices.
+  // store this rank's slice everywhere first (when this kernel is given it), then wait, with a
+  // bound, for all the slices.  The CTAs of this small grid are all resident, so the ones that
+  // wait for this rank's own flag do not keep the one that sets it from running.
+  PeerPublishSlice(publish);
   PeerWaitAll(gathered);
   const std::int64_t i = (static_cast<std::int64_t>(blockIdx.x) * kThreads) + threadIdx.x;
   const bool live = i < total_lanes;  // whole groups of 8 lanes are live or not
@@ -85,9 +89,12 @@ extern "C" int64_t llmp_b200_q8_1_row_blocks(int64_t k) { return (k + 511) / 512
 namespace llmp_b200 {
 PeerWait PeerWaitOf(const llmp_b200_peer_site& site, const std::int32_t* local_flags, int polls,
                     std::int32_t* status);
+PeerPublish PeerPublishOf(const llmp_b200_peer_site& site, const void* slice, std::size_t offset,
+                          std::size_t bytes);
 namespace {
 int Quantize(const float* x, int64_t k, int64_t rows, int64_t planes, int64_t stride_row,
-             int64_t stride_plane, void* out, const PeerWait& gathered, void* stream) {
+             int64_t stride_plane, void* out, const PeerWait& gathered, const PeerPublish& publish,
+             void* stream) {
   if (x == nullptr || out == nullptr || k < 1 || rows < 1 || planes < 1) {
     return Reject("q8_1: F32 input [k, rows, planes] and an output, all non-empty");
   }
@@ -104,10 +111,10 @@ int Quantize(const float* x, int64_t k, int64_t rows, int64_t planes, int64_t st
   const cudaError_t e =
       vec ? LaunchPdl(QuantizeQ8_1Kernel<true>, grid, dim3(kThreads), 0,
                       static_cast<cudaStream_t>(stream), x, k, rows, stride_row, stride_plane,
-                      row_blocks, total, o, gathered)
+                      row_blocks, total, o, gathered, publish)
           : LaunchPdl(QuantizeQ8_1Kernel<false>, grid, dim3(kThreads), 0,
                       static_cast<cudaStream_t>(stream), x, k, rows, stride_row, stride_plane,
-                      row_blocks, total, o, gathered);
+                      row_blocks, total, o, gathered, publish);
   if (e != cudaSuccess) return Failed(e, "q8_1 launch");
   return 0;
 }
@@ -119,7 +126,7 @@ extern "C" {
 int llmp_b200_q8_1_quantize(const float* x, int64_t k, int64_t rows, int64_t planes,
                             int64_t stride_row, int64_t stride_plane, void* out, void* stream) {
   return llmp_b200::Quantize(x, k, rows, planes, stride_row, stride_plane, out, llmp_b200::PeerWait{},
-                             stream);
+                             llmp_b200::PeerPublish{}, stream);
 }
 
 int llmp_b200_q8_1_quantize_gathered(const float* x, int64_t k, int64_t rows, int64_t stride_row,
@@ -132,7 +139,24 @@ int llmp_b200_q8_1_quantize_gathered(const float* x, int64_t k, int64_t rows, in
     return Reject("q8_1 gathered: a site, this rank's flag words and a poll limit");
   }
   return Quantize(x, k, rows, 1, stride_row, 0, out, PeerWaitOf(*site, local_flags, polls, status),
-                  stream);
+                  PeerPublish{}, stream);
+}
+
+int llmp_b200_q8_1_quantize_exchange(const float* x, int64_t k, void* out,
+                                     const llmp_b200_peer_site* site, const int32_t* local_flags,
+                                     const void* slice, size_t offset, size_t bytes, int polls,
+                                     int32_t* status, void* stream) {
+  using namespace llmp_b200;
+  if (site == nullptr || local_flags == nullptr || polls < 1 || site->world < 1 || site->world > 32 ||
+      site->step == nullptr || site->site < 0 || site->buffers == nullptr || site->flags == nullptr ||
+      site->rank < 0 || site->rank >= site->world) {
+    return Reject("q8_1 exchange: a site, this rank's flag words and a poll limit");
+  }
+  if (slice == nullptr || bytes == 0 || !Aligned(slice, 16) || offset % 16 != 0) {
+    return Reject("q8_1 exchange: a 16-byte aligned slice at a 16-byte aligned offset");
+  }
+  return Quantize(x, k, 1, 1, k, 0, out, PeerWaitOf(*site, local_flags, polls, status),
+                  PeerPublishOf(*site, slice, offset, bytes), stream);
 }
 
 }  // extern "C"

@@ -124,6 +124,22 @@ class PeerExchange:
             polls, self._status, _stream()), "llmp_b200_q8_1_quantize_gathered")
         return out
 
+    def exchange_quantize_q8(self, name: str, site: int, piece: torch.Tensor, offset_floats: int,
+                             out: torch.Tensor, polls: int = DEFAULT_POLLS,
+                             x: torch.Tensor | None = None) -> torch.Tensor:
+        """publish() + quantize_q8() as one launch."""
+        if piece.dtype != torch.float32 or not piece.is_contiguous():
+            raise N.Rejected("peer exchange: a contiguous F32 slice")
+        x = self.vectors[name] if x is None else x.reshape(-1)
+        if x.dtype != torch.float32 or not x.is_contiguous():
+            raise N.Rejected("peer exchange: a contiguous F32 vector")
+        s = self._site(name, site)
+        N.check(N.lib().llmp_b200_q8_1_quantize_exchange(
+            x.data_ptr(), x.numel(), out.data_ptr(), C.byref(s), self._local_flags,
+            piece.data_ptr(), offset_floats * 4, piece.numel() * 4, polls, self._status, _stream()),
+            "llmp_b200_q8_1_quantize_exchange")
+        return out
+
     def timed_out(self) -> bool:
         """Whether a wait of this rank ran out since the last call (reads the device word)."""
         hit = int(self.status.item()) != 0

@@ -45,6 +45,35 @@ def test_slices_published_by_every_rank_are_what_the_gathered_quantizer_reads(cu
         x.close()
 
 
+def test_publish_wait_and_quantize_in_one_launch(cuda):
+    torch = cuda
+    import llmp_b200 as ops
+    world, n = 2, 2560
+    ranks = _pair(world, {"y": n}, sites=2)
+    rng = np.random.default_rng(6)
+    whole = torch.from_numpy(rng.normal(0, 1, size=n).astype(np.float32)).cuda()
+    other = torch.from_numpy(rng.normal(0, 1, size=512).astype(np.float32)).cuda()
+    per = n // world
+    for x in ranks:
+        x.begin_step()
+    torch.cuda.synchronize()
+    ranks[1].publish("y", 1, whole[per:].contiguous(), per)
+    torch.cuda.synchronize()                   # rank 1's flag is set before rank 0 waits for it
+    got = torch.empty((1, ops.q8_1_row_blocks(n) * 36), dtype=torch.uint8, device="cuda")
+    ranks[0].exchange_quantize_q8("y", 1, whole[:per].contiguous(), 0, got)
+    torch.cuda.synchronize()
+    assert torch.equal(got, ops.quantize_q8(whole.view(1, n)))
+    assert torch.equal(ranks[1].vectors["y"], whole)      # rank 0's slice reached rank 1 too
+    # the exchange as back-pressure only: another input is quantized once the flags are there
+    got2 = torch.empty((1, ops.q8_1_row_blocks(512) * 36), dtype=torch.uint8, device="cuda")
+    ranks[1].quantize_q8("y", 1, got2, x=other)
+    torch.cuda.synchronize()
+    assert torch.equal(got2, ops.quantize_q8(other.view(1, 512)))
+    assert not ranks[0].timed_out() and not ranks[1].timed_out() and ops.device_faults() == 0
+    for x in ranks:
+        x.close()
+
+
 def test_a_wait_for_a_flag_nobody_sets_gives_up_and_says_so(cuda):
     torch = cuda
     import llmp_b200 as ops
