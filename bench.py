@@ -997,25 +997,30 @@ def bench_ffn_columns(torch, dist, ops, rank, world, batch, steps=5, warmup=2):
                        "parallelism": f"N-column shards x{world}, NCCL all-gather of the GLU output "
                                       "and of the layer output, plain stream launches"}}
     if batch == 1:
-        try:
-            line["peer_stores"] = _ffn_columns_peer(torch, dist, ops, rank, world, layers, whole,
-                                                    check_layers, x, n_glu, n_down, steps=20, warmup=3)
-        except Exception as e:                       # the NCCL form above stands by itself
-            line["peer_stores"] = {"unavailable": repr(e)[:200]}
+        for key, in_band in (("peer_stores", False), ("peer_words", True)):
+            try:
+                line[key] = _ffn_columns_peer(torch, dist, ops, rank, world, layers, whole, check_layers,
+                                              x, n_glu, n_down, steps=20, warmup=3, in_band=in_band)
+            except Exception as e:                   # the NCCL form above stands by itself
+                line[key] = {"unavailable": repr(e)[:200]}
     return line
 
 
 def _ffn_columns_peer(torch, dist, ops, rank, world, layers, whole, check_layers, x, n_glu, n_down,
-                      steps, warmup):
+                      steps, warmup, in_band):
     """The same sharded step with no collective library in it: each shard product's slice is
     stored into every rank's copy of the vector by llmp_b200_peer_publish (plain peer stores
     into CUDA-IPC mapped memory) and the next quantizer starts by waiting, with a bound, for
     every rank's flag.  No NCCL call inside the step, so the step is one replayed CUDA graph.
     The layers' inputs are independent, as in the one-GPU step, but every layer waits for the
-    layer before's output exchange: that is what lets one gathered buffer be reused."""
+    layer before's output exchange: that is what lets one gathered buffer be reused.
+    in_band: the product kernels themselves store their rows, as tagged 8-byte words, into every
+    rank's vector (llmp_b200_vecq_fan) and the quantizers poll the words they read: no flag
+    words, no fence, no publishing step."""
     from llmp_b200 import peer
     T = ops.TYPE_Q4_K
-    ex = peer.PeerExchange(world, rank, {"h": INTER, "y": LAYERS * HIDDEN}, sites=2 * LAYERS)
+    ex = peer.PeerExchange(world, rank, {"h": INTER, "y": LAYERS * HIDDEN}, sites=2 * LAYERS,
+                           words={"hw": INTER, "yw": LAYERS * HIDDEN})
     everyone = [None] * world
     dist.all_gather_object(everyone, ex.handles())
     ex.connect(everyone)
@@ -1026,7 +1031,27 @@ def _ffn_columns_peer(torch, dist, ops, rank, world, layers, whole, check_layers
     y_shard = torch.empty((1, n_down), device="cuda")
     h_seen = {}
 
-    def step(keep=False):
+    def step_words(keep=False):
+        # Four launches a layer and nothing between a product's stores and the next rank's
+        # reads but NVLink: tags 2l (GLU output) and 2l + 1 (layer output).
+        ex.begin_step()
+        for l, (gate, up, down) in enumerate(layers):
+            if l == 0:
+                ops.quantize_q8(x[0], out=q8x)
+            else:       # back-pressure: layer l - 1's output has reached this rank from everyone
+                ex.quantize_words(q8x, x=x[l], hold=("yw", (l - 1) * HIDDEN, HIDDEN, (2 * l) - 1),
+                                  polls=polls)
+            ops.vecq(up, T, HIDDEN, n_glu, q8x, 1, gate=gate, glu=ops.GLU_GEGLU, out=h_shard,
+                     fan=ex.fan("hw", rank * n_glu, 2 * l))
+            ex.quantize_words(q8h, name="hw", first=0, count=INTER, tag=2 * l, polls=polls)
+            if keep and l in check_layers:
+                h_seen[l] = ex.word_values("hw", 0, INTER)
+            ops.vecq(down, T, INTER, n_down, q8h, 1, out=y_shard,
+                     fan=ex.fan("yw", (l * HIDDEN) + (rank * n_down), (2 * l) + 1))
+        last = LAYERS - 1
+        ex.quantize_words(q8x, x=x[0], hold=("yw", last * HIDDEN, HIDDEN, (2 * last) + 1), polls=polls)
+
+    def step_flags(keep=False):
         # Four launches a layer, as on one GPU: each quantizer first stores the product
         # before's slice into every rank's vector, then waits for all of them.
         ex.begin_step()
@@ -1045,6 +1070,7 @@ def _ffn_columns_peer(torch, dist, ops, rank, world, layers, whole, check_layers
         ex.publish("y", (2 * last) + 1, y_shard.view(-1), (last * HIDDEN) + (rank * n_down))
         ex.wait("y", (2 * last) + 1, polls)
 
+    step = step_words if in_band else step_flags
     dist.barrier()
     torch.cuda.synchronize()
     step()                                           # plain launches once
@@ -1079,7 +1105,8 @@ def _ffn_columns_peer(torch, dist, ops, rank, world, layers, whole, check_layers
             gate, up, down = whole[l]
             h = ops.vecq(up, T, HIDDEN, INTER, ops.quantize_q8(x[l]), 1, gate=gate, glu=ops.GLU_GEGLU)
             y = ops.vecq(down, T, INTER, HIDDEN, ops.quantize_q8(h_seen[l].view(1, -1)), 1)
-            got_y = ex.vectors["y"][l * HIDDEN:(l + 1) * HIDDEN].view(1, -1)
+            got_y = (ex.word_values("yw", l * HIDDEN, HIDDEN) if in_band
+                     else ex.vectors["y"][l * HIDDEN:(l + 1) * HIDDEN]).view(1, -1)
             for got, want in ((h_seen[l].view(1, -1), h), (got_y, y)):
                 err = float((got - want).abs().max() / want.abs().max())
                 worst = max(worst, err)
@@ -1092,8 +1119,11 @@ def _ffn_columns_peer(torch, dist, ops, rank, world, layers, whole, check_layers
             "parity_bar": "1e-5 of the output scale", "max_rel_err": worst,
             "waits_timed_out": bool(timed_out), "faults": ops.device_faults(),
             "launch": "cuda graph replay, no collective library in the step",
-            "parallelism": f"N-column shards x{world}; each slice stored into every rank's vector "
-                           "(CUDA IPC, plain peer stores) and flagged; consumers wait with a bound"}
+            "parallelism": (f"N-column shards x{world}; the product kernels store their rows as tagged "
+                            "8-byte words into every rank's vector (CUDA IPC, plain peer stores); "
+                            "readers poll the words with a bound") if in_band else
+                           (f"N-column shards x{world}; each slice stored into every rank's vector "
+                            "(CUDA IPC, plain peer stores) and flagged; consumers wait with a bound")}
 
 
 def run_sharded_only(args, rank: int, world: int, local_rank: int, which: str):

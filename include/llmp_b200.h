@@ -241,6 +241,31 @@ int llmp_b200_q8_1_quantize_exchange(const float* x, int64_t k, void* out,
                                      const void* slice, size_t offset, size_t bytes, int polls,
                                      int32_t* status, void* stream);
 
+/* The in-band form of the exchange: no flag words, no fence, no publishing kernel.  A value
+ * travels as one 8-byte word {F32 bits, tag}, tag = (step << 8) | an exchange number of 0 to
+ * 255, and it is the PRODUCT KERNEL that stores token 0's results, tagged, into every rank's
+ * vector of words at words[r] + base + row (as well as into desc->dst); a reader polls each word
+ * it needs until it carries the expected tag.  Dense Q4_K products of one token (the two
+ * kernels of the decode step). */
+typedef struct llmp_b200_peer_fan {
+  int world;
+  uint64_t* const* words;  /* device array [world]: every rank's vector (llmp_b200_peer_alloc, zeroed) */
+  const int32_t* step;     /* this rank's step word */
+  int base;                /* word index of this rank's first row */
+  int tag;
+} llmp_b200_peer_fan;
+int llmp_b200_vecq_fan(int type, const llmp_b200_vecq_desc* desc, int variant,
+                       const llmp_b200_peer_fan* fan, void* stream);
+/* The Q8_1 quantizer of one row of k values that arrive as such words (x NULL), each polled
+ * at most `polls` times about 0.1 us apart; or of x (words NULL).  `hold` (or NULL): another
+ * run of hold_count words whose arrival under hold_tag is waited for first, values unused.  A
+ * word that does not arrive writes 1 to *status, raises llmp_b200_device_faults() and the
+ * kernel carries on. */
+int llmp_b200_q8_1_quantize_words(const float* x, const uint64_t* words, int tag, int64_t k,
+                                  const uint64_t* hold, int64_t hold_count, int hold_tag,
+                                  const int32_t* step, void* out, int polls, int32_t* status,
+                                  void* stream);
+
 /* Verification entry with no reference counterpart as a separate call: the
  * int32 per-block sums the product kernels form (the quantity the reference
  * checks bit for bit, tests/unit/dsv4_fast_test.cc:511-540), for nrows weight

@@ -40,6 +40,12 @@ class PeerSite(C.Structure):
                 ("flags", C.c_void_p), ("step", C.c_void_p), ("site", C.c_int)]
 
 
+class PeerFan(C.Structure):
+    """llmp_b200_peer_fan (include/llmp_b200.h)."""
+    _fields_ = [("world", C.c_int), ("words", C.c_void_p), ("step", C.c_void_p), ("base", C.c_int),
+                ("tag", C.c_int)]
+
+
 class MmvqDesc(C.Structure):
     """llmp_b200_mmvq_desc (include/llmp_b200.h)."""
     _fields_ = [("type", C.c_int), ("w", C.c_void_p), ("gate", C.c_void_p), ("glu", C.c_int),
@@ -118,6 +124,11 @@ SIGNATURES = {
                                                    C.POINTER(PeerSite), C.c_void_p, C.c_void_p,
                                                    C.c_size_t, C.c_size_t, C.c_int, C.c_void_p,
                                                    C.c_void_p]),
+    "llmp_b200_vecq_fan": (C.c_int, [C.c_int, C.POINTER(VecQDesc), C.c_int, C.POINTER(PeerFan),
+                                     C.c_void_p]),
+    "llmp_b200_q8_1_quantize_words": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64,
+                                                C.c_void_p, C.c_int64, C.c_int, C.c_void_p,
+                                                C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "llmp_b200_peer_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)]),
     "llmp_b200_peer_free": (C.c_int, [C.c_void_p]),
     "llmp_b200_peer_export": (C.c_int, [C.c_void_p, C.c_void_p]),

@@ -28,7 +28,61 @@ struct PeerPublish {
   int world, rank, site;
 };
 
+// The in-band form (no flag words, no fence): a value travels as one 8-byte word {F32 bits,
+// tag}, tag = (step << 8) | the exchange's number within the step, stored by the PRODUCING
+// kernel itself into every rank's vector; a reader polls the word until it carries the tag it
+// expects.  An 8-byte aligned store lands whole, so a word is either the old one or the new.
+struct PeerFan {
+  unsigned long long* const* words;  // device array [world]: every rank's vector of words
+  const std::int32_t* step;
+  int world;  // 0: the product does not fan out
+  int base;   // word index of this rank's first value
+  int tag;    // 0..255
+};
+// What a reader needs to wait for `count` words of its own vector.
+struct PeerWords {
+  const unsigned long long* words;  // null: nothing to wait for
+  const std::int32_t* step;
+  int count;
+  int tag;
+  int polls;
+  std::int32_t* status;
+  unsigned int* faults;
+};
+
 #ifdef __CUDACC__
+__device__ __forceinline__ std::uint32_t FanTag(const PeerFan& f) {
+  return (static_cast<std::uint32_t>(*f.step) << 8) | static_cast<std::uint32_t>(f.tag);
+}
+// value -> word base + row of every rank's vector.
+__device__ __forceinline__ void FanStore(const PeerFan& f, std::uint32_t tag, int row, float value) {
+  for (int to = 0; to < f.world; ++to) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(f.words[to] + f.base + row),
+                 "r"(__float_as_uint(value)), "r"(tag)
+                 : "memory");
+  }
+}
+// Polls one word until it carries `tag` (at most `polls` looks, about 0.1 us apart); its
+// value, and whether it arrived.
+__device__ __forceinline__ bool AwaitWord(const unsigned long long* word, std::uint32_t tag, int polls,
+                                          float* value) {
+  std::uint32_t lo = 0, hi = 0;
+  for (int i = 0; i < polls; ++i) {
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(lo), "=r"(hi) : "l"(word) : "memory");
+    if (hi == tag) {
+      *value = __uint_as_float(lo);
+      return true;
+    }
+    __nanosleep(100);
+  }
+  *value = __uint_as_float(lo);
+  return false;
+}
+__device__ __forceinline__ void ReportLateWords(const PeerWords& w) {
+  if (w.status != nullptr) *w.status = 1;
+  if (w.faults != nullptr) atomicAdd(w.faults, 1u);
+}
+
 __device__ __forceinline__ std::int32_t LoadAcquireSys(const std::int32_t* p) {
   std::int32_t v;
   asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");

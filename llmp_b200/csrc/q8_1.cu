@@ -81,6 +81,85 @@ QuantizeQ8_1Kernel(const float* __restrict__ x, std::int64_t k, std::int64_t row
   }
 }
 
+// The quantizer over a vector that arrives as tagged words (peer.cuh): a thread polls the four
+// words it quantizes, with a bound, before it uses them.  `hold`, when given, is another
+// vector of words whose arrival the kernel waits for without using its values (the layer
+// before's output, in the sharded step: nobody may overwrite what this rank still reads).
+// With `x` the values come from x and the words are only waited for.
+__global__ void __launch_bounds__(kThreads)
+QuantizeWordsKernel(const float* __restrict__ x, const PeerWords in, const PeerWords hold,
+                    std::int64_t k, std::int64_t row_blocks, std::int64_t total_lanes,
+                    std::uint8_t* __restrict__ out) {
+  GridLaunchDependents();
+  GridDependencyWait();
+  const std::int64_t i = (static_cast<std::int64_t>(blockIdx.x) * kThreads) + threadIdx.x;
+  bool late = false;
+  float unused;
+  if (hold.words != nullptr) {
+    const std::uint32_t tag = (static_cast<std::uint32_t>(*hold.step) << 8) | static_cast<std::uint32_t>(hold.tag);
+    int polls = (hold.status != nullptr && *hold.status != 0) ? 1 : hold.polls;
+    for (std::int64_t w = i; w < hold.count; w += static_cast<std::int64_t>(gridDim.x) * kThreads) {
+      if (!AwaitWord(hold.words + w, tag, polls, &unused)) {
+        late = true;
+        polls = 1;
+      }
+    }
+  }
+  const bool live = i < total_lanes;
+  const std::int64_t b = (live ? i : 0) / 8;
+  const int lane8 = static_cast<int>(i % 8);
+  const std::int64_t at = (b * 32) + (lane8 * 4);
+  float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  if (live) {
+    if (x != nullptr) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        if (at + c < k) v[c] = x[at + c];
+      }
+    } else {
+      const std::uint32_t tag = (static_cast<std::uint32_t>(*in.step) << 8) | static_cast<std::uint32_t>(in.tag);
+      int polls = (in.status != nullptr && *in.status != 0) ? 1 : in.polls;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        if (at + c < k && !AwaitWord(in.words + at + c, tag, polls, &v[c])) {
+          late = true;
+          polls = 1;
+        }
+      }
+    }
+  }
+  if (late) ReportLateWords(hold.words != nullptr ? hold : in);
+  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+  float s[4] = {v[0], v[1], v[2], v[3]};
+#pragma unroll
+  for (int offset = 4; offset > 0; offset >>= 1) {
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      s[c] = s[c] + __shfl_xor_sync(0xffffffffu, s[c], offset);
+    }
+  }
+  const float sum = (s[0] + s[2]) + (s[1] + s[3]);
+  const float d = amax / 127.0f;
+  std::uint32_t packed = 0;
+  if (amax != 0.0f) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int q = static_cast<int>(roundf(v[c] / d));
+      packed |= (static_cast<std::uint32_t>(q) & 0xffu) << (8 * c);
+    }
+  }
+  if (!live) return;
+  std::uint8_t* o = out + (b * 36);
+  *reinterpret_cast<std::uint32_t*>(o + 4 + (lane8 * 4)) = packed;
+  if (lane8 == 0) {
+    const std::uint32_t ds = static_cast<std::uint32_t>(__half_as_ushort(__float2half_rn(d))) |
+                             (static_cast<std::uint32_t>(__half_as_ushort(__float2half_rn(sum)))
+                              << 16);
+    *reinterpret_cast<std::uint32_t*>(o) = ds;
+  }
+}
+
 }  // namespace
 }  // namespace llmp_b200
 
@@ -140,6 +219,40 @@ int llmp_b200_q8_1_quantize_gathered(const float* x, int64_t k, int64_t rows, in
   }
   return Quantize(x, k, rows, 1, stride_row, 0, out, PeerWaitOf(*site, local_flags, polls, status),
                   PeerPublish{}, stream);
+}
+
+int llmp_b200_q8_1_quantize_words(const float* x, const uint64_t* words, int tag, int64_t k,
+                                  const uint64_t* hold, int64_t hold_count, int hold_tag,
+                                  const int32_t* step, void* out, int polls, int32_t* status,
+                                  void* stream) {
+  using namespace llmp_b200;
+  if ((x == nullptr) == (words == nullptr) || out == nullptr || step == nullptr || k < 1 || polls < 1 ||
+      tag < 0 || tag > 255 || hold_tag < 0 || hold_tag > 255 || (hold != nullptr && hold_count < 1)) {
+    return Reject("q8_1 words: either x or a vector of words, the step word, tags of 0 to 255");
+  }
+  if (!Aligned(words, 8) || !Aligned(hold, 8) || !Aligned(x, 4) || !Aligned(out, 4)) {
+    return Reject("q8_1 words: 8-byte aligned words");
+  }
+  if (const int code = DeviceStatus(); code != 0) return code;
+  PeerWords in{}, held{};
+  in.words = reinterpret_cast<const unsigned long long*>(words);
+  in.step = step;
+  in.count = static_cast<int>(k);
+  in.tag = tag;
+  in.polls = polls;
+  in.status = status;
+  in.faults = FaultCounter();
+  held = in;
+  held.words = reinterpret_cast<const unsigned long long*>(hold);
+  held.count = static_cast<int>(hold_count);
+  held.tag = hold_tag;
+  const std::int64_t row_blocks = llmp_b200_q8_1_row_blocks(k);
+  const std::int64_t total = row_blocks * 8;
+  const dim3 grid(static_cast<unsigned>((total + kThreads - 1) / kThreads));
+  const cudaError_t e = LaunchPdl(QuantizeWordsKernel, grid, dim3(kThreads), 0,
+                                  static_cast<cudaStream_t>(stream), x, in, held, k, row_blocks, total,
+                                  static_cast<std::uint8_t*>(out));
+  return e == cudaSuccess ? 0 : Failed(e, "q8_1 words launch");
 }
 
 int llmp_b200_q8_1_quantize_exchange(const float* x, int64_t k, void* out,

@@ -182,7 +182,7 @@ const char* llmp_b200_vecq_rank(int row, int* k, int* n, int* glu, int* tokens, 
 namespace llmp_b200 {
 namespace {
 int LaunchVecQ(int type, const llmp_b200_vecq_desc* desc, int variant, bool f32_input, void* q8_out,
-               void* q8_dst, unsigned int* rows_done, void* stream);
+               void* q8_dst, unsigned int* rows_done, void* stream, const PeerFan* fan = nullptr);
 }  // namespace
 }  // namespace llmp_b200
 
@@ -200,6 +200,22 @@ int llmp_b200_vecq_q8(int type, const llmp_b200_vecq_desc* desc, void* q8_dst, u
     return llmp_b200::Reject("vecq_q8: the output blocks and the row counters");
   }
   return llmp_b200::LaunchVecQ(type, desc, -1, false, nullptr, q8_dst, rows_done, stream);
+}
+
+int llmp_b200_vecq_fan(int type, const llmp_b200_vecq_desc* desc, int variant,
+                       const llmp_b200_peer_fan* fan, void* stream) {
+  using namespace llmp_b200;
+  if (fan == nullptr || fan->world < 1 || fan->world > 32 || fan->words == nullptr ||
+      fan->step == nullptr || fan->base < 0 || fan->tag < 0 || fan->tag > 255) {
+    return Reject("vecq_fan: 1 to 32 ranks' word vectors, the step word, a base and a tag of 0 to 255");
+  }
+  PeerFan f{};
+  f.words = reinterpret_cast<unsigned long long* const*>(fan->words);
+  f.step = fan->step;
+  f.world = fan->world;
+  f.base = fan->base;
+  f.tag = fan->tag;
+  return LaunchVecQ(type, desc, variant, false, nullptr, nullptr, nullptr, stream, &f);
 }
 
 size_t llmp_b200_vecq_q8_scratch(int nrows, int tokens) {
@@ -229,11 +245,12 @@ bool ChooseRowLane(const Desc& d, int p, RowLanePlan* lanes) {
 }
 
 int LaunchVecQ(int type, const llmp_b200_vecq_desc* desc, int variant, bool f32_input, void* q8_out,
-               void* q8_dst, unsigned int* rows_done, void* stream) {
+               void* q8_dst, unsigned int* rows_done, void* stream, const PeerFan* fan) {
   if (desc == nullptr) return Reject("vecq: null descriptor");
   bool q8_fast = false;
   if (const int status = Check(type, *desc, &q8_fast); status != 0) return status;
   if (variant < -2 || variant >= kVariantCount) return Reject("vecq: no variant %d", variant);
+  if (fan != nullptr && desc->tokens != 1) return Reject("vecq_fan: one token a call");
   if (const int status = DeviceStatus(); status != 0) return status;
   const Desc& d = *desc;
   const bool glu = d.glu != LLMP_B200_GLU_NONE;
@@ -256,7 +273,7 @@ int LaunchVecQ(int type, const llmp_b200_vecq_desc* desc, int variant, bool f32_
       for (int v = 0; v < kVariantCount; ++v) {
         if (std::strcmp(kVariants[v].name, r.variant) != 0) continue;
         if (v == kRowLaneVariant) break;  // the rule below is that kernel
-        const int status = LaunchVecQ(type, desc, v, false, nullptr, nullptr, nullptr, stream);
+        const int status = LaunchVecQ(type, desc, v, false, nullptr, nullptr, nullptr, stream, fan);
         if (status <= 0) return status;   // queued, or failed after queueing
         break;                            // refused cleanly: the rule below
       }
@@ -280,12 +297,13 @@ int LaunchVecQ(int type, const llmp_b200_vecq_desc* desc, int variant, bool f32_
   RowLanePlan lanes;
   const bool aligned16 = Aligned(d.w, 16) && (d.g == nullptr || Aligned(d.g, 16));
   if (variant >= kRowMmaVariant) {
-    RowMmaPlan tiles;
+    RowMmaPlan tiles{};
     const int ctas = variant == kRowMmaVariant ? 1 : kVariants[variant].u;
     if (!(dense && q4 && aligned16 && f32_input == false && q8_dst == nullptr &&
           PlanRowMma(d, p, SmCount(), &tiles, ctas))) {
       return Reject("vecq: the rowmma variant takes dense Q4_K products of up to 8 tokens");
     }
+    if (fan != nullptr) tiles.fan = *fan;
     e = LaunchRowMma(d, p, tiles, s);
     if (e != cudaSuccess) return Failed(e, "vecq rowmma launch");
     return 0;
@@ -335,7 +353,12 @@ int LaunchVecQ(int type, const llmp_b200_vecq_desc* desc, int variant, bool f32_
     lanes.q8_dst = static_cast<std::uint8_t*>(q8_dst);
     lanes.q8_rows_done = rows_done;
   }
+  if (fan != nullptr && !(rowlane_ok && (wants_rowlane || variant < 0))) {
+    // The fan-out lives in the two dense Q4_K kernels' stores only.
+    return Reject("vecq_fan: dense Q4_K products of one token a call");
+  }
   if (rowlane_ok && (wants_rowlane || variant < 0)) {
+    if (fan != nullptr) lanes.fan = *fan;
     e = LaunchRowLane(d, p, lanes, s);
     if (e != cudaSuccess) return Failed(e, "vecq rowlane launch");
     return 0;

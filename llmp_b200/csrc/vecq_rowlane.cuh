@@ -28,6 +28,7 @@
 #ifndef LLMP_B200_CSRC_VECQ_ROWLANE_CUH_
 #define LLMP_B200_CSRC_VECQ_ROWLANE_CUH_
 
+#include "peer.cuh"
 #include "vecq_stream.cuh"
 
 namespace llmp_b200 {
@@ -59,6 +60,7 @@ struct RowLanePlan {
   std::uint8_t* q8_dst;
   unsigned int* q8_rows_done;  // [tokens][nrows / 32] counters, zero between launches
   unsigned int* faults;
+  PeerFan fan;  // world > 0: token 0's results also go, tagged, into every rank's vector (peer.cuh)
 };
 
 // kHalf: at most half an SM's registers and shared memory, so that the kernel
@@ -336,11 +338,14 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
     }
     if (ph == 0 && r < my_rows && t < a.tokens) {
       float* dst = a.dst + (static_cast<std::size_t>(t) * a.dst_token) + row_begin + r;
+      float result;
       if constexpr (kGlu) {
-        *dst = Glu(a.glu, v[1], v[0], a.limit);
+        result = Glu(a.glu, v[1], v[0], a.limit);
       } else {
-        *dst = v[0];
+        result = v[0];
       }
+      *dst = result;
+      if (plan.fan.world > 0 && t == 0) FanStore(plan.fan, FanTag(plan.fan), row_begin + r, result);
     }
   }
 

@@ -37,6 +37,7 @@
 #ifndef LLMP_B200_CSRC_VECQ_ROWMMA_CUH_
 #define LLMP_B200_CSRC_VECQ_ROWMMA_CUH_
 
+#include "peer.cuh"
 #include "vecq_stream.cuh"
 
 namespace llmp_b200 {
@@ -62,6 +63,7 @@ struct RowMmaPlan {
   int partial_floats; // col_groups * pass_rows(16-padded) * P * mats
   int smem_bytes;
   unsigned int* faults;
+  PeerFan fan;  // world > 0: token 0's results also go, tagged, into every rank's vector (peer.cuh)
 };
 
 __device__ __forceinline__ void MmaU8S8(int (&c)[4], std::uint32_t a0, std::uint32_t a1,
@@ -310,11 +312,14 @@ VecQRowMmaKernel(const Desc a, const RowMmaPlan plan) {
         v[m] = s;
       }
       float* dst = a.dst + (static_cast<std::size_t>(p) * a.dst_token) + first + r;
+      float result;
       if constexpr (kGlu) {
-        *dst = Glu(a.glu, v[1], v[0], a.limit);
+        result = Glu(a.glu, v[1], v[0], a.limit);
       } else {
-        *dst = v[0];
+        result = v[0];
       }
+      *dst = result;
+      if (plan.fan.world > 0 && p == 0) FanStore(plan.fan, FanTag(plan.fan), first + r, result);
     }
     __syncthreads();  // before the next pass overwrites rows and partial sums
     parity ^= 1u;
@@ -382,6 +387,7 @@ inline bool PlanRowMma(const Desc& d, int p, int sms, RowMmaPlan* plan, int ctas
     rows = std::max(16, ((rows / 2) + 15) / 16 * 16);  // more passes of fewer rows
   }
   plan->faults = FaultCounter();
+  plan->fan = PeerFan{};
   return plan->faults != nullptr;
 }
 

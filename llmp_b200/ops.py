@@ -109,7 +109,7 @@ def vecq_ranks() -> list[dict]:
 def vecq(weights: torch.Tensor, wtype: int, k: int, n: int, q8: torch.Tensor, tokens: int, *,
          ids: torch.Tensor | None = None, per_slot: bool = False, gate: torch.Tensor | None = None,
          glu: int = GLU_NONE, limit: float = 0.0, groups: int = 1, stride_row: int | None = None,
-         stride_expert: int | None = None, variant: int = -1,
+         stride_expert: int | None = None, variant: int = -1, fan=None,
          out: torch.Tensor | None = None) -> torch.Tensor:
     """VecQ.  Dense: weights [n, k] blocks, q8 of [tokens, k] -> F32 [tokens, n].
     Grouped (groups > 1, per_slot): matrix g over row g of q8 of [tokens, groups, k]
@@ -154,6 +154,10 @@ def vecq(weights: torch.Tensor, wtype: int, k: int, n: int, q8: torch.Tensor, to
     d.dst_token = used * n if slotted else n
     d.dst_slot = n if slotted else 0
     d.glu, d.limit = glu, limit
+    if fan is not None:     # also into every rank's vector of tagged words (llmp_b200/peer.py)
+        N.check(N.lib().llmp_b200_vecq_fan(wtype, C.byref(d), variant, C.byref(fan), _stream()),
+                "llmp_b200_vecq_fan")
+        return out
     N.check(N.lib().llmp_b200_vecq(wtype, C.byref(d), variant, _stream()), "llmp_b200_vecq")
     return out
 

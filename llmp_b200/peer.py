@@ -33,17 +33,23 @@ class PeerExchange:
     Construct on every rank, trade `handles()` (or, for ranks emulated inside one process,
     `pointers()`), then `connect()`."""
 
-    def __init__(self, world: int, rank: int, vectors: dict[str, int], sites: int):
+    def __init__(self, world: int, rank: int, vectors: dict[str, int], sites: int,
+                 words: dict[str, int] | None = None):
+        """`words`: name -> length of a vector of tagged 8-byte words (the in-band form)."""
         self.world, self.rank, self.sites = world, rank, sites
         self._owned, self._opened = [], []
-        self._names = list(vectors)
-        self._local = {name: self._alloc(vectors[name] * 4) for name in self._names}
+        words = words or {}
+        self._names = list(vectors) + list(words)
+        self._local = {name: self._alloc(vectors[name] * 4) for name in vectors}
+        self._local.update({name: self._alloc(words[name] * 8) for name in words})
+        self.words = {name: torch.as_tensor(_Device(self._local[name], (words[name],), "<i8"),
+                                            device="cuda") for name in words}
         self._local_flags = self._alloc(sites * world * 4)
         self._step = self._alloc(256)
         self._status = self._alloc(256)
         self._tables, self._flag_table = {}, None
         self.vectors = {name: torch.as_tensor(_Device(self._local[name], (vectors[name],), "<f4"),
-                                              device="cuda") for name in self._names}
+                                              device="cuda") for name in vectors}
         self.status = torch.as_tensor(_Device(self._status, (1,), "<i4"), device="cuda")
         self.step = torch.as_tensor(_Device(self._step, (1,), "<i4"), device="cuda")
 
@@ -139,6 +145,43 @@ class PeerExchange:
             piece.data_ptr(), offset_floats * 4, piece.numel() * 4, polls, self._status, _stream()),
             "llmp_b200_q8_1_quantize_exchange")
         return out
+
+    # ---- the in-band form: values as tagged words, stored by the product kernel itself
+    def fan(self, name: str, base: int, tag: int) -> N.PeerFan:
+        """For ops.vecq(..., fan=): token 0's results also go to words[base + row] of every rank."""
+        f = N.PeerFan()
+        f.world, f.words, f.step = self.world, self._tables[name].data_ptr(), self._step
+        f.base, f.tag = base, tag
+        return f
+
+    def quantize_words(self, out: torch.Tensor, *, name: str | None = None, first: int = 0,
+                       count: int = 0, tag: int = 0, x: torch.Tensor | None = None,
+                       hold: tuple[str, int, int, int] | None = None,
+                       polls: int = DEFAULT_POLLS) -> torch.Tensor:
+        """Q8_1 blocks of words[name][first:first + count] once they carry `tag`, or of `x` (F32);
+        `hold` = (name, first, count, tag): words waited for first, values unused."""
+        L = N.lib()
+        if (x is None) == (name is None):
+            raise N.Rejected("peer quantize_words: either a word vector or x")
+        if x is not None:
+            x = x.reshape(-1)
+            if x.dtype != torch.float32 or not x.is_contiguous():
+                raise N.Rejected("peer quantize_words: a contiguous F32 vector")
+            k, words_ptr, x_ptr = x.numel(), None, x.data_ptr()
+        else:
+            k, words_ptr, x_ptr = count, self._local[name] + (first * 8), None
+        hold_ptr, hold_count, hold_tag = None, 0, 0
+        if hold is not None:
+            hold_ptr, hold_count, hold_tag = self._local[hold[0]] + (hold[1] * 8), hold[2], hold[3]
+        N.check(L.llmp_b200_q8_1_quantize_words(x_ptr, words_ptr, tag, k, hold_ptr, hold_count,
+                                                hold_tag, self._step, out.data_ptr(), polls,
+                                                self._status, _stream()),
+                "llmp_b200_q8_1_quantize_words")
+        return out
+
+    def word_values(self, name: str, first: int, count: int) -> torch.Tensor:
+        """The F32 values of a run of words (their low halves)."""
+        return self.words[name][first:first + count].view(torch.int32)[::2].contiguous().view(torch.float32)
 
     def timed_out(self) -> bool:
         """Whether a wait of this rank ran out since the last call (reads the device word)."""

@@ -74,6 +74,66 @@ def test_publish_wait_and_quantize_in_one_launch(cuda):
         x.close()
 
 
+def _pair_words(world, words):
+    from llmp_b200 import peer
+    ranks = [peer.PeerExchange(world, r, {}, 1, words=words) for r in range(world)]
+    everyone = [x.pointers() for x in ranks]
+    for x in ranks:
+        x.connect(everyone)
+    return ranks
+
+
+@pytest.mark.parametrize("n,k,glu", [(10240, 2560, True), (2560, 10240, False)])
+def test_products_fan_their_rows_out_as_tagged_words(cuda, n, k, glu):
+    """The two dense decode kernels store token 0's results, tagged, into every rank's vector;
+    the word quantizer gives the Q8_1 blocks of exactly those values, for two steps running."""
+    torch = cuda
+    import llmp_b200 as ops
+    from llmp_b200 import synth
+    world = 2
+    ranks = _pair_words(world, {"h": n})
+    rng = np.random.default_rng(n)
+    per = n // world
+    w = torch.from_numpy(synth.q4_k_weights(rng, n, k)).cuda()
+    g = torch.from_numpy(synth.q4_k_weights(rng, n, k)).cuda() if glu else None
+    for step in range(2):
+        x = torch.from_numpy(rng.normal(0, 1, size=(1, k)).astype(np.float32)).cuda()
+        q8 = ops.quantize_q8(x)
+        for r in ranks:
+            r.begin_step()
+        shards = []
+        for r, ex in enumerate(ranks):
+            rows = slice(r * per, (r + 1) * per)
+            out = ops.vecq(w[rows].contiguous(), ops.TYPE_Q4_K, k, per, q8, 1,
+                           gate=g[rows].contiguous() if glu else None,
+                           glu=ops.GLU_GEGLU if glu else ops.GLU_NONE, fan=ex.fan("h", r * per, 7))
+            shards.append(out)
+        torch.cuda.synchronize()               # every word is there before any reader polls
+        whole = torch.cat(shards, dim=1)
+        want = ops.quantize_q8(whole)
+        for ex in ranks:
+            assert torch.equal(ex.word_values("h", 0, n), whole.view(-1)), step
+            got = torch.empty_like(want)
+            ex.quantize_words(got, name="h", first=0, count=n, tag=7)
+            torch.cuda.synchronize()
+            assert torch.equal(got, want), step
+            # ... and as back-pressure only: x is quantized once the held words are there
+            got_x = torch.empty_like(q8)
+            ex.quantize_words(got_x, x=x, hold=("h", 0, n, 7))
+            torch.cuda.synchronize()
+            assert torch.equal(got_x, q8)
+            assert not ex.timed_out()
+    assert ops.device_faults() == 0
+    # a tag nobody stored: the reader gives up and says so
+    before = ops.device_faults()
+    ranks[0].quantize_words(torch.empty_like(want), name="h", first=0, count=n, tag=9, polls=20)
+    torch.cuda.synchronize()
+    assert ranks[0].timed_out() and ops.device_faults() > before
+    ops.device_faults_clear()
+    for ex in ranks:
+        ex.close()
+
+
 def test_a_wait_for_a_flag_nobody_sets_gives_up_and_says_so(cuda):
     torch = cuda
     import llmp_b200 as ops
