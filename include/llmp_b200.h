@@ -40,6 +40,14 @@ extern "C" {
 #define LLMP_B200_TYPE_Q8_0 8
 #define LLMP_B200_TYPE_Q8_1 9
 #define LLMP_B200_TYPE_Q4_K 12
+/* The other block types of the reference's llmp.vecq (src/kernels/ggml/vecq.cu:54-96) that this
+ * build's llmp_b200_vecq also takes, dense or grouped, 1 to 16 tokens, with or without a GLU:
+ * one launch configuration each, not tuned.  Numbers are GGML's type ids. */
+#define LLMP_B200_TYPE_Q4_0 2
+#define LLMP_B200_TYPE_Q5_0 6
+#define LLMP_B200_TYPE_Q5_K 13
+#define LLMP_B200_TYPE_Q6_K 14
+#define LLMP_B200_TYPE_IQ4_NL 20
 
 /* VecQGlu (src/kernels/ggml/llmp_ops.h:1072). */
 #define LLMP_B200_GLU_NONE 0

@@ -12,6 +12,7 @@ namespace vecq {
 extern template cudaError_t LaunchType<Q4KUnit>(const Desc&, int, const Variant&, cudaStream_t);
 extern template cudaError_t LaunchType<Q8_0Unit<4>>(const Desc&, int, const Variant&, cudaStream_t);
 extern template cudaError_t LaunchType<Q8_0Unit<1>>(const Desc&, int, const Variant&, cudaStream_t);
+cudaError_t LaunchMore(int type, const Desc& d, int p, cudaStream_t stream);  // vecq_more.cu
 extern template cudaError_t LaunchStream<Q4KUnit>(const Desc&, int, const StreamPlan&, cudaStream_t);
 extern template cudaError_t LaunchStream<Q4KBlockUnit>(const Desc&, int, const StreamPlan&,
                                                        cudaStream_t);
@@ -91,9 +92,29 @@ __global__ void BlockSumsQ8_0(const std::uint8_t* __restrict__ w, const std::uin
 
 // Operand checks: the part of CheckVecQ (src/kernels/ggml/llmp_ops.cc:2915-2982)
 // that a raw descriptor can express.
+// The other block types (vecq_more.cuh): bytes and values a block, alignment of a block.
+bool MoreType(int type) {
+  return type == LLMP_B200_TYPE_Q4_0 || type == LLMP_B200_TYPE_Q5_0 || type == LLMP_B200_TYPE_IQ4_NL ||
+         type == LLMP_B200_TYPE_Q5_K || type == LLMP_B200_TYPE_Q6_K;
+}
+int BlockBytesOf(int type) {
+  switch (type) {
+    case LLMP_B200_TYPE_Q4_K: return 144;
+    case LLMP_B200_TYPE_Q8_0: return 34;
+    case LLMP_B200_TYPE_Q5_0: return 22;
+    case LLMP_B200_TYPE_Q5_K: return 176;
+    case LLMP_B200_TYPE_Q6_K: return 210;
+    default: return 18;  // Q4_0, IQ4_NL
+  }
+}
+int BlockElemsOf(int type) {
+  return type == LLMP_B200_TYPE_Q4_K || type == LLMP_B200_TYPE_Q5_K || type == LLMP_B200_TYPE_Q6_K ? 256 : 32;
+}
+
 int Check(int type, const Desc& d, bool* q8_fast) {
-  if (type != LLMP_B200_TYPE_Q8_0 && type != LLMP_B200_TYPE_Q4_K) {
-    return Reject("vecq: weight type %d is not one this build computes (Q8_0, Q4_K)", type);
+  if (type != LLMP_B200_TYPE_Q8_0 && type != LLMP_B200_TYPE_Q4_K && !MoreType(type)) {
+    return Reject("vecq: weight type %d is not one this build computes (Q8_0, Q4_K, Q4_0, Q5_0, "
+                  "IQ4_NL, Q5_K, Q6_K)", type);
   }
   if (d.w == nullptr || d.y == nullptr || d.dst == nullptr) {
     return Reject("vecq: quantized weights, a llmp.q8_1 input and an F32 output");
@@ -105,26 +126,32 @@ int Check(int type, const Desc& d, bool* q8_fast) {
   if (d.glu == LLMP_B200_GLU_GEGLU && d.limit != 0.0f) {
     return Reject("vecq: GeGLU uses GELU-tanh without a clamp limit");
   }
-  const int elems = type == LLMP_B200_TYPE_Q4_K ? 256 : 32;
+  // (the 32-value types are taken four blocks a unit: k a multiple of 128 for them)
+  const int elems = MoreType(type) && BlockElemsOf(type) == 32 ? 128 : BlockElemsOf(type);
   if (d.ncols_x < elems || d.ncols_x % elems != 0 || d.nrows < 1) {
-    return Reject("vecq: k a positive multiple of the block's %d values, n >= 1", elems);
+    return Reject("vecq: k a positive multiple of %d values for this type, n >= 1", elems);
   }
   if (d.used < 1 || d.used > 256 || d.used * d.tokens > (d.ids != nullptr ? kMaxPairs : 256 * 16)) {
     return Reject("vecq: used * tokens <= 1024 routed; at most 256 groups");
   }
   if (d.ids == nullptr && d.tokens > kMaxPairs) return Reject("vecq: tokens");
-  if (d.stride_row < d.ncols_x / elems || d.stride_expert < 0 || d.y_token < 0 || d.y_slot < 0 ||
+  if (d.stride_row < d.ncols_x / BlockElemsOf(type) || d.stride_expert < 0 || d.y_token < 0 || d.y_slot < 0 ||
       d.dst_token < 0 || d.dst_slot < 0 || (d.ids != nullptr && d.ids_stride < d.used)) {
     return Reject("vecq: strides must cover a row and be non-negative");
   }
   if (!Aligned(d.dst, 4) || !Aligned(d.y, 4) || (d.ids != nullptr && !Aligned(d.ids, 4))) {
     return Reject("vecq: output, Q8_1 input and ids 4-byte aligned");
   }
-  if (type == LLMP_B200_TYPE_Q4_K) {
-    // 144-byte super-blocks: any block offset keeps a 16-byte aligned base aligned.
+  if (type == LLMP_B200_TYPE_Q4_K || type == LLMP_B200_TYPE_Q5_K) {
+    // 144- and 176-byte super-blocks: any block offset keeps a 16-byte aligned base aligned.
     if (!Aligned(d.w, 16) || (d.g != nullptr && !Aligned(d.g, 16))) {
-      return Reject("vecq: Q4_K weights 16-byte aligned");
+      return Reject("vecq: Q4_K / Q5_K weights 16-byte aligned");
     }
+  } else if (MoreType(type)) {
+    if (!Aligned(d.w, 2) || (d.g != nullptr && !Aligned(d.g, 2))) {
+      return Reject("vecq: weights 2-byte aligned");
+    }
+    if (d.ids != nullptr) return Reject("vecq: routed products take Q8_0 and Q4_K only");
   } else {
     if (!Aligned(d.w, 2) || (d.g != nullptr && !Aligned(d.g, 2))) {
       return Reject("vecq: Q8_0 weights 2-byte aligned");
@@ -145,7 +172,7 @@ int Check(int type, const Desc& d, bool* q8_fast) {
       (static_cast<std::uint64_t>(d.tokens - 1) * d.dst_token +
        static_cast<std::uint64_t>(d.used - 1) * d.dst_slot + d.nrows) * 4;
   const std::uint64_t w_bytes = (static_cast<std::uint64_t>(d.nrows - 1) * d.stride_row +
-                                 d.ncols_x / elems) * (type == LLMP_B200_TYPE_Q4_K ? 144 : 34);
+                                 d.ncols_x / BlockElemsOf(type)) * BlockBytesOf(type);
   if (!disjoint(d.dst, dst_bytes, d.w, w_bytes) ||
       (d.g != nullptr && !disjoint(d.dst, dst_bytes, d.g, w_bytes)) ||
       !disjoint(d.dst, dst_bytes, d.y, static_cast<std::uint64_t>(d.ncols_x / 32) * 36)) {
@@ -284,6 +311,15 @@ int LaunchVecQ(int type, const llmp_b200_vecq_desc* desc, int variant, bool f32_
   const int slots = d.ids != nullptr ? d.used * d.tokens : d.used;
   auto* s = static_cast<cudaStream_t>(stream);
   cudaError_t e;
+  if (MoreType(type)) {
+    if (variant >= 0 || f32_input || q8_dst != nullptr || fan != nullptr) {
+      return Reject("vecq: this block type has one launch configuration and no fused forms");
+    }
+    if (slots > 65535) return Reject("vecq: grid too large");
+    e = LaunchMore(type, d, p, s);
+    if (e != cudaSuccess) return Failed(e, "vecq launch");
+    return 0;
+  }
   // Dense products whose rows start on 16-byte boundaries stream through the
   // TMA ring; the rest (routed, grouped, more than 8 tokens, odd alignment)
   // take the register-staged kernel.

@@ -436,11 +436,16 @@ VecQKernel(const Desc a) {
                 for (int r = 0; r < R; ++r)
 #pragma unroll
                   for (int m = 0; m < kMats; ++m) {
-                    int sumi = 0;
+                    if constexpr (Unit::kType == LLMP_B200_TYPE_Q8_0) {
+                      int sumi = 0;
 #pragma unroll
-                    for (int q = 0; q < 8; ++q) sumi = Dp4a(raw[i][r][m].Int(b, q), xs[q], sumi);
-                    // d8_0 * d8_1 * sumi (vecq.cu:398-418)
-                    acc[j][r][m] += raw[i][r][m].Scale(b) * d8 * static_cast<float>(sumi);
+                      for (int q = 0; q < 8; ++q) sumi = Dp4a(raw[i][r][m].Int(b, q), xs[q], sumi);
+                      // d8_0 * d8_1 * sumi (vecq.cu:398-418)
+                      acc[j][r][m] += raw[i][r][m].Scale(b) * d8 * static_cast<float>(sumi);
+                    } else {
+                      // the other block types (vecq_more.cuh) know their own sub-block product
+                      acc[j][r][m] += raw[i][r][m].Dot(b, xs, d8, sv[b].y);
+                    }
                   }
               }
             }

@@ -21,9 +21,12 @@ __all__ = ["available", "sm_count", "device_faults", "device_faults_clear", "blo
            "DECODER_MXFP8_ATOMS", "DECODER_BF16", "DECODER_F16", "DECODER_NVFP4_SPLIT", "DECODER_NVFP4_ATOMS",
            "DECODER_MXFP4_SPLIT", "DECODER_MXFP4_ATOMS", "mmq_quantize", "mmq", "mmq_scratch", "mmq_block_sums", "q4k_relayout", "moe_route", "grouped_gemm",
            "moe_glu_quantize", "moe_combine", "moe_ep_pack", "moe_ffn", "TYPE_Q8_0", "TYPE_Q4_K",
+           "TYPE_Q4_0", "TYPE_Q5_0", "TYPE_Q5_K", "TYPE_Q6_K", "TYPE_IQ4_NL",
            "GLU_NONE", "GLU_SWIGLU", "GLU_SWIGLU_CLAMP", "GLU_GEGLU", "Rejected", "LaunchFailed"]
 
-_BLOCK = {TYPE_Q8_0: (32, 34), TYPE_Q4_K: (256, 144), N.TYPE_Q8_1: (32, 36)}
+TYPE_Q4_0, TYPE_Q5_0, TYPE_Q5_K, TYPE_Q6_K, TYPE_IQ4_NL = 2, 6, 13, 14, 20   # GGML's type ids
+_BLOCK = {TYPE_Q8_0: (32, 34), TYPE_Q4_K: (256, 144), N.TYPE_Q8_1: (32, 36), TYPE_Q4_0: (32, 18),
+          TYPE_Q5_0: (32, 22), TYPE_IQ4_NL: (32, 18), TYPE_Q5_K: (256, 176), TYPE_Q6_K: (256, 210)}
 # moe_ffn: up to this many tokens take the routed decode products (measured on B200 against the
 # grouped tensor-core GEMM for 128 experts, top-8, hidden 2048, intermediate 768).
 DECODE_TOKENS = 96
@@ -118,7 +121,7 @@ def vecq(weights: torch.Tensor, wtype: int, k: int, n: int, q8: torch.Tensor, to
     gate: weights like `weights`; the result is glu(gate.x, weights.x)."""
     _need(weights, torch.uint8, "vecq weights")
     _need(q8, torch.uint8, "vecq q8")
-    elems, nbytes = _BLOCK[wtype] if wtype in (TYPE_Q8_0, TYPE_Q4_K) else (0, 0)
+    elems, nbytes = _BLOCK.get(wtype, (0, 0)) if wtype != N.TYPE_Q8_1 else (0, 0)
     if elems == 0:
         raise Rejected(f"vecq: weight type {wtype}")
     routed = ids is not None

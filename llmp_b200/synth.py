@@ -47,6 +47,31 @@ def q4_k_weights(rng: np.random.Generator, n: int, k: int) -> np.ndarray:
     return out.reshape(n, nb * 144)
 
 
+def more_weights(rng: np.random.Generator, wtype: int, n: int, k: int) -> np.ndarray:
+    """uint8 [n, row bytes] of random blocks of GGML type `wtype` (2 Q4_0, 6 Q5_0, 20 IQ4_NL,
+    13 Q5_K, 14 Q6_K): every code and scale field uniform over its range, FP16 scales
+    |N(0, 0.02)| over the codes' span."""
+    def halves(scale, shape):
+        return (np.abs(rng.normal(0.0, 0.02, size=shape)) / scale).astype(np.float16).view(np.uint8)
+    if wtype in (2, 20, 6):
+        size = 22 if wtype == 6 else 18
+        nb = k // 32
+        out = rng.integers(0, 256, size=(n, nb, size), dtype=np.uint8)
+        out[:, :, 0:2] = halves(127.0 if wtype == 20 else 16.0, (n, nb)).reshape(n, nb, 2)
+        return out.reshape(n, nb * size)
+    nb = k // 256
+    if wtype == 13:
+        out = rng.integers(0, 256, size=(n, nb, 176), dtype=np.uint8)
+        out[:, :, 0:2] = halves(31.0 * 32.0, (n, nb)).reshape(n, nb, 2)
+        out[:, :, 2:4] = halves(32.0, (n, nb)).reshape(n, nb, 2)
+        return out.reshape(n, nb * 176)
+    if wtype == 14:
+        out = rng.integers(0, 256, size=(n, nb, 210), dtype=np.uint8)
+        out[:, :, 208:210] = halves(32.0 * 64.0, (n, nb)).reshape(n, nb, 2)
+        return out.reshape(n, nb * 210)
+    raise ValueError(wtype)
+
+
 def topk_route(rng: np.random.Generator, tokens: int, experts: int, used: int):
     """Router of the MoE config: logits N(0,1) -> softmax -> top-`used` (ties to the
     lower index), weights renormalised.  Returns (ids I32 [tokens, used], w F32)."""

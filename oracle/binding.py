@@ -15,6 +15,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "_build", "liboracle.so")
 
 Q8_0, Q8_1, Q4_K = 8, 9, 12
+Q4_0, Q5_0, Q5_K, Q6_K, IQ4_NL = 2, 6, 13, 14, 20      # decoders only (orc_dequant_more)
 GLU_NONE, GLU_SWIGLU, GLU_SWIGLU_CLAMP, GLU_GEGLU = 0, 1, 2, 3
 
 
@@ -84,6 +85,7 @@ def lib():
             "orc_dequant_q8_0": [C.c_void_p, C.c_int64, C.c_void_p],
             "orc_dequant_q4_k": [C.c_void_p, C.c_int64, C.c_void_p],
             "orc_dequant_q8_1": [C.c_void_p, C.c_int64, C.c_void_p],
+            "orc_dequant_more": [C.c_int, C.c_void_p, C.c_int64, C.c_void_p],
             "orc_q4_k_scales": [C.c_void_p, C.c_void_p, C.c_void_p],
             "orc_quantize_q8_1": [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p],
             "orc_q8_0_block_sums": [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p],
@@ -134,11 +136,11 @@ def host_threads() -> int:
 
 # ----------------------------------------------------------------- geometry
 def block_bytes(t):
-    return {Q8_0: 34, Q8_1: 36, Q4_K: 144}[t]
+    return {Q8_0: 34, Q8_1: 36, Q4_K: 144, Q4_0: 18, IQ4_NL: 18, Q5_0: 22, Q5_K: 176, Q6_K: 210}[t]
 
 
 def block_elems(t):
-    return {Q8_0: 32, Q8_1: 32, Q4_K: 256}[t]
+    return {Q8_0: 32, Q8_1: 32, Q4_K: 256, Q4_0: 32, IQ4_NL: 32, Q5_0: 32, Q5_K: 256, Q6_K: 256}[t]
 
 
 def q8_row_blocks(k):
@@ -150,6 +152,9 @@ def dequant(t, blocks: np.ndarray) -> np.ndarray:
     blocks = _c(blocks, np.uint8).reshape(-1)
     nb = blocks.size // block_bytes(t)
     out = np.empty(nb * block_elems(t), np.float32)
+    if t in (Q4_0, Q5_0, Q5_K, Q6_K, IQ4_NL):
+        lib().orc_dequant_more(t, _p(blocks), nb, _p(out))
+        return out
     fn = {Q8_0: lib().orc_dequant_q8_0, Q4_K: lib().orc_dequant_q4_k, Q8_1: lib().orc_dequant_q8_1}[t]
     fn(_p(blocks), nb, _p(out))
     return out

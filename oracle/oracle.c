@@ -120,8 +120,9 @@ uint8_t orc_f32_to_e4m3_satfinite(float value) {
 
 int64_t orc_block_elems(int type) {
   switch (type) {
-    case ORC_TYPE_Q8_0: case ORC_TYPE_Q8_1: return 32;
-    case ORC_TYPE_Q4_K: return 256;
+    case ORC_TYPE_Q8_0: case ORC_TYPE_Q8_1: case ORC_TYPE_Q4_0: case ORC_TYPE_Q5_0:
+    case ORC_TYPE_IQ4_NL: return 32;
+    case ORC_TYPE_Q4_K: case ORC_TYPE_Q5_K: case ORC_TYPE_Q6_K: return 256;
   }
   return 0;
 }
@@ -130,6 +131,10 @@ int64_t orc_block_bytes(int type) {
     case ORC_TYPE_Q8_0: return ORC_Q8_0_BYTES;
     case ORC_TYPE_Q8_1: return ORC_Q8_1_BYTES;
     case ORC_TYPE_Q4_K: return ORC_Q4_K_BYTES;
+    case ORC_TYPE_Q4_0: case ORC_TYPE_IQ4_NL: return 18;
+    case ORC_TYPE_Q5_0: return 22;
+    case ORC_TYPE_Q5_K: return 176;
+    case ORC_TYPE_Q6_K: return 210;
   }
   return 0;
 }
@@ -175,6 +180,91 @@ void orc_dequant_q4_k(const uint8_t* blocks, int64_t nblocks, float* out) {
       }
     }
   }
+}
+
+/* The other block types the reference's llmp.vecq hands to GGML's vec_dot functions
+ * (src/kernels/ggml/vecq.cu:54-96).  Their layouts are GGML's published block formats
+ * (ggml-common.h of the pinned GGML v0.6.0, absent from the reference tree); each decoder
+ * below is checked bit for bit against gguf-py's dequantizer (tests/golden/gguf_blocks.npz).
+ *   Q4_0   18 B: FP16 d, 16 bytes: value i = low nibble of byte i, value i + 16 = its high
+ *          nibble; w = d * (code - 8).
+ *   Q5_0   22 B: FP16 d, 32 fifth bits (bit i: value i), 16 bytes as Q4_0; w = d * (code - 16).
+ *   IQ4_NL 18 B: as Q4_0 with the nibble an index into a fixed table of 16 int8 levels.
+ *   Q5_K   176 B: FP16 d, FP16 dmin, Q4_K's 12 scale bytes, 32 bytes of fifth bits (byte l:
+ *          bit g of value l of sub-block g), 128 nibble bytes as Q4_K; w = d*sc*code - dmin*m.
+ *   Q6_K   210 B: 128 bytes of low nibbles, 64 bytes of two-bit tops, 16 int8 scales (one per
+ *          16 values), FP16 d last; per 128-value half: byte l of the lows' first 32 gives
+ *          values l (low) and l + 64 (high), byte l + 32 values l + 32 and l + 96, byte l of the
+ *          tops their bits 4-5 in that order; w = d * scale * (code - 32). */
+static const int8_t kIq4NlLevels[16] = {-127, -104, -83, -65, -49, -35, -22, -10,
+                                        1,    13,   25,  38,  53,  69,  89,  113};
+
+int orc_dequant_more(int type, const uint8_t* blocks, int64_t nblocks, float* out) {
+  for (int64_t b = 0; b < nblocks; ++b) {
+    if (type == ORC_TYPE_Q4_0 || type == ORC_TYPE_IQ4_NL) {
+      const uint8_t* p = blocks + b * 18;
+      const float d = orc_f16_to_f32(load_u16(p));
+      for (int i = 0; i < 16; ++i) {
+        const int lo = p[2 + i] & 15, hi = p[2 + i] >> 4;
+        if (type == ORC_TYPE_Q4_0) {
+          out[b * 32 + i] = d * (float)(lo - 8);
+          out[b * 32 + 16 + i] = d * (float)(hi - 8);
+        } else {
+          out[b * 32 + i] = d * (float)kIq4NlLevels[lo];
+          out[b * 32 + 16 + i] = d * (float)kIq4NlLevels[hi];
+        }
+      }
+    } else if (type == ORC_TYPE_Q5_0) {
+      const uint8_t* p = blocks + b * 22;
+      const float d = orc_f16_to_f32(load_u16(p));
+      const uint32_t top = (uint32_t)p[2] | ((uint32_t)p[3] << 8) | ((uint32_t)p[4] << 16) |
+                           ((uint32_t)p[5] << 24);
+      for (int i = 0; i < 16; ++i) {
+        const int lo = (p[6 + i] & 15) | (int)(((top >> i) & 1u) << 4);
+        const int hi = (p[6 + i] >> 4) | (int)(((top >> (i + 16)) & 1u) << 4);
+        out[b * 32 + i] = d * (float)(lo - 16);
+        out[b * 32 + 16 + i] = d * (float)(hi - 16);
+      }
+    } else if (type == ORC_TYPE_Q5_K) {
+      const uint8_t* p = blocks + b * 176;
+      const float d = orc_f16_to_f32(load_u16(p)), dmin = orc_f16_to_f32(load_u16(p + 2));
+      int sc[8], mn[8];
+      orc_q4_k_scales(p, sc, mn);
+      const uint8_t* tops = p + 16;
+      const uint8_t* codes = p + 48;
+      for (int g = 0; g < 8; ++g) {
+        const float dl = d * (float)sc[g], ml = dmin * (float)mn[g];
+        for (int i = 0; i < 32; ++i) {
+          const int code = ((codes[(g / 2) * 32 + i] >> ((g % 2) * 4)) & 15) |
+                           (((tops[i] >> g) & 1) << 4);
+          out[b * 256 + g * 32 + i] = dl * (float)code - ml;
+        }
+      }
+    } else if (type == ORC_TYPE_Q6_K) {
+      const uint8_t* p = blocks + b * 210;
+      const float d = orc_f16_to_f32(load_u16(p + 208));
+      for (int half = 0; half < 2; ++half) {
+        const uint8_t* lows = p + 64 * half;
+        const uint8_t* tops = p + 128 + 32 * half;
+        const int8_t* scales = (const int8_t*)(p + 192 + 8 * half);
+        float* y = out + b * 256 + 128 * half;
+        for (int l = 0; l < 32; ++l) {
+          const int is = l / 16;
+          const int q1 = ((lows[l] & 15) | (((tops[l] >> 0) & 3) << 4)) - 32;
+          const int q2 = ((lows[l + 32] & 15) | (((tops[l] >> 2) & 3) << 4)) - 32;
+          const int q3 = ((lows[l] >> 4) | (((tops[l] >> 4) & 3) << 4)) - 32;
+          const int q4 = ((lows[l + 32] >> 4) | (((tops[l] >> 6) & 3) << 4)) - 32;
+          y[l] = d * (float)scales[is] * (float)q1;
+          y[l + 32] = d * (float)scales[is + 2] * (float)q2;
+          y[l + 64] = d * (float)scales[is + 4] * (float)q3;
+          y[l + 96] = d * (float)scales[is + 6] * (float)q4;
+        }
+      }
+    } else {
+      return 1;
+    }
+  }
+  return 0;
 }
 
 /* ------------------------------------------------------------------------- */

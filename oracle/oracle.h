@@ -27,7 +27,8 @@ extern "C" {
 #endif
 
 /* GGML type numbers (src/format/encoding.cc:111-115). */
-enum { ORC_TYPE_Q8_0 = 8, ORC_TYPE_Q8_1 = 9, ORC_TYPE_Q4_K = 12 };
+enum { ORC_TYPE_Q4_0 = 2, ORC_TYPE_Q5_0 = 6, ORC_TYPE_Q8_0 = 8, ORC_TYPE_Q8_1 = 9, ORC_TYPE_Q4_K = 12,
+       ORC_TYPE_Q5_K = 13, ORC_TYPE_Q6_K = 14, ORC_TYPE_IQ4_NL = 20 };
 enum { ORC_Q8_0_BYTES = 34, ORC_Q8_1_BYTES = 36, ORC_Q4_K_BYTES = 144, ORC_Q8_1_MMQ_BYTES = 144 };
 enum { ORC_GLU_NONE = 0, ORC_GLU_SWIGLU = 1, ORC_GLU_SWIGLU_CLAMP = 2, ORC_GLU_GEGLU = 3 };
 
@@ -56,6 +57,8 @@ void orc_q4_k_scales(const uint8_t* block, int sc[8], int mn[8]);
 /* ---- Q8_1 activation quantizer (PARITY UNPINNED) ---- */
 void orc_quantize_q8_1(const float* x, int64_t k, int64_t rows, int64_t row_stride, uint8_t* out);
 void orc_dequant_q8_1(const uint8_t* blocks, int64_t nblocks, float* out);
+/* Q4_0, Q5_0, IQ4_NL, Q5_K, Q6_K (GGML's published block formats); 0, or 1 for another type. */
+int orc_dequant_more(int type, const uint8_t* blocks, int64_t nblocks, float* out);
 
 /* ---- per-block integer sums (bit-exact contract) ---- */
 /* Q8_0: sums[b] = sum_i w.q[i]*y.q[i] for each of k/32 blocks. */

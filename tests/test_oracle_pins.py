@@ -173,3 +173,14 @@ def test_fp4_and_dense16_decoders_match_reference_decode_rows(orc, pins):
     # an id outside the matrix: a zero row and the flag
     got, bad = orc.decode_rows(3, raw, np.array([1, 6, -1], np.int32), 64)
     assert bad == 1 and not got[1].any() and not got[2].any() and got[0].any()
+
+
+@pytest.mark.parametrize("wtype", [2, 6, 20, 13, 14], ids=["Q4_0", "Q5_0", "IQ4_NL", "Q5_K", "Q6_K"])
+def test_more_block_decoders_match_gguf(orc, wtype):
+    """The decoders restated from GGML's published block formats against gguf-py's reader
+    (tests/golden/gguf_blocks.npz, written by tests/golden/make_gguf_blocks.py)."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "gguf_blocks.npz"))
+    blocks = g[f"blocks_{wtype}"]
+    got = orc.dequant(wtype, blocks).view(np.uint32).reshape(blocks.shape[0], -1)
+    assert np.array_equal(got, g[f"decoded_bits_{wtype}"])

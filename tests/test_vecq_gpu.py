@@ -247,7 +247,7 @@ def test_operands_the_kernels_do_not_take_are_refused_before_launch(cuda, orc):
     with pytest.raises(ops.Rejected):
         ops.vecq(w, orc.Q4_K, 512, 8, q8, 17)                         # too many tokens
     with pytest.raises(ops.Rejected):
-        ops.vecq(w, 2, 512, 8, q8, 1)                                 # a type not built
+        ops.vecq(w, 10, 512, 8, q8, 1)                                # a type not built (Q2_K)
     with pytest.raises(ops.Rejected):
         ops.vecq(w, orc.Q4_K, 512, 8, q8, 1, glu=1)                   # GLU without gate
     with pytest.raises(ops.Rejected):
