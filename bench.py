@@ -686,8 +686,11 @@ def run_other(args):
         ids, w = synth.topk_route(np.random.default_rng(0), tokens, experts, used)
         ids_d, w_d = torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda()
         x = torch.randn((tokens, hidden), device="cuda", generator=gen)
-        slabs = (ops.q4k_relayout(gate_up, hidden, 2 * inter), ops.q4k_relayout(down, inter, hidden)) \
-            if tokens > ops.ops.DECODE_TOKENS else None         # load time: outside the timing
+        # load time, outside the timing: the gate | up slab interleaves its rows for the GLU
+        # write-back (the third entry says so)
+        slabs = (ops.q4k_relayout(gate_up, hidden, 2 * inter, glu=True),
+                 ops.q4k_relayout(down, inter, hidden), True) \
+            if tokens > ops.ops.DECODE_TOKENS else None
         fns = [lambda: ops.moe_ffn(x, ids_d, w_d, gate_up, down, hidden, inter, slabs=slabs)]
         if not args.no_graph:
             # The block queues 7 to 40 small launches: replay them as one captured graph so
@@ -842,7 +845,8 @@ def bench_moe_ep(torch, dist, ops, rank, world, tokens=1024, steps=10, warmup=3)
     b = rank * per
     gate_up = gate_up_all[b:b + per].contiguous()
     down = down_all[b:b + per].contiguous()
-    slabs = (ops.q4k_relayout(gate_up, hidden, 2 * inter), ops.q4k_relayout(down, inter, hidden))
+    slabs = (ops.q4k_relayout(gate_up, hidden, 2 * inter, glu=True),
+             ops.q4k_relayout(down, inter, hidden), True)          # GLU in the product's write-back
     if rank != 0:
         gate_up_all = down_all = None
         torch.cuda.empty_cache()

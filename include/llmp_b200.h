@@ -337,6 +337,19 @@ int llmp_b200_q4k_relayout(const void* w, int nrows, int k, int stride_row, int6
  * fixup pass. */
 size_t llmp_b200_mmq_scratch(const llmp_b200_mmq_desc* desc, int sms);
 int llmp_b200_mmq(const llmp_b200_mmq_desc* desc, int sms, void* stream);
+/* The gate | up product with the GLU and the requantization in its write-back (the reference's
+ * MulMatQGlu, src/kernels/ggml/mul_mat_q_glu.cu:143-218): instead of F32 [2 * inter] a column,
+ * the Q8_1-MMQ blocks of glu(gate . y, up . y), [inter / 128][ncols] x 144 bytes, which the
+ * down product reads.  The weights come as a slab whose rows interleave gate and up rows
+ * (llmp_b200_q4k_relayout_glu at load time: the source holds inter gate rows, then inter up
+ * rows, per expert); desc->nrows = 2 * inter (a multiple of 64), desc->dst is unused,
+ * desc->ids_dst NULL.  The blocks equal, bit for bit, what llmp_b200_moe_glu_quantize makes of
+ * the F32 product. */
+int llmp_b200_q4k_relayout_glu(const void* w, int inter, int k, int stride_row, int64_t stride_expert,
+                               int experts, void* slab, void* stream);
+int llmp_b200_mmq_glu(const llmp_b200_mmq_desc* desc, int glu, float limit, void* blocks,
+                      void* stream);
+
 /* Verification entry with no reference counterpart as a separate call: the dense product as
  * llmp_b200_mmq queues it and, besides, the exact int32 sums C = sum code * q of every
  * (column, weight row, 32-value group), read out of tensor memory before the fold:
@@ -388,6 +401,11 @@ typedef struct llmp_b200_grouped_gemm_desc {
 int llmp_b200_grouped_gemm_available(void);
 size_t llmp_b200_grouped_gemm_scratch(int groups, int rows, int sms);
 int llmp_b200_grouped_gemm(const llmp_b200_grouped_gemm_desc* gemm, int sms, void* stream);
+/* The grouped gate | up product with the GLU write-back (see llmp_b200_mmq_glu): gemm->n = 2 * inter,
+ * gemm->weights_slab from llmp_b200_q4k_relayout_glu, gemm->d unused; blocks: Q8_1-MMQ
+ * [inter / 128][rows]. */
+int llmp_b200_grouped_gemm_glu(const llmp_b200_grouped_gemm_desc* gemm, int glu, float limit,
+                               void* blocks, int sms, void* stream);
 
 /* No counterpart in the reference.  The grouped GEMM for callers that have no
  * way to hand over scratch: code running where device allocation is off the
@@ -429,6 +447,33 @@ int llmp_b200_moe_ep_pack(const float* x, int64_t x_stride, int hidden, const in
                           int ids_stride, int used, int tokens, int experts, int world, int capacity,
                           const int32_t* route, float* send_rows, int32_t* send_ids, int32_t* home,
                           int32_t* dropped, void* stream);
+
+/* The routed block for 1 to 16 tokens as ONE launch: what the reference runs as llmp.q8_1,
+ * llmp.vecq with ids and a GLU, llmp.q8_1, llmp.vecq per slot and llmp.moe.combine
+ * (src/kernels/ggml/vecq.cu:457-665, llmp_moe.cu:393-435; src/components/moe.cc's decode
+ * branch).  dst[t] = sum over the token's slots j, in slot order, of weights[t][j] *
+ * (down_e . Q8_1(glu(gate_e . Q8_1(x_t), up_e . Q8_1(x_t)))), e = ids[t][j]; a slot outside
+ * the experts contributes NaN.  A cooperative launch of one CTA an SM with one grid barrier,
+ * waited for with a bound (it raises llmp_b200_device_faults() and stores nothing if it
+ * runs out).  scratch: llmp_b200_moe_decode_scratch() bytes, 256-byte aligned, its first 256
+ * bytes zeroed ONCE (not between calls). */
+typedef struct llmp_b200_moe_decode_desc {
+  const float* x;          /* F32 [tokens, hidden], rows x_stride floats apart, 16-byte aligned */
+  int64_t x_stride;
+  const int32_t* ids;      /* I32 [tokens, used], rows ids_stride apart */
+  int ids_stride;
+  const float* weights;    /* F32 [tokens, used], packed */
+  const void* gate_up;     /* Q4_K [experts][2 * inter][hidden / 256]: gate rows, then up rows */
+  const void* down;        /* Q4_K [experts][hidden][inter / 256] */
+  int experts, used, tokens, hidden, inter;
+  int glu;                 /* LLMP_B200_GLU_SWIGLU / _SWIGLU_CLAMP / _GEGLU */
+  float limit;
+  float* dst;              /* F32 [tokens, hidden], rows dst_stride floats apart */
+  int64_t dst_stride;
+  void* scratch;
+} llmp_b200_moe_decode_desc;
+size_t llmp_b200_moe_decode_scratch(int used, int tokens, int inter);
+int llmp_b200_moe_decode(const llmp_b200_moe_decode_desc* desc, void* stream);
 
 /* Replaces llmp.moe.combine_sorted (llmp_moe.cu:393-435) without NVFP4's global
  * scales and the shared expert: dst[t] = sum over the token's slots, in slot

@@ -46,6 +46,15 @@ class PeerFan(C.Structure):
                 ("tag", C.c_int)]
 
 
+class MoeDecodeDesc(C.Structure):
+    """llmp_b200_moe_decode_desc (include/llmp_b200.h)."""
+    _fields_ = [("x", C.c_void_p), ("x_stride", C.c_int64), ("ids", C.c_void_p), ("ids_stride", C.c_int),
+                ("weights", C.c_void_p), ("gate_up", C.c_void_p), ("down", C.c_void_p),
+                ("experts", C.c_int), ("used", C.c_int), ("tokens", C.c_int), ("hidden", C.c_int),
+                ("inter", C.c_int), ("glu", C.c_int), ("limit", C.c_float), ("dst", C.c_void_p),
+                ("dst_stride", C.c_int64), ("scratch", C.c_void_p)]
+
+
 class MmvqDesc(C.Structure):
     """llmp_b200_mmvq_desc (include/llmp_b200.h)."""
     _fields_ = [("type", C.c_int), ("w", C.c_void_p), ("gate", C.c_void_p), ("glu", C.c_int),
@@ -129,6 +138,8 @@ SIGNATURES = {
     "llmp_b200_q8_1_quantize_words": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64,
                                                 C.c_void_p, C.c_int64, C.c_int, C.c_void_p,
                                                 C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
+    "llmp_b200_moe_decode_scratch": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
+    "llmp_b200_moe_decode": (C.c_int, [C.POINTER(MoeDecodeDesc), C.c_void_p]),
     "llmp_b200_peer_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)]),
     "llmp_b200_peer_free": (C.c_int, [C.c_void_p]),
     "llmp_b200_peer_export": (C.c_int, [C.c_void_p, C.c_void_p]),
@@ -161,6 +172,11 @@ SIGNATURES = {
     "llmp_b200_grouped_gemm_available": (C.c_int, []),
     "llmp_b200_grouped_gemm_scratch": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
     "llmp_b200_grouped_gemm": (C.c_int, [C.POINTER(GroupedGemmDesc), C.c_int, C.c_void_p]),
+    "llmp_b200_grouped_gemm_glu": (C.c_int, [C.POINTER(GroupedGemmDesc), C.c_int, C.c_float,
+                                             C.c_void_p, C.c_int, C.c_void_p]),
+    "llmp_b200_mmq_glu": (C.c_int, [C.POINTER(MmqDesc), C.c_int, C.c_float, C.c_void_p, C.c_void_p]),
+    "llmp_b200_q4k_relayout_glu": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int64,
+                                             C.c_int, C.c_void_p, C.c_void_p]),
     "llmp_b200_grouped_gemm_static": (C.c_int, [C.POINTER(GroupedGemmDesc), C.c_int, C.c_void_p]),
     "llmp_b200_moe_glu_quantize": (C.c_int, [C.c_void_p, C.c_int64, C.c_int, C.c_int64, C.c_int,
                                              C.c_float, C.c_void_p, C.c_void_p]),

@@ -163,7 +163,7 @@ __device__ __forceinline__ void ScaleAndMin(std::uint32_t s0, std::uint32_t s1, 
 __global__ void __launch_bounds__(256)
 RelayoutQ4KKernel(const std::uint8_t* __restrict__ w, int n, int k, std::int64_t stride_row,
                   std::int64_t stride_expert, int experts, std::uint8_t* __restrict__ slab,
-                  const Slab layout) {
+                  const Slab layout, int glu_inter) {
   GridLaunchDependents();
   GridDependencyWait();  // the slab may still be read by the product queued before
   const int lane = static_cast<int>(threadIdx.x) & 31;
@@ -179,9 +179,15 @@ RelayoutQ4KKernel(const std::uint8_t* __restrict__ w, int n, int k, std::int64_t
   uint4 head = make_uint4(0, 0, 0, 0), q[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) q[i] = make_uint4(0, 0, 0, 0);
+  // For the GLU write-back the slab's rows interleave the gate and up rows (the source holds
+  // glu_inter gate rows, then as many up rows): slab rows 32g .. 32g + 15 are gate rows
+  // 16g .. 16g + 15 and slab rows 32g + 16 .. 32g + 31 the up rows of the same outputs, so an
+  // epilogue thread's 32 rows are 16 (gate, up) pairs.
+  int from = row;
+  if (glu_inter > 0) from = (lane < 16 ? 0 : glu_inter) + (rg * 16) + (lane & 15);
   if (live) {
     const auto* src = reinterpret_cast<const uint4*>(
-        w + ((static_cast<std::int64_t>(e) * stride_expert + static_cast<std::int64_t>(row) * stride_row + sb) * 144));
+        w + ((static_cast<std::int64_t>(e) * stride_expert + static_cast<std::int64_t>(from) * stride_row + sb) * 144));
     head = LoadStream16(src);
 #pragma unroll
     for (int i = 0; i < 8; ++i) q[i] = LoadStream16(src + 1 + i);
@@ -302,6 +308,11 @@ struct Params {
   int ax_ksteps;         // k-steps a row tile's scales span
   int ax_row_tiles;
   std::int32_t* sums;    // verification: the int32 group sums [col][row][k / 32], or null
+  // GLU write-back (slab with interleaved gate / up rows): the GLU of every (gate, up) pair,
+  // requantized to Q8_1-MMQ blocks [nrows / 2 / 128][ncols], instead of the F32 output.
+  std::uint8_t* glu_out;
+  int glu;
+  float limit;
 };
 
 template <bool kSlab>
@@ -708,7 +719,64 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
       acc[2 * i] += lo;
       acc[(2 * i) + 1] += hi;
     }
-    if (ok && col < c_end) {
+    if (p.glu_out != nullptr) {
+      // The thread's 32 rows are 16 gate rows then the 16 up rows of the same outputs.  A
+      // Q8_1-MMQ group is 32 outputs: this thread's 16 and those of the thread of the same
+      // token one row group over (another warp), so the two trade their maxima and their
+      // four-value partial sums through shared memory (the first weight stage: every MMA has
+      // retired) and each forms the group's scale and sum exactly as the quantizer kernel
+      // does (eight lanes of four values, xor tree 4, 2, 1).  Every epilogue warp reaches the
+      // barrier, also one whose wait ran out: it stores nothing.
+      float h[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) h[j] = Glu(p.glu, acc[j], acc[16 + j], p.limit);
+      float part[4], amax = 0.0f;
+#pragma unroll
+      for (int l = 0; l < 4; ++l) {
+        part[l] = ((h[4 * l] + h[(4 * l) + 1]) + h[(4 * l) + 2]) + h[(4 * l) + 3];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) amax = fmaxf(amax, fabsf(h[(4 * l) + c]));
+      }
+      float* trade = reinterpret_cast<float*>(w_tiles);  // [4 row groups][128 tokens][8]
+      float* mine = trade + (((rowgroup * kTileCols) + tt) * 8);
+      mine[0] = amax;
+      mine[1] = ok ? 1.0f : 0.0f;
+      *reinterpret_cast<float4*>(mine + 4) = make_float4(part[0], part[1], part[2], part[3]);
+      asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueWarps * 32) : "memory");
+      const float* other = trade + ((((rowgroup ^ 1) * kTileCols) + tt) * 8);
+      const float4 theirs = *reinterpret_cast<const float4*>(other + 4);
+      const bool both = ok && other[1] != 0.0f;
+      amax = fmaxf(amax, other[0]);
+      // lanes 0..3 of the quantizer hold the lower row group's values, 4..7 the upper's
+      const bool low = (rowgroup & 1) == 0;
+      const float p0 = low ? part[0] : theirs.x, p1 = low ? part[1] : theirs.y;
+      const float p2 = low ? part[2] : theirs.z, p3 = low ? part[3] : theirs.w;
+      const float p4 = low ? theirs.x : part[0], p5 = low ? theirs.y : part[1];
+      const float p6 = low ? theirs.z : part[2], p7 = low ? theirs.w : part[3];
+      const float sum = ((p0 + p4) + (p2 + p6)) + ((p1 + p5) + (p3 + p7));
+      const int out_first = (row0 / 2) + (rowgroup * 16);  // this thread's first GLU output
+      if (both && col < c_end && row0 + (rowgroup * kEpilogueRows) < a.nrows) {
+        std::uint32_t packed[4] = {0, 0, 0, 0};
+        float d = 0.0f;
+        if (amax > 0.0f) {
+          const float d_inv = 127.0f / amax;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int q = static_cast<int>(roundf(h[j] * d_inv));
+            packed[j >> 2] |= (static_cast<std::uint32_t>(q) & 0xffu) << (8 * (j & 3));
+          }
+          d = 1.0f / d_inv;
+        }
+        std::uint8_t* block = p.glu_out + (((static_cast<std::size_t>(out_first >> 7) * a.ncols) + col) * 144);
+        const int at = out_first & 127;
+        *reinterpret_cast<uint4*>(block + 16 + at) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        if (low) {
+          *reinterpret_cast<std::uint32_t*>(block + ((at >> 5) * 4)) =
+              static_cast<std::uint32_t>(__half_as_ushort(__float2half_rn(d))) |
+              (static_cast<std::uint32_t>(__half_as_ushort(__float2half_rn(sum))) << 16);
+        }
+      }
+    } else if (ok && col < c_end) {
       const int dst_col = a.ids_dst != nullptr ? a.ids_dst[col] : col;
       const int first = row0 + (rowgroup * kEpilogueRows);
       float* out = a.dst + (static_cast<std::size_t>(dst_col) * a.dst_col_stride) + first;
@@ -738,16 +806,18 @@ MmqQ4KKernel(const __grid_constant__ CUtensorMap map_y, const __grid_constant__ 
   }
 }
 
-int CheckDesc(const Desc& d) {
+int CheckDesc(const Desc& d, bool no_f32_output) {
   if (d.type != LLMP_B200_TYPE_Q4_K) {
     return Reject("mmq: weight type %d is not one this build computes (Q4_K)", d.type);
   }
-  if ((d.w == nullptr && d.w_slab == nullptr) || d.y == nullptr || d.dst == nullptr || d.k < 256 ||
+  if ((d.w == nullptr && d.w_slab == nullptr) || d.y == nullptr ||
+      (d.dst == nullptr && !no_f32_output) || d.k < 256 ||
       d.k % 256 != 0 || d.nrows < 1 || d.ncols < 1) {
     return Reject("mmq: Q4_K weights [k, n] (blocks or slab), Q8_1-MMQ activations of ncols columns, "
                   "an F32 output; k a positive multiple of 256");
   }
-  if (d.stride_row < d.k / 256 || d.stride_expert < 0 || d.dst_col_stride < d.nrows) {
+  if (d.stride_row < d.k / 256 || d.stride_expert < 0 ||
+      (d.dst_col_stride < d.nrows && !no_f32_output)) {
     return Reject("mmq: strides must cover a row");
   }
   if ((d.w != nullptr && !Aligned(d.w, 16)) || !Aligned(d.y, 16) || !Aligned(d.dst, 4) ||
@@ -779,7 +849,7 @@ bool Encode3D(CUtensorMap* map, Fn encode, const void* base, cuuint64_t d0, cuui
 }
 
 int Relayout(const void* w, int n, int k, std::int64_t stride_row, std::int64_t stride_expert,
-             int experts, void* slab, void* stream) {
+             int experts, void* slab, void* stream, int glu_inter = 0) {
   const Slab layout = SlabOf(n, k, experts);
   const std::int64_t items = static_cast<std::int64_t>(experts) * layout.row_tiles * 4 * (k / 256);
   const std::int64_t grid = (items + 7) / 8;
@@ -787,7 +857,7 @@ int Relayout(const void* w, int n, int k, std::int64_t stride_row, std::int64_t 
   const cudaError_t e = LaunchPdl(RelayoutQ4KKernel, dim3(static_cast<unsigned>(grid)), dim3(256), 0,
                                   static_cast<cudaStream_t>(stream),
                                   static_cast<const std::uint8_t*>(w), n, k, stride_row, stride_expert,
-                                  experts, static_cast<std::uint8_t*>(slab), layout);
+                                  experts, static_cast<std::uint8_t*>(slab), layout, glu_inter);
   if (e != cudaSuccess) return Failed(e, "q4k_relayout launch");
   return 0;
 }
@@ -795,8 +865,16 @@ int Relayout(const void* w, int n, int k, std::int64_t stride_row, std::int64_t 
 }  // namespace
 
 int LaunchMmq(const llmp_b200_mmq_desc& d, const std::int32_t* worklist, int max_tiles,
-              void* stream, std::int32_t* sums) {
-  if (const int status = CheckDesc(d); status != 0) return status;
+              void* stream, std::int32_t* sums, const MmqGlu* glu) {
+  if (const int status = CheckDesc(d, glu != nullptr); status != 0) return status;
+  if (glu != nullptr) {
+    if (d.w_slab == nullptr || glu->blocks == nullptr || d.nrows % 64 != 0 || d.ids_dst != nullptr ||
+        sums != nullptr || !Aligned(glu->blocks, 16) || glu->glu < LLMP_B200_GLU_SWIGLU ||
+        glu->glu > LLMP_B200_GLU_GEGLU || (glu->glu == LLMP_B200_GLU_GEGLU && glu->limit != 0.0f)) {
+      return Reject("mmq_glu: a slab of interleaved gate / up rows (llmp_b200_q4k_relayout_glu), rows a "
+                    "multiple of 64, no output scatter, 16-byte aligned output blocks, a GLU");
+    }
+  }
   if (const int status = DeviceStatus(); status != 0) return status;
   const tc::EncodeTiledFn encode = tc::EncodeTiled();
   if (encode == nullptr) return Reject("mmq: the driver has no tensor-map encoder");
@@ -863,6 +941,11 @@ int LaunchMmq(const llmp_b200_mmq_desc& d, const std::int32_t* worklist, int max
   p.ax_ksteps = layout.ksteps;
   p.ax_row_tiles = layout.row_tiles;
   p.sums = sums;
+  if (glu != nullptr) {
+    p.glu_out = static_cast<std::uint8_t*>(glu->blocks);
+    p.glu = glu->glu;
+    p.limit = glu->limit;
+  }
   static thread_local int configured_device = -1;
   int device = -1;
   cudaGetDevice(&device);
@@ -960,6 +1043,30 @@ int llmp_b200_mmq(const llmp_b200_mmq_desc* desc, int sms, void* stream) {
   (void)sms;
   if (desc == nullptr) return llmp_b200::Reject("mmq: null descriptor");
   return llmp_b200::LaunchMmq(*desc, nullptr, 0, stream, nullptr);
+}
+
+int llmp_b200_q4k_relayout_glu(const void* w, int inter, int k, int stride_row, int64_t stride_expert,
+                               int experts, void* slab, void* stream) {
+  using namespace llmp_b200;
+  if (w == nullptr || slab == nullptr || inter < 32 || inter % 32 != 0 || k < 256 || k % 256 != 0 ||
+      experts < 1 || stride_row < k / 256 ||
+      (experts > 1 && stride_expert < static_cast<int64_t>(stride_row) * 2 * inter)) {
+    return Reject("q4k_relayout_glu: Q4_K blocks [experts][2 * inter][k / 256] (gate rows, then up "
+                  "rows), inter a positive multiple of 32, k of 256, and a slab");
+  }
+  if (!Aligned(w, 16) || !Aligned(slab, 256)) {
+    return Reject("q4k_relayout_glu: blocks 16-byte aligned, the slab 256");
+  }
+  if (const int status = DeviceStatus(); status != 0) return status;
+  return Relayout(w, 2 * inter, k, stride_row, stride_expert, experts, slab, stream, inter);
+}
+
+int llmp_b200_mmq_glu(const llmp_b200_mmq_desc* desc, int glu, float limit, void* blocks,
+                      void* stream) {
+  using namespace llmp_b200;
+  if (desc == nullptr) return Reject("mmq_glu: null descriptor");
+  const MmqGlu g{blocks, glu, limit};
+  return LaunchMmq(*desc, nullptr, 0, stream, nullptr, &g);
 }
 
 int llmp_b200_mmq_block_sums(const llmp_b200_mmq_desc* desc, int32_t* sums, void* stream) {

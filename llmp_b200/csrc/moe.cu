@@ -354,13 +354,13 @@ __global__ void FillKernel(std::int32_t* __restrict__ p, std::int64_t n, std::in
   if (i < n) p[i] = v;
 }
 
-int CheckGrouped(const llmp_b200_grouped_gemm_desc& g) {
+int CheckGrouped(const llmp_b200_grouped_gemm_desc& g, bool no_f32_output = false) {
   if (g.groups < 1 || g.groups > kMaxExperts || g.n < 1 || g.k < 256 || g.k % 256 != 0 ||
       g.rows < 1) {
     return Reject("grouped_gemm: 1..1024 groups, n >= 1, k a positive multiple of 256, rows >= 1");
   }
   if (g.offsets == nullptr || g.a == nullptr || (g.weights == nullptr && g.weights_slab == nullptr) ||
-      g.d == nullptr) {
+      (g.d == nullptr && !no_f32_output)) {
     return Reject("grouped_gemm: offsets, activation blocks, weights (blocks or slab) and an output");
   }
   if (g.expert_stride % 144 != 0 || g.expert_stride < static_cast<std::uint64_t>(g.n) * (g.k / 256) * 144) {
@@ -473,12 +473,32 @@ size_t llmp_b200_grouped_gemm_scratch(int groups, int rows, int sms) {
   return (ints * sizeof(int32_t) + 255) / 256 * 256;
 }
 
+namespace llmp_b200 {
+namespace {
+int GroupedGemm(const llmp_b200_grouped_gemm_desc* gemm, const MmqGlu* glu, void* stream);
+}  // namespace
+}  // namespace llmp_b200
+
 int llmp_b200_grouped_gemm(const llmp_b200_grouped_gemm_desc* gemm, int sms, void* stream) {
-  using namespace llmp_b200;
   (void)sms;
+  return llmp_b200::GroupedGemm(gemm, nullptr, stream);
+}
+
+int llmp_b200_grouped_gemm_glu(const llmp_b200_grouped_gemm_desc* gemm, int glu, float limit,
+                               void* blocks, int sms, void* stream) {
+  (void)sms;
+  const llmp_b200::MmqGlu g{blocks, glu, limit};
+  return llmp_b200::GroupedGemm(gemm, &g, stream);
+}
+
+}  // extern "C"
+
+namespace llmp_b200 {
+namespace {
+int GroupedGemm(const llmp_b200_grouped_gemm_desc* gemm, const MmqGlu* glu, void* stream) {
   if (gemm == nullptr) return Reject("grouped_gemm: null descriptor");
   const llmp_b200_grouped_gemm_desc& g = *gemm;
-  if (const int status = CheckGrouped(g); status != 0) return status;
+  if (const int status = CheckGrouped(g, glu != nullptr); status != 0) return status;
   if (g.scratch == nullptr || !Aligned(g.scratch, 256)) {
     return Reject("grouped_gemm: 256-byte aligned scratch of llmp_b200_grouped_gemm_scratch bytes");
   }
@@ -488,11 +508,15 @@ int llmp_b200_grouped_gemm(const llmp_b200_grouped_gemm_desc* gemm, int sms, voi
   BuildTiles<<<1, 256, (g.groups + 1) * sizeof(int), static_cast<cudaStream_t>(stream)>>>(
       g.offsets, g.groups, capacity, worklist);
   if (const int status = Launched("grouped_gemm tile list"); status != 0) return status;
-  const int status = LaunchMmq(MmqOf(g), worklist, capacity, stream);
+  const int status = LaunchMmq(MmqOf(g), worklist, capacity, stream, nullptr, glu);
   // The tile list is queued: a refusal now would leave work behind, so report
   // it as a failure after queueing.
   return status > 0 ? -status : status;
 }
+}  // namespace
+}  // namespace llmp_b200
+
+extern "C" {
 
 int llmp_b200_grouped_gemm_static(const llmp_b200_grouped_gemm_desc* gemm, int sms, void* stream) {
   using namespace llmp_b200;

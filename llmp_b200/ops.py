@@ -20,7 +20,8 @@ __all__ = ["available", "sm_count", "device_faults", "device_faults_clear", "blo
            "mxfp8_quantize", "mxfp8_swizzle", "mxfp8_gemm", "mxfp8_mul_mat_vec", "decode_vector", "decode_rows", "decode_matrix", "decode_grouped", "DECODER_Q8_0", "DECODER_MXFP8_SPLIT",
            "DECODER_MXFP8_ATOMS", "DECODER_BF16", "DECODER_F16", "DECODER_NVFP4_SPLIT", "DECODER_NVFP4_ATOMS",
            "DECODER_MXFP4_SPLIT", "DECODER_MXFP4_ATOMS", "mmq_quantize", "mmq", "mmq_scratch", "mmq_block_sums", "q4k_relayout", "moe_route", "grouped_gemm",
-           "moe_glu_quantize", "moe_combine", "moe_ep_pack", "moe_ffn", "TYPE_Q8_0", "TYPE_Q4_K",
+           "moe_glu_quantize", "moe_combine", "moe_ep_pack", "moe_ffn", "moe_decode", "moe_decode_fits",
+           "mmq_glu", "grouped_gemm_glu", "TYPE_Q8_0", "TYPE_Q4_K",
            "TYPE_Q4_0", "TYPE_Q5_0", "TYPE_Q5_K", "TYPE_Q6_K", "TYPE_IQ4_NL",
            "GLU_NONE", "GLU_SWIGLU", "GLU_SWIGLU_CLAMP", "GLU_GEGLU", "Rejected", "LaunchFailed"]
 
@@ -371,19 +372,69 @@ def mmq_quantize(x: torch.Tensor, ids_src: torch.Tensor | None = None,
     return out
 
 
-def q4k_relayout(weights: torch.Tensor, k: int, n: int) -> torch.Tensor:
+def q4k_relayout(weights: torch.Tensor, k: int, n: int, *, glu: bool = False) -> torch.Tensor:
     """The load-time relayout of Q4_K weights [n, k blocks] or experts [experts, n, k blocks]
-    into the tensor core's slab (llmp_b200_q4k_relayout): a uint8 tensor to pass as `slab`."""
+    into the tensor core's slab (llmp_b200_q4k_relayout): a uint8 tensor to pass as `slab`.
+    glu: the n rows are n / 2 gate rows then n / 2 up rows and the slab interleaves them for the
+    GLU write-back (llmp_b200_q4k_relayout_glu; for mmq_glu / grouped_gemm_glu only)."""
     _need(weights, torch.uint8, "q4k_relayout weights")
     experts = weights.shape[0] if weights.dim() == 3 else 1
     stride_row = weights.stride(-2) // 144
     stride_expert = weights.stride(0) // 144 if weights.dim() == 3 else n * stride_row
     slab = torch.empty((int(N.lib().llmp_b200_q4k_slab_bytes(n, k, experts)),), dtype=torch.uint8,
                        device=weights.device)
+    if glu:
+        N.check(N.lib().llmp_b200_q4k_relayout_glu(weights.data_ptr(), n // 2, k, stride_row,
+                                                   stride_expert, experts, slab.data_ptr(), _stream()),
+                "llmp_b200_q4k_relayout_glu")
+        return slab
     N.check(N.lib().llmp_b200_q4k_relayout(weights.data_ptr(), n, k, stride_row, stride_expert,
                                            experts, slab.data_ptr(), _stream()),
             "llmp_b200_q4k_relayout")
     return slab
+
+
+def mmq_glu(yq: torch.Tensor, k: int, inter: int, slab: torch.Tensor, glu: int = GLU_SWIGLU,
+            limit: float = 0.0) -> torch.Tensor:
+    """MulMatQGlu: the gate | up product (slab from q4k_relayout(..., glu=True)) with the GLU and the
+    requantization in its write-back -> Q8_1-MMQ blocks [inter / 128, cols, 144]."""
+    _need(yq, torch.uint8, "mmq_glu activations")
+    if yq.dim() != 3 or yq.shape[2] != 144 or not yq.is_contiguous() or inter % 128 != 0:
+        raise Rejected("mmq_glu: packed Q8_1-MMQ blocks [k / 128, cols, 144], inter a multiple of 128")
+    cols = yq.shape[1]
+    out = torch.empty((inter // 128, cols, 144), dtype=torch.uint8, device=yq.device)
+    d = N.MmqDesc()
+    d.type, d.y, d.k, d.nrows, d.ncols = TYPE_Q4_K, yq.data_ptr(), k, 2 * inter, cols
+    d.stride_row, d.dst_col_stride, d.experts, d.max_cols_per_expert = k // 256, 2 * inter, 1, cols
+    d.w_slab = slab.data_ptr()
+    N.check(N.lib().llmp_b200_mmq_glu(C.byref(d), glu, limit, out.data_ptr(), _stream()),
+            "llmp_b200_mmq_glu")
+    return out
+
+
+def grouped_gemm_glu(a: torch.Tensor, offsets: torch.Tensor, k: int, inter: int, slab: torch.Tensor,
+                     glu: int = GLU_SWIGLU, limit: float = 0.0, *,
+                     scratch: torch.Tensor | None = None) -> torch.Tensor:
+    """The grouped gate | up product with the GLU write-back (llmp_b200_grouped_gemm_glu): a Q8_1-MMQ
+    blocks [k / 128, rows, 144] of expert-sorted rows, slab from q4k_relayout(experts' gate_up,
+    glu=True) -> Q8_1-MMQ blocks [inter / 128, rows, 144]."""
+    _need(a, torch.uint8, "grouped_gemm_glu activations")
+    _need(offsets, torch.int32, "grouped_gemm_glu offsets")
+    groups, rows = offsets.numel() - 1, a.shape[1]
+    if inter % 128 != 0:
+        raise Rejected("grouped_gemm_glu: inter a multiple of 128")
+    out = torch.empty((inter // 128, rows, 144), dtype=torch.uint8, device=a.device)
+    need = int(N.lib().llmp_b200_grouped_gemm_scratch(groups, rows, 0))
+    if scratch is None:
+        scratch = torch.empty((need,), dtype=torch.uint8, device=a.device)
+    g = N.GroupedGemmDesc()
+    g.groups, g.n, g.k, g.rows = groups, 2 * inter, k, rows
+    g.offsets, g.a = offsets.data_ptr(), a.data_ptr()
+    g.expert_stride = 2 * inter * (k // 256) * 144
+    g.weights_slab, g.scratch = slab.data_ptr(), scratch.data_ptr()
+    N.check(N.lib().llmp_b200_grouped_gemm_glu(C.byref(g), glu, limit, out.data_ptr(), 0, _stream()),
+            "llmp_b200_grouped_gemm_glu")
+    return out
 
 
 def _mmq_desc(weights, yq, k, n, wtype, ids_dst, expert_bounds, out_cols, max_cols_per_expert,
@@ -551,6 +602,53 @@ def moe_combine(rows: torch.Tensor, position: torch.Tensor | None, weights: torc
     return out
 
 
+_MOE_DECODE_SCRATCH: dict = {}
+MOE_DECODE_TOKENS = 4      # up to here the one-launch block beats the five-launch one
+
+
+def moe_decode_fits(tokens: int, used: int, hidden: int, inter: int) -> bool:
+    """Whether llmp_b200_moe_decode takes the shape."""
+    ur_a, span = hidden // 256, 1
+    while span < inter // 256:
+        span *= 2
+    return (hidden % 256 == 0 and inter % 256 == 0 and 256 <= hidden <= 8192 and inter >= 256 and
+            ur_a & (ur_a - 1) == 0 and ur_a <= 32 and used * span <= 32 and used * inter <= 16384 and
+            1 <= tokens <= 16)
+
+
+def moe_decode(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, gate_up: torch.Tensor,
+               down: torch.Tensor, hidden: int, inter: int, glu: int = GLU_SWIGLU, limit: float = 0.0,
+               *, out: torch.Tensor | None = None, scratch: torch.Tensor | None = None) -> torch.Tensor:
+    """The routed block for 1 to 16 tokens as one launch (llmp_b200_moe_decode).  Without
+    `scratch` a cached buffer per device and size is used: calls that may overlap on the GPU
+    (several streams) must bring their own (uint8, llmp_b200_moe_decode_scratch bytes, zeroed)."""
+    _need(x, torch.float32, "moe_decode x")
+    _need(ids, torch.int32, "moe_decode ids")
+    _need(weights, torch.float32, "moe_decode weights")
+    tokens, used = ids.shape
+    if x.dim() != 2 or x.shape != (tokens, hidden) or x.stride(1) != 1 or ids.stride(1) != 1 or \
+            not weights.is_contiguous() or tuple(weights.shape) != (tokens, used):
+        raise Rejected("moe_decode: x F32 [tokens, hidden], ids I32 and weights F32 [tokens, used]")
+    if not gate_up.is_contiguous() or not down.is_contiguous():
+        raise Rejected("moe_decode: packed expert tensors")
+    nbytes = int(N.lib().llmp_b200_moe_decode_scratch(used, tokens, inter))
+    if scratch is None:
+        key = (x.device, nbytes)
+        scratch = _MOE_DECODE_SCRATCH.get(key)
+        if scratch is None:
+            scratch = _MOE_DECODE_SCRATCH[key] = torch.zeros((nbytes,), dtype=torch.uint8, device=x.device)
+    if out is None:
+        out = torch.empty((tokens, hidden), dtype=torch.float32, device=x.device)
+    d = N.MoeDecodeDesc()
+    d.x, d.x_stride, d.ids, d.ids_stride = x.data_ptr(), x.stride(0), ids.data_ptr(), ids.stride(0)
+    d.weights, d.gate_up, d.down = weights.data_ptr(), gate_up.data_ptr(), down.data_ptr()
+    d.experts, d.used, d.tokens, d.hidden, d.inter = gate_up.shape[0], used, tokens, hidden, inter
+    d.glu, d.limit = glu, limit
+    d.dst, d.dst_stride, d.scratch = out.data_ptr(), out.stride(0), scratch.data_ptr()
+    N.check(N.lib().llmp_b200_moe_decode(C.byref(d), _stream()), "llmp_b200_moe_decode")
+    return out
+
+
 def moe_ffn(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, gate_up: torch.Tensor,
             down: torch.Tensor, hidden: int, inter: int, glu: int = GLU_SWIGLU,
             decode_tokens: int | None = None, slabs: tuple | None = None) -> torch.Tensor:
@@ -568,6 +666,10 @@ def moe_ffn(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, gate_up: 
     # kernel's limits).  Up to DECODE_TOKENS tokens that beats the tensor-core GEMM, whose
     # 128-row tiles are nearly empty when an expert sees a handful of rows.
     chunk = min(128, max(1, 1024 // used))
+    if tokens <= MOE_DECODE_TOKENS and (decode_tokens is None or decode_tokens > 0) and \
+            x.dtype == torch.float32 and x.stride(-1) == 1 and moe_decode_fits(tokens, used, hidden, inter):
+        return moe_decode(x, ids, weights if weights.is_contiguous() else weights.contiguous(),
+                          gate_up, down, hidden, inter, glu)
     if tokens <= (DECODE_TOKENS if decode_tokens is None else decode_tokens) and used <= 128:
         gate_w = gate_up[:, :inter]
         up_w = gate_up[:, inter:]
@@ -592,9 +694,14 @@ def moe_ffn(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, gate_up: 
     route = moe_route(ids, experts)
     slots = tokens * used
     aq = mmq_quantize(x, ids_src=route["token"], cols=slots)
-    gu = grouped_gemm(gate_up, aq, route["offsets"], hidden, 2 * inter,
-                      slab=slabs[0] if slabs is not None else None)
-    hq = moe_glu_quantize(gu, inter, glu)
+    if slabs is not None and len(slabs) > 2 and slabs[2] and inter % 128 == 0:
+        # slabs[0] interleaves gate and up rows: the GLU and the requantization happen in the
+        # gate | up product's write-back (no F32 round trip, no separate pass)
+        hq = grouped_gemm_glu(aq, route["offsets"], hidden, inter, slabs[0], glu)
+    else:
+        gu = grouped_gemm(gate_up, aq, route["offsets"], hidden, 2 * inter,
+                          slab=slabs[0] if slabs is not None else None)
+        hq = moe_glu_quantize(gu, inter, glu)
     y = grouped_gemm(down, hq, route["offsets"], inter, hidden,
                      slab=slabs[1] if slabs is not None else None)
     return moe_combine(y, route["position"], weights.contiguous(), tokens, used)

@@ -193,3 +193,41 @@ def test_routed_mmq_takes_a_slab_of_experts(cuda, orc):
     want32, want64 = orc.mmq_q4_k(w, yq.cpu().numpy(), k, n, expert_bounds=bounds,
                                   stride_expert=n * (k // 256), want64=True)
     _check(slab.cpu().numpy(), want32, want64)
+
+
+@pytest.mark.parametrize("cols,inter,k,glu", [(200, 256, 512, 1), (513, 768, 2048, 1), (64, 128, 256, 3)])
+def test_glu_write_back_equals_the_product_then_the_glu_quantizer(cuda, cols, inter, k, glu):
+    """MulMatQGlu: the GLU and the requantization inside the gate | up product's write-back give,
+    bit for bit, the blocks llmp_b200_moe_glu_quantize makes of the F32 product."""
+    torch = cuda
+    import llmp_b200 as ops
+    from llmp_b200 import synth
+    rng = np.random.default_rng(cols + inter)
+    w = to_dev(torch, synth.q4_k_weights(rng, 2 * inter, k))
+    x = to_dev(torch, rng.normal(0, 1, size=(cols, k)).astype(np.float32))
+    yq = ops.mmq_quantize(x)
+    plain = ops.mmq(None, yq, k, 2 * inter, slab=ops.q4k_relayout(w, k, 2 * inter))
+    want = ops.moe_glu_quantize(plain, inter, glu)
+    got = ops.mmq_glu(yq, k, inter, ops.q4k_relayout(w, k, 2 * inter, glu=True), glu)
+    torch.cuda.synchronize()
+    assert ops.device_faults() == 0
+    assert torch.equal(got, want)
+
+
+def test_grouped_glu_write_back(cuda):
+    torch = cuda
+    import llmp_b200 as ops
+    from llmp_b200 import synth
+    rng = np.random.default_rng(99)
+    experts, used, tokens, inter, k = 6, 2, 150, 256, 512
+    w = to_dev(torch, synth.q4_k_weights(rng, experts * 2 * inter, k).reshape(experts, 2 * inter, -1))
+    ids, _ = synth.topk_route(rng, tokens, experts, used)
+    route = ops.moe_route(to_dev(torch, ids), experts)
+    x = to_dev(torch, rng.normal(0, 1, size=(tokens, k)).astype(np.float32))
+    aq = ops.mmq_quantize(x, ids_src=route["token"], cols=tokens * used)
+    plain = ops.grouped_gemm(w, aq, route["offsets"], k, 2 * inter)
+    want = ops.moe_glu_quantize(plain, inter, ops.GLU_SWIGLU)
+    got = ops.grouped_gemm_glu(aq, route["offsets"], k, inter, ops.q4k_relayout(w, k, 2 * inter, glu=True))
+    torch.cuda.synchronize()
+    assert ops.device_faults() == 0
+    assert torch.equal(got, want)

@@ -220,3 +220,64 @@ def test_routed_expert_block_at_4096_tokens_stage_by_stage(cuda, orc):
     rows = np.concatenate([position[t * used:(t + 1) * used] for t in sample])
     want = orc.moe_combine(y_h[rows], np.arange(rows.size, dtype=np.int32), w[sample], 32, used)
     assert np.array_equal(out.cpu().numpy()[sample], want)
+
+
+@pytest.mark.parametrize("tokens,glu", [(1, 1), (3, 1), (4, 3), (16, 1)])
+def test_one_launch_block_equals_the_five_launch_block(cuda, orc, tokens, glu):
+    """llmp_b200_moe_decode against the same block as five launches (quantize, routed gate|up GLU,
+    quantize, routed down, combine): the same arithmetic with the super-blocks' sums added in
+    another order, so equal to rounding; twice in a row (its grid barrier's counter only grows);
+    a slot outside the experts gives NaN in both."""
+    torch = cuda
+    ops = _ops()
+    rng = np.random.default_rng(tokens + glu)
+    experts, used, hidden, inter = 128, 8, 2048, 768
+    gate_up = to_dev(torch, synth.q4_k_weights(rng, experts * 2 * inter, hidden).reshape(experts, 2 * inter, -1))
+    down = to_dev(torch, synth.q4_k_weights(rng, experts * hidden, inter).reshape(experts, hidden, -1))
+    x = to_dev(torch, rng.normal(0, 1, size=(tokens, hidden)).astype(np.float32))
+    ids, w = synth.topk_route(rng, tokens, experts, used)
+    ids_d, w_d = to_dev(torch, ids), to_dev(torch, w)
+    assert ops.moe_decode_fits(tokens, used, hidden, inter)
+    keep = ops.ops.MOE_DECODE_TOKENS
+    try:
+        ops.ops.MOE_DECODE_TOKENS = 0
+        want = ops.moe_ffn(x, ids_d, w_d, gate_up, down, hidden, inter, glu=glu)
+    finally:
+        ops.ops.MOE_DECODE_TOKENS = keep
+    for again in range(2):
+        got = torch.full((tokens, hidden), float("nan"), device="cuda")
+        ops.moe_decode(x, ids_d, w_d, gate_up, down, hidden, inter, glu=glu, out=got)
+        torch.cuda.synchronize()
+        assert ops.device_faults() == 0 and torch.isfinite(got).all()
+        scale = float(want.abs().max())
+        assert float(((got - want) ** 2).sum() / (want ** 2).sum()) <= 1e-6, again
+        assert float((got - want).abs().max()) <= 1e-3 * scale
+    ids_bad = ids_d.clone()
+    ids_bad[0, 2] = experts + 5
+    got = ops.moe_decode(x, ids_bad, w_d, gate_up, down, hidden, inter, glu=glu)
+    assert torch.isnan(got[0]).all() and (tokens == 1 or torch.isfinite(got[1:]).all())
+    with pytest.raises(ops.Rejected):
+        ops.moe_decode(x[:, :1280].contiguous(), ids_d, w_d, gate_up, down, 1280, inter)   # 5 super-blocks a row
+    torch.cuda.synchronize()
+
+
+def test_block_with_the_glu_in_the_write_back_equals_the_block_without(cuda):
+    """moe_ffn over slabs whose gate | up rows are interleaved (GLU and requantization inside the
+    grouped product) against the same block over plain slabs (F32 product, then the GLU quantizer):
+    the same bits."""
+    torch = cuda
+    ops = _ops()
+    rng = np.random.default_rng(31)
+    experts, used, hidden, inter, tokens = 16, 4, 1024, 512, 300
+    gate_up = to_dev(torch, synth.q4_k_weights(rng, experts * 2 * inter, hidden).reshape(experts, 2 * inter, -1))
+    down = to_dev(torch, synth.q4_k_weights(rng, experts * hidden, inter).reshape(experts, hidden, -1))
+    x = to_dev(torch, rng.normal(0, 1, size=(tokens, hidden)).astype(np.float32))
+    ids, w = synth.topk_route(rng, tokens, experts, used)
+    ids_d, w_d = to_dev(torch, ids), to_dev(torch, w)
+    plain = (ops.q4k_relayout(gate_up, hidden, 2 * inter), ops.q4k_relayout(down, inter, hidden))
+    fused = (ops.q4k_relayout(gate_up, hidden, 2 * inter, glu=True), plain[1], True)
+    want = ops.moe_ffn(x, ids_d, w_d, gate_up, down, hidden, inter, slabs=plain, decode_tokens=0)
+    got = ops.moe_ffn(x, ids_d, w_d, gate_up, down, hidden, inter, slabs=fused, decode_tokens=0)
+    torch.cuda.synchronize()
+    assert ops.device_faults() == 0 and torch.isfinite(got).all()
+    assert torch.equal(got, want)
