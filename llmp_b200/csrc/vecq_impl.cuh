@@ -211,12 +211,18 @@ struct Q8_0Unit {
 };
 
 // ------------------------------------------------------------------ staging
-// Shared memory a pass holds: for each of its P tokens, k int8 values
-// (16-byte aligned) then k / 32 float2 (d, d * sum q).
+// Shared memory a pass holds: for each of its P tokens, the k int8 values (16-byte aligned),
+// then k / 32 float2 (d, d * sum q).  Every 64 values are followed by 16 bytes of padding: the
+// lanes of a team read consecutive units at once, and at a pitch of 64 or 128 bytes their
+// 128-bit loads would meet on two bank groups, or one; at 80 they spread over all eight.
+__host__ __device__ inline int StagedAt(int value) { return value + ((value >> 6) << 4); }
 __host__ __device__ inline std::size_t StageBytes(int k, int tokens) {
-  const std::size_t one = (static_cast<std::size_t>(k) + (k / 32) * 8 + 15) / 16 * 16;
+  const std::size_t one =
+      (static_cast<std::size_t>(StagedAt(k)) + 16 + (static_cast<std::size_t>(k / 32) * 8) + 15) / 16 * 16;
   return static_cast<std::size_t>(tokens) * one;
 }
+// Where a token's scales start (16-byte aligned: the float4 reads of the Q4_K path).
+__host__ __device__ inline int StagedScales(int k) { return (StagedAt(k) + 15) / 16 * 16; }
 
 // One Q8_1 block (36 bytes, 4-byte aligned) a thread.
 __device__ __forceinline__ void StageRow(const std::uint8_t* __restrict__ y, int k,
@@ -232,7 +238,7 @@ __device__ __forceinline__ void StageRow(const std::uint8_t* __restrict__ y, int
       v[i] = src[1 + i];
       isum = Dp4a(0x01010101, static_cast<int>(v[i]), isum);
     }
-    auto* dst = reinterpret_cast<uint4*>(qs + (static_cast<std::size_t>(b) * 32));
+    auto* dst = reinterpret_cast<uint4*>(qs + StagedAt(b * 32));
     dst[0] = make_uint4(v[0], v[1], v[2], v[3]);
     dst[1] = make_uint4(v[4], v[5], v[6], v[7]);
     const float d = HalfBitsToFloat(ds & 0xffffu);
@@ -371,7 +377,7 @@ VecQKernel(const Desc a) {
                               ((static_cast<std::size_t>(pr >> 8) * a.y_token +
                                 static_cast<std::size_t>(pr & 0xff) * a.y_slot) * 36);
       std::uint8_t* qs = stage + (j * token_bytes);
-      StageRow(y, k, qs, reinterpret_cast<float2*>(qs + k), tid, threads);
+      StageRow(y, k, qs, reinterpret_cast<float2*>(qs + StagedScales(k)), tid, threads);
     }
     __syncthreads();
 
@@ -398,9 +404,9 @@ VecQKernel(const Desc a) {
           for (int j = 0; j < P; ++j) {
             if (j < m_live) {
               const std::uint8_t* qs = stage + (j * token_bytes);
-              const uint4* av = reinterpret_cast<const uint4*>(qs + (u * 64));
+              const uint4* av = reinterpret_cast<const uint4*>(qs + (u * 80));
               const uint4 a4[4] = {av[0], av[1], av[2], av[3]};
-              const float4 s4 = *reinterpret_cast<const float4*>(qs + k + (u * 16));
+              const float4 s4 = *reinterpret_cast<const float4*>(qs + StagedScales(k) + (u * 16));
 #pragma unroll
               for (int r = 0; r < R; ++r)
 #pragma unroll
@@ -422,11 +428,12 @@ VecQKernel(const Desc a) {
           for (int j = 0; j < P; ++j) {
             if (j < m_live) {
               const std::uint8_t* qs = stage + (j * token_bytes);
-              const uint4* av = reinterpret_cast<const uint4*>(qs + (u * Unit::kUnitElems));
-              const float2* sv = reinterpret_cast<const float2*>(qs + k) + (u * kB);
+              const float2* sv = reinterpret_cast<const float2*>(qs + StagedScales(k)) + (u * kB);
 #pragma unroll
               for (int b = 0; b < kB; ++b) {
-                const uint4 x0 = av[2 * b], x1 = av[2 * b + 1];
+                const uint4* av =
+                    reinterpret_cast<const uint4*>(qs + StagedAt((u * Unit::kUnitElems) + (32 * b)));
+                const uint4 x0 = av[0], x1 = av[1];
                 const float d8 = sv[b].x;
                 const int xs[8] = {static_cast<int>(x0.x), static_cast<int>(x0.y),
                                    static_cast<int>(x0.z), static_cast<int>(x0.w),
