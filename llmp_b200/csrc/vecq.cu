@@ -334,13 +334,17 @@ int LaunchVecQ(int type, const llmp_b200_vecq_desc* desc, int variant, bool f32_
   const bool aligned16 = Aligned(d.w, 16) && (d.g == nullptr || Aligned(d.g, 16));
   if (variant >= kRowMmaVariant) {
     RowMmaPlan tiles{};
-    const int ctas = variant == kRowMmaVariant ? 1 : kVariants[variant].u;
+    const int ctas = kVariants[variant].u == 0 ? 1 : kVariants[variant].u;
+    const bool token_columns = kVariants[variant].r == 8;
+    if (token_columns && d.tokens < 2) {
+      return Reject("vecq: the token-column rowmma variants take 2 to 8 tokens");
+    }
     if (!(dense && q4 && aligned16 && f32_input == false && q8_dst == nullptr &&
-          PlanRowMma(d, p, SmCount(), &tiles, ctas))) {
+          PlanRowMma(d, token_columns ? 8 : p, SmCount(), &tiles, ctas, token_columns))) {
       return Reject("vecq: the rowmma variant takes dense Q4_K products of up to 8 tokens");
     }
     if (fan != nullptr) tiles.fan = *fan;
-    e = LaunchRowMma(d, p, tiles, s);
+    e = token_columns ? LaunchRowMmaTokens(d, tiles, s) : LaunchRowMma(d, p, tiles, s);
     if (e != cudaSuccess) return Failed(e, "vecq rowmma launch");
     return 0;
   }

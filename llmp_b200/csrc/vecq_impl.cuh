@@ -528,11 +528,15 @@ constexpr Variant kVariants[] = {
     {"rowmma.c2", 0, 0, 2, 0},
     {"rowmma.c3", 0, 0, 3, 0},
     {"rowmma.c4", 0, 0, 4, 0},
+    // The MMA's columns are the tokens (r field = 8): eight MMAs a super-block for up to eight
+    // tokens; 2 to 8 tokens.
+    {"rowmma.t8", 0, 8, 0, 0},
+    {"rowmma.t8c2", 0, 8, 2, 0},
 };
 constexpr int kVariantCount = static_cast<int>(sizeof(kVariants) / sizeof(kVariants[0]));
-constexpr int kStreamVariant = kVariantCount - 13;
-constexpr int kRowLaneVariant = kVariantCount - 12;  // and its seven forced forms after it
-constexpr int kRowMmaVariant = kVariantCount - 4;    // and its three split forms after it
+constexpr int kStreamVariant = kVariantCount - 15;
+constexpr int kRowLaneVariant = kVariantCount - 14;  // and its seven forced forms after it
+constexpr int kRowMmaVariant = kVariantCount - 6;    // its three split forms and the two token-column forms after it
 
 template <typename Unit, int P, int LPR, int R, int U, bool kGlu>
 cudaError_t LaunchOne(const Desc& d, int warps, cudaStream_t stream) {

@@ -30,5 +30,9 @@ cudaError_t LaunchRowMma(const Desc& d, int p, const RowMmaPlan& plan, cudaStrea
 #undef LLMP_P
   return cudaErrorInvalidValue;
 }
+cudaError_t LaunchRowMmaTokens(const Desc& d, const RowMmaPlan& plan, cudaStream_t stream) {
+  return d.glu != LLMP_B200_GLU_NONE ? LaunchRowMmaTokensOne<true>(d, plan, stream)
+                                     : LaunchRowMmaTokensOne<false>(d, plan, stream);
+}
 }  // namespace vecq
 }  // namespace llmp_b200

@@ -76,9 +76,16 @@ __device__ __forceinline__ void MmaU8S8(int (&c)[4], std::uint32_t a0, std::uint
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int P, bool kGlu>
+// kTokenColumns (P == 8): the MMA's eight columns are the TOKENS, not the sub-blocks.  One MMA
+// a sub-block takes all (up to eight) tokens at once - eight MMAs a super-block whatever the
+// token count, against eight a token - and the fragment hands lane (g, t) the sums of rows g
+// and g + 8 for tokens 2t and 2t + 1: it folds all eight sub-blocks itself, in order, and no
+// lanes have to meet.  (A token's F32 bits then differ from the one-token kernels': the order
+// of the sub-blocks' terms is another.)
+template <int P, bool kGlu, bool kTokenColumns = false>
 __global__ void __launch_bounds__(RowMmaWarpLimit(P) * 32, 1)
 VecQRowMmaKernel(const Desc a, const RowMmaPlan plan) {
+  static_assert(!kTokenColumns || P == 8, "token columns: eight tokens a pass");
   constexpr int kMats = kGlu ? 2 : 1;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) std::uint64_t full[kRowMmaMaxTiles];
@@ -201,6 +208,88 @@ VecQRowMmaKernel(const Desc a, const RowMmaPlan plan) {
 #pragma unroll
           for (int p = 0; p < P; ++p) acc[m][h][p] = 0.0f;
 
+      if constexpr (kTokenColumns) {
+        // lane (g, t): column g of B is token g; its results are tokens 2t and 2t + 1
+        const unsigned char* b_tok =
+            acts + (static_cast<std::size_t>(min(g, a.tokens - 1)) * plan.acts_bytes);
+        const float2* sc_a = reinterpret_cast<const float2*>(
+            acts + (static_cast<std::size_t>(min(2 * t, a.tokens - 1)) * plan.acts_bytes) +
+            (static_cast<std::size_t>(UR) * 256));
+        const float2* sc_b = reinterpret_cast<const float2*>(
+            acts + (static_cast<std::size_t>(min((2 * t) + 1, a.tokens - 1)) * plan.acts_bytes) +
+            (static_cast<std::size_t>(UR) * 256));
+        float sums[kMats][2][2];  // [matrix][row g / g + 8][token 2t / 2t + 1]
+#pragma unroll
+        for (int m = 0; m < kMats; ++m)
+#pragma unroll
+          for (int h = 0; h < 2; ++h) sums[m][h][0] = sums[m][h][1] = 0.0f;
+        for (int c = wc; c < UR; c += plan.col_groups) {
+          uint2 bq[8];
+#pragma unroll
+          for (int sb = 0; sb < 8; ++sb) {
+            bq[sb] = *reinterpret_cast<const uint2*>(b_tok + (((c * 8) + sb) * 32) + (8 * t));
+          }
+#pragma unroll
+          for (int m = 0; m < kMats; ++m) {
+            const unsigned char* lo_row =
+                rows_at + ((static_cast<std::size_t>(m) * plan.pass_rows + r_lo) * plan.pitch) + (c * 144);
+            const unsigned char* hi_row =
+                rows_at + ((static_cast<std::size_t>(m) * plan.pass_rows + r_hi) * plan.pitch) + (c * 144);
+            const uint4 h0 = *reinterpret_cast<const uint4*>(lo_row);
+            const uint4 h1 = *reinterpret_cast<const uint4*>(hi_row);
+            float pr[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}}, mr[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {
+              const uint2 x = *reinterpret_cast<const uint2*>(lo_row + 16 + (cc * 32) + (8 * t));
+              const uint2 y = *reinterpret_cast<const uint2*>(hi_row + 16 + (cc * 32) + (8 * t));
+              int even[4] = {0, 0, 0, 0}, odd[4] = {0, 0, 0, 0};
+              MmaU8S8(even, x.x & 0x0f0f0f0fu, y.x & 0x0f0f0f0fu, x.y & 0x0f0f0f0fu, y.y & 0x0f0f0f0fu,
+                      bq[2 * cc].x, bq[2 * cc].y);
+              MmaU8S8(odd, x.x & 0xf0f0f0f0u, y.x & 0xf0f0f0f0u, x.y & 0xf0f0f0f0u, y.y & 0xf0f0f0f0u,
+                      bq[(2 * cc) + 1].x, bq[(2 * cc) + 1].y);
+              std::uint32_t sc0, mn0, sc1, mn1;
+              Q4KScalePair(h0.y, h0.z, h0.w, cc, &sc0, &mn0);
+              Q4KScalePair(h1.y, h1.z, h1.w, cc, &sc1, &mn1);
+              const int scale[2][2] = {{static_cast<int>(sc0 & 0xffu), static_cast<int>(sc0 >> 8)},
+                                       {static_cast<int>(sc1 & 0xffu), static_cast<int>(sc1 >> 8)}};
+              const float minimum[2][2] = {{static_cast<float>(mn0 & 0xffu), static_cast<float>(mn0 >> 8)},
+                                           {static_cast<float>(mn1 & 0xffu), static_cast<float>(mn1 >> 8)}};
+              // sub-blocks 2cc and 2cc + 1, in that order: d8 * (sc * dot) and (d8 * sum q) * m
+#pragma unroll
+              for (int o = 0; o < 2; ++o) {
+                const float2 ta = sc_a[(c * 8) + (2 * cc) + o], tb = sc_b[(c * 8) + (2 * cc) + o];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                  const int da = o == 0 ? even[2 * h] : (odd[2 * h] >> 4);
+                  const int db = o == 0 ? even[(2 * h) + 1] : (odd[(2 * h) + 1] >> 4);
+                  pr[h][0] = fmaf(ta.x, static_cast<float>(da * scale[h][o]), pr[h][0]);
+                  pr[h][1] = fmaf(tb.x, static_cast<float>(db * scale[h][o]), pr[h][1]);
+                  mr[h][0] = fmaf(ta.y, minimum[h][o], mr[h][0]);
+                  mr[h][1] = fmaf(tb.y, minimum[h][o], mr[h][1]);
+                }
+              }
+            }
+            const float d0 = HalfBitsToFloat(h0.x & 0xffffu), dm0 = HalfBitsToFloat(h0.x >> 16);
+            const float d1 = HalfBitsToFloat(h1.x & 0xffffu), dm1 = HalfBitsToFloat(h1.x >> 16);
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              sums[m][0][j] += (d0 * pr[0][j]) - (dm0 * mr[0][j]);
+              sums[m][1][j] += (d1 * pr[1][j]) - (dm1 * mr[1][j]);
+            }
+          }
+        }
+        // a lane's sums are whole: rows g, g + 8 x tokens 2t, 2t + 1 of this column group
+#pragma unroll
+        for (int m = 0; m < kMats; ++m)
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const int r = (tile * 16) + g + (8 * h);
+              partial[(((static_cast<std::size_t>(wc) * plan.pass_pad + r) * P + (2 * t) + j) * kMats) + m] =
+                  sums[m][h][j];
+            }
+      } else {
       for (int c = wc; c < UR; c += plan.col_groups) {
         // The token's B fragments for this column when there is one token: built
         // once, used for both matrices.
@@ -295,6 +384,7 @@ VecQRowMmaKernel(const Desc a, const RowMmaPlan plan) {
             }
           }
     }
+      }
     // every column group's partial sums of the pass are written; a wait that ran out
     // anywhere in the CTA ends it for all: nothing of an incomplete pass is stored
     if (__syncthreads_or(healthy ? 0 : 1) != 0) return;
@@ -328,7 +418,8 @@ VecQRowMmaKernel(const Desc a, const RowMmaPlan plan) {
 
 // Host: the geometry, or false if the product does not fit (k too long for one
 // 16-row tile a pass).
-inline bool PlanRowMma(const Desc& d, int p, int sms, RowMmaPlan* plan, int ctas_per_sm = 1) {
+inline bool PlanRowMma(const Desc& d, int p, int sms, RowMmaPlan* plan, int ctas_per_sm = 1,
+                       bool token_columns = false) {
   const int mats = d.glu != LLMP_B200_GLU_NONE ? 2 : 1;
   const int ur = d.ncols_x / 256;
   if (ur < 1) return false;
@@ -342,7 +433,10 @@ inline bool PlanRowMma(const Desc& d, int p, int sms, RowMmaPlan* plan, int ctas
   // A pitch that spreads rows g = 0..7 over the banks for 64-bit loads: 32 or 96 mod 128.
   const bool good = (row_bytes % 128 == 32) || (row_bytes % 128 == 96);
   const int pitch = (contiguous && good) ? row_bytes : ((row_bytes + 127) / 128 * 128) + 32;
-  const int acts_bytes = (ur * 256) + (ur * 8 * 8);
+  // (token columns: lanes of eight different tokens read at once; a token pitch of 32 bytes
+  // mod 128 keeps their 64-bit loads on different banks)
+  const int acts_bytes = token_columns ? ((((ur * 256) + (ur * 8 * 8)) + 127) / 128 * 128) + 32
+                                       : (ur * 256) + (ur * 8 * 8);
   const int budget = (218 * 1024 / ctas_per_sm) - (p * acts_bytes) - 2048;
   if (budget <= 0) return false;
   // Warps: column groups x tile groups.  The column split fixes the order a row's
@@ -408,7 +502,25 @@ cudaError_t LaunchRowMmaOne(const Desc& d, const RowMmaPlan& plan, cudaStream_t 
                    static_cast<std::size_t>(plan.smem_bytes), stream, d, plan);
 }
 
+template <bool kGlu>
+cudaError_t LaunchRowMmaTokensOne(const Desc& d, const RowMmaPlan& plan, cudaStream_t stream) {
+  auto* kernel = VecQRowMmaKernel<8, kGlu, true>;
+  static thread_local int configured_device = -1;
+  int device = -1;
+  cudaGetDevice(&device);
+  if (configured_device != device) {
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               220 * 1024);
+    if (e != cudaSuccess) return e;
+    configured_device = device;
+  }
+  return LaunchPdl(kernel, dim3(static_cast<unsigned>(plan.grid)),
+                   dim3(static_cast<unsigned>(plan.warps * 32)),
+                   static_cast<std::size_t>(plan.smem_bytes), stream, d, plan);
+}
+
 cudaError_t LaunchRowMma(const Desc& d, int p, const RowMmaPlan& plan, cudaStream_t stream);
+cudaError_t LaunchRowMmaTokens(const Desc& d, const RowMmaPlan& plan, cudaStream_t stream);
 
 }  // namespace vecq
 }  // namespace llmp_b200

@@ -400,6 +400,44 @@ def test_rowmma_matches_the_oracle_and_keeps_a_token_alone(cuda, orc, n, k, toke
         assert torch.equal(alone[0], out[j])
 
 
+@pytest.mark.parametrize("variant", ["rowmma.t8", "rowmma.t8c2"])
+@pytest.mark.parametrize("n,k,tokens,glu", [(10240, 2560, 8, 3), (2560, 10240, 8, 0), (333, 2560, 3, 1),
+                                            (41, 512, 2, 0), (5000, 7168, 5, 1), (1000, 4096, 7, 0)])
+def test_token_column_rowmma_matches_the_oracle(cuda, orc, variant, n, k, tokens, glu):
+    """The kernel whose MMA columns are the tokens (eight MMAs a super-block for up to eight
+    tokens): against the oracle, and a token's bits do not depend on the tokens beside it."""
+    torch = cuda
+    ops = _ops()
+    rng = np.random.default_rng(n + k + tokens)
+    v = ops.vecq_variants().index(variant)
+    w = synth.q4_k_weights(rng, n, k)
+    g = synth.q4_k_weights(rng, n, k) if glu else None
+    x = rng.normal(0, 1, size=(tokens, k)).astype(np.float32)
+    q8 = ops.quantize_q8(to_dev(torch, x))
+    wd, gd = to_dev(torch, w), (to_dev(torch, g) if glu else None)
+    buf = torch.full((tokens * n + 32,), float("nan"), device="cuda")
+    out = buf[: tokens * n].view(tokens, n)
+    try:
+        ops.vecq(wd, orc.Q4_K, k, n, q8, tokens, gate=gd, glu=glu, out=out, variant=v)
+    except ops.Rejected:
+        pytest.skip(f"{variant} does not take this shape (its share of the rows does not fit half an SM)")
+    torch.cuda.synchronize()
+    assert ops.device_faults() == 0
+    assert torch.isnan(buf[tokens * n:]).all() and torch.isfinite(out).all()
+    if glu:
+        want = orc.vecq(orc.Q4_K, w, q8.cpu().numpy(), k, n, tokens, g=g, glu=glu)[:, 0, :]
+        assert np.abs(out.cpu().numpy() - want).max() <= 4e-5 * np.abs(want).max()
+    else:
+        f32, s64, a64 = orc.vecq(orc.Q4_K, w, q8.cpu().numpy(), k, n, tokens, want64=True)
+        assert_close_to_f64(out.cpu().numpy(), f32[:, 0, :], s64[:, 0, :], a64[:, 0, :], variant)
+    if tokens > 2:
+        pair = ops.vecq(wd, orc.Q4_K, k, n, ops.quantize_q8(to_dev(torch, x[tokens - 2:])), 2, gate=gd,
+                        glu=glu, variant=v)
+        assert torch.equal(pair, out[tokens - 2:])
+    with pytest.raises(ops.Rejected):
+        ops.vecq(wd, orc.Q4_K, k, n, ops.quantize_q8(to_dev(torch, x[:1])), 1, gate=gd, glu=glu, variant=v)
+
+
 def test_rank_table_names_configurations_the_library_has(cuda, orc):
     """Every row of the measured rank table names a launch configuration that exists, and
     the default launch of a listed product gives the oracle's result."""
