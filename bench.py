@@ -535,7 +535,7 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
 
 
 def _q8_0_roofline(torch, ops, stream, use_graph, repeats):
-    """BASELINE configs[0]: Q8_0 4096 x 4096, batch 1; 16 weight copies (285 MB) walked in
+    """the benchmark specification's config 0: Q8_0 4096 x 4096, batch 1; 16 weight copies (285 MB) walked in
     order inside one captured graph."""
     import numpy as np
 
@@ -562,7 +562,7 @@ def _q8_0_roofline(torch, ops, stream, use_graph, repeats):
 
 # --------------------------------------------------------------------------- other configs
 def run_other(args):
-    """The other BASELINE configs' kernels, one JSON line each (not the headline
+    """The other benchmark configs' kernels, one JSON line each (not the headline
     bench line; parity cases that also serve as small, committed ncu drivers).
     Operands rotate over two copies so that a launch's inputs are not L2-resident."""
     import torch
@@ -612,7 +612,7 @@ def run_other(args):
                              "frac": round(rate / peaks["mxf8f6f4"], 4),
                              "peak_source": "bare tcgen05.mma loop measured on this pool"}}
     elif args.workload == "q8_0_gemv":
-        # BASELINE configs[0]: Q8_0 4096 x 4096, batch 1 (the reference's CPU-runnable case);
+        # the benchmark specification's config 0: Q8_0 4096 x 4096, batch 1 (the reference's CPU-runnable case);
         # 16 weight copies (285 MB) walked in order inside one captured graph.
         import numpy as np
 
@@ -742,7 +742,7 @@ def _all_true(torch, dist, flag: bool) -> bool:
 
 
 def bench_mmq_sharded(torch, dist, ops, rank, world, tokens=4096, steps=10, warmup=3, chunks=4):
-    """The prefill GEMM N-column sharded (BASELINE configs[2]).  Every rank holds the weight
+    """The prefill GEMM N-column sharded (the benchmark specification's config 2).  Every rank holds the weight
     rows [rank * n / world, +n / world) (relaid into its slab at load time) and the whole
     activation batch, which it quantizes itself; the product runs in `chunks` token chunks,
     and each chunk's F32 slice is all-gathered over NVLink (NCCL) while the next chunk's
@@ -825,7 +825,7 @@ def bench_mmq_sharded(torch, dist, ops, rank, world, tokens=4096, steps=10, warm
 
 
 def bench_moe_ep(torch, dist, ops, rank, world, tokens=1024, steps=10, warmup=3):
-    """Expert-parallel MoE block (BASELINE configs[4]): each rank owns 128 / world whole experts
+    """Expert-parallel MoE block (the benchmark specification's config 4): each rank owns 128 / world whole experts
     (relaid into slabs at load time) and `tokens` tokens (weak scaling); rows travel to their
     experts' owners and back in NCCL all-to-alls of fixed size (llmp_b200.moe_ep_pack packs
     lanes of a set capacity, so no split size reaches the host) and are combined on the home
