@@ -651,6 +651,48 @@ def run_other(args):
                 "config": {"workload": "Q8_0 decode GEMV 4096 x 4096, batch 1, 16 rotating copies"},
                 "roofline": {"bound": "hbm", "achieved": round(rate, 1), "peak": peak, "unit": "GB/s",
                              "frac": round(rate / peak, 4), "bytes_per_launch": nbytes}}
+    elif args.workload == "decode_vector":
+        # The decode module's vector product (F32 activations, the reference's summation
+        # order): Q8_0 4096 x 4096, one activation row, 16 weight copies walked in order
+        # inside one captured graph.
+        import numpy as np
+
+        from llmp_b200 import synth
+        n = k = 4096
+        rng = np.random.default_rng(0)
+        ws = [torch.from_numpy(synth.q8_0_weights(rng, n, k)).cuda() for _ in range(16)]
+        x = torch.randn((1, k), device="cuda", generator=gen)
+        out = torch.empty((1, n), device="cuda")
+
+        def body():
+            for w in ws:
+                ops.decode_vector(ops.DECODER_Q8_0, w, x, k, n, out=out)
+
+        fns = [body]
+        if not args.no_graph:
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                body()
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    body()
+            torch.cuda.synchronize()
+            fns = [graph.replay]
+        ms = timed(fns, args.steps, args.warmup) / len(ws)
+        nbytes = 17_825_792 + 16_384 + 16_384
+        rate = nbytes / (ms * 1e-3) / 1e9
+        peak = 6535.7
+        try:
+            peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"])
+        except (OSError, KeyError, ValueError):
+            pass
+        line = {"metric": "q8_0_decode_vector_hbm_throughput", "value": round(rate, 1), "unit": "GB/s",
+                "ms_per_step": round(ms, 6),
+                "config": {"workload": "decode-module vector product, Q8_0 4096 x 4096, F32 activations, "
+                                       "one row, 16 rotating copies"},
+                "roofline": {"bound": "hbm", "achieved": round(rate, 1), "peak": peak, "unit": "GB/s",
+                             "frac": round(rate / peak, 4), "bytes_per_launch": nbytes}}
     elif args.workload == "mmq_q4k":
         m, n, k = args.tokens or 4096, 14336, 4096
         x = torch.randn((m, k), device="cuda", generator=gen).bfloat16()
@@ -1162,7 +1204,7 @@ def main():
                     help="distinct layer copies a step walks (34: the model's; fewer for a small "
                          "ncu capture, keep >= 4 so the weights exceed L2)")
     ap.add_argument("--workload", default="ffn_q4k",
-                    choices=["ffn_q4k", "q8_0_gemv", "mxfp8_gemm", "mmq_q4k", "moe"],
+                    choices=["ffn_q4k", "q8_0_gemv", "decode_vector", "mxfp8_gemm", "mmq_q4k", "moe"],
                     help="ffn_q4k is the bench line; the others time the other configs' kernels")
     ap.add_argument("--tokens", type=int, default=0,
                     help="tokens / rows of the other workloads")

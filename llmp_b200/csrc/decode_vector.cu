@@ -13,19 +13,20 @@
 //
 //   * persistent CTAs, one an SM, each owning a contiguous run of output rows
 //     that its warps split; a warp walks its rows one at a time;
-//   * a row's bytes (both matrices' with a GLU) arrive in the warp's PRIVATE
-//     ring of shared-memory stages by the bulk-copy engine (cp.async.bulk
-//     completing on the stage's mbarrier), several rows ahead of the one being
-//     summed, and the first of them are requested before the programmatic-
-//     dependency wait: weights depend on no earlier kernel.  Warps never
-//     synchronize with each other after the activations are staged;
+//   * a row's bytes (both matrices' with a GLU; two rows at a time for up to
+//     four activation rows) arrive chunk by chunk in the warp's PRIVATE ring of
+//     shared-memory stages by the bulk-copy engine (cp.async.bulk completing on
+//     the stage's mbarrier), several chunks ahead of the one being summed, and
+//     the first of them are requested before the programmatic-dependency wait:
+//     weights depend on no earlier kernel.  Warps never synchronize with each
+//     other after the activations are staged;
 //   * a lane reads its segment out of the staged row with the widest aligned
 //     shared load the encoding allows (Q8_0's 34-byte blocks put a segment on a
 //     2-byte boundary: five aligned words and a funnel shift);
 //   * the activation rows are staged once a CTA when they fit, else read
 //     through L1;
-//   * rows that are not 16-byte aligned (Q8_0 only promises 2), or too long for
-//     the ring, are read in place with the loads their alignment allows.
+//   * rows that are not 16-byte aligned (Q8_0 only promises 2) are read in place
+//     with the loads their alignment allows.
 // Every mbarrier wait is bounded; a wait that runs out raises the device fault
 // counter and the warp stores nothing more.
 #include <cuda_bf16.h>
@@ -33,6 +34,7 @@
 #include <cuda_fp8.h>
 
 #include <algorithm>
+#include <type_traits>
 
 #include "common.cuh"
 #include "tc.cuh"
@@ -43,9 +45,9 @@ namespace {
 using Operand = llmp_b200_decode_operand;
 
 constexpr int kMaxWarps = 16;
-constexpr int kMaxStages = 4;
+constexpr int kMaxStages = 8;
 constexpr int kRingBudget = 144 * 1024;
-constexpr int kActsBudget = 64 * 1024;
+constexpr int kActsBudget = 80 * 1024;
 
 struct Args {
   Operand w, w2;
@@ -60,8 +62,17 @@ struct Args {
 
 struct Plan {
   int grid, warps, stages;
-  std::uint32_t copy_bytes;   // a row's bytes as the bulk copy moves them (0: rows are read in place)
-  std::uint32_t stage_bytes;  // one stage: copy_bytes x matrices, 16-byte multiples
+  // The split of the outputs: CTA b owns rows_q + (b < rows_rem) of them, and a CTA
+  // of span rows_q + e gives warp w warp_q[e] + (w < warp_rem[e]); no division runs
+  // on the device.
+  std::uint32_t rows_q, rows_rem, warp_q[2], warp_rem[2];
+  int group;                  // weight rows summed together (a stage holds them all): 1 or 2
+  std::uint32_t row_bytes;    // a row's code bytes
+  std::uint32_t copy_bytes;   // a chunk: the bytes of chunk_segs segments of one row, as one bulk
+                              // copy moves them (0: rows are read in place); the last may be shorter
+  std::uint32_t chunk_segs;   // segments a chunk: a multiple of 32 (whole rounds of the lanes)
+  std::uint32_t chunks;       // chunks a row
+  std::uint32_t stage_bytes;  // one stage: copy_bytes x matrices x group, 16-byte multiples
   std::uint32_t acts_bytes;   // the staged activations (0: read through L1)
   unsigned int* faults;
 };
@@ -94,6 +105,33 @@ __host__ __device__ constexpr std::uint64_t AtomAt(std::uint64_t row, std::uint6
          (((row % 128) / 32) * 4) + (block % 4);
 }
 
+// Loads from a shared-memory ADDRESS.  A pointer that is global memory on one
+// path and shared memory on another compiles to generic loads, which queue with
+// the global ones; the staged paths therefore carry 32-bit shared addresses.
+__device__ __forceinline__ std::uint32_t SharedU16(std::uint32_t at) {
+  std::uint32_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(at));
+  return v;
+}
+template <int kOffset = 0>
+__device__ __forceinline__ std::uint32_t SharedU32(std::uint32_t at) {
+  std::uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(at), "n"(kOffset));
+  return v;
+}
+__device__ __forceinline__ uint2 SharedU64(std::uint32_t at) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(at));
+  return v;
+}
+template <int kOffset = 0>
+__device__ __forceinline__ uint4 SharedU128(std::uint32_t at) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4+%5];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(at), "n"(kOffset));
+  return v;
+}
+
 // ---------------------------------------------------------------- decoders
 // Bytes of a row's codes that hold one 16-value segment, per decoder.
 __host__ __device__ constexpr int SegmentBytesX2(int decoder) {  // twice the bytes (Q8_0: 17)
@@ -103,123 +141,227 @@ __host__ __device__ constexpr int SegmentBytesX2(int decoder) {  // twice the by
                                                                                                    : 16;
 }
 
-// Segment `seg` of a row whose code bytes start at `codes` (shared memory when
-// `staged`, 16-byte aligned there; else global memory with the alignment the
-// entry point checked) into v[16], each value decoded exactly as the reference's
-// decoder does (decoders.cuh: code times block scale, exact in F32).
-template <int kDecoder>
-__device__ __forceinline__ void LoadSegment(const Operand& p, const std::uint8_t* codes, bool staged,
-                                            std::uint32_t row, std::uint32_t seg, float (&v)[16]) {
+// One 16-value segment as it is stored: the code words and the block's scale.
+struct Raw {
+  std::uint32_t w[8];  // Q8_0: 4 words of int8; MXFP8: 4 of E4M3; dense: 8 of two 16-bit values; FP4: 2 of E2M1
+  float scale;         // d, the E8M0 or the UE4M3 value; unused by the dense encodings
+};
+
+// Raw segment to v[16], each value decoded exactly as the reference's decoder does
+// (decoders.cuh: code times block scale, exact in F32).  kSummed: the values only
+// feed sums that start at +0, so a zero's sign is free.
+template <int kDecoder, bool kSummed>
+__device__ __forceinline__ void Expand(const Raw& raw, float (&v)[16]) {
   if constexpr (kDecoder == LLMP_B200_DECODER_Q8_0_BLOCKS) {
-    // Half a 34-byte block: d at byte 34 b, the segment's 16 int8 at 34 b + 2 + 16 h.
-    const std::uint32_t at = ((seg >> 1) * 34u) + 2u + ((seg & 1u) * 16u);
-    std::uint32_t q[4];
-    float d;
-    if (staged) {
-      // five aligned words cover the 16 bytes; they start two bytes in when at % 4 == 2
-      const auto* words = reinterpret_cast<const std::uint32_t*>(codes + (at & ~3u));
-      const std::uint32_t w0 = words[0], w1 = words[1], w2 = words[2], w3 = words[3];
-      const std::uint32_t shift = (at & 2u) * 8u;
-      const std::uint32_t w4 = shift != 0 ? words[4] : 0u;
-      q[0] = __funnelshift_r(w0, w1, shift);
-      q[1] = __funnelshift_r(w1, w2, shift);
-      q[2] = __funnelshift_r(w2, w3, shift);
-      q[3] = __funnelshift_r(w3, w4, shift);
-      d = HalfBitsToFloat(*reinterpret_cast<const unsigned short*>(codes + ((seg >> 1) * 34u)));
-    } else {
-      const auto* h = reinterpret_cast<const unsigned short*>(codes + at);
+    const float d = raw.scale;
+    if constexpr (kSummed) {
+      // d b in one fused multiply-add a value, without the conversion unit: b + 128
+      // goes into bits 8-15 of 1.0f, which reads 1 + (b + 128) 2^-15, and
+      // (2^15 d) (1 + (b + 128) 2^-15) - (1 + 2^-8) (2^15 d) = d b.  Both constants
+      // are exact (a half's 11 significant bits times 257 is 20 bits) and so is the
+      // result (19 bits): the bits of d times float(b) for every finite d, but for
+      // b = 0 under a negative d, which gives +0 here and -0 there; a sum that
+      // starts at +0 is the same with either.
+      const float ds = d * 32768.0f, offset = ds * -1.00390625f;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        q[i] = static_cast<std::uint32_t>(__ldg(h + (2 * i))) |
-               (static_cast<std::uint32_t>(__ldg(h + (2 * i) + 1)) << 16);
+      for (int i = 0; i < 16; ++i) {
+        const std::uint32_t bits =
+            __byte_perm(raw.w[i / 4] ^ 0x80808080u, 0x3F800000u, 0x7604u | ((i % 4) << 4));
+        v[i] = fmaf(__uint_as_float(bits), ds, offset);
       }
-      d = HalfBitsToFloat(__ldg(reinterpret_cast<const unsigned short*>(codes + ((seg >> 1) * 34u))));
-    }
+    } else {
+      // b + 128 as the low mantissa byte of 2^23, minus (2^23 + 128), times d: exact
+      // steps that keep the sign of a zero.
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      v[i] = d * static_cast<float>(static_cast<std::int8_t>((q[i / 4] >> (8 * (i % 4))) & 0xffu));
+      for (int i = 0; i < 16; ++i) {
+        const std::uint32_t bits = __byte_perm(raw.w[i / 4] ^ 0x80808080u, 0x4B000000u, 0x7440u | (i % 4));
+        v[i] = d * (__uint_as_float(bits) - 8388736.0f);
+      }
     }
   } else if constexpr (kDecoder == LLMP_B200_DECODER_MXFP8_SPLIT ||
                        kDecoder == LLMP_B200_DECODER_MXFP8_ATOMS) {
-    const auto* scales = static_cast<const std::uint8_t*>(p.scales);
-    const std::uint32_t blocks = p.k / 32;
-    const float s = E8m0(__ldg(scales + (kDecoder == LLMP_B200_DECODER_MXFP8_SPLIT
-                                             ? (static_cast<std::uint64_t>(row) * blocks) + (seg >> 1)
-                                             : AtomAt(row, seg >> 1, blocks))));
-    const auto* src = reinterpret_cast<const uint4*>(codes + (seg * 16u));
-    const uint4 c = staged ? *src : __ldg(src);
-    const std::uint32_t w[4] = {c.x, c.y, c.z, c.w};
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       // two E4M3 bytes to two halves (exact), then to F32
       const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(
-          static_cast<__nv_fp8x2_storage_t>((w[i / 2] >> (16 * (i % 2))) & 0xffffu), __NV_E4M3);
-      v[2 * i] = __half2float(__ushort_as_half(h.x)) * s;
-      v[(2 * i) + 1] = __half2float(__ushort_as_half(h.y)) * s;
+          static_cast<__nv_fp8x2_storage_t>((raw.w[i / 2] >> (16 * (i % 2))) & 0xffffu), __NV_E4M3);
+      v[2 * i] = __half2float(__ushort_as_half(h.x)) * raw.scale;
+      v[(2 * i) + 1] = __half2float(__ushort_as_half(h.y)) * raw.scale;
     }
   } else if constexpr (kDecoder == LLMP_B200_DECODER_BF16_DENSE ||
                        kDecoder == LLMP_B200_DECODER_F16_DENSE) {
-    const auto* src = reinterpret_cast<const uint4*>(codes + (seg * 32u));
-    const uint4 c0 = staged ? src[0] : __ldg(src);
-    const uint4 c1 = staged ? src[1] : __ldg(src + 1);
-    const std::uint32_t w[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       if constexpr (kDecoder == LLMP_B200_DECODER_BF16_DENSE) {
-        v[2 * i] = __uint_as_float(w[i] << 16);
-        v[(2 * i) + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        v[2 * i] = __uint_as_float(raw.w[i] << 16);
+        v[(2 * i) + 1] = __uint_as_float(raw.w[i] & 0xffff0000u);
       } else {
-        v[2 * i] = HalfBitsToFloat(w[i] & 0xffffu);
-        v[(2 * i) + 1] = HalfBitsToFloat(w[i] >> 16);
+        v[2 * i] = HalfBitsToFloat(raw.w[i] & 0xffffu);
+        v[(2 * i) + 1] = HalfBitsToFloat(raw.w[i] >> 16);
       }
     }
   } else {
-    // E2M1 codes, value 2 i in byte i's low nibble: NVFP4 (a UE4M3 scale a segment)
-    // or MXFP4 (an E8M0 scale two segments), scales row-major or in scale atoms.
-    const auto* scales = static_cast<const std::uint8_t*>(p.scales);
-    constexpr bool kNv = kDecoder == LLMP_B200_DECODER_NVFP4_SPLIT ||
-                         kDecoder == LLMP_B200_DECODER_NVFP4_ATOMS;
-    constexpr bool kAtoms = kDecoder == LLMP_B200_DECODER_NVFP4_ATOMS ||
-                            kDecoder == LLMP_B200_DECODER_MXFP4_ATOMS;
-    const std::uint32_t blocks = kNv ? p.k / 16 : p.k / 32;
-    const std::uint32_t block = kNv ? seg : seg >> 1;
-    const std::uint32_t code = __ldg(scales + (kAtoms ? AtomAt(row, block, blocks)
-                                                      : (static_cast<std::uint64_t>(row) * blocks) + block));
-    const float s = kNv ? Ue4m3(code) : E8m0(code);
-    const auto* src = reinterpret_cast<const uint2*>(codes + (seg * 8u));
-    const uint2 c = staged ? *src : __ldg(src);
-    const std::uint32_t w[2] = {c.x, c.y};
+    // E2M1 codes, value 2 i in byte i's low nibble
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const std::uint32_t b = (w[i / 4] >> (8 * (i % 4))) & 0xffu;
-      v[2 * i] = E2m1(b & 15u) * s;
-      v[(2 * i) + 1] = E2m1(b >> 4) * s;
+      const std::uint32_t b = (raw.w[i / 4] >> (8 * (i % 4))) & 0xffu;
+      v[2 * i] = E2m1(b & 15u) * raw.scale;
+      v[(2 * i) + 1] = E2m1(b >> 4) * raw.scale;
     }
   }
 }
 
-// acc[t] += v . x[t, 16 seg ..), one fused multiply-add a value in index order.
-template <int kCols>
-__device__ __forceinline__ void Accumulate(const float* xs, std::uint64_t xs_stride, bool xs_shared,
-                                           std::uint32_t rows, std::uint32_t seg, const float (&w)[16],
-                                           float (&acc)[kCols]) {
+// The block scale of segment `seg` of row `row` for the block-scaled encodings
+// (scales row-major or in scale atoms; NVFP4 a UE4M3 a segment, the MX encodings
+// an E8M0 two segments).
+template <int kDecoder>
+__device__ __forceinline__ float BlockScale(const Operand& p, std::uint32_t row, std::uint32_t seg) {
+  constexpr bool kNv = kDecoder == LLMP_B200_DECODER_NVFP4_SPLIT || kDecoder == LLMP_B200_DECODER_NVFP4_ATOMS;
+  constexpr bool kAtoms = kDecoder == LLMP_B200_DECODER_MXFP8_ATOMS ||
+                          kDecoder == LLMP_B200_DECODER_NVFP4_ATOMS ||
+                          kDecoder == LLMP_B200_DECODER_MXFP4_ATOMS;
+  const auto* scales = static_cast<const std::uint8_t*>(p.scales);
+  const std::uint32_t blocks = kNv ? p.k / 16 : p.k / 32;
+  const std::uint32_t block = kNv ? seg : seg >> 1;
+  const std::uint32_t code = __ldg(scales + (kAtoms ? AtomAt(row, block, blocks)
+                                                    : (static_cast<std::uint64_t>(row) * blocks) + block));
+  return kNv ? Ue4m3(code) : E8m0(code);
+}
+
+__host__ __device__ constexpr bool BlockScaled(int decoder) {
+  return decoder != LLMP_B200_DECODER_Q8_0_BLOCKS && decoder != LLMP_B200_DECODER_BF16_DENSE &&
+         decoder != LLMP_B200_DECODER_F16_DENSE;
+}
+
+// Segment `seg` of a row whose code bytes start at `codes` in global memory, with
+// the alignment the entry point checked (Q8_0 rows only promise two bytes).
+template <int kDecoder>
+__device__ __forceinline__ void FetchGlobal(const Operand& p, const std::uint8_t* codes, std::uint32_t row,
+                                            std::uint32_t seg, Raw& raw) {
+  if constexpr (kDecoder == LLMP_B200_DECODER_Q8_0_BLOCKS) {
+    // Half a 34-byte block: d at byte 34 b, the segment's 16 int8 at 34 b + 2 + 16 h.
+    const std::uint32_t at = ((seg >> 1) * 34u) + 2u + ((seg & 1u) * 16u);
+    const auto* h = reinterpret_cast<const unsigned short*>(codes + at);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      raw.w[i] = static_cast<std::uint32_t>(__ldg(h + (2 * i))) |
+                 (static_cast<std::uint32_t>(__ldg(h + (2 * i) + 1)) << 16);
+    }
+    raw.scale = HalfBitsToFloat(__ldg(reinterpret_cast<const unsigned short*>(codes + ((seg >> 1) * 34u))));
+  } else {
+    constexpr int kBytes = SegmentBytesX2(kDecoder) / 2;  // 16, 32 or 8
+    if constexpr (kBytes == 8) {
+      const uint2 c = __ldg(reinterpret_cast<const uint2*>(codes + (seg * 8u)));
+      raw.w[0] = c.x, raw.w[1] = c.y;
+    } else {
+#pragma unroll
+      for (int i = 0; i < kBytes / 16; ++i) {
+        const uint4 c = __ldg(reinterpret_cast<const uint4*>(codes + (seg * kBytes)) + i);
+        raw.w[4 * i] = c.x, raw.w[(4 * i) + 1] = c.y, raw.w[(4 * i) + 2] = c.z, raw.w[(4 * i) + 3] = c.w;
+      }
+    }
+    if constexpr (BlockScaled(kDecoder)) raw.scale = BlockScale<kDecoder>(p, row, seg);
+  }
+}
+
+// What a lane needs to find its segments lane, lane + 32, ... in a staged row; they
+// are a round's bytes apart (Q8_0: 544, a multiple of 4), so all of this is the
+// lane's own and the loop only moves the round's shared address.
+template <int kDecoder>
+struct StagedLane {
+  std::uint32_t words;  // from the round's address to the segment's first aligned word
+  std::uint32_t last;   // Q8_0: to the fifth word when the codes start two bytes in, else the fourth again
+  std::uint32_t scale;  // Q8_0: to the block's d
+  std::uint32_t shift;  // Q8_0: 16 when the codes start two bytes into their first word
+  __device__ __forceinline__ explicit StagedLane(std::uint32_t lane) {
+    if constexpr (kDecoder == LLMP_B200_DECODER_Q8_0_BLOCKS) {
+      const std::uint32_t odd = lane & 1u;
+      const std::uint32_t at = (17u * lane) + 2u - odd;  // 34 (lane / 2) + 2 + 16 (lane % 2)
+      shift = (at & 2u) * 8u;
+      words = at & ~3u;
+      last = words + (shift != 0 ? 16u : 12u);  // nothing past the segment is touched
+      scale = 17u * (lane - odd);
+    } else {
+      words = lane * (SegmentBytesX2(kDecoder) / 2);
+      last = 0, scale = 0, shift = 0;
+    }
+  }
+};
+__host__ __device__ constexpr std::uint32_t RoundBytes(int decoder) { return 16u * SegmentBytesX2(decoder); }
+
+// The lane's segment of the round staged at shared address `round` (16-byte
+// aligned): the widest aligned shared loads the encoding allows (Q8_0's 34-byte
+// blocks put a segment on a 2-byte boundary: five aligned words and a funnel shift).
+template <int kDecoder>
+__device__ __forceinline__ void FetchStaged(const Operand& p, std::uint32_t round, const StagedLane<kDecoder>& at,
+                                            std::uint32_t row, std::uint32_t seg, Raw& raw) {
+  if constexpr (kDecoder == LLMP_B200_DECODER_Q8_0_BLOCKS) {
+    const std::uint32_t words = round + at.words;
+    const std::uint32_t w0 = SharedU32<0>(words), w1 = SharedU32<4>(words), w2 = SharedU32<8>(words),
+                        w3 = SharedU32<12>(words), w4 = SharedU32<0>(round + at.last);
+    raw.w[0] = __funnelshift_r(w0, w1, at.shift);
+    raw.w[1] = __funnelshift_r(w1, w2, at.shift);
+    raw.w[2] = __funnelshift_r(w2, w3, at.shift);
+    raw.w[3] = __funnelshift_r(w3, w4, at.shift);
+    raw.scale = HalfBitsToFloat(static_cast<unsigned short>(SharedU16(round + at.scale)));
+  } else {
+    constexpr int kBytes = SegmentBytesX2(kDecoder) / 2;
+    const std::uint32_t words = round + at.words;
+    if constexpr (kBytes == 8) {
+      const uint2 c = SharedU64(words);
+      raw.w[0] = c.x, raw.w[1] = c.y;
+    } else {
+      const uint4 c = SharedU128<0>(words);
+      raw.w[0] = c.x, raw.w[1] = c.y, raw.w[2] = c.z, raw.w[3] = c.w;
+      if constexpr (kBytes == 32) {
+        const uint4 c1 = SharedU128<16>(words);
+        raw.w[4] = c1.x, raw.w[5] = c1.y, raw.w[6] = c1.z, raw.w[7] = c1.w;
+      }
+    }
+    if constexpr (BlockScaled(kDecoder)) raw.scale = BlockScale<kDecoder>(p, row, seg);
+  }
+}
+
+// The staged activations: a segment's 64 bytes every 80.  The lanes of a quarter
+// warp read the same quad of eight consecutive segments at once; 64 bytes apart
+// those meet on two 16-byte bank groups, 80 apart they take all eight.
+constexpr std::uint32_t kSegmentPitch = 80;
+__host__ __device__ constexpr std::uint64_t StagedRowBytes(std::uint64_t k) { return (k / 16) * kSegmentPitch; }
+
+// acc[r][t] += w[r] . x[t, 16 seg ..) for the kG weight rows of a group, one fused
+// multiply-add a value in index order; an activation value is read once a group.
+// Quad q (four activations) of row t comes from `quad(t, q)`.
+template <int kCols, int kG, typename Quad>
+__device__ __forceinline__ void Accumulate(std::uint32_t rows, const float (&w)[kG][16],
+                                           float (&acc)[kG][kCols], Quad quad) {
 #pragma unroll
   for (int t = 0; t < kCols; ++t) {
     if (static_cast<std::uint32_t>(t) < rows) {
-      const auto* xp = reinterpret_cast<const float4*>(xs + (static_cast<std::uint64_t>(t) * xs_stride) +
-                                                       (seg * 16u));
-      float s = acc[t];
+      float s[kG];
+#pragma unroll
+      for (int r = 0; r < kG; ++r) s[r] = acc[r][t];
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        const float4 x = xs_shared ? xp[q] : __ldg(xp + q);
-        s = fmaf(w[4 * q], x.x, s);
-        s = fmaf(w[(4 * q) + 1], x.y, s);
-        s = fmaf(w[(4 * q) + 2], x.z, s);
-        s = fmaf(w[(4 * q) + 3], x.w, s);
+        const float4 x = quad(t, q);
+#pragma unroll
+        for (int r = 0; r < kG; ++r) {
+          s[r] = fmaf(w[r][4 * q], x.x, s[r]);
+          s[r] = fmaf(w[r][(4 * q) + 1], x.y, s[r]);
+          s[r] = fmaf(w[r][(4 * q) + 2], x.z, s[r]);
+          s[r] = fmaf(w[r][(4 * q) + 3], x.w, s[r]);
+        }
       }
-      acc[t] = s;
+#pragma unroll
+      for (int r = 0; r < kG; ++r) acc[r][t] = s[r];
     }
   }
+}
+// Quad q of the segment staged at shared address `at` (q a constant after unrolling).
+__device__ __forceinline__ float4 StagedQuad(std::uint32_t at, int q) {
+  const uint4 bits = q == 0 ? SharedU128<0>(at) : q == 1 ? SharedU128<16>(at)
+                     : q == 2 ? SharedU128<32>(at) : SharedU128<48>(at);
+  return make_float4(__uint_as_float(bits.x), __uint_as_float(bits.y), __uint_as_float(bits.z),
+                     __uint_as_float(bits.w));
 }
 
 __device__ __forceinline__ float Butterfly(float v) {
@@ -235,7 +377,7 @@ __device__ __forceinline__ float TensorScale(const Operand& p, std::uint32_t row
   return p.tensor_scale != nullptr ? __ldg(p.tensor_scale + (row / p.rows_per_scale)) : 1.0f;
 }
 
-template <int kDecoder, int kCols, bool kGlu>
+template <int kDecoder, int kCols, bool kGlu, int kG>
 __global__ void __launch_bounds__(kMaxWarps * 32, 1)
 DecodeVectorKernel(const Args a, const Plan plan) {
   constexpr int kMats = kGlu ? 2 : 1;
@@ -248,44 +390,71 @@ DecodeVectorKernel(const Args a, const Plan plan) {
   const bool staged = plan.copy_bytes != 0;
   const int S = plan.stages;
 
-  // This CTA's outputs, then this warp's share of them.
-  const std::uint32_t cta_begin =
-      static_cast<std::uint32_t>((static_cast<std::uint64_t>(blockIdx.x) * a.outputs) / gridDim.x);
-  const std::uint32_t cta_end =
-      static_cast<std::uint32_t>((static_cast<std::uint64_t>(blockIdx.x + 1) * a.outputs) / gridDim.x);
-  const std::uint32_t span = cta_end - cta_begin;
-  const std::uint32_t begin = cta_begin + ((static_cast<std::uint32_t>(warp) * span) / plan.warps);
-  const std::uint32_t end = cta_begin + ((static_cast<std::uint32_t>(warp + 1) * span) / plan.warps);
-  const int mine = static_cast<int>(end - begin);
+  // This CTA's outputs, then this warp's share of them, walked kG rows (a group) at a time.
+  const std::uint32_t cta = blockIdx.x, extra = cta < plan.rows_rem ? 1u : 0u;
+  const std::uint32_t cta_begin = (cta * plan.rows_q) + min(cta, plan.rows_rem);
+  const std::uint32_t uwarp = static_cast<std::uint32_t>(warp);
+  // (a parameter array indexed by a variable would be copied to local memory)
+  const std::uint32_t warp_q = extra != 0 ? plan.warp_q[1] : plan.warp_q[0];
+  const std::uint32_t warp_rem = extra != 0 ? plan.warp_rem[1] : plan.warp_rem[0];
+  const std::uint32_t begin = cta_begin + (uwarp * warp_q) + min(uwarp, warp_rem);
+  const int mine = static_cast<int>(warp_q + (uwarp < warp_rem ? 1u : 0u));
+  const int groups = (mine + kG - 1) / kG;
 
   unsigned char* ring = smem + plan.acts_bytes + (static_cast<std::size_t>(warp) * S * plan.stage_bytes);
+  const std::uint32_t ring_at = tc::Smem(ring);
   const auto* w_data = static_cast<const std::uint8_t*>(a.w.data);
   const auto* w2_data = static_cast<const std::uint8_t*>(a.w2.data);
 
-  // Row j of this warp's run into its stage: one bulk copy a matrix.
-  auto request = [&](int j) {
-    const int s = j % S;
-    if (lane == 0) tc::MbarExpectTx(&full[warp][s], plan.copy_bytes * kMats);
-    __syncwarp();
-    if (lane < kMats) {
-      const std::uint8_t* src =
-          lane == 0 ? w_data + (static_cast<std::uint64_t>(a.first + begin + j) * a.w.row_bytes)
-                    : w2_data + (static_cast<std::uint64_t>(a.first2 + begin + j) * a.w2.row_bytes);
-      tc::BulkLoad(ring + (static_cast<std::size_t>(s) * plan.stage_bytes) + (lane * plan.copy_bytes),
-                   src, plan.copy_bytes, &full[warp][s]);
+  // Item i of this warp's run is chunk i % C of group i / C and goes to stage i % S:
+  // one bulk copy a row and matrix (row r of the group, matrix m at
+  // (r kMats + m) copy_bytes).  Chunks let the sums start when the first part of
+  // a row has landed instead of the whole of it.
+  const int C = static_cast<int>(plan.chunks);
+  const int items = groups * C;
+  int next = 0, next_group = 0, next_chunk = 0, next_stage = 0;  // the next item to request
+  auto request = [&]() __attribute__((always_inline)) {
+    const std::uint32_t live = static_cast<std::uint32_t>(min(kG, mine - (next_group * kG)));
+    const std::uint32_t offset = static_cast<std::uint32_t>(next_chunk) * plan.copy_bytes;
+    const std::uint32_t bytes = min(plan.copy_bytes, plan.row_bytes - offset);
+    // One elected lane issues the item (the whole warp walks here: instructions of
+    // the copy engine issued from a one-lane branch cost several times as much).
+    if (tc::ElectOne()) {
+      tc::MbarExpectTx(&full[warp][next_stage], bytes * kMats * live);
+      unsigned char* dst = ring + (static_cast<std::size_t>(next_stage) * plan.stage_bytes);
+      const std::uint64_t n = begin + (static_cast<std::uint32_t>(next_group) * kG);
+#pragma unroll
+      for (std::uint32_t r = 0; r < static_cast<std::uint32_t>(kG); ++r) {
+        if (r < live) {
+          tc::BulkLoad(dst + (r * kMats * plan.copy_bytes),
+                       w_data + ((a.first + n + r) * a.w.row_bytes) + offset, bytes, &full[warp][next_stage]);
+          if constexpr (kGlu) {
+            tc::BulkLoad(dst + (((r * kMats) + 1) * plan.copy_bytes),
+                         w2_data + ((a.first2 + n + r) * a.w2.row_bytes) + offset, bytes,
+                         &full[warp][next_stage]);
+          }
+        }
+      }
     }
+    __syncwarp();
+    ++next;
+    if (++next_chunk == C) {
+      next_chunk = 0;
+      ++next_group;
+    }
+    if (++next_stage == S) next_stage = 0;
   };
 
   if (staged) {
-    if (lane == 0) {
-      for (int s = 0; s < S; ++s) tc::MbarInit(&full[warp][s], 1);
+    if (lane < static_cast<std::uint32_t>(S)) {
+      tc::MbarInit(&full[warp][lane], 1);
       tc::MbarInitFence();
     }
     __syncwarp();
   }
   GridLaunchDependents();
   if (staged) {
-    for (int j = 0; j < min(S, mine); ++j) request(j);
+    while (next < min(S, items)) request();
   }
   GridDependencyWait();
 
@@ -294,68 +463,165 @@ DecodeVectorKernel(const Args a, const Plan plan) {
   const float* xs = a.x;
   std::uint64_t xs_stride = a.x_stride;
   if (xs_shared) {
-    auto* dst = reinterpret_cast<float4*>(smem);
     const std::uint32_t quads = a.w.k / 4;
     for (std::uint32_t t = 0; t < a.rows; ++t) {
       const auto* src = reinterpret_cast<const float4*>(a.x + (static_cast<std::uint64_t>(t) * a.x_stride));
+      unsigned char* dst = smem + (static_cast<std::size_t>(t) * StagedRowBytes(a.w.k));
+#pragma unroll 4
       for (std::uint32_t i = static_cast<std::uint32_t>(tid); i < quads; i += blockDim.x) {
-        dst[(static_cast<std::size_t>(t) * quads) + i] = __ldg(src + i);
+        *reinterpret_cast<float4*>(dst + ((i >> 2) * kSegmentPitch) + ((i & 3u) * 16u)) = __ldg(src + i);
       }
     }
-    xs = reinterpret_cast<const float*>(smem);
-    xs_stride = a.w.k;
     __syncthreads();
   }
+  const std::uint32_t xs_at = tc::Smem(smem);
+  const std::uint32_t xs_row_bytes = static_cast<std::uint32_t>(StagedRowBytes(a.w.k));
+  const StagedLane<kDecoder> in_round(lane);
 
-  const std::uint32_t segs = a.w.k / 16;
-  for (int j = 0; j < mine; ++j) {
-    const std::uint32_t n = begin + static_cast<std::uint32_t>(j);
-    const std::uint32_t row = a.first + n, row2 = a.first2 + n;
-    const std::uint8_t* codes = w_data + (static_cast<std::uint64_t>(row) * a.w.row_bytes);
-    const std::uint8_t* codes2 = w2_data + (static_cast<std::uint64_t>(row2) * a.w2.row_bytes);
-    if (staged) {
-      const int s = j % S;
-      bool ok = true;
-      if (lane == 0) ok = tc::MbarWait(&full[warp][s], static_cast<std::uint32_t>((j / S) & 1));
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (!ok) {
-        if (lane == 0) atomicAdd(plan.faults, 1u);
-        return;  // nothing of an incomplete stage is summed or stored
-      }
-      codes = ring + (static_cast<std::size_t>(s) * plan.stage_bytes);
-      codes2 = codes + plan.copy_bytes;
-    }
-    float g[kCols], u[kGlu ? kCols : 1];
+  const std::uint32_t segs = a.w.k / 16, chunk_segs = plan.chunk_segs;
+  int item = 0, stage = 0;
+  std::uint32_t phase = 0;
+  for (int j = 0; j < groups; ++j) {
+    const std::uint32_t n0 = begin + (static_cast<std::uint32_t>(j) * kG);
+    const int live = min(kG, mine - (j * kG));
+    // Row r of the group; a group's missing rows repeat its first (summed, never stored).
+    std::uint32_t row[kG], row2[kG];
+    const std::uint8_t* codes[kG];
+    const std::uint8_t* codes2[kG];
 #pragma unroll
-    for (int t = 0; t < kCols; ++t) g[t] = 0.0f;
-    if constexpr (kGlu) {
-#pragma unroll
-      for (int t = 0; t < kCols; ++t) u[t] = 0.0f;
+    for (int r = 0; r < kG; ++r) {
+      const std::uint32_t n = n0 + static_cast<std::uint32_t>(r < live ? r : 0);
+      row[r] = a.first + n;
+      row2[r] = a.first2 + n;
+      codes[r] = w_data + (static_cast<std::uint64_t>(row[r]) * a.w.row_bytes);
+      codes2[r] = w2_data + (static_cast<std::uint64_t>(row2[r]) * a.w2.row_bytes);
     }
-    for (std::uint32_t seg = lane; seg < segs; seg += 32u) {
-      float v[16];
-      LoadSegment<kDecoder>(a.w, codes, staged, row, seg, v);
-      Accumulate<kCols>(xs, xs_stride, xs_shared, a.rows, seg, v, g);
-      if constexpr (kGlu) {
-        LoadSegment<kDecoder>(a.w2, codes2, staged, row2, seg, v);
-        Accumulate<kCols>(xs, xs_stride, xs_shared, a.rows, seg, v, u);
+    float g[kG][kCols], u[kGlu ? kG : 1][kCols];
+#pragma unroll
+    for (int r = 0; r < kG; ++r) {
+#pragma unroll
+      for (int t = 0; t < kCols; ++t) {
+        g[r][t] = 0.0f;
+        if constexpr (kGlu) u[r][t] = 0.0f;
       }
     }
-    if (staged) {
-      __syncwarp();  // every lane has read the stage
-      if (j + S < mine) {
-        tc::FenceProxyAsync();
-        request(j + S);
+    for (int c = 0; c < C; ++c, ++item) {
+      // Where the row would start in shared memory if all of it were staged as this chunk is.
+      std::uint32_t scodes[kG] = {}, scodes2[kG] = {};
+      if (staged) {
+        // Every lane looks once without blocking (a chunk requested long ago has
+        // usually landed, and a blocking wait costs a few hundred cycles even then);
+        // only if some lane saw the phase open does lane 0 wait, with its bound.
+        if (!__all_sync(0xffffffffu, tc::MbarTest(&full[warp][stage], phase) ? 1 : 0)) {
+          bool ok = true;
+          if (lane == 0) ok = tc::MbarWait(&full[warp][stage], phase);
+          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+          if (!ok) {
+            if (lane == 0) atomicAdd(plan.faults, 1u);
+            return;  // nothing of an incomplete stage is summed or stored
+          }
+        }
+#pragma unroll
+        for (int r = 0; r < kG; ++r) {
+          const int at = r < live ? r : 0;
+          scodes[r] = ring_at + (static_cast<std::uint32_t>(stage) * plan.stage_bytes) +
+                      (static_cast<std::uint32_t>(at) * kMats * plan.copy_bytes) -
+                      (static_cast<std::uint32_t>(c) * plan.copy_bytes);
+          scodes2[r] = scodes[r] + plan.copy_bytes;
+        }
+      }
+      const std::uint32_t seg_begin = static_cast<std::uint32_t>(c) * chunk_segs;
+      const std::uint32_t seg_end = min(segs, seg_begin + chunk_segs);
+      // The rounds of the chunk.  The usual case (rows staged, activations staged)
+      // is compiled with both facts known: its loop holds no branch on them, no
+      // global-memory addressing, and shared addresses that only advance.
+      auto rounds = [&](auto usual) {
+        constexpr bool kUsual = decltype(usual)::value;
+        const bool st = kUsual ? true : staged;
+        const bool xsh = kUsual ? true : xs_shared;
+        std::uint32_t round[kG], round2[kG];  // the round's bytes of each row, in the stage
+#pragma unroll
+        for (int r = 0; r < kG; ++r) {
+          round[r] = scodes[r] + ((seg_begin / 32u) * RoundBytes(kDecoder));
+          round2[r] = scodes2[r] + ((seg_begin / 32u) * RoundBytes(kDecoder));
+        }
+        std::uint32_t xa = xs_at + ((seg_begin + lane) * kSegmentPitch);  // the lane's staged activations
+        for (std::uint32_t seg = seg_begin + lane; seg < seg_end; seg += 32u) {
+          const auto staged_quad = [&](int t, int q) {
+            return StagedQuad(xa + (static_cast<std::uint32_t>(t) * xs_row_bytes), q);
+          };
+          const auto global_quad = [&](int t, int q) {
+            return __ldg(reinterpret_cast<const float4*>(xs + (static_cast<std::uint64_t>(t) * xs_stride)) +
+                         (seg * 4u) + static_cast<std::uint32_t>(q));
+          };
+          float v[kG][16];
+#pragma unroll
+          for (int r = 0; r < kG; ++r) {
+            Raw raw;
+            if (st) {
+              FetchStaged<kDecoder>(a.w, round[r], in_round, row[r], seg, raw);
+            } else {
+              FetchGlobal<kDecoder>(a.w, codes[r], row[r], seg, raw);
+            }
+            Expand<kDecoder, true>(raw, v[r]);
+            round[r] += RoundBytes(kDecoder);
+          }
+          if (xsh) {
+            Accumulate<kCols, kG>(a.rows, v, g, staged_quad);
+          } else {
+            Accumulate<kCols, kG>(a.rows, v, g, global_quad);
+          }
+          if constexpr (kGlu) {
+#pragma unroll
+            for (int r = 0; r < kG; ++r) {
+              Raw raw;
+              if (st) {
+                FetchStaged<kDecoder>(a.w2, round2[r], in_round, row2[r], seg, raw);
+              } else {
+                FetchGlobal<kDecoder>(a.w2, codes2[r], row2[r], seg, raw);
+              }
+              Expand<kDecoder, true>(raw, v[r]);
+              round2[r] += RoundBytes(kDecoder);
+            }
+            if (xsh) {
+              Accumulate<kCols, kG>(a.rows, v, u, staged_quad);
+            } else {
+              Accumulate<kCols, kG>(a.rows, v, u, global_quad);
+            }
+          }
+          xa += 32u * kSegmentPitch;
+        }
+      };
+      if (staged && xs_shared) {
+        rounds(std::true_type{});
+      } else {
+        rounds(std::false_type{});
+      }
+      if (staged) {
+        __syncwarp();  // every lane has read the stage
+        if (next < items) {  // the stage just read takes the next item
+          tc::FenceProxyAsync();
+          request();
+        }
+        if (++stage == S) {
+          stage = 0;
+          phase ^= 1u;
+        }
       }
     }
-    const float scale = TensorScale(a.w, row);
-    const float scale2 = kGlu ? TensorScale(a.w2, row2) : 1.0f;
 #pragma unroll
-    for (int t = 0; t < kCols; ++t) {
-      if (static_cast<std::uint32_t>(t) < a.rows) {
-        float out = Butterfly(g[t]) * scale;
-        if constexpr (kGlu) out = Glu(a.glu, out, Butterfly(u[t]) * scale2, a.limit);
-        if (lane == 0) a.y[(static_cast<std::uint64_t>(t) * a.y_stride) + n] = out;
+    for (int r = 0; r < kG; ++r) {
+      if (r < live) {
+        const float scale = TensorScale(a.w, row[r]);
+        const float scale2 = kGlu ? TensorScale(a.w2, row2[r]) : 1.0f;
+#pragma unroll
+        for (int t = 0; t < kCols; ++t) {
+          if (static_cast<std::uint32_t>(t) < a.rows) {
+            float out = Butterfly(g[r][t]) * scale;
+            if constexpr (kGlu) out = Glu(a.glu, out, Butterfly(u[r][t]) * scale2, a.limit);
+            if (lane == 0) a.y[(static_cast<std::uint64_t>(t) * a.y_stride) + n0 + r] = out;
+          }
+        }
       }
     }
   }
@@ -389,7 +655,9 @@ DecodeRowsKernel(const Operand w, const std::int32_t* __restrict__ ids, std::uin
   const std::uint8_t* codes = static_cast<const std::uint8_t*>(w.data) + (static_cast<std::uint64_t>(row) * w.row_bytes);
   for (std::uint32_t seg = lane; seg < segs; seg += 32u) {
     float v[16];
-    LoadSegment<kDecoder>(w, codes, false, row, seg, v);
+    Raw raw;
+    FetchGlobal<kDecoder>(w, codes, row, seg, raw);
+    Expand<kDecoder, false>(raw, v);
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       out[(seg * 4u) + q] = make_float4(v[4 * q] * scale, v[(4 * q) + 1] * scale, v[(4 * q) + 2] * scale,
@@ -436,32 +704,55 @@ bool MakePlan(const Args& a, int mats, Plan* plan) {
   const auto bulk_ok = [&](const Operand& p) {
     return Aligned(p.data, 16) && p.row_bytes % 16 == 0 && row % 16 == 0;
   };
-  const std::uint64_t acts = static_cast<std::uint64_t>(a.rows) * a.w.k * 4;
+  const std::uint64_t acts = static_cast<std::uint64_t>(a.rows) * StagedRowBytes(a.w.k);
   plan->acts_bytes = acts <= kActsBudget ? static_cast<std::uint32_t>(acts) : 0u;
   plan->grid = static_cast<int>(std::min<std::uint64_t>(static_cast<std::uint64_t>(sms), a.outputs));
   const std::uint64_t per_cta = (a.outputs + plan->grid - 1) / plan->grid;
-  int warps = static_cast<int>(std::min<std::uint64_t>(kMaxWarps, per_cta));
+  const int warps = static_cast<int>(std::min<std::uint64_t>(kMaxWarps, per_cta));
+  plan->rows_q = a.outputs / static_cast<std::uint32_t>(plan->grid);
+  plan->rows_rem = a.outputs % static_cast<std::uint32_t>(plan->grid);
+  for (std::uint32_t e = 0; e < 2; ++e) {
+    plan->warp_q[e] = (plan->rows_q + e) / static_cast<std::uint32_t>(warps);
+    plan->warp_rem[e] = (plan->rows_q + e) % static_cast<std::uint32_t>(warps);
+  }
+  plan->row_bytes = static_cast<std::uint32_t>(row);
   plan->copy_bytes = 0;
   plan->stage_bytes = 0;
   plan->stages = 1;
-  if (bulk_ok(a.w) && (mats == 1 || bulk_ok(a.w2)) && row * mats * 2 <= kRingBudget) {
-    // at least two stages a warp; fewer warps when rows are long
-    while (warps > 1 && row * mats * 2 * warps > kRingBudget) --warps;
-    const std::uint64_t rows_a_warp = (per_cta + warps - 1) / warps;
-    std::uint64_t stages = kRingBudget / (row * mats * warps);
+  plan->chunk_segs = a.w.k / 16;
+  plan->chunks = 1;
+  // A warp's part of the ring, the bytes of one round (32 segments, one a lane) of a row.
+  const std::uint64_t per_warp = (static_cast<std::uint64_t>(kRingBudget) / warps) & ~std::uint64_t{15};
+  const std::uint64_t round = static_cast<std::uint64_t>(16) * SegmentBytesX2(d);
+  // Two rows a group for up to four activation rows (an activation value read from
+  // shared memory serves both; more columns would spill), when some warp has two
+  // rows to sum and two stages of one round each fit.
+  plan->group = (a.rows <= 4 && per_cta > static_cast<std::uint64_t>(warps) &&
+                 round * mats * 2 * 2 <= per_warp) ? 2 : 1;
+  const std::uint64_t unit = round * mats * plan->group;
+  if (bulk_ok(a.w) && (mats == 1 || bulk_ok(a.w2)) && row <= 0xffffffffull && unit * 2 <= per_warp) {
+    // Chunks of whole rounds, about four stages of them in a warp's part.
+    const std::uint64_t rounds = (static_cast<std::uint64_t>(a.w.k / 16) + 31) / 32;
+    const std::uint64_t r = std::min(rounds, std::max<std::uint64_t>(1, per_warp / (4 * unit)));
+    const std::uint64_t chunks = (rounds + r - 1) / r;
+    const std::uint64_t stage = r * unit;
+    const std::uint64_t groups_a_warp = (((per_cta + warps - 1) / warps) + plan->group - 1) / plan->group;
+    std::uint64_t stages = per_warp / stage;
     stages = std::min<std::uint64_t>(stages, static_cast<std::uint64_t>(kMaxStages));
-    stages = std::min<std::uint64_t>(stages, std::max<std::uint64_t>(rows_a_warp, 1));
+    stages = std::min<std::uint64_t>(stages, std::max<std::uint64_t>(groups_a_warp * chunks, 1));
     plan->stages = static_cast<int>(stages);
-    plan->copy_bytes = static_cast<std::uint32_t>(row);
-    plan->stage_bytes = static_cast<std::uint32_t>(row * mats);
+    plan->copy_bytes = static_cast<std::uint32_t>(r * round);
+    plan->chunk_segs = static_cast<std::uint32_t>(r * 32);
+    plan->chunks = static_cast<std::uint32_t>(chunks);
+    plan->stage_bytes = static_cast<std::uint32_t>(stage);
   }
   plan->warps = warps;
   return true;
 }
 
-template <int kDecoder, int kCols, bool kGlu>
+template <int kDecoder, int kCols, bool kGlu, int kG>
 cudaError_t LaunchOne(const Args& a, const Plan& plan, cudaStream_t s) {
-  auto* kernel = DecodeVectorKernel<kDecoder, kCols, kGlu>;
+  auto* kernel = DecodeVectorKernel<kDecoder, kCols, kGlu, kG>;
   const std::size_t smem = plan.acts_bytes +
                            (static_cast<std::size_t>(plan.warps) * plan.stages * plan.stage_bytes);
   static thread_local int configured_device = -1;
@@ -479,11 +770,16 @@ cudaError_t LaunchOne(const Args& a, const Plan& plan, cudaStream_t s) {
 
 template <int kDecoder, bool kGlu>
 cudaError_t LaunchCols(const Args& a, const Plan& plan, cudaStream_t s) {
-  if (a.rows <= 1) return LaunchOne<kDecoder, 1, kGlu>(a, plan, s);
-  if (a.rows <= 2) return LaunchOne<kDecoder, 2, kGlu>(a, plan, s);
-  if (a.rows <= 4) return LaunchOne<kDecoder, 4, kGlu>(a, plan, s);
-  if (a.rows <= 8) return LaunchOne<kDecoder, 8, kGlu>(a, plan, s);
-  return LaunchOne<kDecoder, 16, kGlu>(a, plan, s);
+  if (plan.group == 2) {
+    if (a.rows <= 1) return LaunchOne<kDecoder, 1, kGlu, 2>(a, plan, s);
+    if (a.rows <= 2) return LaunchOne<kDecoder, 2, kGlu, 2>(a, plan, s);
+    return LaunchOne<kDecoder, 4, kGlu, 2>(a, plan, s);
+  }
+  if (a.rows <= 1) return LaunchOne<kDecoder, 1, kGlu, 1>(a, plan, s);
+  if (a.rows <= 2) return LaunchOne<kDecoder, 2, kGlu, 1>(a, plan, s);
+  if (a.rows <= 4) return LaunchOne<kDecoder, 4, kGlu, 1>(a, plan, s);
+  if (a.rows <= 8) return LaunchOne<kDecoder, 8, kGlu, 1>(a, plan, s);
+  return LaunchOne<kDecoder, 16, kGlu, 1>(a, plan, s);
 }
 
 template <bool kGlu>
