@@ -61,6 +61,8 @@ struct RowLanePlan {
   unsigned int* q8_rows_done;  // [tokens][nrows / 32] counters, zero between launches
   unsigned int* faults;
   PeerFan fan;  // world > 0: token 0's results also go, tagged, into every rank's vector (peer.cuh)
+  RowSplit split;        // the rows of a CTA and of its warps (at most R a warp)
+  int phase_reciprocal;  // ceil(65536 / R): lane / R without a division
 };
 
 // kHalf: at most half an SM's registers and shared memory, so that the kernel
@@ -83,55 +85,54 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
   const int J = plan.steps;
   const int S = plan.stages;
   // Lanes R * PH and up (when R * PH < 32) idle through the column steps.
-  const int r = lane % R;
-  const int ph = lane / R;
+  const int ph = (lane * plan.phase_reciprocal) >> 16;  // lane / R
+  const int r = lane - (ph * R);
 
   // This CTA's rows, then this warp's share of them (at most R).
-  const int cta_begin = static_cast<int>((static_cast<long>(blockIdx.x) * a.nrows) / gridDim.x);
-  const int cta_end = static_cast<int>((static_cast<long>(blockIdx.x + 1) * a.nrows) / gridDim.x);
-  const int cta_rows = cta_end - cta_begin;
-  const int row_begin = cta_begin + ((warp * cta_rows) / plan.warps);
-  const int row_end = cta_begin + (((warp + 1) * cta_rows) / plan.warps);
-  const int my_rows = row_end - row_begin;  // <= R by the plan
+  int row_begin, my_rows;
+  WarpRows(plan.split, static_cast<int>(blockIdx.x), warp, &row_begin, &my_rows);
+  const int row_end = row_begin + my_rows;
 
   unsigned char* acts = smem;
   unsigned char* ring = smem + (static_cast<std::size_t>(P) * plan.acts_bytes) +
                         (static_cast<std::size_t>(warp) * S * plan.stage_bytes);
 
-  const std::uint8_t* mats[kMats];
-  mats[0] = static_cast<const std::uint8_t*>(a.w);
-  if constexpr (kGlu) mats[1] = static_cast<const std::uint8_t*>(a.g);
-
-  if (lane == 0) {
-    for (int s = 0; s < S; ++s) MbarInit(&full[warp][s], 1);
+  if (lane < S) {
+    MbarInit(&full[warp][lane], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncwarp();
 
-  // Requests column step j of this warp's rows into its stage.
-  auto request = [&](int j) {
-    const int s = j % S;
-    const int cols = min(PH, UR - (j * PH));
+  // Requests the next column step of this warp's rows into its stage (steps are
+  // requested in order).  Copy c of a step is row c of the first matrix, or row
+  // c - my_rows of the second: no division, and no pointer array indexed by a
+  // variable (which would live in local memory).
+  int next = 0, next_stage = 0;
+  auto request = [&]() __attribute__((always_inline)) {
+    const int cols = min(PH, UR - (next * PH));
     const std::uint32_t piece = static_cast<std::uint32_t>(cols) * 144u;
-    unsigned char* base = ring + (static_cast<std::size_t>(s) * plan.stage_bytes);
+    unsigned char* base = ring + (static_cast<std::size_t>(next_stage) * plan.stage_bytes);
     if (lane == 0) {
-      MbarExpectTx(&full[warp][s], piece * static_cast<std::uint32_t>(my_rows * kMats));
+      MbarExpectTx(&full[warp][next_stage], piece * static_cast<std::uint32_t>(my_rows * kMats));
     }
     __syncwarp();
     for (int c = lane; c < my_rows * kMats; c += 32) {
-      const int m = c / my_rows;
-      const int row = c % my_rows;
+      const int m = c >= my_rows ? 1 : 0;
+      const int row = c - (m * my_rows);
+      const std::uint8_t* mat = static_cast<const std::uint8_t*>(kGlu && m != 0 ? a.g : a.w);
       const std::uint8_t* src =
-          mats[m] + ((static_cast<std::size_t>(row_begin + row) * a.stride_row +
-                      static_cast<std::size_t>(j) * PH) * 144);
+          mat + ((static_cast<std::size_t>(row_begin + row) * a.stride_row +
+                  static_cast<std::size_t>(next) * PH) * 144);
       BulkLoad(base + ((static_cast<std::size_t>(m) * R + row) * plan.pitch), src, piece,
-               &full[warp][s]);
+               &full[warp][next_stage]);
     }
+    ++next;
+    if (++next_stage == S) next_stage = 0;
   };
 
   GridLaunchDependents();
   if (my_rows > 0) {
-    for (int j = 0; j < min(S, J); ++j) request(j);
+    while (next < min(S, J)) request();
   }
   GridDependencyWait();
 
@@ -227,14 +228,13 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
     for (int m = 0; m < kMats; ++m) acc[t][m] = 0.0f;
 
   bool healthy = true;
+  int s = 0;
+  std::uint32_t parity = 0;
   for (int j = 0; j < J; ++j) {
-    const int s = j % S;
-    if (healthy && lane == 0 &&
-        !MbarWait(&full[warp][s], static_cast<std::uint32_t>((j / S) & 1))) {
+    if (healthy && !WarpAwait(&full[warp][s], parity, lane)) {
       healthy = false;
-      atomicAdd(plan.faults, 1u);
+      if (lane == 0) atomicAdd(plan.faults, 1u);
     }
-    __syncwarp();
     const int c = (j * PH) + ph;
     if (ph < PH && c < UR && r < my_rows) {
       const unsigned char* base = ring + (static_cast<std::size_t>(s) * plan.stage_bytes);
@@ -316,14 +316,18 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
       }
     }
     __syncwarp();
-    if (j + S < J) {
+    if (next < J) {  // the stage just read takes the next step
       FenceProxyAsync();
-      request(j + S);
+      request();
+    }
+    if (++s == S) {
+      s = 0;
+      parity ^= 1u;
     }
   }
 
   // A stage that never arrived: nothing of this warp's rows is stored.
-  if (__shfl_sync(0xffffffffu, healthy ? 1 : 0, 0) == 0) return;
+  if (!healthy) return;
 
   // The phases of a row meet in phase order: lane r adds lanes r + R, r + 2R, ...
 #pragma unroll
@@ -481,6 +485,8 @@ inline bool PlanRowLane(const Desc& d, int p, int sms, int force_rows, bool half
   if (best_score < 0.0) return false;
   best.faults = FaultCounter();
   if (best.faults == nullptr) return false;
+  best.split = MakeRowSplit(d.nrows, best.grid, best.warps);
+  best.phase_reciprocal = (65536 + best.rows - 1) / best.rows;
   *plan = best;
   return true;
 }

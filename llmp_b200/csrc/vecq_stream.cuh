@@ -31,6 +31,23 @@ constexpr int kStreamThreads = 256;
 constexpr int kStreamMaxStages = 16;
 constexpr std::uint32_t kWaitLimit = 1u << 22;  // polls of ~20-50 ns
 
+// How a product's rows are dealt to CTAs and a CTA's to its warps, worked out on
+// the host so that no division runs on the device: CTA b owns rows_q + (b <
+// rows_rem) rows, and a CTA of rows_q + e rows gives warp w warp_q[e] + (w <
+// warp_rem[e]) of them.
+struct RowSplit {
+  int rows_q, rows_rem, warp_q0, warp_q1, warp_rem0, warp_rem1;
+};
+inline RowSplit MakeRowSplit(int nrows, int grid, int warps) {
+  RowSplit s{};
+  s.rows_q = nrows / grid;
+  s.rows_rem = nrows % grid;
+  s.warp_q0 = s.rows_q / warps;
+  s.warp_rem0 = s.rows_q % warps;
+  s.warp_q1 = (s.rows_q + 1) / warps;
+  s.warp_rem1 = (s.rows_q + 1) % warps;
+  return s;
+}
 struct StreamPlan {
   int units_per_row;   // UR
   int rows_per_step;   // RS = threads / UR
@@ -43,6 +60,8 @@ struct StreamPlan {
   int grid;
   bool packed;         // rows contiguous: one copy per matrix and stage
   unsigned int* faults;  // device counter a wait that ran out increments
+  RowSplit split;        // the rows of a CTA (the warp part is unused)
+  int unit_reciprocal;   // ceil(2^20 / UR): tid / UR without a division (tid < 1024)
 };
 
 __device__ __forceinline__ std::uint32_t SmemAddr(const void* p) {
@@ -75,6 +94,43 @@ __device__ __forceinline__ bool MbarWait(std::uint64_t* bar, std::uint32_t parit
   }
   return false;
 }
+// One look at the phase without blocking: a blocking wait costs a few hundred
+// cycles even on a phase that completed long ago.
+__device__ __forceinline__ bool MbarTest(std::uint64_t* bar, std::uint32_t parity) {
+  std::uint32_t done;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(done)
+      : "r"(SmemAddr(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// The warp's wait for a stage: every lane looks once; only if some lane saw the
+// phase open does lane 0 wait, with its bound.  False (for all lanes) if it ran out.
+__device__ __forceinline__ bool WarpAwait(std::uint64_t* bar, std::uint32_t parity, int lane) {
+  if (__all_sync(0xffffffffu, MbarTest(bar, parity) ? 1 : 0)) return true;
+  int ok = 1;
+  if (lane == 0) ok = MbarWait(bar, parity) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
+__device__ __forceinline__ void CtaRows(const RowSplit& s, int cta, int* begin, int* count) {
+  *begin = (cta * s.rows_q) + min(cta, s.rows_rem);
+  *count = s.rows_q + (cta < s.rows_rem ? 1 : 0);
+}
+__device__ __forceinline__ void WarpRows(const RowSplit& s, int cta, int warp, int* begin, int* count) {
+  int cta_begin, cta_count;
+  CtaRows(s, cta, &cta_begin, &cta_count);
+  const bool extra = cta < s.rows_rem;
+  const int q = extra ? s.warp_q1 : s.warp_q0, rem = extra ? s.warp_rem1 : s.warp_rem0;
+  *begin = cta_begin + (warp * q) + min(warp, rem);
+  *count = q + (warp < rem ? 1 : 0);
+}
+
 // Global -> this CTA's shared memory, completing `bytes` on the mbarrier.
 __device__ __forceinline__ void BulkLoad(void* smem, const void* gmem, std::uint32_t bytes,
                                          std::uint64_t* bar) {
@@ -273,32 +329,35 @@ VecQStreamKernel(const Desc a, const StreamPlan plan) {
   const int RS = plan.rows_per_step;
   const int RG = plan.rows_per_stage;
   const int S = plan.stages;
-  const int u = tid % UR;
-  const int step_row = tid / UR;
+  const int step_row = static_cast<int>((static_cast<unsigned>(tid) * static_cast<unsigned>(plan.unit_reciprocal)) >> 20);
+  const int u = tid - (step_row * UR);
   const bool active = step_row < RS;
   float* partial = reinterpret_cast<float*>(smem + (static_cast<std::size_t>(S) * plan.stage_bytes));
 
   // This CTA's rows, evenly divided over the grid.
-  const int row_begin = static_cast<int>((static_cast<long>(blockIdx.x) * a.nrows) / gridDim.x);
-  const int row_end = static_cast<int>((static_cast<long>(blockIdx.x + 1) * a.nrows) / gridDim.x);
-  const int my_rows = row_end - row_begin;
+  int row_begin, my_rows;
+  CtaRows(plan.split, static_cast<int>(blockIdx.x), &row_begin, &my_rows);
+  const int row_end = row_begin + my_rows;
   const int iterations = (my_rows + RG - 1) / RG;
 
-  const std::uint8_t* mats[kMats];
-  mats[0] = static_cast<const std::uint8_t*>(a.w);
-  if constexpr (kGlu) mats[1] = static_cast<const std::uint8_t*>(a.g);
+  // (no pointer array indexed by a variable: it would live in local memory)
+  const auto matrix = [&](int m) {
+    return static_cast<const std::uint8_t*>(kGlu && m != 0 ? a.g : a.w);
+  };
   const std::size_t row_pitch = static_cast<std::size_t>(a.stride_row) * Unit::kBlockBytes;
 
-  if (tid == 0) {
-    for (int s = 0; s < S; ++s) MbarInit(&full[s], 1);
+  if (tid < S) {
+    MbarInit(&full[tid], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
 
-  // Requests the rows of iteration `it` into its stage (warp 0, converged).
-  auto request = [&](int it) {
-    const int s = it % S;
-    const int r0 = row_begin + (it * RG);
+  // Requests the rows of the next iteration into its stage (warp 0, converged;
+  // iterations are requested in order).
+  int next = 0, next_stage = 0;
+  auto request = [&]() __attribute__((always_inline)) {
+    const int s = next_stage;
+    const int r0 = row_begin + (next * RG);
     const int rows = min(RG, row_end - r0);
     unsigned char* base = smem + (static_cast<std::size_t>(s) * plan.stage_bytes);
     if (lane == 0) {
@@ -308,23 +367,25 @@ VecQStreamKernel(const Desc a, const StreamPlan plan) {
     if (plan.packed) {
       if (lane < kMats) {
         BulkLoad(base + (static_cast<std::size_t>(lane) * RG * plan.row_bytes),
-                 mats[lane] + (static_cast<std::size_t>(r0) * row_pitch),
+                 matrix(lane) + (static_cast<std::size_t>(r0) * row_pitch),
                  static_cast<std::uint32_t>(rows) * plan.row_bytes, &full[s]);
       }
     } else {
       for (int c = lane; c < rows * kMats; c += 32) {
-        const int m = c / rows;
-        const int r = c % rows;
+        const int m = c >= rows ? 1 : 0;
+        const int r = c - (m * rows);
         BulkLoad(base + ((static_cast<std::size_t>(m) * RG + r) * plan.row_bytes),
-                 mats[m] + (static_cast<std::size_t>(r0 + r) * row_pitch), plan.row_bytes,
+                 matrix(m) + (static_cast<std::size_t>(r0 + r) * row_pitch), plan.row_bytes,
                  &full[s]);
       }
     }
+    ++next;
+    if (++next_stage == S) next_stage = 0;
   };
 
   GridLaunchDependents();
   if (warp == 0) {
-    for (int it = 0; it < min(S, iterations); ++it) request(it);
+    while (next < min(S, iterations)) request();
   }
   GridDependencyWait();
 
@@ -339,16 +400,15 @@ VecQStreamKernel(const Desc a, const StreamPlan plan) {
 
   bool healthy = true;
   const int partial_stride = plan.partial_floats;  // floats in one buffer
+  int s = 0;
+  std::uint32_t parity = 0;
   for (int it = 0; it < iterations; ++it) {
-    const int s = it % S;
     const int r0 = row_begin + (it * RG);
     const int rows = min(RG, row_end - r0);
-    // One lane polls; its warp follows through the warp barrier.
-    if (healthy && lane == 0 && !MbarWait(&full[s], static_cast<std::uint32_t>((it / S) & 1))) {
+    if (healthy && !WarpAwait(&full[s], parity, lane)) {
       healthy = false;
-      atomicAdd(plan.faults, 1u);
+      if (lane == 0) atomicAdd(plan.faults, 1u);
     }
-    __syncwarp();
     const unsigned char* base = smem + (static_cast<std::size_t>(s) * plan.stage_bytes);
     float* part = partial + ((it & 1) * partial_stride);
     if (active) {
@@ -375,9 +435,9 @@ VecQStreamKernel(const Desc a, const StreamPlan plan) {
       }
     }
     __syncthreads();  // partials written; the stage's bytes are consumed
-    if (warp == 0 && it + S < iterations) {
+    if (warp == 0 && next < iterations) {  // the stage just read takes the next iteration
       FenceProxyAsync();
-      request(it + S);
+      request();
     }
     // Row sums: warp w takes (row, token) items w, w + 8, ...
     const int items = rows * P;
@@ -405,6 +465,10 @@ VecQStreamKernel(const Desc a, const StreamPlan plan) {
           *dst = v[0];
         }
       }
+    }
+    if (++s == S) {
+      s = 0;
+      parity ^= 1u;
     }
   }
 }
@@ -439,6 +503,8 @@ inline bool PlanStream(const Desc& d, int unit_elems, int block_bytes, int block
   plan->smem_bytes = (stages * stage_bytes) + (2 * partial_floats * 4);
   plan->grid = std::max(1, std::min(sms, d.nrows));
   plan->packed = d.stride_row == d.ncols_x / block_elems;
+  plan->split = MakeRowSplit(d.nrows, plan->grid, 1);
+  plan->unit_reciprocal = ((1 << 20) + ur - 1) / ur;
   plan->faults = FaultCounter();
   return plan->faults != nullptr;
 }
