@@ -104,28 +104,33 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
   __syncwarp();
 
   // Requests the next column step of this warp's rows into its stage (steps are
-  // requested in order).  Copy c of a step is row c of the first matrix, or row
-  // c - my_rows of the second: no division, and no pointer array indexed by a
-  // variable (which would live in local memory).
+  // requested in order): a copy a row and matrix, issued by one elected lane with
+  // the warp converged, their operands uniform.  (An SM's copy engine takes these
+  // 720-byte copies at about one every 20 cycles, as fast as their bytes arrive;
+  // whole rows a copy, half as many, measured slower: a step's sums could then not
+  // start before the other step's columns had landed.  No pointer array indexed by
+  // a variable: it would live in local memory.)
   int next = 0, next_stage = 0;
   auto request = [&]() __attribute__((always_inline)) {
     const int cols = min(PH, UR - (next * PH));
     const std::uint32_t piece = static_cast<std::uint32_t>(cols) * 144u;
     unsigned char* base = ring + (static_cast<std::size_t>(next_stage) * plan.stage_bytes);
-    if (lane == 0) {
+    if (ElectOne()) {
       MbarExpectTx(&full[warp][next_stage], piece * static_cast<std::uint32_t>(my_rows * kMats));
+#pragma unroll
+      for (int m = 0; m < kMats; ++m) {
+        const std::uint8_t* src =
+            static_cast<const std::uint8_t*>(kGlu && m != 0 ? a.g : a.w) +
+            ((static_cast<std::size_t>(row_begin) * a.stride_row + static_cast<std::size_t>(next) * PH) * 144);
+        unsigned char* dst = base + (static_cast<std::size_t>(m) * R * plan.pitch);
+        for (int row = 0; row < my_rows; ++row) {
+          BulkLoad(dst, src, piece, &full[warp][next_stage]);
+          src += static_cast<std::size_t>(a.stride_row) * 144;
+          dst += plan.pitch;
+        }
+      }
     }
     __syncwarp();
-    for (int c = lane; c < my_rows * kMats; c += 32) {
-      const int m = c >= my_rows ? 1 : 0;
-      const int row = c - (m * my_rows);
-      const std::uint8_t* mat = static_cast<const std::uint8_t*>(kGlu && m != 0 ? a.g : a.w);
-      const std::uint8_t* src =
-          mat + ((static_cast<std::size_t>(row_begin + row) * a.stride_row +
-                  static_cast<std::size_t>(next) * PH) * 144);
-      BulkLoad(base + ((static_cast<std::size_t>(m) * R + row) * plan.pitch), src, piece,
-               &full[warp][next_stage]);
-    }
     ++next;
     if (++next_stage == S) next_stage = 0;
   };

@@ -94,6 +94,20 @@ __device__ __forceinline__ bool MbarWait(std::uint64_t* bar, std::uint32_t parit
   }
   return false;
 }
+// One lane of the (converged) warp: what it issues to the copy engine takes its
+// operands from uniform registers at once.
+__device__ __forceinline__ bool ElectOne() {
+  std::uint32_t pred = 0;
+  asm volatile(
+      "{\n"
+      ".reg .b32 rx;\n"
+      ".reg .pred px;\n"
+      "elect.sync rx|px, 0xffffffff;\n"
+      "selp.u32 %0, 1, 0, px;\n"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
 // One look at the phase without blocking: a blocking wait costs a few hundred
 // cycles even on a phase that completed long ago.
 __device__ __forceinline__ bool MbarTest(std::uint64_t* bar, std::uint32_t parity) {
