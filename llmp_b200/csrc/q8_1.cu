@@ -20,9 +20,29 @@ QuantizeQ8_1Kernel(const float* __restrict__ x, std::int64_t k, std::int64_t row
                    std::int64_t stride_row, std::int64_t stride_plane, std::int64_t row_blocks,
                    std::int64_t total_lanes, std::uint8_t* __restrict__ out, const PeerWait gathered,
                    const PeerPublish publish) {
-  // The input is the kernel before's output; the products after this one may
-  // start fetching their weights now.
+  // The products after this one may start fetching their weights now.
   GridLaunchDependents();
+  // Where this thread reads and writes, worked out BEFORE the wait for the kernel
+  // before (whose output the input is): the divisions, 64-bit only when they have
+  // to be, then run beside that kernel's tail instead of after it.
+  const std::int64_t i = (static_cast<std::int64_t>(blockIdx.x) * kThreads) + threadIdx.x;
+  const bool live = i < total_lanes;  // whole groups of 8 lanes are live or not
+  const std::int64_t block = (live ? i : 0) / 8;
+  const int lane8 = static_cast<int>(i % 8);
+  std::int64_t row, b, plane, plane_row;  // row over rows * planes
+  if (rows == 1 && row_blocks <= 0x7fffffff && block <= 0x7fffffff) {
+    const std::uint32_t block32 = static_cast<std::uint32_t>(block), per = static_cast<std::uint32_t>(row_blocks);
+    const std::uint32_t row32 = block32 / per;
+    row = row32, b = block32 - (row32 * per), plane = row32, plane_row = 0;
+  } else {
+    row = block / row_blocks;
+    b = block % row_blocks;
+    plane = row / rows;
+    plane_row = row % rows;
+  }
+  const std::int64_t at = (b * 32) + (lane8 * 4);
+  const float* src = x + (plane * stride_plane) + (plane_row * stride_row) + at;
+  std::uint8_t* o = out + (block * 36);
   GridDependencyWait();
   // ... or, in the column-sharded step, a vector every rank stores a slice of (peer.cu):
   // store this rank's slice everywhere first (when this kernel is given it), then wait, with a
@@ -30,14 +50,6 @@ QuantizeQ8_1Kernel(const float* __restrict__ x, std::int64_t k, std::int64_t row
   // wait for this rank's own flag do not keep the one that sets it from running.
   PeerPublishSlice(publish);
   PeerWaitAll(gathered);
-  const std::int64_t i = (static_cast<std::int64_t>(blockIdx.x) * kThreads) + threadIdx.x;
-  const bool live = i < total_lanes;  // whole groups of 8 lanes are live or not
-  const std::int64_t block = (live ? i : 0) / 8;
-  const int lane8 = static_cast<int>(i % 8);
-  const std::int64_t row = block / row_blocks;       // over rows * planes
-  const std::int64_t b = block % row_blocks;
-  const std::int64_t at = (b * 32) + (lane8 * 4);
-  const float* src = x + ((row / rows) * stride_plane) + ((row % rows) * stride_row) + at;
   float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
   if (live) {
     if (kVec && at + 4 <= k) {
@@ -71,7 +83,6 @@ QuantizeQ8_1Kernel(const float* __restrict__ x, std::int64_t k, std::int64_t row
     }
   }
   if (!live) return;
-  std::uint8_t* o = out + (block * 36);
   *reinterpret_cast<std::uint32_t*>(o + 4 + (lane8 * 4)) = packed;
   if (lane8 == 0) {
     const std::uint32_t ds = static_cast<std::uint32_t>(__half_as_ushort(__float2half_rn(d))) |
