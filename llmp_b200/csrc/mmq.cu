@@ -67,14 +67,15 @@ QuantizeMmqKernel(const void* __restrict__ x, std::int64_t row_stride, int k, st
                   const std::int32_t* __restrict__ ids_src, std::uint8_t* __restrict__ out,
                   std::int64_t lanes_total) {
   GridLaunchDependents();
-  GridDependencyWait();
+  // (the index arithmetic runs beside the tail of the kernel before, not after it)
   const std::int64_t i = (static_cast<std::int64_t>(blockIdx.x) * 256) + threadIdx.x;
   const bool live = i < lanes_total;
   const std::int64_t group = (live ? i : 0) / 8;  // (col, k / 32)
   const int part = static_cast<int>(i % 8);
   const int groups = k / 32;
   const std::int64_t col = group / groups;
-  const int g = static_cast<int>(group % groups);
+  const int g = static_cast<int>(group - (col * groups));
+  GridDependencyWait();
   float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
   if (live) {
     const std::int64_t src_row = ids_src != nullptr ? ids_src[col] : col;

@@ -234,14 +234,15 @@ __global__ void __launch_bounds__(256)
 GluQuantizeKernel(const float* __restrict__ x, std::int64_t row_stride, int f, std::int64_t rows,
                   int glu, float limit, std::uint8_t* __restrict__ out, std::int64_t lanes_total) {
   GridLaunchDependents();
-  GridDependencyWait();
+  // (the index arithmetic runs beside the tail of the kernel before, not after it)
   const std::int64_t i = (static_cast<std::int64_t>(blockIdx.x) * 256) + threadIdx.x;
   const bool live = i < lanes_total;
   const std::int64_t group = (live ? i : 0) / 8;
   const int part = static_cast<int>(i % 8);
   const int groups = f / 32;
   const std::int64_t row = group / groups;
-  const int g = static_cast<int>(group % groups);
+  const int g = static_cast<int>(group - (row * groups));
+  GridDependencyWait();
   float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
   if (live) {
     const float* p = x + (row * row_stride) + (g * 32) + (part * 4);

@@ -66,14 +66,15 @@ __global__ void __launch_bounds__(256)
 QuantizeKernel(const void* __restrict__ x, std::int64_t x_stride, std::uint8_t* __restrict__ codes,
                std::uint8_t* __restrict__ scales, int k, int rows, std::int64_t lanes_total) {
   GridLaunchDependents();
-  GridDependencyWait();
+  // (the index arithmetic runs beside the tail of the kernel before, not after it)
   const std::int64_t i = (static_cast<std::int64_t>(blockIdx.x) * 256) + threadIdx.x;
   const bool live = i < lanes_total;
   const std::int64_t item = (live ? i : 0) / 8;
   const int part = static_cast<int>(i % 8);
   const int blocks = k / 32;
   const int r = static_cast<int>(item / blocks);
-  const int b = static_cast<int>(item % blocks);
+  const int b = static_cast<int>(item - (static_cast<std::int64_t>(r) * blocks));
+  GridDependencyWait();
   float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
   if (live && r < rows) {
     const std::int64_t at = (static_cast<std::int64_t>(r) * x_stride) + (b * 32) + (part * 4);
