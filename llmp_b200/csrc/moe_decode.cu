@@ -135,13 +135,21 @@ __device__ __forceinline__ float DotStaged(const Q4KBlockUnit& w, const std::uin
 
 // Every CTA arrives; true once all have.  The counter only ever grows (a launch adds
 // gridDim.x), so it needs zeroing once, not between launches.
-__device__ __forceinline__ bool GridMeet(unsigned int* counter, int polls) {
+// In two halves, so that work that needs nothing from the other CTAs (the first down
+// rows' requests) runs while the arrivals travel.
+__device__ __forceinline__ unsigned int GridArrive(unsigned int* counter) {
   __threadfence();
   __syncthreads();
-  bool ok = true;
+  unsigned int target = 0;
   if (threadIdx.x == 0) {
     const unsigned int mine = atomicAdd(counter, 1u);
-    const unsigned int target = ((mine / gridDim.x) + 1u) * gridDim.x;
+    target = ((mine / gridDim.x) + 1u) * gridDim.x;
+  }
+  return target;  // thread 0's: what the counter reads once every CTA has arrived
+}
+__device__ __forceinline__ bool GridAwait(unsigned int* counter, unsigned int target, int polls) {
+  bool ok = true;
+  if (threadIdx.x == 0) {
     ok = false;
     for (int i = 0; i < polls; ++i) {
       unsigned int now;
@@ -217,35 +225,39 @@ MoeDecodeKernel(const llmp_b200_moe_decode_desc a, unsigned int* faults, int pol
       healthy = false;
     }
   };
-  // Phase A's request for the round starting at item `first` of token t: lane l < 2 * items a
-  // warp fetches the gate (l even) or up (l odd) row of item first + l / 2.
+  // Token t's expert ids, read once a phase (each read is a trip to L2 on the kernel's
+  // critical path): lane j < used holds slot j's, the others get it by shuffle.
+  int lane_id = -1;
+  auto token_ids = [&](int t) {
+    lane_id = lane < a.used ? a.ids[(static_cast<std::int64_t>(t) * a.ids_stride) + lane] : -1;
+  };
+  auto slot_id = [&](int j) { return __shfl_sync(0xffffffffu, lane_id, j); };
+  // Phase A's request for the round starting at item `first` of token t: the round's items
+  // are consecutive rows of ONE expert (a slot's items are a multiple of a round's), so their
+  // gate rows are one run of bytes and their up rows another: lane 0 fetches the first, lane 1
+  // the second.  (A copy a row, eight a warp, kept the SM's copy engine busy for 2 K cycles
+  // before the last was accepted: it takes a copy about every 20 cycles whatever its size.)
   const int items = a.used * a.inter;
   const int items_a_warp = 32 / ur_a;
   const std::uint32_t bytes_a = static_cast<std::uint32_t>(ur_a) * 144u;
+  auto round_items = [&](int first) { return min(items_a_warp, items - first); };
   auto request_a = [&](int t, int first) {
-    const int item = first + (lane >> 1);
-    bool mine = lane < 2 * items_a_warp && item < items;
+    const int n = round_items(first);
+    const int j = n > 0 ? first / a.inter : 0, i = first - (j * a.inter);
+    const int e = slot_id(j);
+    const bool mine = lane < 2 && n > 0 && e >= 0 && e < a.experts;
     const std::uint8_t* src = gate_up;
-    if (mine) {
-      const int j = item / a.inter, i = item % a.inter;
-      const int e = a.ids[(static_cast<std::int64_t>(t) * a.ids_stride) + j];
-      mine = e >= 0 && e < a.experts;
-      if (mine) {
-        src += (((static_cast<std::size_t>(e) * 2) + (lane & 1)) * a.inter + i) * bytes_a;
-      }
-    }
-    return request(mine, src, bytes_a, lane);
+    if (mine) src += (((static_cast<std::size_t>(e) * 2) + lane) * a.inter + i) * bytes_a;
+    return request(mine, src, static_cast<std::uint32_t>(max(n, 0)) * bytes_a, lane);
   };
   // Phase B's: lane j < used fetches slot j's row r of the down tensor.
   const std::uint32_t bytes_b = static_cast<std::uint32_t>(ur_b) * 144u;
   auto request_b = [&](int t, int r) {
     bool mine = lane < a.used && r < a.hidden;
     const std::uint8_t* src = down;
-    if (mine) {
-      const int e = a.ids[(static_cast<std::int64_t>(t) * a.ids_stride) + lane];
-      mine = e >= 0 && e < a.experts;
-      if (mine) src += ((static_cast<std::size_t>(e) * a.hidden) + r) * bytes_b;
-    }
+    const int e = lane_id;  // lane j's own slot
+    mine = mine && e >= 0 && e < a.experts;
+    if (mine) src += ((static_cast<std::size_t>(e) * a.hidden) + r) * bytes_b;
     return request(mine, src, bytes_b, lane);
   };
 
@@ -254,6 +266,7 @@ MoeDecodeKernel(const llmp_b200_moe_decode_desc a, unsigned int* faults, int pol
   const int step_a = static_cast<int>(gridDim.x) * kWarps * items_a_warp;
   for (int t = 0; t < a.tokens; ++t) {
     // the first round's rows travel while the token is quantized
+    token_ids(t);
     bool pending = request_a(t, first_a);
     __syncthreads();  // the token before's staged values are no longer read
     QuantizeToShared(a.x + (static_cast<std::int64_t>(t) * a.x_stride), a.hidden, xq, false);
@@ -263,14 +276,15 @@ MoeDecodeKernel(const llmp_b200_moe_decode_desc a, unsigned int* faults, int pol
       wait(pending);
       const int item = first + (lane / ur_a), sb = lane % ur_a;
       const bool valid = item < items;
-      const int j = valid ? item / a.inter : 0, i = valid ? item % a.inter : 0;
-      const int e = a.ids[(static_cast<std::int64_t>(t) * a.ids_stride) + j];
+      const int j = valid ? item / a.inter : 0, i = valid ? item - (j * a.inter) : 0;
+      const int e = slot_id(j);
       const bool named = e >= 0 && e < a.experts;
       float dg = 0.0f, du = 0.0f;
       if (valid && named && healthy) {
         Q4KBlockUnit g, u;
-        g.LoadShared(rows + (static_cast<std::size_t>(2 * (lane / ur_a)) * bytes_a), sb);
-        u.LoadShared(rows + (static_cast<std::size_t>((2 * (lane / ur_a)) + 1) * bytes_a), sb);
+        // the round's gate rows, then its up rows
+        g.LoadShared(rows + (static_cast<std::size_t>(lane / ur_a) * bytes_a), sb);
+        u.LoadShared(rows + (static_cast<std::size_t>(round_items(first) + (lane / ur_a)) * bytes_a), sb);
         dg = DotStaged(g, xq, a.hidden, sb);
         du = DotStaged(u, xq, a.hidden, sb);
       }
@@ -285,11 +299,13 @@ MoeDecodeKernel(const llmp_b200_moe_decode_desc a, unsigned int* faults, int pol
     }
   }
 
-  // The first down rows travel while the CTAs meet: they depend on no GLU row.
+  // The first down rows are requested while the CTAs meet: they depend on no GLU row.
   const int first_b = (static_cast<int>(blockIdx.x) * kWarps) + warp;
   const int step_b = static_cast<int>(gridDim.x) * kWarps;
+  const unsigned int all_arrived = GridArrive(counter);
+  token_ids(0);
   bool pending_b = request_b(0, first_b);
-  if (!GridMeet(counter, polls)) {
+  if (!GridAwait(counter, all_arrived, polls)) {
     if (threadIdx.x == 0) atomicAdd(faults, 1u);
     wait(pending_b);  // nothing may still be writing this CTA's shared memory when it leaves
     return;           // nothing of phase B is stored
@@ -304,7 +320,9 @@ MoeDecodeKernel(const llmp_b200_moe_decode_desc a, unsigned int* faults, int pol
     __syncthreads();
     const int j = lane / span_b, sb = lane % span_b;
     const bool active = j < a.used && sb < ur_b;
-    const int e = active ? a.ids[(static_cast<std::int64_t>(t) * a.ids_stride) + j] : -1;
+    if (t != 0) token_ids(t);  // (token 0's were read before the first down rows' request)
+    const int slot_e = slot_id(active ? j : 0);
+    const int e = active ? slot_e : -1;
     const bool named = e >= 0 && e < a.experts;
     // slot j's row is values [j * inter, (j + 1) * inter) of the staged GLU rows
     const int hsb = active ? (j * ur_b) + sb : 0;
