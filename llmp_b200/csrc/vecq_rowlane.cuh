@@ -136,9 +136,11 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
   };
 
   GridLaunchDependents();
-  if (my_rows > 0) {
-    while (next < min(S, J)) request();
-  }
+  // Only the first column step is requested now, the next one each time a step has
+  // landed (below): the copy engine serves the copies it holds side by side, so with
+  // every step requested at once they all complete together, at the end of the
+  // transfer, and no step's sums overlap it.
+  if (my_rows > 0) request();
   GridDependencyWait();
 
   // Stage the tokens' activations: one Q8_1 block a thread.  Column c's i-th
@@ -240,6 +242,11 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
       healthy = false;
       if (lane == 0) atomicAdd(plan.faults, 1u);
     }
+    // The next step travels while this one is summed (its stage was read a step ago).
+    if (S > 1 && next < J) {
+      FenceProxyAsync();
+      request();
+    }
     const int c = (j * PH) + ph;
     if (ph < PH && c < UR && r < my_rows) {
       const unsigned char* base = ring + (static_cast<std::size_t>(s) * plan.stage_bytes);
@@ -321,7 +328,7 @@ VecQRowLaneKernel(const Desc a, const RowLanePlan plan) {
       }
     }
     __syncwarp();
-    if (next < J) {  // the stage just read takes the next step
+    if (S == 1 && next < J) {  // a one-stage ring: the stage just read takes the next step
       FenceProxyAsync();
       request();
     }
