@@ -453,8 +453,12 @@ DecodeVectorKernel(const Args a, const Plan plan) {
     __syncwarp();
   }
   GridLaunchDependents();
+  // Two chunks in flight now, the next each time one has landed (below), never the whole
+  // ring at once: the copy engine serves the copies it holds side by side, so a ring
+  // requested at once lands at once, at the end of the transfer, and no chunk's sums
+  // overlap it.
   if (staged) {
-    while (next < min(S, items)) request();
+    while (next < min(min(S, 2), items)) request();
   }
   GridDependencyWait();
 
@@ -520,6 +524,12 @@ DecodeVectorKernel(const Args a, const Plan plan) {
             if (lane == 0) atomicAdd(plan.faults, 1u);
             return;  // nothing of an incomplete stage is summed or stored
           }
+        }
+        // this chunk has landed: the next ones travel while it is summed (their stages
+        // were read S chunks ago)
+        while (next < items && next - item < min(S, 3)) {
+          tc::FenceProxyAsync();
+          request();
         }
 #pragma unroll
         for (int r = 0; r < kG; ++r) {
@@ -599,7 +609,7 @@ DecodeVectorKernel(const Args a, const Plan plan) {
       }
       if (staged) {
         __syncwarp();  // every lane has read the stage
-        if (next < items) {  // the stage just read takes the next item
+        if (S == 1 && next < items) {  // a one-stage ring: the stage just read takes the next item
           tc::FenceProxyAsync();
           request();
         }

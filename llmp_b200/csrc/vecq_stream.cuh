@@ -28,6 +28,7 @@ namespace llmp_b200 {
 namespace vecq {
 
 constexpr int kStreamThreads = 256;
+constexpr int kStreamInFlight = 2;  // stages requested ahead of the one being summed
 constexpr int kStreamMaxStages = 16;
 constexpr std::uint32_t kWaitLimit = 1u << 22;  // polls of ~20-50 ns
 
@@ -398,8 +399,11 @@ VecQStreamKernel(const Desc a, const StreamPlan plan) {
   };
 
   GridLaunchDependents();
+  // Two iterations in flight, not the whole ring: the copy engine serves the copies it
+  // holds side by side, so a ring requested at once lands at once, at the end of the
+  // transfer, and no iteration's sums overlap it.
   if (warp == 0) {
-    while (next < min(S, iterations)) request();
+    while (next < min(min(S, kStreamInFlight), iterations)) request();
   }
   GridDependencyWait();
 
