@@ -22,66 +22,66 @@ struct MeasuredRank {
 
 constexpr MeasuredRank kMeasuredRanks[] = {
     // k, n, fused GLU, tokens, variant, microseconds a launch, GB/s of weight bytes
-    {2560, 10240, 1, 1, "rowlane", 8.432f, 3498},
-    {2560, 10240, 1, 2, "rowlane", 10.405f, 2834},
-    {2560, 10240, 1, 4, "rowlane", 13.886f, 2124},
-    {2560, 10240, 1, 8, "rowmma.t8", 15.849f, 1861},
-    {10240, 2560, 0, 1, "rowmma.c2", 5.298f, 2783},
-    {10240, 2560, 0, 2, "rowlane", 8.546f, 1725},
-    {10240, 2560, 0, 4, "rowmma.t8", 10.827f, 1362},
-    {10240, 2560, 0, 8, "rowmma.t8", 11.311f, 1304},
-    {4096, 4096, 0, 1, "rowlane", 3.350f, 2817},
-    {4096, 4096, 0, 2, "rowmma", 4.714f, 2002},
-    {4096, 4096, 0, 4, "rowmma.t8c2", 6.498f, 1452},
-    {4096, 4096, 0, 8, "rowmma.t8c2", 7.071f, 1335},
-    {4096, 14336, 1, 1, "l8r1u2w4", 16.800f, 3932},
-    {4096, 14336, 1, 2, "l8r1u2w4", 20.677f, 3195},
-    {4096, 14336, 1, 4, "l8r1u2w4", 28.357f, 2330},
-    {4096, 14336, 1, 8, "rowmma.t8", 30.517f, 2165},
-    {14336, 4096, 0, 1, "rowmma", 11.085f, 2980},
-    {14336, 4096, 0, 2, "rowmma", 13.259f, 2491},
-    {14336, 4096, 0, 4, "rowmma", 17.568f, 1880},
-    {14336, 4096, 0, 8, "rowlane", 28.381f, 1164},
-    {2048, 2048, 0, 1, "rowlane", 2.231f, 1058},
-    {2048, 2048, 0, 2, "rowlane", 3.021f, 781},
-    {2048, 2048, 0, 4, "rowmma", 4.293f, 550},
-    {2048, 2048, 0, 8, "rowmma.t8", 5.197f, 454},
-    {8192, 8192, 0, 1, "rowmma.c2", 11.232f, 3361},
-    {8192, 8192, 0, 2, "rowmma.c2", 13.391f, 2819},
-    {8192, 8192, 0, 4, "rowmma", 18.703f, 2018},
-    {8192, 8192, 0, 8, "rowmma.t8", 24.515f, 1540},
-    {2048, 1536, 0, 1, "rowlane", 2.265f, 781},
-    {2048, 1536, 0, 2, "rowlane", 2.956f, 599},
-    {2048, 1536, 0, 4, "rowmma", 4.101f, 431},
-    {2048, 1536, 0, 8, "rowmma.t8", 5.095f, 347},
-    {2048, 6144, 1, 1, "l8r1u2w4", 5.114f, 2768},
-    {2048, 6144, 1, 2, "l8r1u2w4", 6.406f, 2210},
-    {2048, 6144, 1, 4, "rowlane", 9.587f, 1477},
-    {2048, 6144, 1, 8, "rowmma.t8c2", 10.269f, 1378},
-    {6144, 2048, 0, 1, "rowlane", 3.477f, 2036},
-    {6144, 2048, 0, 2, "rowlane", 4.994f, 1417},
-    {6144, 2048, 0, 4, "rowmma", 5.704f, 1241},
-    {6144, 2048, 0, 8, "rowmma.t8", 6.554f, 1080},
-    {4096, 11008, 1, 1, "rowlane", 12.748f, 3979},
-    {4096, 11008, 1, 2, "rowlane", 15.992f, 3172},
-    {4096, 11008, 1, 4, "rowlane", 22.240f, 2281},
-    {4096, 11008, 1, 8, "rowmma.t8", 23.632f, 2146},
-    {11008, 4096, 0, 1, "rowmma", 8.058f, 3147},
-    {11008, 4096, 0, 2, "rowmma", 9.834f, 2579},
-    {11008, 4096, 0, 4, "rowmma.t8", 13.492f, 1880},
-    {11008, 4096, 0, 8, "rowmma.t8", 14.060f, 1804},
-    {5120, 5120, 0, 1, "rowlane", 5.691f, 2591},
-    {5120, 5120, 0, 2, "rowlane", 7.486f, 1970},
-    {5120, 5120, 0, 4, "rowmma.t8", 9.502f, 1552},
-    {5120, 5120, 0, 8, "rowmma.t8", 10.155f, 1452},
-    {5120, 27648, 1, 1, "l8r1u2w4", 34.120f, 4667},
-    {5120, 27648, 1, 2, "l8r1u2w4", 41.416f, 3845},
-    {5120, 27648, 1, 4, "l8r1u2w4", 60.928f, 2614},
-    {5120, 27648, 1, 8, "rowmma.t8", 112.464f, 1416},
-    {27648, 5120, 0, 1, "rowlane", 23.635f, 3369},
-    {27648, 5120, 0, 2, "rowlane", 28.685f, 2776},
-    {27648, 5120, 0, 4, "rowlane", 40.064f, 1987},
-    {27648, 5120, 0, 8, "rowlane", 39.642f, 2009},
+    {2560, 10240, 1, 1, "rowlane", 7.287f, 4047},
+    {2560, 10240, 1, 2, "rowlane", 8.946f, 3297},
+    {2560, 10240, 1, 4, "rowlane", 12.542f, 2351},
+    {2560, 10240, 1, 8, "rowmma.t8", 16.011f, 1842},
+    {10240, 2560, 0, 1, "rowmma.c2", 5.213f, 2829},
+    {10240, 2560, 0, 2, "rowlane", 7.483f, 1971},
+    {10240, 2560, 0, 4, "rowmma.t8", 10.561f, 1396},
+    {10240, 2560, 0, 8, "rowmma.t8", 11.093f, 1329},
+    {4096, 4096, 0, 1, "rowlane", 4.016f, 2350},
+    {4096, 4096, 0, 2, "rowlane", 4.806f, 1964},
+    {4096, 4096, 0, 4, "rowlane", 6.474f, 1458},
+    {4096, 4096, 0, 8, "rowmma.t8c2", 7.079f, 1333},
+    {4096, 14336, 1, 1, "rowlane", 16.293f, 4055},
+    {4096, 14336, 1, 2, "rowlane", 20.101f, 3286},
+    {4096, 14336, 1, 4, "l8r1u2w4", 28.192f, 2343},
+    {4096, 14336, 1, 8, "rowmma.t8", 30.523f, 2164},
+    {14336, 4096, 0, 1, "rowlane", 10.299f, 3207},
+    {14336, 4096, 0, 2, "rowlane", 11.459f, 2882},
+    {14336, 4096, 0, 4, "rowlane", 15.789f, 2092},
+    {14336, 4096, 0, 8, "rowlane", 26.141f, 1264},
+    {2048, 2048, 0, 1, "rowlane", 2.075f, 1137},
+    {2048, 2048, 0, 2, "rowlane", 2.759f, 855},
+    {2048, 2048, 0, 4, "rowlane", 4.255f, 554},
+    {2048, 2048, 0, 8, "rowmma.t8", 5.214f, 452},
+    {8192, 8192, 0, 1, "rowlane", 11.215f, 3366},
+    {8192, 8192, 0, 2, "rowlane", 12.262f, 3079},
+    {8192, 8192, 0, 4, "rowlane", 16.625f, 2271},
+    {8192, 8192, 0, 8, "rowmma.t8", 24.492f, 1541},
+    {2048, 1536, 0, 1, "rowlane", 2.056f, 861},
+    {2048, 1536, 0, 2, "rowlane", 2.730f, 648},
+    {2048, 1536, 0, 4, "rowlane", 4.215f, 420},
+    {2048, 1536, 0, 8, "rowmma.t8", 5.112f, 346},
+    {2048, 6144, 1, 1, "rowlane", 4.712f, 3004},
+    {2048, 6144, 1, 2, "rowlane", 6.038f, 2344},
+    {2048, 6144, 1, 4, "rowlane", 9.007f, 1572},
+    {2048, 6144, 1, 8, "rowmma.t8c2", 10.270f, 1378},
+    {6144, 2048, 0, 1, "rowlane", 3.928f, 1802},
+    {6144, 2048, 0, 2, "rowlane", 4.724f, 1498},
+    {6144, 2048, 0, 4, "rowmma", 5.646f, 1254},
+    {6144, 2048, 0, 8, "rowmma.t8", 6.528f, 1084},
+    {4096, 11008, 1, 1, "rowlane", 10.908f, 4650},
+    {4096, 11008, 1, 2, "rowlane", 13.192f, 3845},
+    {4096, 11008, 1, 4, "rowlane", 20.132f, 2520},
+    {4096, 11008, 1, 8, "rowmma.t8", 23.428f, 2165},
+    {11008, 4096, 0, 1, "rowmma", 8.008f, 3167},
+    {11008, 4096, 0, 2, "rowlane", 9.796f, 2589},
+    {11008, 4096, 0, 4, "rowlane", 13.428f, 1889},
+    {11008, 4096, 0, 8, "rowmma.t8", 13.928f, 1821},
+    {5120, 5120, 0, 1, "rowlane", 4.912f, 3002},
+    {5120, 5120, 0, 2, "rowlane", 6.379f, 2312},
+    {5120, 5120, 0, 4, "rowlane", 9.393f, 1570},
+    {5120, 5120, 0, 8, "rowmma.t8", 10.183f, 1448},
+    {5120, 27648, 1, 1, "l8r1u2w4", 33.920f, 4695},
+    {5120, 27648, 1, 2, "l8r1u2w4", 40.944f, 3890},
+    {5120, 27648, 1, 4, "l8r1u2w4", 60.360f, 2638},
+    {5120, 27648, 1, 8, "rowmma.t8", 112.272f, 1418},
+    {27648, 5120, 0, 1, "rowlane", 20.390f, 3905},
+    {27648, 5120, 0, 2, "rowlane", 24.013f, 3316},
+    {27648, 5120, 0, 4, "rowlane", 34.688f, 2295},
+    {27648, 5120, 0, 8, "rowlane", 34.515f, 2307},
 };
 constexpr int kMeasuredRankCount = static_cast<int>(sizeof(kMeasuredRanks) / sizeof(kMeasuredRanks[0]));
 
