@@ -154,14 +154,17 @@ template <int kDecoder, bool kSummed>
 __device__ __forceinline__ void Expand(const Raw& raw, float (&v)[16]) {
   if constexpr (kDecoder == LLMP_B200_DECODER_Q8_0_BLOCKS) {
     const float d = raw.scale;
-    if constexpr (kSummed) {
+    // A half that is not finite (no real block has one) takes the two-step form, which
+    // gives the reference's infinities and NaNs; so does the row lookup, always.
+    const bool finite = (__float_as_uint(d) & 0x7f800000u) != 0x7f800000u;
+    if (kSummed && finite) {
       // d b in one fused multiply-add a value, without the conversion unit: b + 128
       // goes into bits 8-15 of 1.0f, which reads 1 + (b + 128) 2^-15, and
       // (2^15 d) (1 + (b + 128) 2^-15) - (1 + 2^-8) (2^15 d) = d b.  Both constants
       // are exact (a half's 11 significant bits times 257 is 20 bits) and so is the
-      // result (19 bits): the bits of d times float(b) for every finite d, but for
-      // b = 0 under a negative d, which gives +0 here and -0 there; a sum that
-      // starts at +0 is the same with either.
+      // result (19 bits): the bits of d times float(b), but for b = 0 under a
+      // negative d, which gives +0 here and -0 there; a sum that starts at +0 is the
+      // same with either.
       const float ds = d * 32768.0f, offset = ds * -1.00390625f;
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
