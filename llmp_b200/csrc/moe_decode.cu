@@ -264,6 +264,12 @@ MoeDecodeKernel(const llmp_b200_moe_decode_desc a, unsigned int* faults, int pol
   // ---- phase A: h[t][j][i] = glu(gate_e[i] . x_t, up_e[i] . x_t), e = ids[t][j]
   const int first_a = ((static_cast<int>(blockIdx.x) * kWarps) + warp) * items_a_warp;
   const int step_a = static_cast<int>(gridDim.x) * kWarps * items_a_warp;
+  const int cta_items = kWarps * items_a_warp;  // items a CTA and round: consecutive
+  const int cta_first = static_cast<int>(blockIdx.x) * cta_items;
+  const bool at_source = cta_items % 32 == 0;   // ... and whole Q8_1 blocks
+  float* exchange = reinterpret_cast<float*>(hq);  // phase A only: the staged GLU rows' place
+  std::uint8_t* staged_rows = reinterpret_cast<std::uint8_t*>(glu_rows);  // in scratch, a token's
+  const std::size_t staged_pitch = static_cast<std::size_t>(Round128(StagedBytes(items)));
   for (int t = 0; t < a.tokens; ++t) {
     // the first round's rows travel while the token is quantized
     token_ids(t);
@@ -271,7 +277,8 @@ MoeDecodeKernel(const llmp_b200_moe_decode_desc a, unsigned int* faults, int pol
     __syncthreads();  // the token before's staged values are no longer read
     QuantizeToShared(a.x + (static_cast<std::int64_t>(t) * a.x_stride), a.hidden, xq, false);
     __syncthreads();
-    for (int first = first_a; first < items; first += step_a) {
+    // (a CTA's warps walk the same number of rounds: the rounds meet at CTA barriers below)
+    for (int base = cta_first, first = first_a; base < items; base += step_a, first += step_a) {
       if (first != first_a) pending = request_a(t, first);
       wait(pending);
       const int item = first + (lane / ur_a), sb = lane % ur_a;
@@ -292,10 +299,45 @@ MoeDecodeKernel(const llmp_b200_moe_decode_desc a, unsigned int* faults, int pol
         dg += __shfl_xor_sync(0xffffffffu, dg, offset);
         du += __shfl_xor_sync(0xffffffffu, du, offset);
       }
-      if (valid && sb == 0 && healthy) {
-        glu_rows[((static_cast<std::size_t>(t) * a.used) + j) * a.inter + i] =
-            named ? Glu(a.glu, dg, du, a.limit) : __uint_as_float(0x7fc00000u);
+      const float value = named ? Glu(a.glu, dg, du, a.limit) : __uint_as_float(0x7fc00000u);
+      if (!at_source) {
+        if (valid && sb == 0 && healthy) {
+          glu_rows[((static_cast<std::size_t>(t) * a.used) + j) * a.inter + i] = value;
+        }
+        continue;
       }
+      // The round's GLU rows are quantized where they are: the CTA's items of a round are
+      // whole 32-value blocks, so its warps pass their values through shared memory and
+      // warp w quantizes block w with QuantizeToShared's arithmetic (the same d, codes and
+      // sum whatever the lanes' order), straight into the staged form, in scratch; phase B
+      // then only copies the staged bytes instead of every CTA quantizing every row again.
+      if (sb == 0) exchange[(warp * items_a_warp) + (lane / ur_a)] = valid ? value : 0.0f;
+      __syncthreads();
+      const int n0 = base + (warp * 32);  // the block's first value among the token's used * inter
+      if (warp < cta_items / 32 && n0 < items && healthy) {
+        const float v = exchange[(warp * 32) + lane];
+        float amax = fabsf(v);
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) {
+          amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
+        }
+        const float d = amax / 127.0f;
+        int q = 0;
+        if (amax != 0.0f) q = static_cast<int>(roundf(v / d));
+        q = static_cast<int>(static_cast<signed char>(q & 0xff));
+        int isum = q;
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) isum += __shfl_xor_sync(0xffffffffu, isum, offset);
+        std::uint8_t* staged = staged_rows + (static_cast<std::size_t>(t) * staged_pitch);
+        const int block = n0 >> 5;
+        staged[((block >> 3) * kCodePitch) + ((block & 7) * 32) + lane] = static_cast<std::uint8_t>(q & 0xff);
+        if (lane == 0) {
+          const float d8 = __half2float(__float2half_rn(d));
+          *reinterpret_cast<float2*>(staged + ((items / 256) * kCodePitch) + ((block >> 3) * kScalePitch) +
+                                     ((block & 7) * 8)) = make_float2(d8, d8 * static_cast<float>(isum));
+        }
+      }
+      __syncthreads();  // before the next round's values take the exchange's place
     }
   }
 
@@ -315,8 +357,16 @@ MoeDecodeKernel(const llmp_b200_moe_decode_desc a, unsigned int* faults, int pol
   // ---- phase B: dst[t][r] = sum_j weight[t][j] * (down_e[r] . h[t][j])
   for (int t = 0; t < a.tokens; ++t) {
     __syncthreads();
-    QuantizeToShared(glu_rows + (static_cast<std::size_t>(t) * a.used * a.inter), a.used * a.inter, hq,
-                     true);
+    if (at_source) {
+      const uint2* src = reinterpret_cast<const uint2*>(staged_rows + (static_cast<std::size_t>(t) * staged_pitch));
+      uint2* dst = reinterpret_cast<uint2*>(hq);
+      for (int i = static_cast<int>(threadIdx.x); i < StagedBytes(items) / 8; i += kThreads) {
+        dst[i] = __ldcg(src + i);  // written by other SMs: not through L1
+      }
+    } else {
+      QuantizeToShared(glu_rows + (static_cast<std::size_t>(t) * a.used * a.inter), a.used * a.inter, hq,
+                       true);
+    }
     __syncthreads();
     const int j = lane / span_b, sb = lane % span_b;
     const bool active = j < a.used && sb < ur_b;
