@@ -337,7 +337,7 @@ MoeDecodeKernel(const llmp_b200_moe_decode_desc a, unsigned int* faults, int pol
                                      ((block & 7) * 8)) = make_float2(d8, d8 * static_cast<float>(isum));
         }
       }
-      __syncthreads();  // before the next round's values take the exchange's place
+      if (base + step_a < items) __syncthreads();  // before the next round's values take the exchange's place
     }
   }
 
